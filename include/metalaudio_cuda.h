@@ -1,0 +1,247 @@
+/*
+ * metalaudio_cuda.h - C ABI of the CUDA (sm_100a) backend for the MetalDSP hot path:
+ * batched real-input FFT / inverse FFT, STFT / iSTFT and uniformly partitioned FFT
+ * convolution.
+ *
+ * The reference (a Swift package) has no FFI of its own: its boundary for this path is
+ * the public Swift API of `FFT` and `Convolution`.  Every entry point below names the
+ * reference interface (file:line within the reference tree) whose arithmetic it
+ * replaces; a Swift `FFT` / `Convolution` / `AudioDevice` / `Tensor` shim calls these
+ * through a system-library module target.
+ *
+ * Conventions
+ *  - plain C: opaque handles, pointers, sizes; every call returns an ma_status.
+ *  - `_dev` entry points take device pointers, are ordered on the context's stream, do
+ *    not allocate and do not synchronise.  `_host` entry points take host pointers,
+ *    copy through the context (directly when the memory is pinned, e.g. from
+ *    ma_host_alloc, through the context's pinned staging buffer otherwise) and return
+ *    after the result is in the caller's buffer.
+ *  - all data is float32; complex data is interleaved (re, im) unless a layout says
+ *    otherwise; all index arithmetic is 64-bit and overflow-checked on the host.
+ *  - there is no CPU fallback: without a usable CUDA device every call fails.
+ */
+#ifndef METALAUDIO_CUDA_H
+#define METALAUDIO_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t ma_status;
+
+/* Status codes.  The FFT / convolution codes map 1:1 onto the reference's Swift error
+ * enums: FFTError (Sources/MetalDSP/FFT.swift:12-33), ConvolutionError
+ * (Sources/MetalDSP/Convolution.swift:8-27), MetalAudioError
+ * (Sources/MetalAudioKit/Core/AudioDevice.swift:11-32). */
+enum {
+    MA_OK = 0,
+    MA_ERR_INVALID_ARGUMENT = 1,       /* MetalAudioError.invalidConfiguration */
+    MA_ERR_SIZE_NOT_POW2 = 2,          /* FFTError.sizeNotPowerOf2 */
+    MA_ERR_SIZE_TOO_LARGE = 3,         /* FFTError.sizeTooLarge (N > 2^24) */
+    MA_ERR_INVALID_HOP = 4,            /* FFTError.invalidHopSize */
+    MA_ERR_INPUT_TOO_SHORT = 5,        /* FFTError.inputTooShort */
+    MA_ERR_BATCH_OVERFLOW = 6,         /* FFTError.batchSizeOverflow */
+    MA_ERR_ISTFT_OVERFLOW = 7,         /* FFTError.istftOutputOverflow / istftFrameOverflow */
+    MA_ERR_EMPTY_KERNEL = 8,           /* invalidConfiguration("Kernel must not be empty ...") */
+    MA_ERR_KERNEL_NOT_CONFIGURED = 9,  /* ConvolutionError.fftNotInitialized */
+    MA_ERR_INVALID_PARTITION_STATE = 10, /* ConvolutionError.invalidPartitionState */
+    MA_ERR_OUTPUT_OVERFLOW = 11,       /* ConvolutionError.outputSizeOverflow */
+    MA_ERR_ALLOC = 12,                 /* MetalAudioError.bufferAllocationFailed */
+    MA_ERR_TIMEOUT = 13,               /* MetalAudioError.gpuTimeout */
+    MA_ERR_DEVICE_LOST = 14,           /* MetalAudioError.deviceLost / deviceNotFound */
+    MA_ERR_CUDA = 15,                  /* MetalAudioError.gpuExecutionError; see ma_last_cuda_error */
+    MA_ERR_UNSUPPORTED = 16
+};
+
+/* Spectrum layouts accepted / produced by the transforms (N = FFT size). */
+enum {
+    MA_LAYOUT_HALF_INTERLEAVED = 0, /* N/2+1 interleaved complex bins per frame (re,im pairs) */
+    MA_LAYOUT_FULL_SPLIT = 1,       /* the reference's layout: real[N] and imag[N] per frame,
+                                       bins N/2+1..N-1 the conjugate mirror (FFT.swift:799-802) */
+    MA_LAYOUT_HALF_PACKED = 2       /* N/2 interleaved complex bins, bin 0 = (DC, Nyquist);
+                                       internal format of the convolution delay line */
+};
+
+/* Magnitude kinds (FFT.swift:1780-1847). */
+enum { MA_MAG_MAGNITUDE = 0, MA_MAG_POWER = 1, MA_MAG_DB = 2 };
+
+/* Host-side fault injection sites (ma_test_inject_fault). */
+enum { MA_FAULT_ALLOC = 0, MA_FAULT_LAUNCH = 1, MA_FAULT_SYNC = 2, MA_FAULT_DEVICE_LOST = 3 };
+
+typedef struct ma_context ma_context;
+typedef struct ma_fft_plan ma_fft_plan;
+typedef struct ma_pconv ma_pconv;
+
+/* ------------------------------------------------------------------ library */
+
+/* Human-readable text for a status code. */
+const char* ma_status_string(ma_status s);
+/* Last cudaError_t seen by this thread's most recent failing call (0 if none). */
+int32_t ma_last_cuda_error(void);
+/* Number of kernels this library has launched in this process (all contexts). */
+uint64_t ma_kernel_launch_count(void);
+/* Number of visible CUDA devices; 0 when none (then every create call fails). */
+int32_t ma_device_count(void);
+
+/* ------------------------------------------------------------------ context
+ * Replaces AudioDevice (device + queue ownership, AudioDevice.swift:222, :323-332) and
+ * the executeSync / executeSyncWithTiming slice of ComputeContext
+ * (Sources/MetalAudioKit/Core/ComputeContext.swift:154-211, :232-297). */
+
+/* Create a context on `device_index` with its own stream and a pinned staging buffer of
+ * `pinned_bytes` (0 picks 64 MiB). */
+ma_status ma_context_create(int32_t device_index, size_t pinned_bytes, ma_context** out);
+ma_status ma_context_destroy(ma_context* ctx);
+/* Wait for all work queued on the context, at most `timeout_s` seconds (<= 0: the
+ * reference's default of 2 s, ComputeContext.swift:137).  Polls an event; on expiry
+ * returns MA_ERR_TIMEOUT and leaves the stream draining. */
+ma_status ma_context_sync(ma_context* ctx, double timeout_s);
+/* Device name into `buf` (AudioDevice.name). */
+ma_status ma_context_device_name(ma_context* ctx, char* buf, size_t buf_len);
+/* The context's cudaStream_t as an opaque pointer, for callers that order their own
+ * device work (e.g. event timing) against it. */
+void* ma_context_stream(ma_context* ctx);
+/* AudioDevice.markDeviceLost / ensureAvailable (AudioDevice.swift:434-472, :733-741):
+ * after mark_lost every call on the context returns MA_ERR_DEVICE_LOST. */
+ma_status ma_context_mark_lost(ma_context* ctx);
+ma_status ma_context_is_available(ma_context* ctx, int32_t* available);
+/* executeSyncWithTiming: bracket queued work with events; end returns elapsed ms and
+ * waits for the work. */
+ma_status ma_timing_begin(ma_context* ctx);
+ma_status ma_timing_end(ma_context* ctx, float* milliseconds);
+/* Test hook, host side only: the next call that reaches `site` fails with
+ * `cuda_error` (no GPU work is disturbed). */
+ma_status ma_test_inject_fault(ma_context* ctx, int32_t site, int32_t cuda_error);
+
+/* ------------------------------------------------------------------ buffers
+ * Backing store of Tensor (Sources/MetalAudioKit/Buffers/Tensor.swift:59, :272, :325,
+ * :390): a device allocation plus explicit host copies. */
+ma_status ma_buffer_alloc(ma_context* ctx, size_t bytes, void** dptr);
+ma_status ma_buffer_free(ma_context* ctx, void* dptr);
+ma_status ma_buffer_zero(ma_context* ctx, void* dptr, size_t bytes);           /* Tensor.zero */
+ma_status ma_memcpy_h2d(ma_context* ctx, void* dptr, const void* host, size_t bytes); /* Tensor.copy(from:) */
+ma_status ma_memcpy_d2h(ma_context* ctx, void* host, const void* dptr, size_t bytes); /* Tensor.toArray / copy(to:) */
+/* Stream-ordered copies that return immediately; `host` must be pinned. */
+ma_status ma_memcpy_h2d_async(ma_context* ctx, void* dptr, const void* host, size_t bytes);
+ma_status ma_memcpy_d2h_async(ma_context* ctx, void* host, const void* dptr, size_t bytes);
+/* Pinned host memory for callers that want zero-staging transfers. */
+ma_status ma_host_alloc(ma_context* ctx, size_t bytes, void** hptr);
+ma_status ma_host_free(ma_context* ctx, void* hptr);
+
+/* ------------------------------------------------------------------ FFT plan
+ * Replaces FFT.init(device:config:) (FFT.swift:441-495): validates N (power of two,
+ * 2 <= N <= 2^24) and 0 < hop <= N, keeps the window table on the device.
+ * `window` is a host array of N coefficients computed by the caller exactly as
+ * FFT.swift:461 does (symmetric, float64 then rounded) or NULL for no window;
+ * forward()/inverse() never apply it, stft/istft do (FFT.swift:783-786,
+ * STFT.swift:63-68, :462). */
+ma_status ma_fft_plan_create(ma_context* ctx, int32_t n, const float* window, int32_t hop,
+                             ma_fft_plan** out);
+ma_status ma_fft_plan_destroy(ma_fft_plan* plan);
+/* Bytes of device scratch the plan holds for N > 8192 (0 below), and the largest batch
+ * one launch of the large-N path processes per pass. */
+ma_status ma_fft_plan_scratch_bytes(ma_fft_plan* plan, size_t* bytes);
+
+/* Unnormalised forward DFT of `batch` contiguous real frames of N samples.
+ * Replaces FFT.forward (FFT.swift:818-855), forwardBatch (STFT.swift:94-128) and the
+ * GPU / MPSGraph / auto variants (FFT.swift:945-1107, :1372-1431, :1639-1687).
+ * layout HALF_INTERLEAVED / HALF_PACKED: `out_a` receives the interleaved bins, `out_b`
+ * is ignored.  layout FULL_SPLIT: `out_a` = real[batch][N], `out_b` = imag[batch][N].
+ * `mag` (may be NULL) receives batch x (N/2+1) magnitudes of `mag_kind` computed in the
+ * same pass (db_reference used for MA_MAG_DB). */
+ma_status ma_fft_forward_dev(ma_fft_plan* plan, const float* in, float* out_a, float* out_b,
+                             float* mag, int32_t mag_kind, float db_reference,
+                             int64_t batch, int32_t layout);
+ma_status ma_fft_forward_host(ma_fft_plan* plan, const float* in, float* out_a, float* out_b,
+                              float* mag, int32_t mag_kind, float db_reference,
+                              int64_t batch, int32_t layout);
+
+/* Inverse DFT with the 1/N scale fused.  Replaces FFT.inverse (FFT.swift:889-919),
+ * inverseBatch (STFT.swift:327-373), inverseGPU / inverseMPSGraph / inverseAuto.
+ * The input spectrum is taken as Hermitian: only bins 0..N/2 are read (for FULL_SPLIT
+ * from in_a = real, in_b = imag). */
+ma_status ma_fft_inverse_dev(ma_fft_plan* plan, const float* in_a, const float* in_b, float* out,
+                             int64_t batch, int32_t layout);
+ma_status ma_fft_inverse_host(ma_fft_plan* plan, const float* in_a, const float* in_b, float* out,
+                              int64_t batch, int32_t layout);
+
+/* Magnitude / power / dB over bins 0..N/2 of caller-supplied FULL_SPLIT spectra.
+ * Replaces FFT.magnitude / power / magnitudeDB (FFT.swift:1780-1847). */
+ma_status ma_fft_magnitude_dev(ma_fft_plan* plan, const float* re, const float* im, float* out,
+                               int64_t batch, int32_t kind, float db_reference);
+ma_status ma_fft_magnitude_host(ma_fft_plan* plan, const float* re, const float* im, float* out,
+                                int64_t batch, int32_t kind, float db_reference);
+
+/* ------------------------------------------------------------------ STFT / iSTFT */
+
+/* Frame count (L - N)/hop + 1 for a signal of `length` (STFT.swift:45-49);
+ * MA_ERR_INPUT_TOO_SHORT when length < N. */
+ma_status ma_stft_frame_count(ma_fft_plan* plan, int64_t length, int64_t* frames);
+/* Output length (F-1)*hop + N with the overflow check of STFT.swift:393-397. */
+ma_status ma_istft_output_length(ma_fft_plan* plan, int64_t frames, int64_t* length);
+
+/* STFT of `n_signals` signals of `length` samples, signal s starting at
+ * signals + s*signal_stride: frames at i*hop, analysis window, forward DFT.
+ * Replaces FFT.stft (STFT.swift:40-81) run over a set of signals.  Outputs are indexed
+ * by global frame g = s*F + f with the layouts of ma_fft_forward_dev; `mag` optional. */
+ma_status ma_stft_dev(ma_fft_plan* plan, const float* signals, int64_t length,
+                      int64_t signal_stride, int64_t n_signals, float* out_a, float* out_b,
+                      float* mag, int32_t mag_kind, float db_reference, int32_t layout);
+ma_status ma_stft_host(ma_fft_plan* plan, const float* signals, int64_t length,
+                       int64_t signal_stride, int64_t n_signals, float* out_a, float* out_b,
+                       float* mag, int32_t mag_kind, float db_reference, int32_t layout);
+
+/* iSTFT of `frames` frames per signal: inverse DFT (1/N), synthesis window, overlap-add,
+ * division by max(sum of squared window, floor), all in one pass.  Replaces FFT.istft
+ * (STFT.swift:384-527); uses the true inverse transform (the reference runs the object's
+ * forward-direction setup, which returns frames time-reversed).  `floor` is the already
+ * validated window floor (STFT.swift:491-501).  out: n_signals rows of out_stride floats,
+ * each holding (frames-1)*hop + N samples. */
+ma_status ma_istft_dev(ma_fft_plan* plan, const float* in_a, const float* in_b, int64_t frames,
+                       int64_t n_signals, float* out, int64_t out_stride, float floor,
+                       int32_t layout);
+ma_status ma_istft_host(ma_fft_plan* plan, const float* in_a, const float* in_b, int64_t frames,
+                        int64_t n_signals, float* out, int64_t out_stride, float floor,
+                        int32_t layout);
+
+/* ------------------------------------------------------------------ partitioned convolution
+ * Replaces Convolution(device:mode: .partitioned(blockSize:)) + setKernel + process +
+ * reset (Convolution.swift:112-125, :188-208, :250-322, :336-352, :529-758, :764-775),
+ * for `n_channels` independent channels at once (the reference holds one object per
+ * channel). */
+ma_status ma_pconv_create(ma_context* ctx, int32_t block_size, int32_t n_channels, ma_pconv** out);
+ma_status ma_pconv_destroy(ma_pconv* pc);
+/* Partition `n_irs` impulse responses of `taps` floats (host memory, row-major) into
+ * P = ceil(taps/B) zero-padded blocks and transform them; channel c uses IR
+ * channel_to_ir[c] (NULL: every channel uses IR 0).  Allocates the delay line
+ * (n_channels x P spectra) and clears it. */
+ma_status ma_pconv_set_kernels(ma_pconv* pc, const float* irs, int64_t taps, int32_t n_irs,
+                               const int32_t* channel_to_ir);
+ma_status ma_pconv_partition_count(ma_pconv* pc, int32_t* partitions);
+/* Whole-signal call, as process(input:output:): every channel receives len samples
+ * (row c at in + c*in_stride) and produces the full len + taps - 1 output samples
+ * (row c at out + c*out_stride), ceil((len+taps-1)/B) blocks pushed through the delay
+ * line; the delay line keeps its state for the next call.  `max_len` passed to
+ * ma_pconv_reserve bounds len for the _dev form, which never allocates. */
+ma_status ma_pconv_reserve(ma_pconv* pc, int64_t max_len);
+ma_status ma_pconv_process_dev(ma_pconv* pc, const float* in, int64_t len, int64_t in_stride,
+                               float* out, int64_t out_stride);
+ma_status ma_pconv_process_host(ma_pconv* pc, const float* in, int64_t len, int64_t in_stride,
+                                float* out, int64_t out_stride);
+/* Causal streaming step: one block of B input samples per channel in (row stride
+ * in_stride), one block of B output samples out; the block's second half is kept in the
+ * object and added to the next step's output.  Every step reads the whole delay line:
+ * this is the HBM-streaming kernel.  No reference counterpart call (the reference loops
+ * blocks inside process()); the arithmetic per block is Convolution.swift:580-757. */
+ma_status ma_pconv_step_dev(ma_pconv* pc, const float* in_block, int64_t in_stride,
+                            float* out_block, int64_t out_stride);
+/* Zero the delay line, the write index and the overlap tail (Convolution.reset). */
+ma_status ma_pconv_reset(ma_pconv* pc);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* METALAUDIO_CUDA_H */

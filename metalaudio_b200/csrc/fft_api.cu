@@ -1,0 +1,414 @@
+// C ABI: FFT plan, forward / inverse / magnitude, STFT / iSTFT.
+#include <limits>
+#include <new>
+
+#include "fft_plan.h"
+#include "host_tables.h"
+
+namespace ma {
+ma_status launch_magnitude(ma_fft_plan* plan, const float* re, const float* im, float* out, int64_t batch,
+                           int kind, float db_scale);
+}
+using namespace ma;
+
+static bool mul_overflow(int64_t a, int64_t b, int64_t* r) { return __builtin_mul_overflow(a, b, r); }
+static bool add_overflow(int64_t a, int64_t b, int64_t* r) { return __builtin_add_overflow(a, b, r); }
+
+static ma_status upload(ma_context* ctx, const void* host, size_t bytes, void** dptr) {
+    MA_CUDA(cudaMalloc(dptr, bytes));
+    return copy_h2d(ctx, *dptr, host, bytes);
+}
+
+static bool valid_layout(int layout) {
+    return layout == MA_LAYOUT_HALF_INTERLEAVED || layout == MA_LAYOUT_FULL_SPLIT || layout == MA_LAYOUT_HALF_PACKED;
+}
+
+// Output floats per frame in array a / b for a layout.
+static int64_t floats_a(int n, int layout) {
+    if (layout == MA_LAYOUT_FULL_SPLIT) return n;
+    if (layout == MA_LAYOUT_HALF_PACKED) return n;  // N/2 complex
+    return 2 * (int64_t)(n / 2 + 1);
+}
+static int64_t complex_per_frame(int n, int layout) {
+    return layout == MA_LAYOUT_HALF_PACKED ? n / 2 : n / 2 + 1;
+}
+
+extern "C" {
+
+ma_status ma_fft_plan_create(ma_context* ctx, int32_t n, const float* window, int32_t hop, ma_fft_plan** out) {
+    if (out == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    // Validation order of FFT.init (FFT.swift:443-455).
+    if (n < 2 || (n & (n - 1)) != 0) return MA_ERR_SIZE_NOT_POW2;
+    if (n > (1 << 24)) return MA_ERR_SIZE_TOO_LARGE;
+    if (hop <= 0 || hop > n) return MA_ERR_INVALID_HOP;
+    MA_TRY(enter(ctx, MA_FAULT_ALLOC));
+    ma_fft_plan* p = new (std::nothrow) ma_fft_plan();
+    if (p == nullptr) return MA_ERR_ALLOC;
+    p->ctx = ctx;
+    p->n = n;
+    p->m = n / 2;
+    p->hop = hop;
+    p->large = n > kMaxSmallN;
+    ma_status st = MA_OK;
+    if (window != nullptr) st = upload(ctx, window, sizeof(float) * (size_t)n, (void**)&p->d_window);
+    if (st == MA_OK && !p->large) {
+        auto twM = make_twiddles(p->m, p->m);
+        auto twN = make_twiddles(n, p->m / 2 + 1);
+        st = upload(ctx, twM.data(), twM.size() * sizeof(float2), (void**)&p->d_twM);
+        if (st == MA_OK) st = upload(ctx, twN.data(), twN.size() * sizeof(float2), (void**)&p->d_twN);
+    }
+    if (st == MA_OK && p->large) st = large_plan_init(p);
+    if (st != MA_OK) {
+        ma_fft_plan_destroy(p);
+        return st;
+    }
+    *out = p;
+    return MA_OK;
+}
+
+ma_status ma_fft_plan_destroy(ma_fft_plan* plan) {
+    if (plan == nullptr) return MA_OK;
+    if (plan->ctx) {
+        (void)cudaSetDevice(plan->ctx->device);
+        (void)cudaStreamSynchronize(plan->ctx->stream);
+    }
+    large_plan_destroy(plan);
+    if (plan->d_window) (void)cudaFree(plan->d_window);
+    if (plan->d_twM) (void)cudaFree(plan->d_twM);
+    if (plan->d_twN) (void)cudaFree(plan->d_twN);
+    (void)cudaGetLastError();
+    delete plan;
+    return MA_OK;
+}
+
+ma_status ma_fft_plan_scratch_bytes(ma_fft_plan* plan, size_t* bytes) {
+    if (plan == nullptr || bytes == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    *bytes = plan->large ? (size_t)plan->scratch_batch * (size_t)(plan->n2 / 2 + 1) * plan->n1 * sizeof(float2) : 0;
+    return MA_OK;
+}
+
+ma_status ma_fft_forward_dev(ma_fft_plan* plan, const float* in, float* out_a, float* out_b, float* mag,
+                             int32_t mag_kind, float db_reference, int64_t batch, int32_t layout) {
+    if (plan == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    MA_TRY(enter(plan->ctx, MA_FAULT_LAUNCH));
+    if (batch == 0) return MA_OK;  // empty batch is a no-op (STFT.swift:99-100)
+    if (batch < 0 || !valid_layout(layout) || in == nullptr || out_a == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (layout == MA_LAYOUT_FULL_SPLIT && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (mag != nullptr && (mag_kind < MA_MAG_MAGNITUDE || mag_kind > MA_MAG_DB)) return MA_ERR_INVALID_ARGUMENT;
+    int64_t total;
+    if (mul_overflow(batch, plan->n, &total)) return MA_ERR_BATCH_OVERFLOW;
+    const float db_scale = 1.0f / db_reference;
+    if (plan->large) return launch_r2c_large(plan, in, out_a, out_b, mag, mag_kind, db_scale, batch, layout);
+    R2CParams p{};
+    p.in = in;
+    p.signal_stride = 0;
+    p.frames_per_signal = batch;
+    p.total_frames = batch;
+    p.signal_len = total;
+    p.hop = plan->n;
+    p.frame_valid = plan->n;
+    p.window = nullptr;
+    p.out_a = out_a;
+    p.out_b = out_b;
+    p.mag = mag;
+    p.out_signal_stride = 0;
+    p.out_frame_stride = complex_per_frame(plan->n, layout);
+    p.layout = layout;
+    p.mag_kind = mag_kind;
+    p.db_scale = db_scale;
+    return launch_r2c_small(plan, p);
+}
+
+ma_status ma_fft_inverse_dev(ma_fft_plan* plan, const float* in_a, const float* in_b, float* out, int64_t batch,
+                             int32_t layout) {
+    if (plan == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    MA_TRY(enter(plan->ctx, MA_FAULT_LAUNCH));
+    if (batch == 0) return MA_OK;
+    if (batch < 0 || !valid_layout(layout) || in_a == nullptr || out == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (layout == MA_LAYOUT_FULL_SPLIT && in_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    int64_t total;
+    if (mul_overflow(batch, plan->n, &total)) return MA_ERR_BATCH_OVERFLOW;
+    if (plan->large) return launch_c2r_large(plan, in_a, in_b, out, batch, layout);
+    C2RParams p{};
+    p.in_a = in_a;
+    p.in_b = in_b;
+    p.in_signal_stride = 0;
+    p.in_frame_stride = complex_per_frame(plan->n, layout);
+    p.frames_per_signal = batch;
+    p.n_signals = 1;
+    p.layout = layout;
+    p.out = out;
+    return launch_c2r_small(plan, p);
+}
+
+ma_status ma_fft_magnitude_dev(ma_fft_plan* plan, const float* re, const float* im, float* out, int64_t batch,
+                               int32_t kind, float db_reference) {
+    if (plan == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    MA_TRY(enter(plan->ctx, MA_FAULT_LAUNCH));
+    if (batch == 0) return MA_OK;
+    if (batch < 0 || re == nullptr || im == nullptr || out == nullptr || kind < MA_MAG_MAGNITUDE || kind > MA_MAG_DB)
+        return MA_ERR_INVALID_ARGUMENT;
+    return launch_magnitude(plan, re, im, out, batch, kind, 1.0f / db_reference);
+}
+
+ma_status ma_stft_frame_count(ma_fft_plan* plan, int64_t length, int64_t* frames) {
+    if (plan == nullptr || frames == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    *frames = 0;
+    if (length < plan->n) return MA_ERR_INPUT_TOO_SHORT;
+    *frames = (length - plan->n) / plan->hop + 1;
+    return MA_OK;
+}
+
+ma_status ma_istft_output_length(ma_fft_plan* plan, int64_t frames, int64_t* length) {
+    if (plan == nullptr || length == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    *length = 0;
+    if (frames <= 0) return MA_OK;
+    int64_t a, b;
+    if (mul_overflow(frames - 1, plan->hop, &a) || add_overflow(a, plan->n, &b)) return MA_ERR_ISTFT_OVERFLOW;
+    *length = b;
+    return MA_OK;
+}
+
+ma_status ma_stft_dev(ma_fft_plan* plan, const float* signals, int64_t length, int64_t signal_stride,
+                      int64_t n_signals, float* out_a, float* out_b, float* mag, int32_t mag_kind,
+                      float db_reference, int32_t layout) {
+    if (plan == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    MA_TRY(enter(plan->ctx, MA_FAULT_LAUNCH));
+    if (n_signals == 0) return MA_OK;
+    if (n_signals < 0 || !valid_layout(layout) || signals == nullptr || out_a == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (layout == MA_LAYOUT_FULL_SPLIT && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (mag != nullptr && (mag_kind < MA_MAG_MAGNITUDE || mag_kind > MA_MAG_DB)) return MA_ERR_INVALID_ARGUMENT;
+    int64_t frames;
+    MA_TRY(ma_stft_frame_count(plan, length, &frames));
+    if (n_signals > 1 && signal_stride < length) return MA_ERR_INVALID_ARGUMENT;
+    int64_t total, total_out;
+    if (mul_overflow(frames, n_signals, &total) || mul_overflow(total, plan->n, &total_out))
+        return MA_ERR_BATCH_OVERFLOW;
+    if (plan->large) return MA_ERR_UNSUPPORTED;  // STFT frames above 8192 points are not served
+    R2CParams p{};
+    p.in = signals;
+    p.signal_stride = signal_stride;
+    p.frames_per_signal = frames;
+    p.total_frames = total;
+    p.signal_len = length;
+    p.hop = plan->hop;
+    p.frame_valid = plan->n;
+    p.window = plan->d_window;
+    p.out_a = out_a;
+    p.out_b = out_b;
+    p.mag = mag;
+    p.out_frame_stride = complex_per_frame(plan->n, layout);
+    p.out_signal_stride = frames * p.out_frame_stride;
+    p.layout = layout;
+    p.mag_kind = mag_kind;
+    p.db_scale = 1.0f / db_reference;
+    return launch_r2c_small(plan, p);
+}
+
+ma_status ma_istft_dev(ma_fft_plan* plan, const float* in_a, const float* in_b, int64_t frames,
+                       int64_t n_signals, float* out, int64_t out_stride, float floor, int32_t layout) {
+    if (plan == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    MA_TRY(enter(plan->ctx, MA_FAULT_LAUNCH));
+    if (frames == 0 || n_signals == 0) return MA_OK;  // frameCount == 0 -> empty output (STFT.swift:389)
+    if (frames < 0 || n_signals < 0 || !valid_layout(layout) || in_a == nullptr || out == nullptr)
+        return MA_ERR_INVALID_ARGUMENT;
+    if (layout == MA_LAYOUT_FULL_SPLIT && in_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (!(floor > 0.f)) return MA_ERR_INVALID_ARGUMENT;
+    int64_t out_len;
+    MA_TRY(ma_istft_output_length(plan, frames, &out_len));
+    if (n_signals > 1 && out_stride < out_len) return MA_ERR_INVALID_ARGUMENT;
+    int64_t total, total_in;
+    if (mul_overflow(frames, n_signals, &total) || mul_overflow(total, plan->n, &total_in))
+        return MA_ERR_BATCH_OVERFLOW;
+    if (plan->large) return MA_ERR_UNSUPPORTED;
+    C2RParams p{};
+    p.in_a = in_a;
+    p.in_b = in_b;
+    p.in_frame_stride = complex_per_frame(plan->n, layout);
+    p.in_signal_stride = frames * p.in_frame_stride;
+    p.frames_per_signal = frames;
+    p.n_signals = n_signals;
+    p.layout = layout;
+    p.hop = plan->hop;
+    p.window = plan->d_window;
+    p.out = out;
+    p.out_signal_stride = out_stride;
+    p.out_len = out_len;
+    p.floor = floor;
+    return launch_istft_small(plan, p);
+}
+
+// ------------------------------------------------------------------ host-pointer forms
+
+ma_status ma_fft_forward_host(ma_fft_plan* plan, const float* in, float* out_a, float* out_b, float* mag,
+                              int32_t mag_kind, float db_reference, int64_t batch, int32_t layout) {
+    if (plan == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    ma_context* ctx = plan->ctx;
+    MA_TRY(enter(ctx, MA_FAULT_LAUNCH));
+    if (batch == 0) return MA_OK;
+    if (batch < 0 || !valid_layout(layout) || in == nullptr || out_a == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (layout == MA_LAYOUT_FULL_SPLIT && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    int64_t total;
+    if (mul_overflow(batch, plan->n, &total) || total > (int64_t)(std::numeric_limits<int64_t>::max() / 16))
+        return MA_ERR_BATCH_OVERFLOW;
+    const size_t in_b_ = (size_t)total * sizeof(float);
+    const size_t a_b = (size_t)(batch * floats_a(plan->n, layout)) * sizeof(float);
+    const size_t b_b = layout == MA_LAYOUT_FULL_SPLIT ? a_b : 0;
+    const size_t m_b = mag ? (size_t)(batch * (plan->n / 2 + 1)) * sizeof(float) : 0;
+    float *d_in = nullptr, *d_a = nullptr, *d_b = nullptr, *d_m = nullptr;
+    ma_status st = temp_alloc(ctx, in_b_, (void**)&d_in);
+    if (st == MA_OK) st = temp_alloc(ctx, a_b, (void**)&d_a);
+    if (st == MA_OK && b_b) st = temp_alloc(ctx, b_b, (void**)&d_b);
+    if (st == MA_OK && m_b) st = temp_alloc(ctx, m_b, (void**)&d_m);
+    if (st == MA_OK) st = copy_h2d(ctx, d_in, in, in_b_);
+    if (st == MA_OK) st = ma_fft_forward_dev(plan, d_in, d_a, d_b, d_m, mag_kind, db_reference, batch, layout);
+    if (st == MA_OK) st = copy_d2h(ctx, out_a, d_a, a_b);
+    if (st == MA_OK && b_b) st = copy_d2h(ctx, out_b, d_b, b_b);
+    if (st == MA_OK && m_b) st = copy_d2h(ctx, mag, d_m, m_b);
+    temp_free(ctx, d_in);
+    temp_free(ctx, d_a);
+    temp_free(ctx, d_b);
+    temp_free(ctx, d_m);
+    return st;
+}
+
+ma_status ma_fft_inverse_host(ma_fft_plan* plan, const float* in_a, const float* in_b, float* out, int64_t batch,
+                              int32_t layout) {
+    if (plan == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    ma_context* ctx = plan->ctx;
+    MA_TRY(enter(ctx, MA_FAULT_LAUNCH));
+    if (batch == 0) return MA_OK;
+    if (batch < 0 || !valid_layout(layout) || in_a == nullptr || out == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (layout == MA_LAYOUT_FULL_SPLIT && in_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    int64_t total;
+    if (mul_overflow(batch, plan->n, &total) || total > (int64_t)(std::numeric_limits<int64_t>::max() / 16))
+        return MA_ERR_BATCH_OVERFLOW;
+    const size_t a_b = (size_t)(batch * floats_a(plan->n, layout)) * sizeof(float);
+    const size_t b_b = layout == MA_LAYOUT_FULL_SPLIT ? a_b : 0;
+    const size_t o_b = (size_t)total * sizeof(float);
+    float *d_a = nullptr, *d_b = nullptr, *d_o = nullptr;
+    ma_status st = temp_alloc(ctx, a_b, (void**)&d_a);
+    if (st == MA_OK && b_b) st = temp_alloc(ctx, b_b, (void**)&d_b);
+    if (st == MA_OK) st = temp_alloc(ctx, o_b, (void**)&d_o);
+    if (st == MA_OK) st = copy_h2d(ctx, d_a, in_a, a_b);
+    if (st == MA_OK && b_b) st = copy_h2d(ctx, d_b, in_b, b_b);
+    if (st == MA_OK) st = ma_fft_inverse_dev(plan, d_a, d_b, d_o, batch, layout);
+    if (st == MA_OK) st = copy_d2h(ctx, out, d_o, o_b);
+    temp_free(ctx, d_a);
+    temp_free(ctx, d_b);
+    temp_free(ctx, d_o);
+    return st;
+}
+
+ma_status ma_fft_magnitude_host(ma_fft_plan* plan, const float* re, const float* im, float* out, int64_t batch,
+                                int32_t kind, float db_reference) {
+    if (plan == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    ma_context* ctx = plan->ctx;
+    MA_TRY(enter(ctx, MA_FAULT_LAUNCH));
+    if (batch == 0) return MA_OK;
+    if (batch < 0 || re == nullptr || im == nullptr || out == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    // The reference reads only bins 0..N/2 of each array (FFT.swift:1785-1790); a single
+    // frame may therefore be passed with just N/2+1 valid elements.
+    const int kh = plan->n / 2 + 1;
+    const size_t row = (size_t)plan->n * sizeof(float);
+    const size_t in_bytes = batch == 1 ? (size_t)kh * sizeof(float) : (size_t)batch * row;
+    const size_t o_b = (size_t)batch * kh * sizeof(float);
+    float *d_re = nullptr, *d_im = nullptr, *d_o = nullptr;
+    ma_status st = temp_alloc(ctx, (size_t)batch * row, (void**)&d_re);
+    if (st == MA_OK) st = temp_alloc(ctx, (size_t)batch * row, (void**)&d_im);
+    if (st == MA_OK) st = temp_alloc(ctx, o_b, (void**)&d_o);
+    if (st == MA_OK) st = copy_h2d(ctx, d_re, re, in_bytes);
+    if (st == MA_OK) st = copy_h2d(ctx, d_im, im, in_bytes);
+    if (st == MA_OK) st = ma_fft_magnitude_dev(plan, d_re, d_im, d_o, batch, kind, db_reference);
+    if (st == MA_OK) st = copy_d2h(ctx, out, d_o, o_b);
+    temp_free(ctx, d_re);
+    temp_free(ctx, d_im);
+    temp_free(ctx, d_o);
+    return st;
+}
+
+ma_status ma_stft_host(ma_fft_plan* plan, const float* signals, int64_t length, int64_t signal_stride,
+                       int64_t n_signals, float* out_a, float* out_b, float* mag, int32_t mag_kind,
+                       float db_reference, int32_t layout) {
+    if (plan == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    ma_context* ctx = plan->ctx;
+    MA_TRY(enter(ctx, MA_FAULT_LAUNCH));
+    if (n_signals == 0) return MA_OK;
+    if (n_signals < 0 || !valid_layout(layout) || signals == nullptr || out_a == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (layout == MA_LAYOUT_FULL_SPLIT && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    int64_t frames;
+    MA_TRY(ma_stft_frame_count(plan, length, &frames));
+    if (n_signals > 1 && signal_stride < length) return MA_ERR_INVALID_ARGUMENT;
+    int64_t total, total_out;
+    if (mul_overflow(frames, n_signals, &total) || mul_overflow(total, 4 * (int64_t)plan->n, &total_out))
+        return MA_ERR_BATCH_OVERFLOW;
+    // Device copy of the signals is dense: signal s at s*dlen (dlen even keeps pairs aligned).
+    const int64_t dlen = length + (length & 1);
+    const size_t a_b = (size_t)(total * floats_a(plan->n, layout)) * sizeof(float);
+    const size_t b_b = layout == MA_LAYOUT_FULL_SPLIT ? a_b : 0;
+    const size_t m_b = mag ? (size_t)(total * (plan->n / 2 + 1)) * sizeof(float) : 0;
+    float *d_in = nullptr, *d_a = nullptr, *d_b = nullptr, *d_m = nullptr;
+    ma_status st = temp_alloc(ctx, (size_t)(dlen * n_signals) * sizeof(float), (void**)&d_in);
+    if (st == MA_OK) st = temp_alloc(ctx, a_b, (void**)&d_a);
+    if (st == MA_OK && b_b) st = temp_alloc(ctx, b_b, (void**)&d_b);
+    if (st == MA_OK && m_b) st = temp_alloc(ctx, m_b, (void**)&d_m);
+    if (st == MA_OK) {
+        if (signal_stride == length && dlen == length) {
+            st = copy_h2d(ctx, d_in, signals, (size_t)(length * n_signals) * sizeof(float));
+        } else {
+            for (int64_t s = 0; s < n_signals && st == MA_OK; ++s)
+                st = copy_h2d(ctx, d_in + s * dlen, signals + s * signal_stride, (size_t)length * sizeof(float));
+        }
+    }
+    if (st == MA_OK)
+        st = ma_stft_dev(plan, d_in, length, dlen, n_signals, d_a, d_b, d_m, mag_kind, db_reference, layout);
+    if (st == MA_OK) st = copy_d2h(ctx, out_a, d_a, a_b);
+    if (st == MA_OK && b_b) st = copy_d2h(ctx, out_b, d_b, b_b);
+    if (st == MA_OK && m_b) st = copy_d2h(ctx, mag, d_m, m_b);
+    temp_free(ctx, d_in);
+    temp_free(ctx, d_a);
+    temp_free(ctx, d_b);
+    temp_free(ctx, d_m);
+    return st;
+}
+
+ma_status ma_istft_host(ma_fft_plan* plan, const float* in_a, const float* in_b, int64_t frames,
+                        int64_t n_signals, float* out, int64_t out_stride, float floor, int32_t layout) {
+    if (plan == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    ma_context* ctx = plan->ctx;
+    MA_TRY(enter(ctx, MA_FAULT_LAUNCH));
+    if (frames == 0 || n_signals == 0) return MA_OK;
+    if (frames < 0 || n_signals < 0 || !valid_layout(layout) || in_a == nullptr || out == nullptr)
+        return MA_ERR_INVALID_ARGUMENT;
+    if (layout == MA_LAYOUT_FULL_SPLIT && in_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    int64_t out_len;
+    MA_TRY(ma_istft_output_length(plan, frames, &out_len));
+    if (n_signals > 1 && out_stride < out_len) return MA_ERR_INVALID_ARGUMENT;
+    int64_t total, total_in;
+    if (mul_overflow(frames, n_signals, &total) || mul_overflow(total, 4 * (int64_t)plan->n, &total_in))
+        return MA_ERR_BATCH_OVERFLOW;
+    const size_t a_b = (size_t)(total * floats_a(plan->n, layout)) * sizeof(float);
+    const size_t b_b = layout == MA_LAYOUT_FULL_SPLIT ? a_b : 0;
+    float *d_a = nullptr, *d_b = nullptr, *d_o = nullptr;
+    ma_status st = temp_alloc(ctx, a_b, (void**)&d_a);
+    if (st == MA_OK && b_b) st = temp_alloc(ctx, b_b, (void**)&d_b);
+    if (st == MA_OK) st = temp_alloc(ctx, (size_t)(out_len * n_signals) * sizeof(float), (void**)&d_o);
+    if (st == MA_OK) st = copy_h2d(ctx, d_a, in_a, a_b);
+    if (st == MA_OK && b_b) st = copy_h2d(ctx, d_b, in_b, b_b);
+    if (st == MA_OK) st = ma_istft_dev(plan, d_a, d_b, frames, n_signals, d_o, out_len, floor, layout);
+    if (st == MA_OK) {
+        if (out_stride == out_len || n_signals == 1) {
+            st = copy_d2h(ctx, out, d_o, (size_t)(out_len * n_signals) * sizeof(float));
+        } else {
+            for (int64_t s = 0; s < n_signals && st == MA_OK; ++s)
+                st = copy_d2h(ctx, out + s * out_stride, d_o + s * out_len, (size_t)out_len * sizeof(float));
+        }
+    }
+    temp_free(ctx, d_a);
+    temp_free(ctx, d_b);
+    temp_free(ctx, d_o);
+    return st;
+}
+
+}  // extern "C"

@@ -1,0 +1,277 @@
+// Register/shared-memory Stockham FFT building blocks (FP32 SIMT, sm_100a).
+//
+// A complex transform of length M is run by T = M/R threads that each hold R points in
+// registers.  Stage 0 is an R-point butterfly on points loaded with stride T; every
+// later stage exchanges through shared memory in the Stockham autosort pattern
+// (read element jv + k*M/r, twiddle, r-point butterfly, write element
+// (jv/Ns)*Ns*r + jv%Ns + k*Ns), so no bit-reversal pass exists.  The exchange buffer is
+// double-buffered: one barrier per exchange.
+//
+// Everything here is __host__ __device__ and templated on a "Cta" type that supplies the
+// barrier, so that the index arithmetic can be executed on the CPU by a thread-per-lane
+// emulator in the test-suite as well as by the kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MA_HD __host__ __device__ __forceinline__
+
+#ifdef __CUDA_ARCH__
+#define MA_LDG(p) __ldg(p)
+#else
+#define MA_LDG(p) (*(p))
+#endif
+
+namespace ma {
+
+// ---------------------------------------------------------------- complex helpers
+MA_HD float2 cadd(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
+MA_HD float2 csub(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
+MA_HD float2 cmul(float2 a, float2 b) {
+    return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
+}
+MA_HD float2 cconj(float2 a) { return make_float2(a.x, -a.y); }
+// a * (-i)
+MA_HD float2 cmul_mi(float2 a) { return make_float2(a.y, -a.x); }
+
+// Multiply by W_R^K = exp(-2*pi*i*K/R) with the trivial cases resolved at compile time.
+template <int R, int K>
+MA_HD float2 mul_wconst(float2 v) {
+    constexpr float kS = 0.70710678118654752440f;  // sqrt(1/2)
+    constexpr float kC1 = 0.92387953251128675613f; // cos(pi/8)
+    constexpr float kS1 = 0.38268343236508977173f; // sin(pi/8)
+    if constexpr (K == 0) {
+        return v;
+    } else if constexpr (4 * K == R) {  // -i
+        return make_float2(v.y, -v.x);
+    } else if constexpr (8 * K == R) {  // (1 - i)/sqrt2
+        return make_float2((v.x + v.y) * kS, (v.y - v.x) * kS);
+    } else if constexpr (8 * K == 3 * R) {  // (-1 - i)/sqrt2
+        return make_float2((v.y - v.x) * kS, -(v.x + v.y) * kS);
+    } else if constexpr (16 * K == R) {  // W16^1 = (c1, -s1)
+        return make_float2(v.x * kC1 + v.y * kS1, v.y * kC1 - v.x * kS1);
+    } else if constexpr (16 * K == 3 * R) {  // W16^3 = (s1, -c1)
+        return make_float2(v.x * kS1 + v.y * kC1, v.y * kS1 - v.x * kC1);
+    } else if constexpr (16 * K == 5 * R) {  // W16^5 = (-s1, -c1)
+        return make_float2(v.y * kC1 - v.x * kS1, -v.x * kC1 - v.y * kS1);
+    } else {  // 16*K == 7*R : W16^7 = (-c1, -s1)
+        static_assert(16 * K == 7 * R, "unsupported constant twiddle");
+        return make_float2(v.y * kS1 - v.x * kC1, -v.x * kS1 - v.y * kC1);
+    }
+}
+
+// ---------------------------------------------------------------- register butterflies
+// In-place forward DFT (sign -) of R points held in registers, natural order in and out.
+template <int R>
+struct Bfly;
+
+template <>
+struct Bfly<1> {
+    static MA_HD void run(float2* a) { (void)a; }
+};
+template <>
+struct Bfly<2> {
+    static MA_HD void run(float2* a) {
+        float2 t = a[0];
+        a[0] = cadd(t, a[1]);
+        a[1] = csub(t, a[1]);
+    }
+};
+template <>
+struct Bfly<4> {
+    static MA_HD void run(float2* a) {
+        float2 t0 = cadd(a[0], a[2]);
+        float2 t1 = csub(a[0], a[2]);
+        float2 t2 = cadd(a[1], a[3]);
+        float2 t3 = cmul_mi(csub(a[1], a[3]));
+        a[0] = cadd(t0, t2);
+        a[1] = cadd(t1, t3);
+        a[2] = csub(t0, t2);
+        a[3] = csub(t1, t3);
+    }
+};
+
+template <int R, int K>
+struct BflyCombine {
+    static MA_HD void run(float2* a, const float2* e, const float2* o) {
+        float2 t = mul_wconst<R, K>(o[K]);
+        a[K] = cadd(e[K], t);
+        a[K + R / 2] = csub(e[K], t);
+        if constexpr (K + 1 < R / 2) BflyCombine<R, K + 1>::run(a, e, o);
+    }
+};
+
+template <int R>
+struct Bfly {
+    static_assert(R == 8 || R == 16, "radix");
+    static MA_HD void run(float2* a) {
+        float2 e[R / 2], o[R / 2];
+#pragma unroll
+        for (int k = 0; k < R / 2; ++k) {
+            e[k] = a[2 * k];
+            o[k] = a[2 * k + 1];
+        }
+        Bfly<R / 2>::run(e);
+        Bfly<R / 2>::run(o);
+        BflyCombine<R, 0>::run(a, e, o);
+    }
+};
+
+// ---------------------------------------------------------------- plans
+// Radix chain per complex length M.  The first radix is always R (points per thread);
+// later radices divide R.  Chains are chosen so that every shared-memory exchange is
+// bank-conflict free with the 1-in-16 padding below.
+template <int M>
+struct FftPlan;
+
+#define MA_DEFINE_PLAN(M_, R_, NS_, R0, R1, R2)                                     \
+    template <>                                                                     \
+    struct FftPlan<M_> {                                                            \
+        static constexpr int R = R_;                                                \
+        static constexpr int T = M_ / R_;                                           \
+        static constexpr int NS = NS_;                                              \
+        static constexpr __host__ __device__ int radix(int s) { return s == 0 ? R0 : (s == 1 ? R1 : R2); } \
+        static constexpr __host__ __device__ int ns_before(int s) {                                     \
+            return s == 0 ? 1 : (s == 1 ? R0 : R0 * R1);                            \
+        }                                                                           \
+    };
+
+MA_DEFINE_PLAN(1, 1, 1, 1, 1, 1)
+MA_DEFINE_PLAN(2, 2, 1, 2, 1, 1)
+MA_DEFINE_PLAN(4, 4, 1, 4, 1, 1)
+MA_DEFINE_PLAN(8, 8, 1, 8, 1, 1)
+MA_DEFINE_PLAN(16, 16, 1, 16, 1, 1)
+MA_DEFINE_PLAN(32, 8, 2, 8, 4, 1)
+MA_DEFINE_PLAN(64, 8, 2, 8, 8, 1)
+MA_DEFINE_PLAN(128, 16, 2, 16, 8, 1)
+MA_DEFINE_PLAN(256, 16, 2, 16, 16, 1)
+MA_DEFINE_PLAN(512, 16, 3, 16, 8, 4)
+MA_DEFINE_PLAN(1024, 16, 3, 16, 8, 8)
+MA_DEFINE_PLAN(2048, 16, 3, 16, 16, 8)
+MA_DEFINE_PLAN(4096, 16, 3, 16, 16, 16)
+#undef MA_DEFINE_PLAN
+
+// Shared-memory addressing.  W == 1: one transform owns a contiguous region, element idx
+// lives at idx + idx/16 (float2 units).  W > 1: W transforms are interleaved, element idx
+// of transform slot i lives at idx*W + i (the caller passes the base already offset by i),
+// which is conflict-free for any idx pattern when a half-warp spans 16 slots.
+template <int W>
+MA_HD int saddr(int idx) {
+    if constexpr (W == 1) return idx + (idx >> 4);
+    else return idx * W;
+}
+
+// float2 elements one transform needs in ONE exchange buffer.
+template <int M, int W>
+constexpr __host__ __device__ int smem_elems_per_fft() {
+    if constexpr (W == 1) {
+        constexpr int T = FftPlan<M>::T;
+        int padded = M + (M >> 4) + 1;
+        // Several small transforms share a half-warp: stagger their regions.
+        if (T < 16) {
+            while ((padded & 15) != (T & 15)) ++padded;
+        }
+        return padded;
+    } else {
+        return M;  // per slot; total M*W
+    }
+}
+
+// ---------------------------------------------------------------- twiddled stages
+// Twiddles: twM[j] = exp(-2*pi*i*j/M), j in [0, M).  For a stage of radix r the thread
+// needs w^k, k = 1..r-1, with w = twM[base]; w^1..w^4 (w^1..w^3 for r <= 4) are loaded
+// exactly, the rest are products of at most two exact values times one product.
+template <int r>
+MA_HD void load_twiddles(float2* w, const float2* __restrict__ twM, int base, int M) {
+    // indices base*k stay below M because base < M/r.
+    (void)M;
+    if constexpr (r >= 2) w[1] = MA_LDG(twM + base);
+    if constexpr (r >= 4) {
+        w[2] = MA_LDG(twM + 2 * base);
+        w[3] = MA_LDG(twM + 3 * base);
+    }
+    if constexpr (r >= 8) {
+        w[4] = MA_LDG(twM + 4 * base);
+        w[5] = cmul(w[1], w[4]);
+        w[6] = cmul(w[2], w[4]);
+        w[7] = cmul(w[3], w[4]);
+    }
+    if constexpr (r >= 16) {
+        w[8] = cmul(w[4], w[4]);
+#pragma unroll
+        for (int k = 1; k < 8; ++k) w[8 + k] = cmul(w[k], w[8]);
+    }
+}
+
+template <int M, int W, int S>
+MA_HD void stage_write(const float2* v, int t, float2* sbuf) {
+    using P = FftPlan<M>;
+    constexpr int r = P::radix(S), Ns = P::ns_before(S), NB = P::R / r, T = P::T;
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+        const int jv = t + b * T;
+        const int o0 = (jv / Ns) * (Ns * r) + (jv % Ns);
+#pragma unroll
+        for (int k = 0; k < r; ++k) sbuf[saddr<W>(o0 + k * Ns)] = v[b * r + k];
+    }
+}
+
+template <int M, int W, int S>
+MA_HD void stage_read_compute(float2* v, int t, const float2* sbuf,
+                              const float2* __restrict__ twM) {
+    using P = FftPlan<M>;
+    constexpr int r = P::radix(S), Ns = P::ns_before(S), NB = P::R / r, T = P::T;
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+        const int jv = t + b * T;
+#pragma unroll
+        for (int k = 0; k < r; ++k) v[b * r + k] = sbuf[saddr<W>(jv + k * (M / r))];
+        float2 w[r];
+        load_twiddles<r>(w, twM, (jv % Ns) * (M / (Ns * r)), M);
+#pragma unroll
+        for (int k = 1; k < r; ++k) v[b * r + k] = cmul(v[b * r + k], w[k]);
+        Bfly<r>::run(v + b * r);
+    }
+}
+
+template <int M, int W, int S, class Cta>
+struct StageChain {
+    static MA_HD void run(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
+                          const float2* __restrict__ twM, Cta& cta) {
+        using P = FftPlan<M>;
+        if constexpr (S < P::NS) {
+            float2* sbuf = sbuf0 + parity * buf_stride;
+            stage_write<M, W, S - 1>(v, t, sbuf);
+            cta.sync();
+            stage_read_compute<M, W, S>(v, t, sbuf, twM);
+            parity ^= 1;
+            StageChain<M, W, S + 1, Cta>::run(v, t, sbuf0, buf_stride, parity, twM, cta);
+        }
+    }
+};
+
+// Complex forward FFT of length M.  In: v[q] = z[t + q*T].  Out: v[q] = Z[t + q*T].
+// sbuf0 is the transform's exchange region (already offset by the slot when W > 1);
+// buf_stride is the distance in float2 between the two exchange buffers; parity selects
+// the buffer of the next exchange and is updated.
+template <int M, int W, class Cta>
+MA_HD void fft_forward_regs(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
+                            const float2* __restrict__ twM, Cta& cta) {
+    using P = FftPlan<M>;
+    constexpr int R = P::R;
+    Bfly<R>::run(v);  // stage 0: radix R, no twiddles
+    StageChain<M, W, 1, Cta>::run(v, t, sbuf0, buf_stride, parity, twM, cta);
+    // After the last stage, element (b, k) of the flat array is Z[t + (b + k*NB)*T].
+    constexpr int rl = P::radix(P::NS - 1), NB = R / rl;
+    if constexpr (NB > 1) {
+        float2 tmp[R];
+#pragma unroll
+        for (int i = 0; i < R; ++i) tmp[i] = v[i];
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int k = 0; k < rl; ++k) v[b + k * NB] = tmp[b * rl + k];
+    }
+}
+
+}  // namespace ma

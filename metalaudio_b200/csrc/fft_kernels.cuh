@@ -1,0 +1,419 @@
+// Kernel bodies for real-input transforms that fit in shared memory (N <= 8192):
+//   r2c_body   - forward: frame gather (STFT) + analysis window + packed-real complex FFT
+//                + Hermitian post-process + optional magnitude, one HBM read and one HBM
+//                write per frame.
+//   c2r_body   - inverse: Hermitian pre-process + complex FFT + 1/N scale, optional
+//                synthesis window, overlap-add and window-sum normalisation (iSTFT).
+// The bodies are templated on a Cta type (barrier + ids) so the CPU emulator in the
+// test-suite can execute exactly this index arithmetic.
+#pragma once
+#include "fft_core.cuh"
+
+namespace ma {
+
+enum : int { LAYOUT_HALF_INTERLEAVED = 0, LAYOUT_FULL_SPLIT = 1, LAYOUT_HALF_PACKED = 2 };
+enum : int { MAG_NONE = -1, MAG_MAGNITUDE = 0, MAG_POWER = 1, MAG_DB = 2 };
+
+struct R2CParams {
+    const float* in;            // signals
+    int64_t signal_stride;      // floats between signals
+    int64_t frames_per_signal;  // F
+    int64_t total_frames;       // n_signals * F
+    int64_t signal_len;         // samples at/after this index of a signal read as zero
+    int32_t hop;                // frame f starts at f*hop
+    int32_t frame_valid;        // samples at/after this index of a frame read as zero
+    const float* window;        // N coefficients or nullptr
+    float* out_a;               // half layouts: interleaved bins; FULL_SPLIT: real
+    float* out_b;               // FULL_SPLIT: imag
+    float* mag;                 // optional (N/2+1 per frame)
+    int64_t out_signal_stride;  // float2 units, half layouts
+    int64_t out_frame_stride;   // float2 units, half layouts
+    int32_t layout;
+    int32_t mag_kind;
+    float db_scale;             // 1/reference for MAG_DB
+    const float2* twM;          // exp(-2 pi i j / M), j < M
+    const float2* twN;          // exp(-2 pi i k / N), k <= M/2
+};
+
+MA_HD float mag_value(float2 x, int kind, float db_scale) {
+    float p = x.x * x.x + x.y * x.y;
+    if (kind == MAG_POWER) return p;
+    float m = sqrtf(p);
+    if (kind == MAG_MAGNITUDE) return m;
+    return 20.0f * log10f(m * db_scale);
+}
+
+// Threads per CTA and frames per CTA for the contiguous-frame kernels.
+template <int M>
+struct CtaShape {
+    static constexpr int T = FftPlan<M>::T;
+    static constexpr int THREADS = T >= 128 ? T : 128;
+    static constexpr int FPC = THREADS / T;
+    static constexpr int ELEMS = smem_elems_per_fft<M, 1>();      // one buffer, one frame
+    static constexpr int BUF_STRIDE = ELEMS * FPC;                // float2 between buffers
+    static constexpr int SMEM_BYTES = 2 * BUF_STRIDE * (int)sizeof(float2);
+};
+
+// Hermitian post-process of one pair: a = Z[k], b = Z[(M-k) mod M], w = exp(-2 pi i k/N).
+// xk = X[k], xm = X[M-k].
+MA_HD void herm_post(float2 a, float2 b, float2 w, float2& xk, float2& xm) {
+    float2 xe = make_float2(0.5f * (a.x + b.x), 0.5f * (a.y - b.y));
+    float2 xo = make_float2(0.5f * (a.y + b.y), -0.5f * (a.x - b.x));
+    float2 t = cmul(w, xo);
+    xk = make_float2(xe.x + t.x, xe.y + t.y);
+    xm = make_float2(xe.x - t.x, -(xe.y - t.y));
+}
+
+// Inverse of herm_post without the 1/2 (folded into the final 1/N):
+// a = X[k], b = X[M-k]  ->  zk = 2 Z[k], zm = 2 Z[M-k].
+MA_HD void herm_pre(float2 a, float2 b, float2 w, float2& zk, float2& zm) {
+    float2 xe = make_float2(a.x + b.x, a.y - b.y);   // A + conj(B)
+    float2 d = make_float2(a.x - b.x, a.y + b.y);    // A - conj(B) = W * Xo
+    float2 xo = cmul(cconj(w), d);
+    // Z[k] = Xe + i Xo ; Z[M-k] = conj(Xe - i Xo)
+    zk = make_float2(xe.x - xo.y, xe.y + xo.x);
+    zm = make_float2(xe.x + xo.y, -(xe.y - xo.x));
+}
+
+// ALIGNED: every frame start is 8-byte aligned and no zero padding is requested, so
+// sample pairs are fetched with one float2 load.  Otherwise scalar guarded loads.
+template <int M, bool ALIGNED, class Cta>
+MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
+    using P = FftPlan<M>;
+    using S = CtaShape<M>;
+    constexpr int R = P::R, T = P::T, N = 2 * M;
+    const int tid = cta.tid();
+    const int slot = tid / T;
+    const int t = tid % T;
+    float2* sbuf0 = smem + slot * S::ELEMS;
+    int parity = 0;
+
+    float2 wreg[R];
+    if (p.window != nullptr) {
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int n = t + q * T;
+            wreg[q] = make_float2(MA_LDG(p.window + 2 * n), MA_LDG(p.window + 2 * n + 1));
+        }
+    } else {
+#pragma unroll
+        for (int q = 0; q < R; ++q) wreg[q] = make_float2(1.0f, 1.0f);
+    }
+
+    for (int64_t base = (int64_t)cta.bid() * S::FPC; base < p.total_frames;
+         base += (int64_t)cta.nblocks() * S::FPC) {
+        const int64_t g = base + slot;
+        const bool active = g < p.total_frames;
+        const int64_t s = active ? g / p.frames_per_signal : 0;
+        const int64_t f = active ? g - s * p.frames_per_signal : 0;
+        const int64_t start = f * (int64_t)p.hop;
+        const float* src = p.in + s * p.signal_stride + start;
+
+        float2 v[R];
+        if (ALIGNED) {
+#pragma unroll
+            for (int q = 0; q < R; ++q) {
+                const int n = t + q * T;
+                float2 x = make_float2(0.f, 0.f);
+                if (active) x = MA_LDG(reinterpret_cast<const float2*>(src) + n);
+                v[q] = make_float2(x.x * wreg[q].x, x.y * wreg[q].y);
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < R; ++q) {
+                const int i0 = 2 * (t + q * T);
+                float x0 = 0.f, x1 = 0.f;
+                if (active && i0 < p.frame_valid && start + i0 < p.signal_len) x0 = MA_LDG(src + i0);
+                if (active && i0 + 1 < p.frame_valid && start + i0 + 1 < p.signal_len)
+                    x1 = MA_LDG(src + i0 + 1);
+                v[q] = make_float2(x0 * wreg[q].x, x1 * wreg[q].y);
+            }
+        }
+
+        fft_forward_regs<M, 1, Cta>(v, t, sbuf0, S::BUF_STRIDE, parity, p.twM, cta);
+
+        // exchange for the Hermitian post-process
+        float2* sb = sbuf0 + parity * S::BUF_STRIDE;
+        parity ^= 1;
+#pragma unroll
+        for (int q = 0; q < R; ++q) sb[saddr<1>(t + q * T)] = v[q];
+        cta.sync();
+
+        const int64_t half_off = s * p.out_signal_stride + f * p.out_frame_stride;
+#pragma unroll
+        for (int q = 0; q <= R / 2; ++q) {
+            const int k = t + q * T;
+            if (k > M / 2 || !active) continue;
+            const float2 a = sb[saddr<1>(k)];
+            const float2 b = sb[saddr<1>((M - k) & (M - 1))];
+            const float2 w = MA_LDG(p.twN + k);
+            float2 xk, xm;
+            herm_post(a, b, w, xk, xm);
+            const int km = M - k;
+            if (p.layout == LAYOUT_HALF_INTERLEAVED) {
+                float2* o = reinterpret_cast<float2*>(p.out_a) + half_off;
+                o[k] = xk;
+                o[km] = xm;
+            } else if (p.layout == LAYOUT_HALF_PACKED) {
+                float2* o = reinterpret_cast<float2*>(p.out_a) + half_off;
+                if (k == 0) {
+                    o[0] = make_float2(xk.x, xm.x);
+                } else {
+                    o[k] = xk;
+                    o[km] = xm;
+                }
+            } else {
+                float* re = p.out_a + g * (int64_t)N;
+                float* im = p.out_b + g * (int64_t)N;
+                re[k] = xk.x;
+                im[k] = xk.y;
+                re[km] = xm.x;
+                im[km] = xm.y;
+                if (k > 0) {  // conjugate mirror, bins M+1 .. N-1
+                    re[N - k] = xk.x;
+                    im[N - k] = -xk.y;
+                    if (km < M) {
+                        re[N - km] = xm.x;
+                        im[N - km] = -xm.y;
+                    }
+                }
+            }
+            if (p.mag != nullptr) {
+                float* mg = p.mag + g * (int64_t)(M + 1);
+                mg[k] = mag_value(xk, p.mag_kind, p.db_scale);
+                mg[km] = mag_value(xm, p.mag_kind, p.db_scale);
+            }
+        }
+    }
+}
+
+struct C2RParams {
+    const float* in_a;          // half layouts: interleaved bins; FULL_SPLIT: real
+    const float* in_b;          // FULL_SPLIT: imag
+    int64_t in_signal_stride;   // float2 units, half layouts
+    int64_t in_frame_stride;    // float2 units, half layouts
+    int64_t frames_per_signal;  // F
+    int64_t n_signals;
+    int32_t layout;
+    int32_t hop;
+    const float* window;        // synthesis window (iSTFT) or nullptr
+    float* out;
+    int64_t out_signal_stride;  // floats
+    int64_t out_len;            // iSTFT: (F-1)*hop + N ; plain inverse: unused
+    float floor;                // iSTFT window-sum floor
+    int32_t chunks_per_signal;  // iSTFT: CTAs per signal
+    const float2* twM;
+    const float2* twN;
+};
+
+// Loads the pair (X[k], X[M-k]) of frame g for the inverse pre-process.
+MA_HD void c2r_load_pair(const C2RParams& p, int64_t s, int64_t f, int64_t g, int k, int M,
+                         float2& a, float2& b) {
+    const int km = M - k;
+    if (p.layout == LAYOUT_FULL_SPLIT) {
+        const int N = 2 * M;
+        const float* re = p.in_a + g * (int64_t)N;
+        const float* im = p.in_b + g * (int64_t)N;
+        // Real part of the inverse of an arbitrary spectrum equals the inverse of its
+        // Hermitian part: symmetrise with the mirror bins.
+        if (k == 0) {
+            a = make_float2(MA_LDG(re), 0.f);
+            b = make_float2(MA_LDG(re + M), 0.f);
+        } else {
+            float2 xa = make_float2(MA_LDG(re + k), MA_LDG(im + k));
+            float2 xan = make_float2(MA_LDG(re + N - k), MA_LDG(im + N - k));
+            float2 xb = make_float2(MA_LDG(re + km), MA_LDG(im + km));
+            float2 xbn = make_float2(MA_LDG(re + N - km), MA_LDG(im + N - km));
+            a = make_float2(0.5f * (xa.x + xan.x), 0.5f * (xa.y - xan.y));
+            b = make_float2(0.5f * (xb.x + xbn.x), 0.5f * (xb.y - xbn.y));
+        }
+    } else {
+        const float2* x = reinterpret_cast<const float2*>(p.in_a) + s * p.in_signal_stride +
+                          f * p.in_frame_stride;
+        if (p.layout == LAYOUT_HALF_PACKED) {
+            if (k == 0) {
+                float2 x0 = MA_LDG(x);
+                a = make_float2(x0.x, 0.f);
+                b = make_float2(x0.y, 0.f);
+            } else {
+                a = MA_LDG(x + k);
+                b = MA_LDG(x + km);
+            }
+        } else {
+            a = MA_LDG(x + k);
+            b = MA_LDG(x + km);
+            if (k == 0) {
+                a.y = 0.f;
+                b.y = 0.f;
+            }
+        }
+    }
+}
+
+// Pre-process + FFT of one frame: leaves v[q] = (x[2n+1], x[2n]) * N for n = t + q*T
+// (real and imaginary parts swapped: the inverse transform is run as a forward transform
+// of the swapped spectrum).
+template <int M, class Cta>
+MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int64_t g, int t,
+                     float2* sbuf0, int buf_stride, int& parity, float2* v, Cta& cta) {
+    using P = FftPlan<M>;
+    constexpr int R = P::R, T = P::T;
+    float2* sb = sbuf0 + parity * buf_stride;
+    parity ^= 1;
+#pragma unroll
+    for (int q = 0; q <= R / 2; ++q) {
+        const int k = t + q * T;
+        if (k > M / 2) continue;
+        float2 a = make_float2(0.f, 0.f), b = a;
+        if (active) c2r_load_pair(p, s, f, g, k, M, a, b);
+        const float2 w = MA_LDG(p.twN + k);
+        float2 zk, zm;
+        herm_pre(a, b, w, zk, zm);
+        sb[saddr<1>(k)] = make_float2(zk.y, zk.x);
+        if (k > 0) sb[saddr<1>(M - k)] = make_float2(zm.y, zm.x);
+    }
+    cta.sync();
+#pragma unroll
+    for (int q = 0; q < R; ++q) v[q] = sb[saddr<1>(t + q * T)];
+    fft_forward_regs<M, 1, Cta>(v, t, sbuf0, buf_stride, parity, p.twM, cta);
+}
+
+// Plain batched inverse: out[g][2n], out[g][2n+1].
+template <int M, class Cta>
+MA_HD void c2r_body(const C2RParams& p, Cta& cta, float2* smem) {
+    using P = FftPlan<M>;
+    using S = CtaShape<M>;
+    constexpr int R = P::R, T = P::T, N = 2 * M;
+    const int tid = cta.tid();
+    const int slot = tid / T;
+    const int t = tid % T;
+    float2* sbuf0 = smem + slot * S::ELEMS;
+    int parity = 0;
+    const float scale = 1.0f / (float)N;
+    const int64_t total = p.n_signals * p.frames_per_signal;
+    for (int64_t base = (int64_t)cta.bid() * S::FPC; base < total;
+         base += (int64_t)cta.nblocks() * S::FPC) {
+        const int64_t g = base + slot;
+        const bool active = g < total;
+        const int64_t s = active ? g / p.frames_per_signal : 0;
+        const int64_t f = active ? g - s * p.frames_per_signal : 0;
+        float2 v[R];
+        c2r_frame<M, Cta>(p, active, s, f, g, t, sbuf0, S::BUF_STRIDE, parity, v, cta);
+        if (active) {
+            float2* o = reinterpret_cast<float2*>(p.out + g * (int64_t)N);
+#pragma unroll
+            for (int q = 0; q < R; ++q) o[t + q * T] = make_float2(v[q].y * scale, v[q].x * scale);
+        }
+    }
+}
+
+// Sum of squared window over the frames covering output position o, accumulated in
+// increasing frame order in float32 (the order of the reference's sequential loop),
+// denormal results zeroed, clamped to the floor.
+MA_HD float window_sum_at(const float* __restrict__ window, int64_t o, int N, int hop,
+                          int64_t frames, float floor) {
+    int64_t f_lo = (o >= N) ? (o - N) / hop + 1 : 0;
+    int64_t f_hi = o / hop;
+    if (f_hi > frames - 1) f_hi = frames - 1;
+    float acc = 0.f;
+    for (int64_t f = f_lo; f <= f_hi; ++f) {
+        float w = window ? MA_LDG(window + (o - f * hop)) : 1.0f;
+        acc += w * w;
+    }
+    if (acc < 1.17549435e-38f) acc = 0.f;
+    return acc > floor ? acc : floor;
+}
+
+// iSTFT: one CTA (T threads, one frame at a time) owns the frames [f0, f1) of one signal
+// and the output samples [f0*hop, f1*hop) (through the end of the signal for the last
+// chunk).  Overlap-add runs in a shared-memory ring of N floats; the frames before f0 that
+// reach into the chunk are recomputed instead of exchanged, so no atomics and a fixed
+// summation order.  smem: 2 exchange buffers (float2) followed by the ring (N floats).
+//
+// With window == nullptr and floor < 0 the normaliser is skipped (plain overlap-add of
+// scaled inverse frames): that is the block overlap-add of partitioned convolution.
+template <int M, class Cta>
+MA_HD void istft_body(const C2RParams& p, Cta& cta, float2* smem) {
+    using P = FftPlan<M>;
+    constexpr int R = P::R, T = P::T, N = 2 * M;
+    constexpr int ELEMS = smem_elems_per_fft<M, 1>();
+    const int t = cta.tid();
+    float* ring = reinterpret_cast<float*>(smem + 2 * ELEMS);
+    int parity = 0;
+    const float scale = 1.0f / (float)N;
+    const int hop = p.hop;
+    const int64_t F = p.frames_per_signal;
+    const bool normalise = !(p.window == nullptr && p.floor < 0.f);
+
+    float2 wreg[R];
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+        const int n = t + q * T;
+        if (p.window != nullptr)
+            wreg[q] = make_float2(MA_LDG(p.window + 2 * n) * scale, MA_LDG(p.window + 2 * n + 1) * scale);
+        else
+            wreg[q] = make_float2(scale, scale);
+    }
+
+    const int64_t n_chunks = (int64_t)p.chunks_per_signal;
+    const int64_t total_chunks = p.n_signals * n_chunks;
+    const int64_t per = (F + n_chunks - 1) / n_chunks;
+    const int reach = (N + hop - 1) / hop - 1;  // earlier frames overlapping a frame start
+
+    for (int64_t c = cta.bid(); c < total_chunks; c += cta.nblocks()) {
+        const int64_t s = c / n_chunks;
+        const int64_t ci = c - s * n_chunks;
+        const int64_t f0 = ci * per;
+        int64_t f1 = f0 + per;
+        if (f1 > F) f1 = F;
+        if (f0 >= f1) continue;  // uniform across the CTA
+        int64_t fh = f0 - reach;
+        if (fh < 0) fh = 0;
+        for (int i = t; i < N; i += T) ring[i] = 0.f;
+        cta.sync();
+        for (int64_t f = fh; f < f1; ++f) {
+            float2 v[R];
+            c2r_frame<M, Cta>(p, true, s, f, s * F + f, t, smem, ELEMS, parity, v, cta);
+            const int64_t start = f * (int64_t)hop;
+            if ((hop & 1) == 0) {
+                float2* ring2 = reinterpret_cast<float2*>(ring);
+                const int h0 = (int)((start & (N - 1)) >> 1);
+#pragma unroll
+                for (int q = 0; q < R; ++q) {
+                    const int pp = (h0 + t + q * T) & (M - 1);
+                    float2 r = ring2[pp];
+                    r.x += v[q].y * wreg[q].x;
+                    r.y += v[q].x * wreg[q].y;
+                    ring2[pp] = r;
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < R; ++q) {
+                    const int n2 = 2 * (t + q * T);
+                    const int p0 = (int)((start + n2) & (N - 1));
+                    const int p1 = (int)((start + n2 + 1) & (N - 1));
+                    ring[p0] += v[q].y * wreg[q].x;
+                    ring[p1] += v[q].x * wreg[q].y;
+                }
+            }
+            cta.sync();
+            // Samples [start, start+span) are complete: emit and clear them.
+            const int span = (f == F - 1) ? N : hop;
+            const bool emit = f >= f0;
+            for (int i = t; i < span; i += T) {
+                const int64_t o = start + i;
+                const int rp = (int)(o & (N - 1));
+                const float acc = ring[rp];
+                ring[rp] = 0.f;
+                if (emit && o < p.out_len) {
+                    float r = acc;
+                    if (normalise) r = acc / window_sum_at(p.window, o, N, hop, F, p.floor);
+                    p.out[s * p.out_signal_stride + o] = r;
+                }
+            }
+            cta.sync();
+        }
+    }
+}
+
+}  // namespace ma

@@ -1,0 +1,42 @@
+// FFT plan object and the internal launch entry points other translation units use.
+#pragma once
+#include "fft_kernels.cuh"
+#include "ma_internal.h"
+
+struct ma_fft_plan {
+    ma_context* ctx = nullptr;
+    int n = 0;        // real transform size N
+    int m = 0;        // complex length N/2
+    int hop = 0;
+    bool large = false;         // N > 8192: multi-pass path
+    float* d_window = nullptr;  // N floats or nullptr
+    float2* d_twM = nullptr;    // small path: exp(-2 pi i j/M), j < M
+    float2* d_twN = nullptr;    // small path: exp(-2 pi i k/N), k <= M/2
+    // large path (N = n1 * n2): see fft_large.cu
+    int n1 = 0, n2 = 0;
+    ma_fft_plan* sub_cols = nullptr;  // tables for the n2-point real transforms
+    float2* d_tw1 = nullptr;          // exp(-2 pi i j/n1), j < n1
+    float2* d_twL = nullptr;          // exp(-2 pi i j/N),  j < N (pass twiddles)
+    float2* d_scratch = nullptr;      // (n2/2+1) x n1 complex per transform in a pass
+    int64_t scratch_batch = 0;        // transforms the scratch holds
+};
+
+namespace ma {
+
+constexpr int kMaxSmallN = 8192;
+
+// Queue the forward / inverse / iSTFT kernels for N <= 8192.  Parameters carry device
+// pointers; tables are filled in from the plan.
+ma_status launch_r2c_small(ma_fft_plan* plan, R2CParams p);
+ma_status launch_c2r_small(ma_fft_plan* plan, C2RParams p);
+ma_status launch_istft_small(ma_fft_plan* plan, C2RParams p);
+
+// Large path (N > 8192), contiguous frames only.
+ma_status large_plan_init(ma_fft_plan* plan);
+void large_plan_destroy(ma_fft_plan* plan);
+ma_status launch_r2c_large(ma_fft_plan* plan, const float* in, float* out_a, float* out_b, float* mag,
+                           int mag_kind, float db_scale, int64_t batch, int layout);
+ma_status launch_c2r_large(ma_fft_plan* plan, const float* in_a, const float* in_b, float* out,
+                           int64_t batch, int layout);
+
+}  // namespace ma

@@ -1,0 +1,164 @@
+// __global__ wrappers and launchers for the in-shared-memory transforms (N <= 8192).
+#include "fft_plan.h"
+#include "host_tables.h"
+
+namespace ma {
+
+struct DevCta {
+    __device__ __forceinline__ int tid() const { return threadIdx.x; }
+    __device__ __forceinline__ int bid() const { return blockIdx.x; }
+    __device__ __forceinline__ int nblocks() const { return gridDim.x; }
+    __device__ __forceinline__ void sync() { __syncthreads(); }
+};
+
+extern __shared__ float4 ma_dyn_smem[];
+
+template <int M, bool ALIGNED>
+__global__ void __launch_bounds__(CtaShape<M>::THREADS) r2c_kernel(const R2CParams p) {
+    DevCta cta;
+    r2c_body<M, ALIGNED, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
+}
+
+template <int M>
+__global__ void __launch_bounds__(CtaShape<M>::THREADS) c2r_kernel(const C2RParams p) {
+    DevCta cta;
+    c2r_body<M, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
+}
+
+template <int M>
+__global__ void __launch_bounds__(FftPlan<M>::T) istft_kernel(const C2RParams p) {
+    DevCta cta;
+    istft_body<M, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
+}
+
+// Resident CTAs per SM for a kernel (cached per instantiation and device), after raising
+// its dynamic shared-memory limit.
+template <class K>
+static ma_status occupancy(K kernel, int threads, size_t smem, int* per_sm) {
+    MA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int n = 0;
+    MA_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem));
+    *per_sm = n > 0 ? n : 1;
+    return MA_OK;
+}
+
+template <int M, bool ALIGNED>
+static ma_status launch_r2c_t(ma_fft_plan* plan, const R2CParams& p) {
+    using S = CtaShape<M>;
+    static int per_sm[64] = {0};
+    ma_context* ctx = plan->ctx;
+    int& occ = per_sm[ctx->device & 63];
+    if (occ == 0) MA_TRY(occupancy(r2c_kernel<M, ALIGNED>, S::THREADS, S::SMEM_BYTES, &occ));
+    int64_t want = (p.total_frames + S::FPC - 1) / S::FPC;
+    int64_t cap = (int64_t)ctx->sm_count * occ;
+    int grid = (int)(want < cap ? want : cap);
+    if (grid < 1) return MA_OK;
+    r2c_kernel<M, ALIGNED><<<grid, S::THREADS, S::SMEM_BYTES, ctx->stream>>>(p);
+    return after_launch(ctx);
+}
+
+ma_status launch_r2c_small(ma_fft_plan* plan, R2CParams p) {
+    p.twM = plan->d_twM;
+    p.twN = plan->d_twN;
+    if (p.total_frames <= 0) return MA_OK;
+    const int n = plan->n;
+    const int64_t last_end = (p.frames_per_signal - 1) * (int64_t)p.hop + n;
+    const bool aligned = ((uintptr_t)p.in % 8 == 0) && (p.signal_stride % 2 == 0) && (p.hop % 2 == 0) &&
+                         p.frame_valid >= n && last_end <= p.signal_len;
+    ma_status st = MA_ERR_UNSUPPORTED;
+#define RUN(MM) st = aligned ? launch_r2c_t<MM, true>(plan, p) : launch_r2c_t<MM, false>(plan, p);
+    MA_DISPATCH_M(plan->m, RUN)
+#undef RUN
+    return st;
+}
+
+template <int M>
+static ma_status launch_c2r_t(ma_fft_plan* plan, const C2RParams& p) {
+    using S = CtaShape<M>;
+    static int per_sm[64] = {0};
+    ma_context* ctx = plan->ctx;
+    int& occ = per_sm[ctx->device & 63];
+    if (occ == 0) MA_TRY(occupancy(c2r_kernel<M>, S::THREADS, S::SMEM_BYTES, &occ));
+    const int64_t total = p.n_signals * p.frames_per_signal;
+    int64_t want = (total + S::FPC - 1) / S::FPC;
+    int64_t cap = (int64_t)ctx->sm_count * occ;
+    int grid = (int)(want < cap ? want : cap);
+    if (grid < 1) return MA_OK;
+    c2r_kernel<M><<<grid, S::THREADS, S::SMEM_BYTES, ctx->stream>>>(p);
+    return after_launch(ctx);
+}
+
+ma_status launch_c2r_small(ma_fft_plan* plan, C2RParams p) {
+    p.twM = plan->d_twM;
+    p.twN = plan->d_twN;
+    if (p.n_signals * p.frames_per_signal <= 0) return MA_OK;
+    ma_status st = MA_ERR_UNSUPPORTED;
+#define RUN(MM) st = launch_c2r_t<MM>(plan, p);
+    MA_DISPATCH_M(plan->m, RUN)
+#undef RUN
+    return st;
+}
+
+template <int M>
+static ma_status launch_istft_t(ma_fft_plan* plan, C2RParams& p) {
+    constexpr int T = FftPlan<M>::T;
+    constexpr size_t smem = 2 * smem_elems_per_fft<M, 1>() * sizeof(float2) + 2 * M * sizeof(float);
+    static int per_sm[64] = {0};
+    ma_context* ctx = plan->ctx;
+    int& occ = per_sm[ctx->device & 63];
+    if (occ == 0) MA_TRY(occupancy(istft_kernel<M>, T, smem, &occ));
+    // Chunks per signal: enough CTAs to fill the device a few times over, but chunks long
+    // enough that the recomputed lead-in frames stay a small fraction.
+    const int64_t F = p.frames_per_signal;
+    const int reach = (2 * M + p.hop - 1) / p.hop - 1;
+    const int64_t cap = (int64_t)ctx->sm_count * occ;
+    int64_t chunks = (2 * cap + p.n_signals - 1) / p.n_signals;
+    const int64_t min_len = reach > 0 ? 16 * (int64_t)reach : 1;
+    if (chunks > F / min_len) chunks = F / min_len;
+    if (chunks < 1) chunks = 1;
+    p.chunks_per_signal = (int32_t)chunks;
+    const int64_t total = chunks * p.n_signals;
+    int grid = (int)(total < cap ? total : cap);
+    if (grid < 1) return MA_OK;
+    istft_kernel<M><<<grid, T, smem, ctx->stream>>>(p);
+    return after_launch(ctx);
+}
+
+ma_status launch_istft_small(ma_fft_plan* plan, C2RParams p) {
+    p.twM = plan->d_twM;
+    p.twN = plan->d_twN;
+    if (p.n_signals <= 0 || p.frames_per_signal <= 0) return MA_OK;
+    ma_status st = MA_ERR_UNSUPPORTED;
+#define RUN(MM) st = launch_istft_t<MM>(plan, p);
+    MA_DISPATCH_M(plan->m, RUN)
+#undef RUN
+    return st;
+}
+
+// Magnitude family over bins 0..N/2 of full-N split spectra.
+__global__ void magnitude_kernel(const float* __restrict__ re, const float* __restrict__ im,
+                                 float* __restrict__ out, int64_t batch, int n, int kind, float db_scale) {
+    const int kh = n / 2 + 1;
+    const int64_t total = batch * kh;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t g = i / kh;
+        const int k = (int)(i - g * kh);
+        const float2 x = make_float2(__ldg(re + g * n + k), __ldg(im + g * n + k));
+        out[i] = mag_value(x, kind, db_scale);
+    }
+}
+
+ma_status launch_magnitude(ma_fft_plan* plan, const float* re, const float* im, float* out, int64_t batch,
+                           int kind, float db_scale) {
+    ma_context* ctx = plan->ctx;
+    const int64_t total = batch * (plan->n / 2 + 1);
+    if (total <= 0) return MA_OK;
+    int64_t want = (total + 255) / 256;
+    int64_t cap = (int64_t)ctx->sm_count * 8;
+    int grid = (int)(want < cap ? want : cap);
+    magnitude_kernel<<<grid, 256, 0, ctx->stream>>>(re, im, out, batch, plan->n, kind, db_scale);
+    return after_launch(ctx);
+}
+
+}  // namespace ma

@@ -1,0 +1,60 @@
+// Internal host-side declarations shared by the translation units of the library.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+
+#include "../../include/metalaudio_cuda.h"
+
+struct ma_context {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    cudaStream_t copy_stream = nullptr;
+    void* pinned = nullptr;       // staging buffer, used as two halves
+    size_t pinned_bytes = 0;
+    cudaEvent_t ev_half[2] = {nullptr, nullptr};
+    cudaEvent_t ev_begin = nullptr, ev_end = nullptr, ev_sync = nullptr;
+    bool timing_open = false;
+    bool lost = false;
+    int fault_site = -1;          // host-side fault injection: next call reaching the site fails
+    int fault_error = 0;
+    char name[256] = {0};
+};
+
+namespace ma {
+
+extern std::atomic<uint64_t> g_launch_count;
+extern thread_local int32_t t_last_cuda_error;
+
+// Records a CUDA error for ma_last_cuda_error and maps it to a status.
+ma_status cuda_fail(cudaError_t e);
+// Returns MA_OK, MA_ERR_DEVICE_LOST, or an injected fault for `site`; makes the
+// context's device current.
+ma_status enter(ma_context* ctx, int site);
+// Checks the launch error of the kernel just queued and counts it.
+ma_status after_launch(ma_context* ctx);
+
+// Host <-> device copies through the context (direct for pinned memory, staged
+// through the pinned buffer otherwise).  Synchronous with respect to the host buffer.
+ma_status copy_h2d(ma_context* ctx, void* dptr, const void* host, size_t bytes);
+ma_status copy_d2h(ma_context* ctx, void* host, const void* dptr, size_t bytes);
+
+// Stream-ordered temporary device memory for the *_host entry points.
+ma_status temp_alloc(ma_context* ctx, size_t bytes, void** dptr);
+void temp_free(ma_context* ctx, void* dptr);
+
+}  // namespace ma
+
+#define MA_CUDA(expr)                                         \
+    do {                                                      \
+        cudaError_t _e = (expr);                              \
+        if (_e != cudaSuccess) return ::ma::cuda_fail(_e);    \
+    } while (0)
+
+#define MA_TRY(expr)                         \
+    do {                                     \
+        ma_status _s = (expr);               \
+        if (_s != MA_OK) return _s;          \
+    } while (0)

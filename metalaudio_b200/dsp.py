@@ -1,0 +1,776 @@
+"""Host-side mirror of the reference's public MetalDSP API for the FFT / STFT / partitioned
+convolution path, over the C ABI (``include/metalaudio_cuda.h``).
+
+Names, argument meaning and error behaviour follow the Swift API so that tests read like
+the reference's XCTest suites:
+
+* ``AudioDevice``                       Sources/MetalAudioKit/Core/AudioDevice.swift:222
+* ``Tensor``                            Sources/MetalAudioKit/Buffers/Tensor.swift:12
+* ``FFT``, ``FFT.Config``, ``WindowType``, ``COLACompliance``, ``FFTError``
+                                        Sources/MetalDSP/FFT.swift:12-55, :155-348, :441-495, :818-919, :1780-1847
+* ``FFT.stft`` / ``istft`` / ``forwardBatch`` / ``inverseBatch`` / ``STFTResult``
+                                        Sources/MetalDSP/STFT.swift:10-22, :40-128, :327-527
+* ``Convolution`` (``.partitioned``), ``ConvolutionError``
+                                        Sources/MetalDSP/Convolution.swift:8-47, :112-125, :176-383, :529-775
+
+Every transform runs on the CUDA backend; there is no size routing and no CPU fallback.
+numpy arrays stand in for Swift ``[Float]`` / ``UnsafePointer<Float>``.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+import math
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import numpy as np
+
+from . import _lib as L
+
+_INT_MAX = (1 << 63) - 1
+
+
+# --------------------------------------------------------------------------- errors
+
+class MetalAudioError(Exception):
+    """Sources/MetalAudioKit/Core/AudioDevice.swift:11-77."""
+
+    def __init__(self, case: str, message: str = ""):
+        self.case = case
+        super().__init__(message or case)
+
+    @staticmethod
+    def invalidConfiguration(msg: str) -> "MetalAudioError":
+        return MetalAudioError("invalidConfiguration", f"Invalid configuration: {msg}")
+
+
+class FFTError(Exception):
+    """Sources/MetalDSP/FFT.swift:12-55; ``case`` holds the Swift case name and the payload
+    is kept as attributes; ``errorDescription`` carries the same text."""
+
+    def __init__(self, case: str, description: str, **payload):
+        self.case = case
+        self.errorDescription = description
+        self.__dict__.update(payload)
+        super().__init__(description)
+
+    @staticmethod
+    def inputTooShort(inputSize: int, requiredSize: int) -> "FFTError":
+        return FFTError("inputTooShort",
+                        f"Input size {inputSize} is shorter than the required FFT size {requiredSize}. "
+                        f"Provide at least {requiredSize} samples, or use a smaller FFT size.",
+                        inputSize=inputSize, requiredSize=requiredSize)
+
+    @staticmethod
+    def sizeTooLarge(requestedSize: int, maxSize: int) -> "FFTError":
+        return FFTError("sizeTooLarge", f"FFT size {requestedSize} exceeds maximum supported size {maxSize}.",
+                        requestedSize=requestedSize, maxSize=maxSize)
+
+    @staticmethod
+    def sizeNotPowerOf2(size: int) -> "FFTError":
+        return FFTError("sizeNotPowerOf2",
+                        f"FFT size {size} is not a power of 2. Use sizes like 256, 512, 1024, 2048, etc.", size=size)
+
+    @staticmethod
+    def invalidHopSize(hopSize: int, fftSize: int) -> "FFTError":
+        return FFTError("invalidHopSize", f"Hop size {hopSize} is invalid. Must be > 0 and <= FFT size ({fftSize}).",
+                        hopSize=hopSize, fftSize=fftSize)
+
+    @staticmethod
+    def batchSizeOverflow(batchSize: int, fftSize: int) -> "FFTError":
+        return FFTError("batchSizeOverflow",
+                        f"Batch size {batchSize} with FFT size {fftSize} would overflow buffer limits.",
+                        batchSize=batchSize, fftSize=fftSize)
+
+    @staticmethod
+    def istftOutputOverflow(frameCount: int, hopSize: int, fftSize: int) -> "FFTError":
+        return FFTError("istftOutputOverflow",
+                        f"ISTFT output length calculation overflowed: frameCount={frameCount}, hopSize={hopSize}, "
+                        f"fftSize={fftSize}. Use smaller STFT result or process in chunks.",
+                        frameCount=frameCount, hopSize=hopSize, fftSize=fftSize)
+
+    @staticmethod
+    def istftFrameOverflow(frameIndex: int, hopSize: int, fftSize: int, outputLength: int) -> "FFTError":
+        return FFTError("istftFrameOverflow",
+                        f"ISTFT frame {frameIndex} position overflow: frameIndex*hopSize={frameIndex}*{hopSize} + "
+                        f"fftSize={fftSize} exceeds outputLength={outputLength}. "
+                        "STFT result may be corrupted or parameters are inconsistent.",
+                        frameIndex=frameIndex, hopSize=hopSize, fftSize=fftSize, outputLength=outputLength)
+
+
+class ConvolutionError(Exception):
+    """Sources/MetalDSP/Convolution.swift:8-47."""
+
+    def __init__(self, case: str, description: str, **payload):
+        self.case = case
+        self.errorDescription = description
+        self.__dict__.update(payload)
+        super().__init__(description)
+
+    @staticmethod
+    def inputSizeMismatch(inputSize: int, expectedMaxSize: int, fftSize: int) -> "ConvolutionError":
+        return ConvolutionError("inputSizeMismatch",
+                                f"Convolution input size {inputSize} exceeds expected maximum {expectedMaxSize} "
+                                f"(FFT size: {fftSize}). This would cause circular convolution artifacts. "
+                                "Call setKernel() with a larger expectedInputSize parameter.",
+                                inputSize=inputSize, expectedMaxSize=expectedMaxSize, fftSize=fftSize)
+
+    @staticmethod
+    def kernelNotConfigured() -> "ConvolutionError":
+        return ConvolutionError("kernelNotConfigured",
+                                "Convolution kernel has not been set. Call setKernel() before processing.")
+
+    @staticmethod
+    def emptyKernel() -> "ConvolutionError":
+        return ConvolutionError("emptyKernel", "Convolution kernel cannot be empty. Provide at least one sample.")
+
+    @staticmethod
+    def fftNotInitialized() -> "ConvolutionError":
+        return ConvolutionError("fftNotInitialized",
+                                "FFT resources failed to initialize. This may indicate a Metal device error.")
+
+    @staticmethod
+    def invalidPartitionState(reason: str) -> "ConvolutionError":
+        return ConvolutionError("invalidPartitionState",
+                                f"Partitioned convolution is in an invalid state: {reason}", reason=reason)
+
+    @staticmethod
+    def outputSizeOverflow(inputSize: int, kernelSize: int) -> "ConvolutionError":
+        return ConvolutionError("outputSizeOverflow",
+                                f"Output size would overflow: input ({inputSize}) + kernel ({kernelSize}) - 1 exceeds "
+                                "Int.max. Use smaller buffers or process in chunks.",
+                                inputSize=inputSize, kernelSize=kernelSize)
+
+
+def _raise_status(st: int, where: str = "") -> None:
+    """Map a C status onto the reference's error vocabulary."""
+    if st == L.MA_OK:
+        return
+    lib = L.load()
+    text = lib.ma_status_string(st).decode()
+    if st == L.MA_ERR_DEVICE_LOST:
+        raise MetalAudioError("deviceLost", f"{where}: {text}")
+    if st == L.MA_ERR_TIMEOUT:
+        raise MetalAudioError("gpuTimeout", f"{where}: {text}")
+    if st == L.MA_ERR_ALLOC:
+        raise MetalAudioError("bufferAllocationFailed", f"{where}: {text}")
+    if st == L.MA_ERR_CUDA:
+        raise MetalAudioError("gpuExecutionError", f"{where}: {text} (cudaError {lib.ma_last_cuda_error()})")
+    if st == L.MA_ERR_KERNEL_NOT_CONFIGURED:
+        raise ConvolutionError.fftNotInitialized()
+    raise MetalAudioError("invalidConfiguration", f"{where}: {text}")
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _ptr(a: Optional[np.ndarray]):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+# --------------------------------------------------------------------------- device / tensor
+
+class AudioDevice:
+    """CUDA device + stream context (AudioDevice.swift:222, :323; ComputeContext's
+    executeSync / executeSyncWithTiming slice, ComputeContext.swift:154-297)."""
+
+    def __init__(self, deviceIndex: int = 0, pinnedBytes: int = 0):
+        self._lib = L.load()
+        h = ctypes.c_void_p()
+        st = self._lib.ma_context_create(int(deviceIndex), int(pinnedBytes), ctypes.byref(h))
+        if st != L.MA_OK:
+            if st == L.MA_ERR_DEVICE_LOST:
+                raise MetalAudioError("deviceNotFound", "No CUDA device found; this library has no CPU fallback")
+            _raise_status(st, "AudioDevice()")
+        self._h = h
+        self.deviceIndex = int(deviceIndex)
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def name(self) -> str:
+        buf = ctypes.create_string_buffer(256)
+        self._lib.ma_context_device_name(self._h, buf, 256)
+        return buf.value.decode()
+
+    @property
+    def isDeviceAvailable(self) -> bool:
+        v = ctypes.c_int32(0)
+        self._lib.ma_context_is_available(self._h, ctypes.byref(v))
+        return bool(v.value)
+
+    def markDeviceLost(self) -> None:
+        """AudioDevice.swift:434-472: every later call throws ``deviceLost``."""
+        self._lib.ma_context_mark_lost(self._h)
+
+    def ensureAvailable(self) -> None:
+        if not self.isDeviceAvailable:
+            raise MetalAudioError("deviceLost", "GPU device was lost")
+
+    def synchronize(self, timeout: float = 2.0) -> None:
+        """ComputeContext.executeSync's wait with its 2 s default (ComputeContext.swift:137)."""
+        _raise_status(self._lib.ma_context_sync(self._h, float(timeout)), "synchronize")
+
+    def timingBegin(self) -> None:
+        _raise_status(self._lib.ma_timing_begin(self._h), "timingBegin")
+
+    def timingEnd(self) -> float:
+        """Milliseconds of device time since timingBegin (executeSyncWithTiming)."""
+        ms = ctypes.c_float(0)
+        _raise_status(self._lib.ma_timing_end(self._h, ctypes.byref(ms)), "timingEnd")
+        return float(ms.value)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.ma_context_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Tensor:
+    """float32 device buffer with a shape (Tensor.swift:59, :272, :325, :390)."""
+
+    def __init__(self, device: AudioDevice, shape: Sequence[int]):
+        self.device = device
+        self.shape = tuple(int(s) for s in shape)
+        self.count = int(np.prod(self.shape)) if len(self.shape) else 1
+        p = ctypes.c_void_p()
+        _raise_status(device._lib.ma_buffer_alloc(device.handle, self.count * 4, ctypes.byref(p)), "Tensor()")
+        self._p = p
+
+    @property
+    def pointer(self) -> int:
+        return self._p.value
+
+    @property
+    def byteSize(self) -> int:
+        return self.count * 4
+
+    def copy(self, from_: np.ndarray) -> None:
+        a = _f32(from_)
+        if a.size != self.count:
+            raise MetalAudioError("bufferSizeMismatch", f"expected {self.count} elements, got {a.size}")
+        _raise_status(self.device._lib.ma_memcpy_h2d(self.device.handle, self._p, _ptr(a), a.nbytes), "Tensor.copy")
+
+    def toArray(self) -> np.ndarray:
+        out = np.empty(self.shape, dtype=np.float32)
+        _raise_status(self.device._lib.ma_memcpy_d2h(self.device.handle, _ptr(out), self._p, out.nbytes),
+                      "Tensor.toArray")
+        return out
+
+    def zero(self) -> None:
+        _raise_status(self.device._lib.ma_buffer_zero(self.device.handle, self._p, self.byteSize), "Tensor.zero")
+
+    def free(self) -> None:
+        if getattr(self, "_p", None) and self.device._h:
+            self.device._lib.ma_buffer_free(self.device.handle, self._p)
+        self._p = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+# --------------------------------------------------------------------------- FFT
+
+class WindowType(enum.Enum):
+    """FFT.swift:260-327."""
+    none = "none"
+    hann = "hann"
+    hamming = "hamming"
+    blackman = "blackman"
+
+    def coefficient(self, at: int, length: int) -> np.float32:
+        """Symmetric window (denominator N-1) evaluated in float64 (FFT.swift:268-294)."""
+        if length <= 1:
+            return np.float32(1.0)
+        n = float(at)
+        denom = float(length) - 1.0
+        if self is WindowType.none:
+            return np.float32(1.0)
+        if self is WindowType.hann:
+            return np.float32(0.5 * (1.0 - math.cos(2.0 * math.pi * n / denom)))
+        if self is WindowType.hamming:
+            return np.float32(0.54 - 0.46 * math.cos(2.0 * math.pi * n / denom))
+        return np.float32(0.42 - 0.5 * math.cos(2.0 * math.pi * n / denom) + 0.08 * math.cos(4.0 * math.pi * n / denom))
+
+    def table(self, length: int) -> np.ndarray:
+        if length <= 1 or self is WindowType.none:
+            return np.ones(length, dtype=np.float32)
+        n = np.arange(length, dtype=np.float64)
+        d = float(length) - 1.0
+        if self is WindowType.hann:
+            w = 0.5 * (1.0 - np.cos(2.0 * np.pi * n / d))
+        elif self is WindowType.hamming:
+            w = 0.54 - 0.46 * np.cos(2.0 * np.pi * n / d)
+        else:
+            w = 0.42 - 0.5 * np.cos(2.0 * np.pi * n / d) + 0.08 * np.cos(4.0 * np.pi * n / d)
+        return w.astype(np.float32)
+
+    @property
+    def colaHopDivisors(self) -> List[int]:
+        return {WindowType.none: [1], WindowType.hann: [2, 4], WindowType.hamming: [], WindowType.blackman: [3, 4]}[self]
+
+    @property
+    def name_(self) -> str:
+        return {WindowType.none: "rectangular", WindowType.hann: "Hann", WindowType.hamming: "Hamming",
+                WindowType.blackman: "Blackman"}[self]
+
+
+class COLACompliance(enum.Enum):
+    """FFT.swift:330-348."""
+    perfect = "perfect"
+    nearPerfect = "nearPerfect"
+    nonCompliant = "nonCompliant"
+
+    @property
+    def description(self) -> str:
+        return {COLACompliance.perfect: "Perfect COLA - guaranteed perfect reconstruction",
+                COLACompliance.nearPerfect: "Near-perfect COLA - reconstruction error typically < 0.1%",
+                COLACompliance.nonCompliant: "Non-COLA - reconstruction may have artifacts"}[self]
+
+
+class Backend(enum.Enum):
+    """FFT.swift:1519-1550.  Kept for source compatibility; every size runs on ``cuda``."""
+    vdsp = "vdsp"
+    gpu = "gpu"
+    mpsGraph = "mpsGraph"
+    cuda = "cuda"
+
+
+@dataclass
+class STFTResult:
+    """STFT.swift:10-22: ``real`` / ``imag`` are (frameCount, fftSize) arrays (the reference's
+    array-of-arrays, full-N split layout)."""
+    real: np.ndarray
+    imag: np.ndarray
+
+    @property
+    def frameCount(self) -> int:
+        return int(len(self.real))
+
+    @property
+    def binCount(self) -> int:
+        return int(self.real.shape[1]) if self.frameCount else 0
+
+
+class ToleranceProvider:
+    """The two fields of ToleranceConfiguration the path reads
+    (Sources/MetalAudioKit/Config/ToleranceConfiguration.swift:166-181: ``conservative()``,
+    which is what an unknown GPU family maps to)."""
+    windowFloorEpsilon: float = 1e-8
+    fftAccuracy: float = 1e-6
+    convolutionAccuracy: float = 1e-6
+
+
+def validatedWindowFloor(configured: Optional[float] = None) -> float:
+    """STFT.swift:491-501."""
+    c = np.float32(ToleranceProvider.windowFloorEpsilon if configured is None else configured)
+    if c < np.float32(1e-10):
+        return 1e-6
+    if c > np.float32(0.1):
+        return 0.1
+    return float(c)
+
+
+class FFT:
+    """FFT.swift:155.  One CUDA plan per object."""
+
+    maxFFTSize = 1 << 24  # FFT.swift:422
+
+    @dataclass
+    class Config:
+        """FFT.swift:158-258."""
+        size: int
+        inverse: bool = False
+        windowType: WindowType = WindowType.hann
+        hopSize: Optional[int] = None
+
+        def __post_init__(self):
+            if self.hopSize is None:
+                self.hopSize = max(1, self.size // 4)
+
+        @property
+        def colaCompliance(self) -> COLACompliance:
+            divs = self.windowType.colaHopDivisors
+            if not divs:
+                if self.windowType is WindowType.hamming and self.hopSize in (self.size // 2, self.size // 4):
+                    return COLACompliance.nearPerfect
+                return COLACompliance.nonCompliant
+            for d in divs:
+                if self.size % d == 0 and self.hopSize == self.size // d:
+                    return COLACompliance.perfect
+            return COLACompliance.nonCompliant
+
+        @property
+        def overlapPercent(self) -> int:
+            return 100 - (self.hopSize * 100 // self.size)
+
+        def validateCOLA(self):
+            c = self.colaCompliance
+            w = self.windowType.name_
+            if c is COLACompliance.perfect:
+                return True, c, f"{w} window with hop size {self.hopSize} (overlap {self.overlapPercent}%) satisfies COLA"
+            if c is COLACompliance.nearPerfect:
+                return True, c, f"{w} window with hop size {self.hopSize} is near-COLA (error < 0.1%)"
+            hops = []
+            for d in self.windowType.colaHopDivisors:
+                if self.size % d == 0:
+                    hop = self.size // d
+                    hops.append(f"{hop} ({100 - (hop * 100 // self.size)}% overlap)")
+            sug = ("Suggested hop sizes: " + ", ".join(hops)) if hops else \
+                "Consider using Hann window for COLA-compliant STFT"
+            return False, c, f"{w} window with hop size {self.hopSize} does not satisfy COLA. {sug}"
+
+    def __init__(self, device: AudioDevice, config: "FFT.Config", window: Optional[np.ndarray] = None):
+        """``window`` overrides the table built from ``config.windowType`` (e.g. a periodic
+        Hann); the reference always builds the symmetric table (FFT.swift:461)."""
+        n = int(config.size)
+        if n <= 0 or (n & (n - 1)) != 0:
+            raise FFTError.sizeNotPowerOf2(n)
+        if n > FFT.maxFFTSize:
+            raise FFTError.sizeTooLarge(n, FFT.maxFFTSize)
+        if config.hopSize <= 0 or config.hopSize > n:
+            raise FFTError.invalidHopSize(config.hopSize, n)
+        if n < 2:
+            raise MetalAudioError.invalidConfiguration("FFT size 1 is not served by the CUDA backend")
+        self.device = device
+        self.config = config
+        self.size = n
+        self._lib = device._lib
+        self.window = _f32(window) if window is not None else config.windowType.table(n)
+        if self.window.size != n:
+            raise MetalAudioError.invalidConfiguration("window table must have `size` coefficients")
+        has_window = window is not None or config.windowType is not WindowType.none
+        h = ctypes.c_void_p()
+        st = self._lib.ma_fft_plan_create(device.handle, n, _ptr(self.window) if has_window else None,
+                                          int(config.hopSize), ctypes.byref(h))
+        _raise_status(st, "FFT.init")
+        self._h = h
+
+    # ---- single transforms (pointer API of the reference; arrays here)
+    def forward(self, input: np.ndarray, outputReal: np.ndarray, outputImag: np.ndarray) -> None:
+        """FFT.swift:818-855: unnormalised DFT of N real samples into real[N], imag[N].
+        Direction follows ``config.inverse`` as in the reference (one vDSP setup serves both
+        methods, FFT.swift:470-482): an ``inverse: true`` object conjugates."""
+        n = self.size
+        x = _f32(input).reshape(-1)[:n]
+        st = self._lib.ma_fft_forward_host(self._h, _ptr(x), _ptr(outputReal), _ptr(outputImag), None, 0, 1.0, 1,
+                                           L.LAYOUT_FULL_SPLIT)
+        if st != L.MA_OK:  # non-throwing API: outputs zeroed on failure (FFT.swift:826-835)
+            outputReal[:n] = 0
+            outputImag[:n] = 0
+            return
+        if self.config.inverse:
+            outputImag[:n] *= -1.0
+
+    def inverse(self, inputReal: np.ndarray, inputImag: np.ndarray, output: np.ndarray) -> None:
+        """FFT.swift:889-919: real part of the DFT in the object's direction, times 1/N.
+        With ``config.inverse == True`` this is the inverse transform; a forward-configured
+        object returns the time-reversed sequence, as the reference does."""
+        n = self.size
+        re = _f32(inputReal).reshape(-1)[:n]
+        im = _f32(inputImag).reshape(-1)[:n]
+        out = np.empty(n, dtype=np.float32)
+        st = self._lib.ma_fft_inverse_host(self._h, _ptr(re), _ptr(im), _ptr(out), 1, L.LAYOUT_FULL_SPLIT)
+        if st != L.MA_OK:
+            output[:n] = 0
+            return
+        if not self.config.inverse:
+            out = np.concatenate([out[:1], out[1:][::-1]])
+        output[:n] = out
+
+    def _mag(self, real, imag, out, kind, reference=1.0):
+        kh = self.size // 2 + 1
+        re = _f32(real).reshape(-1)[:kh]
+        im = _f32(imag).reshape(-1)[:kh]
+        tmp = np.empty(kh, dtype=np.float32)
+        st = self._lib.ma_fft_magnitude_host(self._h, _ptr(re), _ptr(im), _ptr(tmp), 1, kind, float(reference))
+        _raise_status(st, "magnitude")
+        out[:kh] = tmp
+
+    def magnitude(self, real, imag, magnitude) -> None:
+        """FFT.swift:1780-1791 (N/2+1 values)."""
+        self._mag(real, imag, magnitude, L.MAG_MAGNITUDE)
+
+    def power(self, real, imag, power) -> None:
+        """FFT.swift:1804-1815."""
+        self._mag(real, imag, power, L.MAG_POWER)
+
+    def magnitudeDB(self, real, imag, magnitudeDB, reference: float = 1.0) -> None:
+        """FFT.swift:1833-1847."""
+        self._mag(real, imag, magnitudeDB, L.MAG_DB, reference)
+
+    # ---- backend shims (FFT.swift:1552-1747): one backend, kept for source compatibility
+    @property
+    def optimalBackend(self) -> Backend:
+        return Backend.cuda
+
+    @property
+    def shouldUseGPU(self) -> bool:
+        return True
+
+    def warmup(self) -> None:
+        x = np.zeros(self.size, dtype=np.float32)
+        r = np.zeros(self.size, dtype=np.float32)
+        i = np.zeros(self.size, dtype=np.float32)
+        self.forward(x, r, i)
+
+    def forwardAuto(self, input, outputReal, outputImag) -> Backend:
+        if len(input) < self.size:
+            raise FFTError.inputTooShort(len(input), self.size)
+        self.forward(np.asarray(input), outputReal, outputImag)
+        return Backend.cuda
+
+    def inverseAuto(self, inputReal, inputImag, output) -> Backend:
+        self.inverse(inputReal, inputImag, output)
+        return Backend.cuda
+
+    # ---- batches
+    def forwardBatch(self, inputs: np.ndarray):
+        """STFT.swift:94-128: batch of forward transforms; returns (real, imag) (B, N)."""
+        n = self.size
+        inputs = np.asarray(inputs, dtype=np.float32)
+        if inputs.size == 0:
+            return np.zeros((0, n), np.float32), np.zeros((0, n), np.float32)
+        for idx, row in enumerate(inputs):
+            if len(row) < n:
+                raise FFTError.inputTooShort(len(row), n)
+        x = _f32(inputs[:, :n])
+        b = x.shape[0]
+        if b * n > _INT_MAX // 8:
+            raise FFTError.batchSizeOverflow(b, n)
+        re = np.empty((b, n), np.float32)
+        im = np.empty((b, n), np.float32)
+        st = self._lib.ma_fft_forward_host(self._h, _ptr(x), _ptr(re), _ptr(im), None, 0, 1.0, b, L.LAYOUT_FULL_SPLIT)
+        _raise_status(st, "forwardBatch")
+        return re, im
+
+    def inverseBatch(self, inputsReal: np.ndarray, inputsImag: np.ndarray) -> np.ndarray:
+        """STFT.swift:327-373 with the true inverse transform."""
+        n = self.size
+        re = _f32(inputsReal)
+        im = _f32(inputsImag)
+        if re.size == 0:
+            return np.zeros((0, n), np.float32)
+        b = re.shape[0]
+        out = np.empty((b, n), np.float32)
+        st = self._lib.ma_fft_inverse_host(self._h, _ptr(re), _ptr(im), _ptr(out), b, L.LAYOUT_FULL_SPLIT)
+        _raise_status(st, "inverseBatch")
+        return out
+
+    # ---- STFT / iSTFT
+    def frameCount(self, inputLength: int) -> int:
+        if inputLength < self.size:
+            raise FFTError.inputTooShort(inputLength, self.size)
+        return (inputLength - self.size) // self.config.hopSize + 1
+
+    def stft(self, input: np.ndarray) -> STFTResult:
+        """STFT.swift:40-81: frames at i*hop, analysis window, forward DFT, full-N split."""
+        x = _f32(input).reshape(-1)
+        f = self.frameCount(x.size)
+        n = self.size
+        re = np.empty((f, n), np.float32)
+        im = np.empty((f, n), np.float32)
+        st = self._lib.ma_stft_host(self._h, _ptr(x), x.size, x.size, 1, _ptr(re), _ptr(im), None, 0, 1.0,
+                                    L.LAYOUT_FULL_SPLIT)
+        _raise_status(st, "stft")
+        return STFTResult(re, im)
+
+    def istft(self, stft: STFTResult) -> np.ndarray:
+        """STFT.swift:384-527.  Uses the true inverse transform per frame; the reference
+        pushes frames through the object's forward-direction setup, which time-reverses
+        them (its tests only assert loose structure)."""
+        f = stft.frameCount
+        if f == 0:
+            return np.zeros(0, np.float32)
+        n, hop = self.size, self.config.hopSize
+        if (f - 1) * hop + n > _INT_MAX:
+            raise FFTError.istftOutputOverflow(f, hop, n)
+        if len(stft.real) < f or len(stft.imag) < f:
+            raise FFTError.inputTooShort(min(len(stft.real), len(stft.imag)), f)
+        out_len = (f - 1) * hop + n
+        re = _f32(stft.real)
+        im = _f32(stft.imag)
+        out = np.empty(out_len, np.float32)
+        st = self._lib.ma_istft_host(self._h, _ptr(re), _ptr(im), f, 1, _ptr(out), out_len,
+                                     validatedWindowFloor(), L.LAYOUT_FULL_SPLIT)
+        _raise_status(st, "istft")
+        return out
+
+    # ---- multi-signal, half-spectrum forms (device-friendly layout; not in the reference)
+    def stftBatch(self, signals: np.ndarray, magnitude: bool = False):
+        """STFT of (S, L) signals -> complex64 (S, F, N/2+1) [, float32 magnitudes]."""
+        x = _f32(signals)
+        s, length = x.shape
+        f = self.frameCount(length)
+        kh = self.size // 2 + 1
+        spec = np.empty((s, f, kh, 2), np.float32)
+        mag = np.empty((s, f, kh), np.float32) if magnitude else None
+        st = self._lib.ma_stft_host(self._h, _ptr(x), length, length, s, _ptr(spec), None, _ptr(mag),
+                                    L.MAG_MAGNITUDE, 1.0, L.LAYOUT_HALF_INTERLEAVED)
+        _raise_status(st, "stftBatch")
+        spec_c = spec.view(np.complex64).reshape(s, f, kh)
+        return (spec_c, mag) if magnitude else spec_c
+
+    def istftBatch(self, spectra: np.ndarray) -> np.ndarray:
+        """Inverse of stftBatch: complex64 (S, F, N/2+1) -> (S, (F-1)*hop+N)."""
+        z = np.ascontiguousarray(spectra, dtype=np.complex64)
+        s, f, kh = z.shape
+        out_len = (f - 1) * self.config.hopSize + self.size
+        out = np.empty((s, out_len), np.float32)
+        st = self._lib.ma_istft_host(self._h, _ptr(z.view(np.float32)), None, f, s, _ptr(out), out_len,
+                                     validatedWindowFloor(), L.LAYOUT_HALF_INTERLEAVED)
+        _raise_status(st, "istftBatch")
+        return out
+
+    def releaseGPUResources(self) -> None:
+        """STFT.swift:537-542.  Device tables are a few KB; kept so the object stays usable."""
+
+    def didReceiveMemoryPressure(self, level: str) -> None:
+        """MemoryPressureResponder hook (STFT.swift:544-559)."""
+        if level == "critical":
+            self.releaseGPUResources()
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) and self.device._h:
+            self._lib.ma_fft_plan_destroy(self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# --------------------------------------------------------------------------- convolution
+
+class Convolution:
+    """Convolution.swift:176.  Only ``Mode.partitioned`` is served by this backend."""
+
+    class Mode:
+        """Convolution.swift:112-125."""
+
+        def __init__(self, kind: str, blockSize: int = 0, useMPSGraphFFT: bool = False):
+            self.kind = kind
+            self.blockSize = blockSize
+            self.useMPSGraphFFT = useMPSGraphFFT
+
+        @staticmethod
+        def partitioned(blockSize: int, useMPSGraphFFT: bool = False) -> "Convolution.Mode":
+            return Convolution.Mode("partitioned", blockSize, useMPSGraphFFT)
+
+    def __init__(self, device: AudioDevice, mode: "Convolution.Mode", channels: int = 1):
+        """``channels`` > 1 runs that many independent channels through one object (the
+        reference holds one object per channel)."""
+        if mode.kind != "partitioned":
+            raise MetalAudioError.invalidConfiguration("only .partitioned mode is served by the CUDA backend")
+        self.device = device
+        self.mode = mode
+        self.channels = int(channels)
+        self.kernel = np.zeros(0, np.float32)
+        self._lib = device._lib
+        self._h = None
+
+    def setKernel(self, kernel: np.ndarray, expectedInputSize: Optional[int] = None,
+                  channelToKernel: Optional[Sequence[int]] = None) -> None:
+        """Convolution.swift:188-208 -> :250-322.  ``kernel`` may be (taps,) or (n_irs, taps)
+        with ``channelToKernel`` mapping each channel to its impulse response."""
+        k = _f32(kernel)
+        if k.size == 0:
+            raise ConvolutionError.emptyKernel()
+        b = int(self.mode.blockSize)
+        if b <= 0:
+            raise MetalAudioError.invalidConfiguration(f"Block size must be positive, got {b}")
+        if (b & (b - 1)) != 0:
+            raise FFTError.sizeNotPowerOf2(2 * b)
+        k2 = k.reshape(1, -1) if k.ndim == 1 else k
+        self.kernel = k2[0] if k.ndim == 1 else k2
+        self._taps = int(k2.shape[1])
+        if self._h is None:
+            h = ctypes.c_void_p()
+            _raise_status(self._lib.ma_pconv_create(self.device.handle, b, self.channels, ctypes.byref(h)),
+                          "Convolution.setKernel")
+            self._h = h
+        cmap = None
+        if channelToKernel is not None:
+            cmap = np.ascontiguousarray(channelToKernel, dtype=np.int32)
+        st = self._lib.ma_pconv_set_kernels(self._h, _ptr(k2), self._taps, int(k2.shape[0]), _ptr(cmap))
+        _raise_status(st, "Convolution.setKernel")
+
+    @property
+    def partitionCount(self) -> int:
+        v = ctypes.c_int32(0)
+        if self._h is None:
+            return 0
+        self._lib.ma_pconv_partition_count(self._h, ctypes.byref(v))
+        return int(v.value)
+
+    @property
+    def kernelTailLength(self) -> int:
+        return 0 if self._h is None else self._taps - 1
+
+    def expectedOutputSize(self, forInputSize: int) -> int:
+        return forInputSize if self._h is None else forInputSize + self._taps - 1
+
+    @property
+    def maxInputSize(self) -> int:
+        return 0
+
+    def process(self, input: np.ndarray, output: Optional[np.ndarray] = None) -> np.ndarray:
+        """Convolution.swift:336-352 -> :529-758.  (L,) for one channel or (channels, L);
+        returns the full L+K-1 samples per channel.  A caller-supplied ``output`` at least
+        that long is zeroed and filled like the reference's ``inout`` array."""
+        x = _f32(input)
+        if x.size == 0:
+            return np.zeros(0, np.float32)
+        if self._h is None:
+            raise ConvolutionError.fftNotInitialized()
+        single = x.ndim == 1
+        x2 = x.reshape(1, -1) if single else x
+        if x2.shape[0] != self.channels:
+            raise MetalAudioError.invalidConfiguration(f"expected {self.channels} channels, got {x2.shape[0]}")
+        length = x2.shape[1]
+        if length + self._taps - 1 > _INT_MAX:
+            raise ConvolutionError.outputSizeOverflow(length, self._taps)
+        full = length + self._taps - 1
+        out = np.empty((self.channels, full), np.float32)
+        st = self._lib.ma_pconv_process_host(self._h, _ptr(x2), length, length, _ptr(out), full)
+        _raise_status(st, "Convolution.process")
+        res = out[0] if single else out
+        if output is not None and single and output.size >= full:
+            output[:] = 0
+            output[:full] = res
+            return output
+        return res
+
+    def reset(self) -> None:
+        """Convolution.swift:764-775."""
+        if self._h is not None:
+            _raise_status(self._lib.ma_pconv_reset(self._h), "Convolution.reset")
+
+    def releaseFFTResources(self) -> None:
+        """Convolution.swift:802."""
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) and self.device._h:
+            self._lib.ma_pconv_destroy(self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

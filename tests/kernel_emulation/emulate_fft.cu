@@ -1,0 +1,96 @@
+// CPU execution of the small-FFT kernel bodies through the thread-block emulator.
+// TEST INFRASTRUCTURE ONLY (built by tests/test_kernel_emulation.py into a private .so).
+#include <cstring>
+#include <vector>
+
+#include "../../metalaudio_b200/csrc/fft_kernels.cuh"
+#include "../../metalaudio_b200/csrc/host_tables.h"
+#include "host_cta.h"
+
+using namespace ma;
+
+extern "C" {
+
+// Forward R2C of total_frames frames; returns 0 on success, -1 for an unsupported size.
+int emul_r2c(int n, int aligned, const float* in, long long signal_stride, long long frames_per_signal,
+             long long total_frames, long long signal_len, int hop, int frame_valid,
+             const float* window, float* out_a, float* out_b, float* mag, long long out_signal_stride,
+             long long out_frame_stride, int layout, int mag_kind, float db_scale, int nblocks) {
+    const int M = n / 2;
+    auto twM = make_twiddles(M, M);
+    auto twN = make_twiddles(n, M / 2 + 1);
+    R2CParams p{};
+    p.in = in; p.signal_stride = signal_stride; p.frames_per_signal = frames_per_signal;
+    p.total_frames = total_frames; p.signal_len = signal_len; p.hop = hop; p.frame_valid = frame_valid;
+    p.window = window; p.out_a = out_a; p.out_b = out_b; p.mag = mag;
+    p.out_signal_stride = out_signal_stride; p.out_frame_stride = out_frame_stride;
+    p.layout = layout; p.mag_kind = mag_kind; p.db_scale = db_scale;
+    p.twM = twM.data(); p.twN = twN.data();
+    int rc = -1;
+#define RUN(MM)                                                                              \
+    {                                                                                        \
+        using S = CtaShape<MM>;                                                              \
+        run_grid(nblocks, S::THREADS, S::SMEM_BYTES, [&](HostCta& cta, void* sm) {           \
+            if (aligned) r2c_body<MM, true, HostCta>(p, cta, (float2*)sm);                   \
+            else r2c_body<MM, false, HostCta>(p, cta, (float2*)sm);                          \
+        });                                                                                  \
+        rc = 0;                                                                              \
+    }
+    MA_DISPATCH_M(M, RUN)
+#undef RUN
+    return rc;
+}
+
+int emul_c2r(int n, const float* in_a, const float* in_b, long long in_signal_stride,
+             long long in_frame_stride, long long frames_per_signal, long long n_signals, int layout,
+             float* out, int nblocks) {
+    const int M = n / 2;
+    auto twM = make_twiddles(M, M);
+    auto twN = make_twiddles(n, M / 2 + 1);
+    C2RParams p{};
+    p.in_a = in_a; p.in_b = in_b; p.in_signal_stride = in_signal_stride; p.in_frame_stride = in_frame_stride;
+    p.frames_per_signal = frames_per_signal; p.n_signals = n_signals; p.layout = layout; p.out = out;
+    p.twM = twM.data(); p.twN = twN.data();
+    int rc = -1;
+#define RUN(MM)                                                                              \
+    {                                                                                        \
+        using S = CtaShape<MM>;                                                              \
+        run_grid(nblocks, S::THREADS, S::SMEM_BYTES, [&](HostCta& cta, void* sm) {           \
+            c2r_body<MM, HostCta>(p, cta, (float2*)sm);                                      \
+        });                                                                                  \
+        rc = 0;                                                                              \
+    }
+    MA_DISPATCH_M(M, RUN)
+#undef RUN
+    return rc;
+}
+
+int emul_istft(int n, int hop, const float* in_a, const float* in_b, long long in_signal_stride,
+               long long in_frame_stride, long long frames, long long n_signals, int layout,
+               const float* window, float floor, float* out, long long out_signal_stride,
+               long long out_len, int chunks_per_signal, int nblocks) {
+    const int M = n / 2;
+    auto twM = make_twiddles(M, M);
+    auto twN = make_twiddles(n, M / 2 + 1);
+    C2RParams p{};
+    p.in_a = in_a; p.in_b = in_b; p.in_signal_stride = in_signal_stride; p.in_frame_stride = in_frame_stride;
+    p.frames_per_signal = frames; p.n_signals = n_signals; p.layout = layout; p.hop = hop;
+    p.window = window; p.out = out; p.out_signal_stride = out_signal_stride; p.out_len = out_len;
+    p.floor = floor; p.chunks_per_signal = chunks_per_signal;
+    p.twM = twM.data(); p.twN = twN.data();
+    int rc = -1;
+#define RUN(MM)                                                                                  \
+    {                                                                                            \
+        constexpr int ELEMS = smem_elems_per_fft<MM, 1>();                                       \
+        const size_t smem = 2 * ELEMS * sizeof(float2) + (size_t)n * sizeof(float);              \
+        run_grid(nblocks, FftPlan<MM>::T, smem, [&](HostCta& cta, void* sm) {                    \
+            istft_body<MM, HostCta>(p, cta, (float2*)sm);                                        \
+        });                                                                                      \
+        rc = 0;                                                                                  \
+    }
+    MA_DISPATCH_M(M, RUN)
+#undef RUN
+    return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,174 @@
+"""GPU parity of the FFT entry points against the float64 oracle and the float32 port,
+through the C ABI (via the host mirror).  Tolerance: relative RMS <= 1e-5 (the benchmark's
+stated bound); the reference's own per-size bounds are asserted where it has them."""
+import numpy as np
+import pytest
+
+from oracle import float64 as o64
+from oracle import reference_path as rp
+from oracle import configs
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+SIZES = [2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192]
+
+
+def make_fft(device, n, **kw):
+    from metalaudio_b200 import FFT, WindowType
+    kw.setdefault("windowType", WindowType.none)
+    return FFT(device, FFT.Config(size=n, **kw))
+
+
+@pytest.mark.parametrize("n", SIZES)
+def test_forward_matches_oracle(device, n):
+    rng = np.random.default_rng(n)
+    x = rng.standard_normal(n).astype(np.float32)
+    fft = make_fft(device, n)
+    re = np.zeros(n, np.float32)
+    im = np.zeros(n, np.float32)
+    fft.forward(x, re, im)
+    ref = o64.fft_forward(x)
+    assert o64.rel_rms(re + 1j * im, ref) <= TOL
+    pre, pim = rp.fft_forward(x)
+    assert o64.rel_rms(re + 1j * im, pre + 1j * pim) <= TOL
+    # reference cross-implementation bound: 2.5e-5*sqrt(N/256) max abs error on unit-scale input
+    assert np.max(np.abs((re + 1j * im) - ref)) < 2.5e-5 * max(1.0, np.sqrt(n / 256)) * np.sqrt(n)
+
+
+@pytest.mark.parametrize("n", SIZES)
+def test_round_trip_two_objects(device, n):
+    """FFTTests round trip: forward object + inverse object reproduce the input."""
+    rng = np.random.default_rng(100 + n)
+    x = rng.standard_normal(n).astype(np.float32)
+    f = make_fft(device, n)
+    i = make_fft(device, n, inverse=True)
+    re = np.zeros(n, np.float32)
+    im = np.zeros(n, np.float32)
+    y = np.zeros(n, np.float32)
+    f.forward(x, re, im)
+    i.inverse(re, im, y)
+    assert o64.rel_rms(y, x) <= TOL
+    assert np.max(np.abs(y - x)) < 1e-5  # reference regression ceiling
+
+
+def test_config1_single_2048(device):
+    """Benchmark configuration 1: one 2048-point frame of N(0,1), window off."""
+    x = configs.c1_frame()
+    n = 2048
+    f = make_fft(device, n)
+    i = make_fft(device, n, inverse=True)
+    re = np.zeros(n, np.float32)
+    im = np.zeros(n, np.float32)
+    mag = np.zeros(n // 2 + 1, np.float32)
+    y = np.zeros(n, np.float32)
+    f.forward(x, re, im)
+    f.magnitude(re, im, mag)
+    i.inverse(re, im, y)
+    ref = o64.fft_forward(x)
+    assert o64.rel_rms(re + 1j * im, ref) <= TOL
+    assert o64.rel_rms(mag, np.abs(ref[: n // 2 + 1])) <= TOL
+    assert o64.rel_rms(y, x) <= TOL
+
+
+def test_known_answers(device):
+    """Impulse -> flat spectrum, DC -> N at bin 0, silence -> zeros, bin-k sine peaks at k,
+    conjugate symmetry with Im X[0] = Im X[N/2] = 0 (FFTTests known-answer rows)."""
+    n = 1024
+    f = make_fft(device, n)
+    re = np.zeros(n, np.float32)
+    im = np.zeros(n, np.float32)
+    x = np.zeros(n, np.float32); x[0] = 1
+    f.forward(x, re, im)
+    assert np.allclose(re, 1, atol=1e-6) and np.allclose(im, 0, atol=1e-6)
+    f.forward(np.ones(n, np.float32), re, im)
+    assert abs(re[0] - n) < 1e-3 and np.max(np.abs(re[1:])) < 1e-3 and np.max(np.abs(im)) < 1e-3
+    f.forward(np.zeros(n, np.float32), re, im)
+    assert not re.any() and not im.any()
+    k = 37
+    x = np.sin(2 * np.pi * k * np.arange(n) / n).astype(np.float32)
+    f.forward(x, re, im)
+    mag = np.zeros(n // 2 + 1, np.float32)
+    f.magnitude(re, im, mag)
+    assert int(np.argmax(mag)) == k and abs(mag[k] - n / 2) < 1e-2
+    rng = np.random.default_rng(5)
+    f.forward(rng.standard_normal(n).astype(np.float32), re, im)
+    assert abs(im[0]) < 1e-5 and abs(im[n // 2]) < 1e-5
+    assert np.allclose(re[1:n // 2], re[n - 1:n // 2:-1], atol=1e-5)
+    assert np.allclose(im[1:n // 2], -im[n - 1:n // 2:-1], atol=1e-5)
+    # Parseval within 1 %
+    x = rng.standard_normal(n).astype(np.float32)
+    f.forward(x, re, im)
+    assert abs(np.sum(re.astype(np.float64) ** 2 + im.astype(np.float64) ** 2) / n - np.sum(x.astype(np.float64) ** 2)) \
+        < 0.01 * np.sum(x.astype(np.float64) ** 2)
+
+
+def test_magnitude_power_db(device):
+    n = 512
+    f = make_fft(device, n)
+    rng = np.random.default_rng(9)
+    re = rng.standard_normal(n).astype(np.float32)
+    im = rng.standard_normal(n).astype(np.float32)
+    kh = n // 2 + 1
+    mag = np.zeros(kh, np.float32); pw = np.zeros(kh, np.float32); db = np.zeros(kh, np.float32)
+    f.magnitude(re, im, mag); f.power(re, im, pw); f.magnitudeDB(re, im, db, reference=2.0)
+    assert o64.rel_rms(mag, rp.magnitude(re, im)) <= TOL
+    assert o64.rel_rms(pw, rp.power(re, im)) <= TOL
+    assert np.max(np.abs(db - rp.magnitude_db(re, im, 2.0))) < 1e-3
+    assert np.allclose(pw, mag * mag, rtol=1e-5)
+
+
+@pytest.mark.parametrize("n,batch", [(64, 37), (256, 200), (1024, 33), (4096, 19), (8192, 5)])
+def test_forward_inverse_batch(device, n, batch):
+    rng = np.random.default_rng(n + batch)
+    x = rng.standard_normal((batch, n)).astype(np.float32)
+    f = make_fft(device, n)
+    re, im = f.forwardBatch(x)
+    assert o64.rel_rms(re + 1j * im, o64.fft_forward(x)) <= TOL
+    y = f.inverseBatch(re, im)
+    assert o64.rel_rms(y, x) <= TOL
+    r0, i0 = f.forwardBatch(np.zeros((0, n), np.float32))
+    assert r0.shape == (0, n)
+
+
+def test_reference_golden_vectors(device):
+    """The 256-point vectors emitted by the reference's scripts/generate_references.py."""
+    import json, os
+    g = os.path.join(os.path.dirname(__file__), "golden")
+    fwd = json.load(open(os.path.join(g, "fft_forward_256.json")))
+    x = np.array(fwd["input"], np.float32)
+    exp = np.array(fwd["expectedOutput"], np.float64)
+    f = make_fft(device, 256)
+    re = np.zeros(256, np.float32); im = np.zeros(256, np.float32)
+    f.forward(x, re, im)
+    assert np.max(np.abs(np.concatenate([re, im]) - exp)) < fwd["tolerance"] * 256 ** 0.5 * 4
+    assert o64.rel_rms(np.concatenate([re, im]), exp) <= TOL
+    rt = json.load(open(os.path.join(g, "fft_roundtrip_256.json")))
+    i = make_fft(device, 256, inverse=True)
+    y = np.zeros(256, np.float32)
+    i.inverse(re, im, y)
+    assert np.max(np.abs(y - np.array(rt["expectedOutput"]))) < rt["tolerance"]
+
+
+def test_inverse_of_forward_object_is_time_reversed(device):
+    """Reference semantics: direction comes from Config.inverse, not from the method."""
+    n = 128
+    f = make_fft(device, n)
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal(n).astype(np.float32)
+    re = np.zeros(n, np.float32); im = np.zeros(n, np.float32); y = np.zeros(n, np.float32)
+    f.forward(x, re, im)
+    f.inverse(re, im, y)
+    assert o64.rel_rms(y, np.concatenate([x[:1], x[1:][::-1]])) <= TOL
+
+
+def test_nan_inf_propagate_and_extremes_finite(device):
+    n = 256
+    f = make_fft(device, n)
+    re = np.zeros(n, np.float32); im = np.zeros(n, np.float32)
+    x = np.ones(n, np.float32); x[3] = np.nan
+    f.forward(x, re, im)
+    assert np.isnan(re).any()
+    f.forward(np.full(n, 1e-30, np.float32), re, im)
+    assert np.isfinite(re).all() and np.isfinite(im).all()
+    f.forward(np.full(n, 1e6, np.float32), re, im)
+    assert np.isfinite(re).all() and np.isfinite(im).all()
