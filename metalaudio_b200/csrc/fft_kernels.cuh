@@ -202,6 +202,9 @@ struct C2RParams {
     int64_t out_len;            // iSTFT: (F-1)*hop + N ; plain inverse: unused
     float floor;                // iSTFT window-sum floor
     int32_t chunks_per_signal;  // iSTFT: CTAs per signal
+    int32_t n_partials;         // HALF_PACKED input: number of partial spectra to sum (>= 1)
+    int64_t partial_stride;     // float2 units between partial spectra
+    float* tail;                // streaming convolution step: per-signal overlap tail (N/2 floats)
     const float2* twM;
     const float2* twN;
 };
@@ -231,13 +234,23 @@ MA_HD void c2r_load_pair(const C2RParams& p, int64_t s, int64_t f, int64_t g, in
         const float2* x = reinterpret_cast<const float2*>(p.in_a) + s * p.in_signal_stride +
                           f * p.in_frame_stride;
         if (p.layout == LAYOUT_HALF_PACKED) {
+            // Optionally the spectrum is the sum of n_partials partial spectra (the
+            // partition-split accumulators of the convolution step).
+            float2 xa = MA_LDG(x + k);
+            float2 xb = MA_LDG(x + (k == 0 ? 0 : km));
+            for (int i = 1; i < p.n_partials; ++i) {
+                const float2* xi = x + (int64_t)i * p.partial_stride;
+                const float2 ya = MA_LDG(xi + k);
+                const float2 yb = MA_LDG(xi + (k == 0 ? 0 : km));
+                xa.x += ya.x; xa.y += ya.y;
+                xb.x += yb.x; xb.y += yb.y;
+            }
             if (k == 0) {
-                float2 x0 = MA_LDG(x);
-                a = make_float2(x0.x, 0.f);
-                b = make_float2(x0.y, 0.f);
+                a = make_float2(xa.x, 0.f);
+                b = make_float2(xa.y, 0.f);
             } else {
-                a = MA_LDG(x + k);
-                b = MA_LDG(x + km);
+                a = xa;
+                b = xb;
             }
         } else {
             a = MA_LDG(x + k);
@@ -299,10 +312,28 @@ MA_HD void c2r_body(const C2RParams& p, Cta& cta, float2* smem) {
         const int64_t f = active ? g - s * p.frames_per_signal : 0;
         float2 v[R];
         c2r_frame<M, Cta>(p, active, s, f, g, t, sbuf0, S::BUF_STRIDE, parity, v, cta);
-        if (active) {
+        if (active && p.tail == nullptr) {
             float2* o = reinterpret_cast<float2*>(p.out + g * (int64_t)N);
 #pragma unroll
             for (int q = 0; q < R; ++q) o[t + q * T] = make_float2(v[q].y * scale, v[q].x * scale);
+        } else if (active) {
+            // Streaming convolution step: emit the first half plus the kept tail of the
+            // previous block, keep the second half as the new tail.
+            float* o = p.out + g * p.out_signal_stride;
+            float* tl = p.tail + g * (int64_t)M;
+            if constexpr (R == 1) {
+                o[0] = v[0].y * scale + tl[0];
+                tl[0] = v[0].x * scale;
+            } else {
+#pragma unroll
+                for (int q = 0; q < R / 2; ++q) {
+                    const int i0 = 2 * (t + q * T);
+                    o[i0] = v[q].y * scale + tl[i0];
+                    o[i0 + 1] = v[q].x * scale + tl[i0 + 1];
+                    tl[i0] = v[q + R / 2].y * scale;
+                    tl[i0 + 1] = v[q + R / 2].x * scale;
+                }
+            }
         }
     }
 }

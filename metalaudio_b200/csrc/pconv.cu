@@ -1,12 +1,622 @@
+// Uniformly partitioned overlap-add convolution with a frequency-domain delay line (FDL).
+//
+// Data in HBM (all float2, "packed" half spectra: B complex bins per 2B-point block, bin 0
+// holding (DC, Nyquist)):
+//   H     [n_irs][P][B]      partition spectra of every impulse response
+//   ring  [C][P][B]          delay line of the last P input-block spectra per channel
+//   tl    [C][P-1+T][B]      whole-signal call: history followed by all T block spectra
+//   Y     [C][T][B]          whole-signal call: accumulated output spectra
+// Kernels:
+//   r2c (fft_small.cu)       input blocks -> spectra (zero-padded to 2B in the loader)
+//   pconv_mac_kernel         Y[c] = sum_p X[c][t-p] * H[ir(c)][p]; streams the delay line once,
+//                            channels that share an IR are tiled so each H element is loaded
+//                            once per tile and reused from registers
+//   c2r / istft (fft_small)  inverse transform + block overlap-add
+#include <new>
+#include <vector>
+
 #include "fft_plan.h"
-extern "C" {
-ma_status ma_pconv_create(ma_context*, int32_t, int32_t, ma_pconv**) { return MA_ERR_UNSUPPORTED; }
-ma_status ma_pconv_destroy(ma_pconv*) { return MA_OK; }
-ma_status ma_pconv_set_kernels(ma_pconv*, const float*, int64_t, int32_t, const int32_t*) { return MA_ERR_UNSUPPORTED; }
-ma_status ma_pconv_partition_count(ma_pconv*, int32_t*) { return MA_ERR_UNSUPPORTED; }
-ma_status ma_pconv_reserve(ma_pconv*, int64_t) { return MA_ERR_UNSUPPORTED; }
-ma_status ma_pconv_process_dev(ma_pconv*, const float*, int64_t, int64_t, float*, int64_t) { return MA_ERR_UNSUPPORTED; }
-ma_status ma_pconv_process_host(ma_pconv*, const float*, int64_t, int64_t, float*, int64_t) { return MA_ERR_UNSUPPORTED; }
-ma_status ma_pconv_step_dev(ma_pconv*, const float*, int64_t, float*, int64_t) { return MA_ERR_UNSUPPORTED; }
-ma_status ma_pconv_reset(ma_pconv*) { return MA_ERR_UNSUPPORTED; }
+
+struct ma_pconv {
+    ma_context* ctx = nullptr;
+    int block = 0;      // B
+    int channels = 0;   // C
+    ma_fft_plan* plan = nullptr;  // N = 2B
+    int64_t taps = 0;
+    int partitions = 0;  // P
+    int n_irs = 0;
+    int share = 1;       // channels per tile that share one IR (1, 2 or 4)
+    float2* d_h = nullptr;
+    int32_t* d_ch2ir = nullptr;
+    float2* d_ring = nullptr;
+    float* d_tail = nullptr;
+    int write_index = 0;
+    int splits = 1;              // partition splits of the streaming step
+    float2* d_partial = nullptr; // [splits][C][B]
+    int64_t reserved_len = 0;
+    int64_t reserved_blocks = 0;
+    float2* d_timeline = nullptr;
+    float2* d_y = nullptr;
+};
+
+namespace ma {
+
+struct MacParams {
+    const float2* x;        // delay line or timeline
+    int64_t x_chan_stride;  // float2 units
+    const float2* h;
+    const int32_t* ch2ir;
+    float2* out;
+    int64_t out_split_stride, out_chan_stride, out_t_stride;  // float2 units
+    int block;       // B
+    int partitions;  // P
+    int w0;          // slot of partition 0 for t = 0
+    int wrap;        // P for the ring, 0 for the timeline
+    int splits;
+    int p_per_split;
+    int bin_tiles;
+    int bpt;         // threads covering one spectrum tile (power of two <= 128)
+};
+
+constexpr int kMacThreads = 128;
+
+template <int VEC>
+struct VecT;
+template <>
+struct VecT<1> { using type = float2; };
+template <>
+struct VecT<2> { using type = float4; };
+
+// One CTA: CT channels sharing an IR, one tile of bins, one range of partitions, one block
+// index t (blockIdx.y).  Threads along bins (VEC bins each); when a spectrum tile needs fewer
+// than 128 threads the remaining thread rows take interleaved partitions and are reduced
+// through shared memory.  STREAM selects evict-first loads for the delay line (read once).
+template <int CT, int VEC, bool STREAM>
+__global__ void __launch_bounds__(kMacThreads) pconv_mac_kernel(const MacParams q) {
+    using V = typename VecT<VEC>::type;
+    __shared__ float2 red[kMacThreads * CT * VEC];
+    const int tid = threadIdx.x;
+    const int bpt = q.bpt;
+    const int kb = tid & (bpt - 1);
+    const int pl = tid / bpt;
+    const int PL = kMacThreads / bpt;
+    int bx = blockIdx.x;
+    const int split = bx % q.splits;
+    bx /= q.splits;
+    const int bt = bx % q.bin_tiles;
+    const int ctile = bx / q.bin_tiles;
+    const int t = blockIdx.y;
+    const int c0 = ctile * CT;
+    const int e = (bt * bpt + kb) * VEC;  // first bin of this thread
+    const bool dc = (e == 0);
+    const int B = q.block;
+    const int p_beg = split * q.p_per_split;
+    int p_end = p_beg + q.p_per_split;
+    if (p_end > q.partitions) p_end = q.partitions;
+
+    const float2* hb = q.h + (int64_t)__ldg(q.ch2ir + c0) * q.partitions * B + e;
+    const float2* xb = q.x + (int64_t)c0 * q.x_chan_stride + e;
+    const int w = q.w0 + t;
+
+    float2 acc[CT][VEC];
+#pragma unroll
+    for (int c = 0; c < CT; ++c)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[c][v] = make_float2(0.f, 0.f);
+
+#pragma unroll 4
+    for (int p = p_beg + pl; p < p_end; p += PL) {
+        const V hv = __ldg(reinterpret_cast<const V*>(hb + (int64_t)p * B));
+        float2 h[VEC];
+        h[0] = make_float2(reinterpret_cast<const float*>(&hv)[0], reinterpret_cast<const float*>(&hv)[1]);
+        if constexpr (VEC == 2)
+            h[1] = make_float2(reinterpret_cast<const float*>(&hv)[2], reinterpret_cast<const float*>(&hv)[3]);
+        // bin 0 carries (DC, Nyquist): component-wise product instead of a complex one
+        const float ha = dc ? 0.f : h[0].y;
+        const float hc = dc ? h[0].y : h[0].x;
+        int slot = w - p;
+        if (slot < 0) slot += q.wrap;
+        const float2* xp = xb + (int64_t)slot * B;
+#pragma unroll
+        for (int c = 0; c < CT; ++c) {
+            const V* src = reinterpret_cast<const V*>(xp + (int64_t)c * q.x_chan_stride);
+            V xv;
+            if (STREAM) xv = __ldcs(src);
+            else xv = __ldg(src);
+            const float* xf = reinterpret_cast<const float*>(&xv);
+            acc[c][0].x = fmaf(xf[0], h[0].x, acc[c][0].x);
+            acc[c][0].x = fmaf(-xf[1], ha, acc[c][0].x);
+            acc[c][0].y = fmaf(xf[0], ha, acc[c][0].y);
+            acc[c][0].y = fmaf(xf[1], hc, acc[c][0].y);
+            if constexpr (VEC == 2) {
+                acc[c][1].x = fmaf(xf[2], h[1].x, acc[c][1].x);
+                acc[c][1].x = fmaf(-xf[3], h[1].y, acc[c][1].x);
+                acc[c][1].y = fmaf(xf[2], h[1].y, acc[c][1].y);
+                acc[c][1].y = fmaf(xf[3], h[1].x, acc[c][1].y);
+            }
+        }
+    }
+
+    if (PL > 1) {
+#pragma unroll
+        for (int c = 0; c < CT; ++c)
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) red[(c * VEC + v) * kMacThreads + tid] = acc[c][v];
+        __syncthreads();
+        if (pl == 0) {
+            for (int r = 1; r < PL; ++r) {
+#pragma unroll
+                for (int c = 0; c < CT; ++c)
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) {
+                        const float2 o = red[(c * VEC + v) * kMacThreads + r * bpt + kb];
+                        acc[c][v].x += o.x;
+                        acc[c][v].y += o.y;
+                    }
+            }
+        }
+    }
+    if (pl == 0) {
+#pragma unroll
+        for (int c = 0; c < CT; ++c) {
+            float2* o = q.out + (int64_t)split * q.out_split_stride + (int64_t)(c0 + c) * q.out_chan_stride +
+                        (int64_t)t * q.out_t_stride + e;
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) o[v] = acc[c][v];
+        }
+    }
 }
+
+template <int CT, int VEC, bool STREAM>
+static ma_status launch_mac_t(ma_context* ctx, const MacParams& q, int chan_tiles, int64_t t_count) {
+    int64_t done = 0;
+    while (done < t_count) {
+        int64_t ny = t_count - done;
+        if (ny > 32768) ny = 32768;
+        MacParams qq = q;
+        qq.w0 = q.w0 + (int)done;
+        qq.out = q.out + done * q.out_t_stride;
+        dim3 grid((unsigned)(chan_tiles * q.bin_tiles * q.splits), (unsigned)ny, 1);
+        pconv_mac_kernel<CT, VEC, STREAM><<<grid, kMacThreads, 0, ctx->stream>>>(qq);
+        MA_TRY(after_launch(ctx));
+        done += ny;
+    }
+    return MA_OK;
+}
+
+static ma_status launch_mac(ma_pconv* pc, MacParams q, bool stream, int64_t t_count) {
+    const int B = pc->block;
+    const int vec = B >= 2 ? 2 : 1;
+    const int bp = B / vec;  // threads per spectrum
+    q.bpt = bp < kMacThreads ? bp : kMacThreads;
+    q.bin_tiles = bp / q.bpt;
+    const int ct = pc->share;
+    const int chan_tiles = pc->channels / ct;
+    ma_context* ctx = pc->ctx;
+#define MAC_CASE(CT_, VEC_)                                                                        \
+    if (ct == CT_ && vec == VEC_)                                                                  \
+        return stream ? launch_mac_t<CT_, VEC_, true>(ctx, q, chan_tiles, t_count)                 \
+                      : launch_mac_t<CT_, VEC_, false>(ctx, q, chan_tiles, t_count);
+    MAC_CASE(1, 1) MAC_CASE(2, 1) MAC_CASE(4, 1) MAC_CASE(1, 2) MAC_CASE(2, 2) MAC_CASE(4, 2)
+#undef MAC_CASE
+    return MA_ERR_UNSUPPORTED;
+}
+
+// Ordered copies between the ring and the timeline.
+// to_timeline: tl[c][j] = ring[c][(w - (P-1-j)) mod P], j < P-1.
+// to_ring:     ring[c][j] = tl[c][first + j], j < P.
+__global__ void pconv_history_kernel(float2* __restrict__ ring, float2* __restrict__ tl, int64_t tl_chan_stride,
+                                     int P, int B, int w, int64_t first, int to_timeline, int channels) {
+    const int rows = to_timeline ? P - 1 : P;
+    const int64_t total = (int64_t)channels * rows * B;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int k = (int)(i % B);
+        const int64_t r = i / B;
+        const int j = (int)(r % rows);
+        const int64_t c = r / rows;
+        if (to_timeline) {
+            int slot = w - (P - 1 - j);
+            slot %= P;
+            if (slot < 0) slot += P;
+            tl[c * tl_chan_stride + (int64_t)j * B + k] = ring[(c * P + slot) * B + k];
+        } else {
+            ring[(c * P + j) * B + k] = tl[c * tl_chan_stride + (first + j) * B + k];
+        }
+    }
+}
+
+static void free_signal_buffers(ma_pconv* pc) {
+    if (pc->d_timeline) (void)cudaFree(pc->d_timeline);
+    if (pc->d_y) (void)cudaFree(pc->d_y);
+    pc->d_timeline = nullptr;
+    pc->d_y = nullptr;
+    pc->reserved_len = 0;
+    pc->reserved_blocks = 0;
+}
+
+static void free_kernel_buffers(ma_pconv* pc) {
+    if (pc->d_h) (void)cudaFree(pc->d_h);
+    if (pc->d_ch2ir) (void)cudaFree(pc->d_ch2ir);
+    if (pc->d_ring) (void)cudaFree(pc->d_ring);
+    if (pc->d_tail) (void)cudaFree(pc->d_tail);
+    if (pc->d_partial) (void)cudaFree(pc->d_partial);
+    pc->d_h = nullptr;
+    pc->d_ch2ir = nullptr;
+    pc->d_ring = nullptr;
+    pc->d_tail = nullptr;
+    pc->d_partial = nullptr;
+    free_signal_buffers(pc);
+    (void)cudaGetLastError();
+}
+
+}  // namespace ma
+
+using namespace ma;
+
+extern "C" {
+
+ma_status ma_pconv_create(ma_context* ctx, int32_t block_size, int32_t n_channels, ma_pconv** out) {
+    if (out == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    MA_TRY(enter(ctx, MA_FAULT_ALLOC));
+    if (block_size <= 0 || n_channels <= 0) return MA_ERR_INVALID_ARGUMENT;
+    if ((block_size & (block_size - 1)) != 0) return MA_ERR_SIZE_NOT_POW2;
+    if (2 * (int64_t)block_size > kMaxSmallN) return MA_ERR_UNSUPPORTED;
+    ma_pconv* pc = new (std::nothrow) ma_pconv();
+    if (pc == nullptr) return MA_ERR_ALLOC;
+    pc->ctx = ctx;
+    pc->block = block_size;
+    pc->channels = n_channels;
+    ma_status st = ma_fft_plan_create(ctx, 2 * block_size, nullptr, block_size, &pc->plan);
+    if (st != MA_OK) {
+        delete pc;
+        return st;
+    }
+    *out = pc;
+    return MA_OK;
+}
+
+ma_status ma_pconv_destroy(ma_pconv* pc) {
+    if (pc == nullptr) return MA_OK;
+    if (pc->ctx) {
+        (void)cudaSetDevice(pc->ctx->device);
+        (void)cudaStreamSynchronize(pc->ctx->stream);
+    }
+    free_kernel_buffers(pc);
+    ma_fft_plan_destroy(pc->plan);
+    delete pc;
+    return MA_OK;
+}
+
+ma_status ma_pconv_set_kernels(ma_pconv* pc, const float* irs, int64_t taps, int32_t n_irs,
+                               const int32_t* channel_to_ir) {
+    if (pc == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    ma_context* ctx = pc->ctx;
+    MA_TRY(enter(ctx, MA_FAULT_ALLOC));
+    if (irs == nullptr || n_irs <= 0) return MA_ERR_INVALID_ARGUMENT;
+    if (taps <= 0) return MA_ERR_EMPTY_KERNEL;
+    const int B = pc->block, C = pc->channels;
+    const int64_t P64 = (taps + B - 1) / B;
+    if (P64 > (1 << 24)) return MA_ERR_OUTPUT_OVERFLOW;
+    const int P = (int)P64;
+    std::vector<int32_t> map((size_t)C, 0);
+    if (channel_to_ir != nullptr) {
+        for (int c = 0; c < C; ++c) {
+            if (channel_to_ir[c] < 0 || channel_to_ir[c] >= n_irs) return MA_ERR_INVALID_ARGUMENT;
+            map[(size_t)c] = channel_to_ir[c];
+        }
+    }
+    // Largest aligned channel group (4, 2, 1) whose members all use one IR.
+    int share = 1;
+    for (int cand : {4, 2}) {
+        if (C % cand != 0) continue;
+        bool ok = true;
+        for (int c = 0; c < C && ok; ++c) ok = map[(size_t)c] == map[(size_t)(c - c % cand)];
+        if (ok) {
+            share = cand;
+            break;
+        }
+    }
+    MA_CUDA(cudaStreamSynchronize(ctx->stream));
+    free_kernel_buffers(pc);
+    pc->taps = taps;
+    pc->partitions = P;
+    pc->n_irs = n_irs;
+    pc->share = share;
+    pc->write_index = 0;
+    // Partition splits of the streaming step: enough CTAs to fill the device about four
+    // times, each still covering at least eight partitions per thread row.
+    {
+        const int vec = B >= 2 ? 2 : 1;
+        const int bp = B / vec;
+        const int bpt = bp < kMacThreads ? bp : kMacThreads;
+        const int rows = kMacThreads / bpt;
+        const int64_t tiles = (int64_t)(C / share) * (bp / bpt);
+        int64_t want = ((int64_t)ctx->sm_count * 4 + tiles - 1) / tiles;
+        int64_t max_splits = P / (8 * rows);
+        if (max_splits < 1) max_splits = 1;
+        if (want > max_splits) want = max_splits;
+        if (want < 1) want = 1;
+        if (want > 64) want = 64;
+        pc->splits = (int)want;
+    }
+    const size_t spec_bytes = (size_t)P * B * sizeof(float2);
+    ma_status st = MA_OK;
+    cudaError_t e = cudaMalloc((void**)&pc->d_h, spec_bytes * (size_t)n_irs);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&pc->d_ch2ir, sizeof(int32_t) * (size_t)C);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&pc->d_ring, spec_bytes * (size_t)C);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&pc->d_tail, sizeof(float) * (size_t)C * B);
+    if (e == cudaSuccess)
+        e = cudaMalloc((void**)&pc->d_partial, sizeof(float2) * (size_t)pc->splits * (size_t)C * B);
+    if (e != cudaSuccess) st = cuda_fail(e);
+    if (st == MA_OK) st = copy_h2d(ctx, pc->d_ch2ir, map.data(), sizeof(int32_t) * (size_t)C);
+    // Partition spectra: the taps are the "signals", partitions the "frames" at hop B, each
+    // frame's samples beyond B (and beyond the end of the IR) read as zero.
+    float* d_taps = nullptr;
+    const int64_t tstride = taps + (taps & 1);
+    if (st == MA_OK) st = temp_alloc(ctx, sizeof(float) * (size_t)(tstride * n_irs), (void**)&d_taps);
+    for (int i = 0; i < n_irs && st == MA_OK; ++i)
+        st = copy_h2d(ctx, d_taps + (int64_t)i * tstride, irs + (int64_t)i * taps, sizeof(float) * (size_t)taps);
+    if (st == MA_OK) {
+        R2CParams p{};
+        p.in = d_taps;
+        p.signal_stride = tstride;
+        p.frames_per_signal = P;
+        p.total_frames = (int64_t)P * n_irs;
+        p.signal_len = taps;
+        p.hop = B;
+        p.frame_valid = B;
+        p.out_a = reinterpret_cast<float*>(pc->d_h);
+        p.out_signal_stride = (int64_t)P * B;
+        p.out_frame_stride = B;
+        p.layout = LAYOUT_HALF_PACKED;
+        p.mag_kind = MAG_NONE;
+        st = launch_r2c_small(pc->plan, p);
+    }
+    temp_free(ctx, d_taps);
+    if (st == MA_OK) st = ma_pconv_reset(pc);
+    if (st == MA_OK) {
+        cudaError_t e2 = cudaStreamSynchronize(ctx->stream);
+        if (e2 != cudaSuccess) st = cuda_fail(e2);
+    }
+    if (st != MA_OK) free_kernel_buffers(pc);
+    return st;
+}
+
+ma_status ma_pconv_partition_count(ma_pconv* pc, int32_t* partitions) {
+    if (pc == nullptr || partitions == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    *partitions = pc->partitions;
+    return MA_OK;
+}
+
+ma_status ma_pconv_reset(ma_pconv* pc) {
+    if (pc == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    MA_TRY(enter(pc->ctx, MA_FAULT_LAUNCH));
+    if (pc->d_ring == nullptr) return MA_OK;  // nothing configured yet
+    const size_t ring_bytes = (size_t)pc->channels * pc->partitions * pc->block * sizeof(float2);
+    MA_CUDA(cudaMemsetAsync(pc->d_ring, 0, ring_bytes, pc->ctx->stream));
+    MA_CUDA(cudaMemsetAsync(pc->d_tail, 0, sizeof(float) * (size_t)pc->channels * pc->block, pc->ctx->stream));
+    pc->write_index = 0;
+    return MA_OK;
+}
+
+ma_status ma_pconv_reserve(ma_pconv* pc, int64_t max_len) {
+    if (pc == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    ma_context* ctx = pc->ctx;
+    MA_TRY(enter(ctx, MA_FAULT_ALLOC));
+    if (pc->d_h == nullptr) return MA_ERR_KERNEL_NOT_CONFIGURED;
+    if (max_len <= 0) return MA_ERR_INVALID_ARGUMENT;
+    if (max_len <= pc->reserved_len) return MA_OK;
+    int64_t full;
+    if (__builtin_add_overflow(max_len, pc->taps - 1, &full)) return MA_ERR_OUTPUT_OVERFLOW;
+    const int64_t blocks = (full + pc->block - 1) / pc->block;
+    MA_CUDA(cudaStreamSynchronize(ctx->stream));
+    free_signal_buffers(pc);
+    const size_t row = (size_t)pc->block * sizeof(float2);
+    const size_t tl_bytes = (size_t)pc->channels * (size_t)(pc->partitions - 1 + blocks) * row;
+    const size_t y_bytes = (size_t)pc->channels * (size_t)blocks * row;
+    cudaError_t e = cudaMalloc((void**)&pc->d_timeline, tl_bytes ? tl_bytes : 16);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&pc->d_y, y_bytes ? y_bytes : 16);
+    if (e != cudaSuccess) {
+        ma_status st = cuda_fail(e);
+        free_signal_buffers(pc);
+        return st;
+    }
+    pc->reserved_len = max_len;
+    pc->reserved_blocks = blocks;
+    return MA_OK;
+}
+
+ma_status ma_pconv_process_dev(ma_pconv* pc, const float* in, int64_t len, int64_t in_stride, float* out,
+                               int64_t out_stride) {
+    if (pc == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    ma_context* ctx = pc->ctx;
+    MA_TRY(enter(ctx, MA_FAULT_LAUNCH));
+    if (pc->d_h == nullptr) return MA_ERR_KERNEL_NOT_CONFIGURED;
+    if (len == 0) return MA_OK;  // empty input -> empty output (Convolution.swift:339-342)
+    if (len < 0 || in == nullptr || out == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (pc->write_index < 0 || pc->write_index >= pc->partitions) return MA_ERR_INVALID_PARTITION_STATE;
+    int64_t full;
+    if (__builtin_add_overflow(len, pc->taps - 1, &full)) return MA_ERR_OUTPUT_OVERFLOW;
+    if (len > pc->reserved_len) return MA_ERR_INVALID_ARGUMENT;
+    if (pc->channels > 1 && (in_stride < len || out_stride < full)) return MA_ERR_INVALID_ARGUMENT;
+    const int B = pc->block, P = pc->partitions, C = pc->channels;
+    const int64_t T = (full + B - 1) / B;
+    const int64_t tl_len = (int64_t)P - 1 + T;
+    const int64_t tl_stride = tl_len * B;
+
+    // 1. history -> timeline prefix
+    if (P > 1) {
+        const int64_t total = (int64_t)C * (P - 1) * B;
+        int grid = (int)((total + 255) / 256 < (int64_t)ctx->sm_count * 8 ? (total + 255) / 256 : (int64_t)ctx->sm_count * 8);
+        pconv_history_kernel<<<grid, 256, 0, ctx->stream>>>(pc->d_ring, pc->d_timeline, tl_stride, P, B,
+                                                            pc->write_index, 0, 1, C);
+        MA_TRY(after_launch(ctx));
+    }
+    // 2. all input blocks -> spectra
+    {
+        R2CParams p{};
+        p.in = in;
+        p.signal_stride = in_stride;
+        p.frames_per_signal = T;
+        p.total_frames = T * C;
+        p.signal_len = len;
+        p.hop = B;
+        p.frame_valid = B;
+        p.out_a = reinterpret_cast<float*>(pc->d_timeline + (int64_t)(P - 1) * B);
+        p.out_signal_stride = tl_stride;
+        p.out_frame_stride = B;
+        p.layout = LAYOUT_HALF_PACKED;
+        p.mag_kind = MAG_NONE;
+        MA_TRY(launch_r2c_small(pc->plan, p));
+    }
+    // 3. delay-line multiply-accumulate for every (channel, block)
+    {
+        MacParams q{};
+        q.x = pc->d_timeline;
+        q.x_chan_stride = tl_stride;
+        q.h = pc->d_h;
+        q.ch2ir = pc->d_ch2ir;
+        q.out = pc->d_y;
+        q.out_split_stride = 0;
+        q.out_chan_stride = T * B;
+        q.out_t_stride = B;
+        q.block = B;
+        q.partitions = P;
+        q.w0 = P - 1;
+        q.wrap = 0;
+        q.splits = 1;
+        q.p_per_split = P;
+        MA_TRY(launch_mac(pc, q, false, T));
+    }
+    // 4. inverse transform + block overlap-add, truncated at len + taps - 1
+    {
+        C2RParams p{};
+        p.in_a = reinterpret_cast<const float*>(pc->d_y);
+        p.in_signal_stride = T * B;
+        p.in_frame_stride = B;
+        p.frames_per_signal = T;
+        p.n_signals = C;
+        p.layout = LAYOUT_HALF_PACKED;
+        p.hop = B;
+        p.window = nullptr;
+        p.out = out;
+        p.out_signal_stride = out_stride;
+        p.out_len = full;
+        p.floor = -1.0f;
+        MA_TRY(launch_istft_small(pc->plan, p));
+    }
+    // 5. the last P block spectra become the delay line
+    {
+        const int64_t total = (int64_t)C * P * B;
+        int grid = (int)((total + 255) / 256 < (int64_t)ctx->sm_count * 8 ? (total + 255) / 256 : (int64_t)ctx->sm_count * 8);
+        pconv_history_kernel<<<grid, 256, 0, ctx->stream>>>(pc->d_ring, pc->d_timeline, tl_stride, P, B, 0, T - 1,
+                                                            0, C);
+        MA_TRY(after_launch(ctx));
+        pc->write_index = 0;
+        MA_CUDA(cudaMemsetAsync(pc->d_tail, 0, sizeof(float) * (size_t)C * B, ctx->stream));
+    }
+    return MA_OK;
+}
+
+ma_status ma_pconv_process_host(ma_pconv* pc, const float* in, int64_t len, int64_t in_stride, float* out,
+                                int64_t out_stride) {
+    if (pc == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    ma_context* ctx = pc->ctx;
+    MA_TRY(enter(ctx, MA_FAULT_LAUNCH));
+    if (pc->d_h == nullptr) return MA_ERR_KERNEL_NOT_CONFIGURED;
+    if (len == 0) return MA_OK;
+    if (len < 0 || in == nullptr || out == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    int64_t full;
+    if (__builtin_add_overflow(len, pc->taps - 1, &full)) return MA_ERR_OUTPUT_OVERFLOW;
+    const int C = pc->channels;
+    if (C > 1 && (in_stride < len || out_stride < full)) return MA_ERR_INVALID_ARGUMENT;
+    MA_TRY(ma_pconv_reserve(pc, len));
+    float *d_in = nullptr, *d_out = nullptr;
+    ma_status st = temp_alloc(ctx, sizeof(float) * (size_t)(len * C), (void**)&d_in);
+    if (st == MA_OK) st = temp_alloc(ctx, sizeof(float) * (size_t)(full * C), (void**)&d_out);
+    for (int c = 0; c < C && st == MA_OK; ++c) {
+        if (in_stride == len && c > 0) break;
+        const size_t n = in_stride == len ? (size_t)(len * C) : (size_t)len;
+        st = copy_h2d(ctx, d_in + (int64_t)c * len, in + (int64_t)c * in_stride, n * sizeof(float));
+    }
+    if (st == MA_OK) st = ma_pconv_process_dev(pc, d_in, len, len, d_out, full);
+    for (int c = 0; c < C && st == MA_OK; ++c) {
+        if (out_stride == full && c > 0) break;
+        const size_t n = out_stride == full ? (size_t)(full * C) : (size_t)full;
+        st = copy_d2h(ctx, out + (int64_t)c * out_stride, d_out + (int64_t)c * full, n * sizeof(float));
+    }
+    temp_free(ctx, d_in);
+    temp_free(ctx, d_out);
+    return st;
+}
+
+ma_status ma_pconv_step_dev(ma_pconv* pc, const float* in_block, int64_t in_stride, float* out_block,
+                            int64_t out_stride) {
+    if (pc == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    ma_context* ctx = pc->ctx;
+    MA_TRY(enter(ctx, MA_FAULT_LAUNCH));
+    if (pc->d_h == nullptr) return MA_ERR_KERNEL_NOT_CONFIGURED;
+    if (in_block == nullptr || out_block == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    const int B = pc->block, P = pc->partitions, C = pc->channels;
+    if (C > 1 && (in_stride < B || out_stride < B)) return MA_ERR_INVALID_ARGUMENT;
+    if (pc->write_index < 0 || pc->write_index >= P) return MA_ERR_INVALID_PARTITION_STATE;
+    const int w = pc->write_index;
+    // 1. this block's spectrum into ring slot w
+    {
+        R2CParams p{};
+        p.in = in_block;
+        p.signal_stride = in_stride;
+        p.frames_per_signal = 1;
+        p.total_frames = C;
+        p.signal_len = B;
+        p.hop = B;
+        p.frame_valid = B;
+        p.out_a = reinterpret_cast<float*>(pc->d_ring + (int64_t)w * B);
+        p.out_signal_stride = (int64_t)P * B;
+        p.out_frame_stride = 0;
+        p.layout = LAYOUT_HALF_PACKED;
+        p.mag_kind = MAG_NONE;
+        MA_TRY(launch_r2c_small(pc->plan, p));
+    }
+    // 2. stream the whole delay line once: partial sums per partition split
+    {
+        MacParams q{};
+        q.x = pc->d_ring;
+        q.x_chan_stride = (int64_t)P * B;
+        q.h = pc->d_h;
+        q.ch2ir = pc->d_ch2ir;
+        q.out = pc->d_partial;
+        q.out_split_stride = (int64_t)C * B;
+        q.out_chan_stride = B;
+        q.out_t_stride = 0;
+        q.block = B;
+        q.partitions = P;
+        q.w0 = w;
+        q.wrap = P;
+        q.splits = pc->splits;
+        q.p_per_split = (P + pc->splits - 1) / pc->splits;
+        MA_TRY(launch_mac(pc, q, true, 1));
+    }
+    // 3. sum the partials, inverse transform, add the kept tail, keep the new one
+    {
+        C2RParams p{};
+        p.in_a = reinterpret_cast<const float*>(pc->d_partial);
+        p.in_signal_stride = B;
+        p.in_frame_stride = 0;
+        p.frames_per_signal = 1;
+        p.n_signals = C;
+        p.layout = LAYOUT_HALF_PACKED;
+        p.n_partials = pc->splits;
+        p.partial_stride = (int64_t)C * B;
+        p.out = out_block;
+        p.out_signal_stride = out_stride;
+        p.tail = pc->d_tail;
+        MA_TRY(launch_c2r_small(pc->plan, p));
+    }
+    pc->write_index = (w + 1) % P;
+    return MA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,172 @@
+"""GPU parity of uniformly partitioned convolution against the float32 port of the
+reference's block loop and the float64 linear-convolution oracle."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from oracle import float64 as o64
+from oracle import reference_path as rp
+from oracle import configs
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+
+def conv(device, block, channels=1):
+    from metalaudio_b200 import Convolution
+    return Convolution(device, Convolution.Mode.partitioned(blockSize=block), channels=channels)
+
+
+def test_identity_kernel(device):
+    """ConvolutionTests: delta kernel, block 64, 256-sample ramp reproduces the input."""
+    c = conv(device, 64)
+    c.setKernel(np.array([1.0], np.float32))
+    x = np.arange(256, dtype=np.float32) / 256
+    y = c.process(x)
+    assert y.shape == (256,)
+    assert np.max(np.abs(y - x)) < 100 * 1e-6
+
+
+@pytest.mark.parametrize("block,taps,length", [(64, 1, 256), (64, 64, 640), (64, 200, 1000), (128, 1000, 5000),
+                                               (256, 4096, 10000), (512, 3000, 7777), (1, 5, 17), (2, 7, 33),
+                                               (4, 9, 40), (16, 100, 333), (1024, 5000, 9000), (4096, 9000, 20000)])
+def test_process_matches_port_and_oracle(device, block, taps, length):
+    rng = np.random.default_rng(block + taps)
+    h = (rng.standard_normal(taps) * np.exp(-np.arange(taps) / max(1, taps / 4))).astype(np.float32)
+    x = rng.standard_normal(length).astype(np.float32)
+    c = conv(device, block)
+    c.setKernel(h)
+    assert c.partitionCount == (taps + block - 1) // block
+    y = c.process(x)
+    assert y.shape == (length + taps - 1,)
+    ref = o64.convolve_full(x, h)
+    assert o64.rel_rms(y, ref) <= TOL
+    port = rp.PartitionedConvolution(block)
+    port.set_kernel(h)
+    assert o64.rel_rms(y, port.process(x)) <= TOL
+    assert c.expectedOutputSize(length) == length + taps - 1 and c.kernelTailLength == taps - 1
+    assert c.maxInputSize == 0
+
+
+def test_consecutive_calls_and_reset(device):
+    """The delay line survives across process() calls (Convolution.swift ring semantics), but
+    every call pushes ceil((L+K-1)/B) >= ceil(L/B) + P - 1 blocks, so the input-bearing
+    spectra have aged out of reach (p <= P-1) by the next call: consecutive calls agree with
+    the port and with a fresh convolution.  reset() then same input -> same output, bit-stable."""
+    block, taps = 64, 257
+    rng = np.random.default_rng(4)
+    h = rng.standard_normal(taps).astype(np.float32)
+    x1 = rng.standard_normal(128).astype(np.float32)
+    x2 = rng.standard_normal(500).astype(np.float32)
+    c = conv(device, block)
+    c.setKernel(h)
+    port = rp.PartitionedConvolution(block)
+    port.set_kernel(h)
+    a1, p1 = c.process(x1), port.process(x1)
+    a2, p2 = c.process(x2), port.process(x2)
+    assert o64.rel_rms(a1, p1) <= TOL and o64.rel_rms(a2, p2) <= TOL
+    assert o64.rel_rms(a2, o64.convolve_full(x2, h)) <= TOL
+    c.reset()
+    a3 = c.process(x2)
+    assert np.array_equal(a3, a2)
+    c.reset()
+    assert np.array_equal(c.process(x2), a3)
+
+
+def test_multichannel_shared_and_per_pair_irs(device):
+    block, taps, length, ch = 64, 1000, 3000, 8
+    rng = np.random.default_rng(8)
+    x = (0.1 * rng.standard_normal((ch, length))).astype(np.float32)
+    # shared IR (configuration 3 shape)
+    h = configs.decaying_ir(taps, 77, rt60_s=0.01)
+    c = conv(device, block, channels=ch)
+    c.setKernel(h)
+    y = c.process(x)
+    for i in range(ch):
+        assert o64.rel_rms(y[i], o64.convolve_full(x[i], h)) <= TOL
+    # one IR per channel pair (configuration 4 shape)
+    hs = np.stack([configs.decaying_ir(taps, [78, i], rt60_s=0.01) for i in range(ch // 2)])
+    c2 = conv(device, block, channels=ch)
+    c2.setKernel(hs, channelToKernel=[i // 2 for i in range(ch)])
+    y2 = c2.process(x)
+    for i in range(ch):
+        assert o64.rel_rms(y2[i], o64.convolve_full(x[i], hs[i // 2])) <= TOL
+    # arbitrary mapping, odd channel count
+    c3 = conv(device, block, channels=3)
+    c3.setKernel(hs, channelToKernel=[2, 0, 2])
+    y3 = c3.process(x[:3])
+    for i, ir in enumerate([2, 0, 2]):
+        assert o64.rel_rms(y3[i], o64.convolve_full(x[i], hs[ir])) <= TOL
+
+
+@pytest.mark.parametrize("block,taps,channels", [(64, 1000, 4), (256, 5000, 3), (1, 3, 2), (2, 9, 5), (32, 700, 8)])
+def test_streaming_step_equals_whole_signal(device, lib, block, taps, channels):
+    """The causal one-block step (the HBM-streaming kernel) produces the same samples as
+    the whole-signal call."""
+    rng = np.random.default_rng(block * 3 + taps)
+    h = (rng.standard_normal(taps) / np.sqrt(taps)).astype(np.float32)
+    n_blocks = 40
+    length = n_blocks * block
+    x = rng.standard_normal((channels, length)).astype(np.float32)
+    c = conv(device, block, channels=channels)
+    c.setKernel(h)
+    from metalaudio_b200 import Tensor
+    tin = Tensor(device, (channels, length)); tin.copy(x)
+    tout = Tensor(device, (channels, length))
+    for t in range(n_blocks):
+        st = lib.ma_pconv_step_dev(c._h, ctypes.c_void_p(tin.pointer + 4 * t * block), length,
+                                   ctypes.c_void_p(tout.pointer + 4 * t * block), length)
+        assert st == 0
+    device.synchronize()
+    y = tout.toArray()
+    for i in range(channels):
+        ref = o64.convolve_full(x[i], h)[:length]
+        assert o64.rel_rms(y[i], ref) <= TOL
+    # whole-signal call after reset agrees on the same samples
+    c.reset()
+    z = c.process(x)
+    assert o64.rel_rms(y, z[:, :length]) <= TOL
+
+
+def test_config3_scaled(device):
+    """Configuration 3 at reduced channel count / length: one shared exponentially decaying
+    noise IR, block 256, float64 oracle plus exact dot-product spot checks."""
+    h = configs.c3_ir(16384)
+    x = configs.c3_input(channels=8, length=1 << 15)
+    c = conv(device, 256, channels=8)
+    c.setKernel(h)
+    assert c.partitionCount == 64
+    y = c.process(x)
+    ref = np.stack([o64.convolve_full(x[i], h) for i in range(8)])
+    assert o64.rel_rms(y, ref) <= TOL
+    idx = np.random.default_rng(0).integers(0, y.shape[1], 200)
+    spot = o64.convolve_spot(x[3], h, idx)
+    assert np.sqrt(np.mean((y[3, idx] - spot) ** 2)) / np.sqrt(np.mean(ref[3] ** 2)) <= TOL
+
+
+def test_config4_scaled(device):
+    """Configuration 4 at reduced size: block 64, one IR per channel pair, long partition
+    count (accumulation over 512 partitions)."""
+    irs = configs.c4_irs(n_irs=4, taps=32768)
+    x = configs.c4_input(channels=8, length=1 << 14)
+    c = conv(device, 64, channels=8)
+    c.setKernel(irs, channelToKernel=[i // 2 for i in range(8)])
+    assert c.partitionCount == 512
+    y = c.process(x)
+    ref = np.stack([o64.convolve_full(x[i], irs[i // 2]) for i in range(8)])
+    assert o64.rel_rms(y, ref) <= TOL
+    assert o64.max_over_rms(y, ref) <= 1e-4
+
+
+def test_errors(device):
+    from metalaudio_b200 import Convolution, ConvolutionError, MetalAudioError
+    c = conv(device, 64)
+    with pytest.raises(ConvolutionError) as e:
+        c.setKernel(np.zeros(0, np.float32))
+    assert e.value.case == "emptyKernel"
+    with pytest.raises(ConvolutionError):
+        c.process(np.ones(10, np.float32))
+    assert c.process(np.zeros(0, np.float32)).size == 0
+    with pytest.raises(MetalAudioError):
+        Convolution(device, Convolution.Mode.partitioned(blockSize=0)).setKernel(np.ones(4, np.float32))
