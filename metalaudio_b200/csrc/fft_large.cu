@@ -1,8 +1,482 @@
-// Placeholder translation unit; replaced below in this file's history by the multi-pass path.
+// Real-input transforms above 8192 points (up to 2^24): two passes through an L2-sized
+// scratch buffer.  N = N1 * N2, sample n = n1 + N1*n2, bin k = k1*N2 + k2.
+//
+//   forward  pass 1 (cols_r2c):  for W1 adjacent n1 at a time, the N2-point real transform over
+//                                n2 of x[n1 + N1*n2], times exp(-2 pi i n1 k2 / N)
+//                                -> C[k2][n1], k2 = 0..N2/2            (lanes run along n1)
+//            pass 2 (rows_fwd):  for W2 adjacent k2 at a time, the N1-point complex transform
+//                                over n1 -> X[k1*N2 + k2]; bins above N/2 come from the
+//                                conjugate mirror; the store is transposed in shared memory so
+//                                that W2 adjacent bins leave together
+//   inverse  pass A (rows_inv):  gather X[k1*N2 + k2] (mirror above N/2), inverse N1-point
+//                                transform over k1, times exp(+2 pi i n1 k2 / N) -> D[k2][n1]
+//            pass B (cols_c2r):  N2-point real inverse over k2 -> x[n1 + N1*n2] / N
+//
+// A batch is cut into chunks whose scratch (about 4*N bytes per transform) stays resident in
+// the 126 MB L2 between the two passes, so HBM sees each transform's input and output once.
+// Plain loads and stores only: no TMA, no multicast.
+#include <new>
+
 #include "fft_plan.h"
+#include "host_tables.h"
+
 namespace ma {
-ma_status large_plan_init(ma_fft_plan*) { return MA_ERR_UNSUPPORTED; }
-void large_plan_destroy(ma_fft_plan*) {}
-ma_status launch_r2c_large(ma_fft_plan*, const float*, float*, float*, float*, int, float, int64_t, int) { return MA_ERR_UNSUPPORTED; }
-ma_status launch_c2r_large(ma_fft_plan*, const float*, const float*, float*, int64_t, int) { return MA_ERR_UNSUPPORTED; }
+
+struct LargeParams {
+    const float* in;     // forward: real input; inverse: layout array a
+    const float* in_b;   // inverse FULL_SPLIT imag
+    float* out_a;
+    float* out_b;
+    float* mag;
+    float2* scratch;
+    int64_t batch;       // transforms in this chunk
+    int n, n1, n2;
+    int layout, mag_kind;
+    float db_scale;
+    const float2* twM2;  // exp(-2 pi i j/M2), j < M2
+    const float2* twN2;  // exp(-2 pi i k/N2), k <= M2/2
+    const float2* tw1;   // exp(-2 pi i j/N1), j < N1
+    const float2* twL;   // exp(-2 pi i j/N),  j < N/2
+};
+
+struct DevCtaL {
+    __device__ __forceinline__ void sync() { __syncthreads(); }
+};
+
+extern __shared__ float4 ma_large_smem[];
+
+// ---------------------------------------------------------------- forward pass 1
+template <int M2, int W1>
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T) cols_r2c_kernel(const LargeParams p) {
+    using P = FftPlan<M2>;
+    constexpr int R = P::R, T = P::T;
+    float2* smem = reinterpret_cast<float2*>(ma_large_smem);
+    const int i = threadIdx.x % W1;
+    const int t = threadIdx.x / W1;
+    const int tiles = p.n1 / W1;
+    DevCtaL cta;
+    for (int64_t blk = blockIdx.x; blk < p.batch * tiles; blk += gridDim.x) {
+        const int64_t b = blk / tiles;
+        const int n1 = (int)(blk - b * tiles) * W1 + i;
+        const float* x = p.in + b * (int64_t)p.n + n1;
+        float2 v[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t j = t + q * T;
+            v[q] = make_float2(__ldcs(x + (2 * j) * p.n1), __ldcs(x + (2 * j + 1) * p.n1));
+        }
+        int parity = 0;
+        float2* sbuf0 = smem + i;
+        fft_forward_regs<M2, W1, DevCtaL>(v, t, sbuf0, M2 * W1, parity, p.twM2, cta);
+        float2* sb = sbuf0 + parity * (M2 * W1);
+#pragma unroll
+        for (int q = 0; q < R; ++q) sb[saddr<W1>(t + q * T)] = v[q];
+        cta.sync();
+        float2* c = p.scratch + b * (int64_t)(M2 + 1) * p.n1 + n1;
+#pragma unroll
+        for (int q = 0; q <= R / 2; ++q) {
+            const int k = t + q * T;
+            if (k > M2 / 2) continue;
+            const float2 a = sb[saddr<W1>(k)];
+            const float2 bb = sb[saddr<W1>((M2 - k) & (M2 - 1))];
+            float2 xk, xm;
+            herm_post(a, bb, __ldg(p.twN2 + k), xk, xm);
+            const int km = M2 - k;
+            c[(int64_t)k * p.n1] = cmul(xk, __ldg(p.twL + (int64_t)n1 * k));
+            c[(int64_t)km * p.n1] = cmul(xm, __ldg(p.twL + (int64_t)n1 * km));
+        }
+        cta.sync();  // the exchange buffers are reused by the next tile
+    }
 }
+
+// Writes bin k (value v) and, where asked, its conjugate mirror, in the requested layout.
+__device__ __forceinline__ void store_bin(const LargeParams& p, int64_t b, int64_t k, int k2, float2 v) {
+    const int64_t n = p.n, half = n / 2;
+    const bool interior = k2 > 0 && k2 < p.n2 / 2;
+    if (p.layout == LAYOUT_FULL_SPLIT) {
+        float* re = p.out_a + b * n;
+        float* im = p.out_b + b * n;
+        re[k] = v.x;
+        im[k] = v.y;
+        if (interior) {
+            re[n - k] = v.x;
+            im[n - k] = -v.y;
+        }
+    } else {
+        int64_t idx = k;
+        float2 val = v;
+        if (k > half) {
+            if (!interior) return;
+            idx = n - k;
+            val.y = -v.y;
+        }
+        if (p.layout == LAYOUT_HALF_PACKED) {
+            float2* o = reinterpret_cast<float2*>(p.out_a) + b * half;
+            if (idx == 0) o[0].x = val.x;
+            else if (idx == half) o[0].y = val.x;
+            else o[idx] = val;
+        } else {
+            float2* o = reinterpret_cast<float2*>(p.out_a) + b * (half + 1);
+            o[idx] = val;
+        }
+        if (p.mag != nullptr) p.mag[b * (half + 1) + idx] = mag_value(val, p.mag_kind, p.db_scale);
+        return;
+    }
+    if (p.mag != nullptr && k <= half) p.mag[b * (half + 1) + k] = mag_value(v, p.mag_kind, p.db_scale);
+    if (p.mag != nullptr && interior && n - k <= half) p.mag[b * (half + 1) + (n - k)] = mag_value(v, p.mag_kind, p.db_scale);
+}
+
+// ---------------------------------------------------------------- forward pass 2
+template <int N1, int W2>
+__global__ void __launch_bounds__(W2* FftPlan<N1>::T) rows_fwd_kernel(const LargeParams p) {
+    using P = FftPlan<N1>;
+    constexpr int R = P::R, T = P::T;
+    constexpr int ELEMS = smem_elems_per_fft<N1, 1>();
+    constexpr int BUF = ELEMS * W2;
+    constexpr int THREADS = W2 * T;
+    float2* smem = reinterpret_cast<float2*>(ma_large_smem);
+    const int slot = threadIdx.x / T;
+    const int t = threadIdx.x % T;
+    const int m2 = p.n2 / 2;
+    const int tiles = (m2 + 1 + W2 - 1) / W2;
+    DevCtaL cta;
+    for (int64_t blk = blockIdx.x; blk < p.batch * tiles; blk += gridDim.x) {
+        const int64_t b = blk / tiles;
+        const int r0 = (int)(blk - b * tiles) * W2;
+        const int k2 = r0 + slot;
+        const bool active = k2 <= m2;
+        const float2* row = p.scratch + (b * (int64_t)(m2 + 1) + (active ? k2 : 0)) * N1;
+        float2 v[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q) v[q] = active ? row[t + q * T] : make_float2(0.f, 0.f);
+        int parity = 0;
+        fft_forward_regs<N1, 1, DevCtaL>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
+        cta.sync();  // everyone is done with the exchange buffers: reuse them as the tile
+        float2* tile = smem;  // [k1][W2+1]
+#pragma unroll
+        for (int q = 0; q < R; ++q) tile[(t + q * T) * (W2 + 1) + slot] = v[q];
+        cta.sync();
+        for (int idx = threadIdx.x; idx < N1 * W2; idx += THREADS) {
+            const int s = idx % W2;
+            const int k1 = idx / W2;
+            const int kk2 = r0 + s;
+            if (kk2 > m2) continue;
+            store_bin(p, b, (int64_t)k1 * p.n2 + kk2, kk2, tile[k1 * (W2 + 1) + s]);
+        }
+        cta.sync();
+    }
+}
+
+// Spectrum bin k of transform b for the inverse, from any layout (Hermitian input assumed).
+__device__ __forceinline__ float2 load_bin(const LargeParams& p, int64_t b, int64_t k) {
+    const int64_t n = p.n, half = n / 2;
+    if (p.layout == LAYOUT_FULL_SPLIT) {
+        float2 v = make_float2(__ldg(p.in + b * n + k), __ldg(p.in_b + b * n + k));
+        if (k == 0 || k == half) v.y = 0.f;
+        return v;
+    }
+    const bool mirror = k > half;
+    const int64_t idx = mirror ? n - k : k;
+    float2 v;
+    if (p.layout == LAYOUT_HALF_PACKED) {
+        const float2* x = reinterpret_cast<const float2*>(p.in) + b * half;
+        if (idx == 0) v = make_float2(__ldg(x).x, 0.f);
+        else if (idx == half) v = make_float2(__ldg(x).y, 0.f);
+        else v = __ldg(x + idx);
+    } else {
+        const float2* x = reinterpret_cast<const float2*>(p.in) + b * (half + 1);
+        v = __ldg(x + idx);
+        if (idx == 0 || idx == half) v.y = 0.f;
+    }
+    if (mirror) v.y = -v.y;
+    return v;
+}
+
+// ---------------------------------------------------------------- inverse pass A
+template <int N1, int W2>
+__global__ void __launch_bounds__(W2* FftPlan<N1>::T) rows_inv_kernel(const LargeParams p) {
+    using P = FftPlan<N1>;
+    constexpr int R = P::R, T = P::T;
+    constexpr int ELEMS = smem_elems_per_fft<N1, 1>();
+    constexpr int BUF = ELEMS * W2;
+    constexpr int THREADS = W2 * T;
+    float2* smem = reinterpret_cast<float2*>(ma_large_smem);
+    const int slot = threadIdx.x / T;
+    const int t = threadIdx.x % T;
+    const int m2 = p.n2 / 2;
+    const int tiles = (m2 + 1 + W2 - 1) / W2;
+    DevCtaL cta;
+    for (int64_t blk = blockIdx.x; blk < p.batch * tiles; blk += gridDim.x) {
+        const int64_t b = blk / tiles;
+        const int r0 = (int)(blk - b * tiles) * W2;
+        float2* tile = smem;
+        for (int idx = threadIdx.x; idx < N1 * W2; idx += THREADS) {
+            const int s = idx % W2;
+            const int k1 = idx / W2;
+            const int kk2 = r0 + s;
+            float2 x = make_float2(0.f, 0.f);
+            if (kk2 <= m2) x = load_bin(p, b, (int64_t)k1 * p.n2 + kk2);
+            tile[k1 * (W2 + 1) + s] = make_float2(x.y, x.x);  // swapped: inverse as forward
+        }
+        cta.sync();
+        float2 v[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q) v[q] = tile[(t + q * T) * (W2 + 1) + slot];
+        cta.sync();
+        int parity = 0;
+        fft_forward_regs<N1, 1, DevCtaL>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
+        const int k2 = r0 + slot;
+        if (k2 <= m2) {
+            float2* row = p.scratch + (b * (int64_t)(m2 + 1) + k2) * N1;
+#pragma unroll
+            for (int q = 0; q < R; ++q) {
+                const int n1 = t + q * T;
+                const float2 w = __ldg(p.twL + (int64_t)n1 * k2);
+                row[n1] = cmul(make_float2(v[q].y, v[q].x), cconj(w));
+            }
+        }
+        cta.sync();
+    }
+}
+
+// ---------------------------------------------------------------- inverse pass B
+template <int M2, int W1>
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T) cols_c2r_kernel(const LargeParams p) {
+    using P = FftPlan<M2>;
+    constexpr int R = P::R, T = P::T;
+    float2* smem = reinterpret_cast<float2*>(ma_large_smem);
+    const int i = threadIdx.x % W1;
+    const int t = threadIdx.x / W1;
+    const int tiles = p.n1 / W1;
+    const float scale = 1.0f / (float)p.n;
+    DevCtaL cta;
+    for (int64_t blk = blockIdx.x; blk < p.batch * tiles; blk += gridDim.x) {
+        const int64_t b = blk / tiles;
+        const int n1 = (int)(blk - b * tiles) * W1 + i;
+        const float2* d = p.scratch + b * (int64_t)(M2 + 1) * p.n1 + n1;
+        int parity = 0;
+        float2* sbuf0 = smem + i;
+        float2* sb = sbuf0 + parity * (M2 * W1);
+        parity ^= 1;
+#pragma unroll
+        for (int q = 0; q <= R / 2; ++q) {
+            const int k = t + q * T;
+            if (k > M2 / 2) continue;
+            float2 a = d[(int64_t)k * p.n1];
+            float2 bb = d[(int64_t)(M2 - k) * p.n1];
+            if (k == 0) {
+                a.y = 0.f;
+                bb.y = 0.f;
+            }
+            float2 zk, zm;
+            herm_pre(a, bb, __ldg(p.twN2 + k), zk, zm);
+            sb[saddr<W1>(k)] = make_float2(zk.y, zk.x);
+            if (k > 0) sb[saddr<W1>(M2 - k)] = make_float2(zm.y, zm.x);
+        }
+        cta.sync();
+        float2 v[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q) v[q] = sb[saddr<W1>(t + q * T)];
+        fft_forward_regs<M2, W1, DevCtaL>(v, t, sbuf0, M2 * W1, parity, p.twM2, cta);
+        float* x = p.out_a + b * (int64_t)p.n + n1;
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t j = t + q * T;
+            __stcs(x + (2 * j) * p.n1, v[q].y * scale);
+            __stcs(x + (2 * j + 1) * p.n1, v[q].x * scale);
+        }
+        cta.sync();
+    }
+}
+
+// ---------------------------------------------------------------- host side
+struct LargeShape {
+    int n1, m2, w1, w2;
+};
+
+static bool large_shape(int n, LargeShape* s) {
+    int lg = 0;
+    while ((1 << lg) < n) ++lg;
+    if (lg < 14 || lg > 24) return false;
+    const int lg2 = (lg + 1) / 2;  // N2 >= N1
+    const int n2 = 1 << lg2;
+    s->n1 = n >> lg2;
+    s->m2 = n2 / 2;
+    s->w1 = 8192 / s->m2 < 32 ? 8192 / s->m2 : 32;
+    s->w2 = 8192 / s->n1 < 16 ? 8192 / s->n1 : 16;
+    return true;
+}
+
+template <int M2, int W1>
+static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse) {
+    constexpr int threads = W1 * FftPlan<M2>::T;
+    constexpr size_t smem = 2 * (size_t)M2 * W1 * sizeof(float2);
+    ma_context* ctx = plan->ctx;
+    auto kf = cols_r2c_kernel<M2, W1>;
+    auto ki = cols_c2r_kernel<M2, W1>;
+    static int occ_f[64] = {0}, occ_i[64] = {0};
+    int& occ = inverse ? occ_i[ctx->device & 63] : occ_f[ctx->device & 63];
+    if (occ == 0) {
+        int n = 0;
+        if (inverse) {
+            MA_CUDA(cudaFuncSetAttribute(ki, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            MA_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, ki, threads, smem));
+        } else {
+            MA_CUDA(cudaFuncSetAttribute(kf, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            MA_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kf, threads, smem));
+        }
+        occ = n > 0 ? n : 1;
+    }
+    const int64_t work = p.batch * (p.n1 / W1);
+    const int64_t cap = (int64_t)ctx->sm_count * occ;
+    const int grid = (int)(work < cap ? work : cap);
+    if (inverse) ki<<<grid, threads, smem, ctx->stream>>>(p);
+    else kf<<<grid, threads, smem, ctx->stream>>>(p);
+    return after_launch(ctx);
+}
+
+template <int N1, int W2>
+static ma_status run_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse) {
+    constexpr int threads = W2 * FftPlan<N1>::T;
+    constexpr size_t smem = 2 * (size_t)smem_elems_per_fft<N1, 1>() * W2 * sizeof(float2);
+    static_assert((size_t)N1 * (W2 + 1) * sizeof(float2) <= smem, "transposed tile must fit the exchange buffers");
+    ma_context* ctx = plan->ctx;
+    auto kf = rows_fwd_kernel<N1, W2>;
+    auto ki = rows_inv_kernel<N1, W2>;
+    static int occ_f[64] = {0}, occ_i[64] = {0};
+    int& occ = inverse ? occ_i[ctx->device & 63] : occ_f[ctx->device & 63];
+    if (occ == 0) {
+        int n = 0;
+        if (inverse) {
+            MA_CUDA(cudaFuncSetAttribute(ki, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            MA_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, ki, threads, smem));
+        } else {
+            MA_CUDA(cudaFuncSetAttribute(kf, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            MA_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kf, threads, smem));
+        }
+        occ = n > 0 ? n : 1;
+    }
+    const int m2 = p.n2 / 2;
+    const int64_t work = p.batch * ((m2 + 1 + W2 - 1) / W2);
+    const int64_t cap = (int64_t)ctx->sm_count * occ;
+    const int grid = (int)(work < cap ? work : cap);
+    if (inverse) ki<<<grid, threads, smem, ctx->stream>>>(p);
+    else kf<<<grid, threads, smem, ctx->stream>>>(p);
+    return after_launch(ctx);
+}
+
+static ma_status dispatch_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse) {
+    switch (p.n2 / 2) {
+        case 64: return run_cols<64, 32>(plan, p, inverse);
+        case 128: return run_cols<128, 32>(plan, p, inverse);
+        case 256: return run_cols<256, 32>(plan, p, inverse);
+        case 512: return run_cols<512, 16>(plan, p, inverse);
+        case 1024: return run_cols<1024, 8>(plan, p, inverse);
+        case 2048: return run_cols<2048, 4>(plan, p, inverse);
+        default: return MA_ERR_UNSUPPORTED;
+    }
+}
+
+static ma_status dispatch_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse) {
+    switch (p.n1) {
+        case 128: return run_rows<128, 16>(plan, p, inverse);
+        case 256: return run_rows<256, 16>(plan, p, inverse);
+        case 512: return run_rows<512, 16>(plan, p, inverse);
+        case 1024: return run_rows<1024, 8>(plan, p, inverse);
+        case 2048: return run_rows<2048, 4>(plan, p, inverse);
+        case 4096: return run_rows<4096, 2>(plan, p, inverse);
+        default: return MA_ERR_UNSUPPORTED;
+    }
+}
+
+static ma_status upload_tw(ma_context* ctx, int64_t len, int64_t count, float2** dptr) {
+    auto tw = make_twiddles(len, count);
+    MA_CUDA(cudaMalloc((void**)dptr, tw.size() * sizeof(float2)));
+    return copy_h2d(ctx, *dptr, tw.data(), tw.size() * sizeof(float2));
+}
+
+ma_status large_plan_init(ma_fft_plan* plan) {
+    LargeShape s;
+    if (!large_shape(plan->n, &s)) return MA_ERR_UNSUPPORTED;
+    ma_context* ctx = plan->ctx;
+    plan->n1 = s.n1;
+    plan->n2 = 2 * s.m2;
+    MA_TRY(upload_tw(ctx, s.m2, s.m2, &plan->d_twM));          // column stage twiddles
+    MA_TRY(upload_tw(ctx, 2 * s.m2, s.m2 / 2 + 1, &plan->d_twN)); // column Hermitian twiddles
+    MA_TRY(upload_tw(ctx, s.n1, s.n1, &plan->d_tw1));
+    MA_TRY(upload_tw(ctx, plan->n, plan->n / 2, &plan->d_twL));
+    // Chunk size: scratch of about 48 MB stays in L2 between the passes.
+    const size_t per = (size_t)(s.m2 + 1) * s.n1 * sizeof(float2);
+    int64_t chunk = (int64_t)(((size_t)48 << 20) / per);
+    if (chunk < 1) chunk = 1;
+    plan->scratch_batch = chunk;
+    MA_CUDA(cudaMalloc((void**)&plan->d_scratch, per * (size_t)chunk));
+    return MA_OK;
+}
+
+void large_plan_destroy(ma_fft_plan* plan) {
+    if (plan->d_tw1) (void)cudaFree(plan->d_tw1);
+    if (plan->d_twL) (void)cudaFree(plan->d_twL);
+    if (plan->d_scratch) (void)cudaFree(plan->d_scratch);
+    plan->d_tw1 = nullptr;
+    plan->d_twL = nullptr;
+    plan->d_scratch = nullptr;
+}
+
+static void fill_tables(ma_fft_plan* plan, LargeParams& p) {
+    p.n = plan->n;
+    p.n1 = plan->n1;
+    p.n2 = plan->n2;
+    p.scratch = plan->d_scratch;
+    p.twM2 = plan->d_twM;
+    p.twN2 = plan->d_twN;
+    p.tw1 = plan->d_tw1;
+    p.twL = plan->d_twL;
+}
+
+ma_status launch_r2c_large(ma_fft_plan* plan, const float* in, float* out_a, float* out_b, float* mag,
+                           int mag_kind, float db_scale, int64_t batch, int layout) {
+    const int64_t n = plan->n, half = n / 2;
+    for (int64_t done = 0; done < batch; done += plan->scratch_batch) {
+        LargeParams p{};
+        fill_tables(plan, p);
+        p.batch = batch - done < plan->scratch_batch ? batch - done : plan->scratch_batch;
+        p.in = in + done * n;
+        p.layout = layout;
+        p.mag_kind = mag_kind;
+        p.db_scale = db_scale;
+        if (layout == LAYOUT_FULL_SPLIT) {
+            p.out_a = out_a + done * n;
+            p.out_b = out_b + done * n;
+        } else {
+            p.out_a = out_a + done * 2 * (layout == LAYOUT_HALF_PACKED ? half : half + 1);
+        }
+        p.mag = mag ? mag + done * (half + 1) : nullptr;
+        MA_TRY(dispatch_cols(plan, p, false));
+        MA_TRY(dispatch_rows(plan, p, false));
+    }
+    return MA_OK;
+}
+
+ma_status launch_c2r_large(ma_fft_plan* plan, const float* in_a, const float* in_b, float* out, int64_t batch,
+                           int layout) {
+    const int64_t n = plan->n, half = n / 2;
+    for (int64_t done = 0; done < batch; done += plan->scratch_batch) {
+        LargeParams p{};
+        fill_tables(plan, p);
+        p.batch = batch - done < plan->scratch_batch ? batch - done : plan->scratch_batch;
+        p.layout = layout;
+        if (layout == LAYOUT_FULL_SPLIT) {
+            p.in = in_a + done * n;
+            p.in_b = in_b + done * n;
+        } else {
+            p.in = in_a + done * 2 * (layout == LAYOUT_HALF_PACKED ? half : half + 1);
+        }
+        p.out_a = out + done * n;
+        MA_TRY(dispatch_rows(plan, p, true));
+        MA_TRY(dispatch_cols(plan, p, true));
+    }
+    return MA_OK;
+}
+
+}  // namespace ma

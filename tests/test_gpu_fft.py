@@ -172,3 +172,61 @@ def test_nan_inf_propagate_and_extremes_finite(device):
     assert np.isfinite(re).all() and np.isfinite(im).all()
     f.forward(np.full(n, 1e6, np.float32), re, im)
     assert np.isfinite(re).all() and np.isfinite(im).all()
+
+
+@pytest.mark.parametrize("n,batch", [(16384, 5), (32768, 3), (65536, 7), (131072, 2), (1 << 18, 1), (1 << 19, 1),
+                                     (1 << 20, 2), (1 << 21, 1), (1 << 22, 1), (1 << 23, 1), (1 << 24, 1)])
+def test_large_transforms(device, lib, n, batch):
+    """Multi-pass path above 8192 points (the reference's MPSGraph size class), all layouts."""
+    import ctypes
+    from metalaudio_b200 import _lib as L
+    rng = np.random.default_rng(n % 1000 + batch)
+    x = rng.standard_normal((batch, n)).astype(np.float32)
+    f = make_fft(device, n)
+    ref = o64.rfft(x)
+    half = n // 2
+
+    def p(a):
+        return a.ctypes.data_as(ctypes.c_void_p)
+    # half-interleaved + magnitude
+    spec = np.zeros((batch, half + 1, 2), np.float32)
+    mag = np.zeros((batch, half + 1), np.float32)
+    assert lib.ma_fft_forward_host(f._h, p(x), p(spec), None, p(mag), L.MAG_MAGNITUDE, 1.0, batch,
+                                   L.LAYOUT_HALF_INTERLEAVED) == 0
+    assert o64.rel_rms(spec[..., 0] + 1j * spec[..., 1], ref) <= TOL
+    assert o64.rel_rms(mag, np.abs(ref)) <= TOL
+    y = np.zeros((batch, n), np.float32)
+    assert lib.ma_fft_inverse_host(f._h, p(spec), None, p(y), batch, L.LAYOUT_HALF_INTERLEAVED) == 0
+    assert o64.rel_rms(y, x) <= TOL
+    if n <= (1 << 20):
+        # the reference's full-N split layout, through the mirrored API
+        re, im = f.forwardBatch(x)
+        assert o64.rel_rms(re + 1j * im, o64.fft_forward(x)) <= TOL
+        assert o64.rel_rms(f.inverseBatch(re, im), x) <= TOL
+        # packed layout
+        pk = np.zeros((batch, half, 2), np.float32)
+        assert lib.ma_fft_forward_host(f._h, p(x), p(pk), None, None, 0, 1.0, batch, L.LAYOUT_HALF_PACKED) == 0
+        assert np.allclose(pk[:, 0, 0], ref[:, 0].real, rtol=1e-4, atol=1e-2)
+        assert np.allclose(pk[:, 0, 1], ref[:, half].real, rtol=1e-4, atol=1e-2)
+        assert o64.rel_rms(pk[:, 1:, 0] + 1j * pk[:, 1:, 1], ref[:, 1:half]) <= TOL
+        y2 = np.zeros((batch, n), np.float32)
+        assert lib.ma_fft_inverse_host(f._h, p(pk), None, p(y2), batch, L.LAYOUT_HALF_PACKED) == 0
+        assert o64.rel_rms(y2, x) <= TOL
+
+
+def test_config5_scaled(device, lib):
+    """Configuration 5 at reduced batch: 65536-point forward + inverse on N(0,1) data, more
+    transforms than one scratch chunk holds."""
+    import ctypes
+    from metalaudio_b200 import _lib as L
+    n, batch = 65536, 400
+    x = configs.c5_batch(batch=batch, n=n)
+    f = make_fft(device, n)
+    spec = np.zeros((batch, n // 2 + 1, 2), np.float32)
+    p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    assert lib.ma_fft_forward_host(f._h, p(x), p(spec), None, None, 0, 1.0, batch, L.LAYOUT_HALF_INTERLEAVED) == 0
+    ref = o64.rfft(x[[0, 199, 399]])
+    assert o64.rel_rms(spec[[0, 199, 399], :, 0] + 1j * spec[[0, 199, 399], :, 1], ref) <= TOL
+    y = np.zeros_like(x)
+    assert lib.ma_fft_inverse_host(f._h, p(spec), None, p(y), batch, L.LAYOUT_HALF_INTERLEAVED) == 0
+    assert o64.rel_rms(y, x) <= TOL
