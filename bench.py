@@ -1,0 +1,483 @@
+#!/usr/bin/env python
+"""Benchmark of the MetalDSP hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" = one pass of the hot path over one batch of synthetic input: the batched
+STFT + iSTFT configuration (256 mono signals of 2^20 uniform[-1,1) samples per GPU,
+n_fft 4096, hop 1024, periodic Hann; half-spectrum complex + magnitude out, COLA
+overlap-add reconstruction back).  Metric: STFT frames/s, whole job over all GPUs, with the
+signals already resident in HBM.  Under torchrun every rank runs its own shard of
+independent signals (no collective on the data path; weak scaling), the timed region is
+bracketed by barrier + device synchronisation and the maximum over ranks is reported.
+
+The JSON line also carries
+  roofline      the dominant kernel's achieved HBM GB/s (algorithmic bytes / CUDA-event time)
+                against the measured copy bandwidth of this pool's B200s,
+  kernels       the same for every kernel of the step,
+  e2e           the same metric through the public Tensor API with pinned host buffers,
+                host->device and device->host copies inside the timed region,
+  cpu_baseline  the float32 CPU port of the reference path timed on the host cores (N=1 only),
+  conv          the partitioned-convolution configuration (512 channels, one shared 131072-tap
+                IR, block 256) as a streaming step, with its own roofline fraction,
+  large_fft     the 65536-point forward + inverse batch.
+
+`--impl reference` times the CPU port of the reference path (the reference itself is Swift +
+Apple Accelerate and cannot run here) on all host cores over a bounded sample per step.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_FFT, HOP = 4096, 1024
+SIGNALS_PER_GPU, SIGNAL_LEN = 256, 1 << 20
+FRAMES = (SIGNAL_LEN - N_FFT) // HOP + 1
+KH = N_FFT // 2 + 1
+STFT_BYTES_PER_SIGNAL = SIGNAL_LEN * 4 + FRAMES * (KH * 8 + KH * 4)   # read signal once, write complex + magnitude
+ISTFT_BYTES_PER_SIGNAL = FRAMES * KH * 8 + SIGNAL_LEN * 4             # read complex, write signal
+CONV = dict(channels=512, block=256, taps=131072, bytes_per_channel_block=1058832)
+LARGE = dict(n=65536, batch=4096)
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs
+    (read-only queries)."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._halt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._halt.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._halt.wait(self.period)
+
+    def stop(self):
+        self._halt.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        med = int(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+
+def cpu_port_stft_istft(signals: np.ndarray, window: np.ndarray, cores: int) -> float:
+    """Runs the float32 port of the reference path (STFT.swift:40-81 then :384-527) over
+    `signals` with a pool of `cores` threads, one signal per task; returns seconds."""
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import reference_path as rp
+
+    def one(x):
+        re, im = rp.stft(x, N_FFT, HOP, window)
+        kh = N_FFT // 2 + 1
+        mag = np.sqrt(re[:, :kh] ** 2 + im[:, :kh] ** 2)
+        y = rp.istft(re, im, N_FFT, HOP, window)
+        return float(y[0]) + float(mag[0, 0])
+
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=cores) as ex:
+        list(ex.map(one, list(signals)))
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank: int, world: int):
+    """`--impl reference`: the CPU port on all host cores; rank 0 only."""
+    if rank != 0:
+        return
+    from oracle import configs, reference_path as rp
+    cores = os.cpu_count() or 1
+    sample = max(cores, 16)
+    x = configs.c2_signals(n_signals=sample, length=SIGNAL_LEN)
+    w = rp.periodic_hann(N_FFT)
+    for _ in range(min(args.warmup, 1)):
+        cpu_port_stft_istft(x[:cores], w, cores)
+    times = [cpu_port_stft_istft(x, w, cores) for _ in range(args.steps)]
+    total = float(np.sum(times))
+    frames = sample * FRAMES * args.steps
+    value = frames / total
+    line = {
+        "impl": "reference", "metric": "stft_istft_frames_per_s", "value": value, "unit": "frames/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus, sample_note=f"each step = {sample} signals on the host CPU"),
+        "cpu_baseline": {"value": value, "unit": "frames/s", "cores": cores, "kind": "port",
+                         "sample": f"{sample} signals x 2^20 samples per step ({sample * FRAMES} frames), "
+                                   f"scipy.fft float32 + numpy, {cores} threads"},
+        "e2e": {"value": value, "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int, sample_note: str | None = None, signals: int = SIGNALS_PER_GPU):
+    cfg = {"workload": f"batched STFT+iSTFT: {signals} mono fp32 signals x 2^20 samples per GPU, uniform[-1,1), "
+                       "n_fft=4096, hop=1024, periodic Hann, half-spectrum complex + magnitude out, "
+                       "COLA overlap-add reconstruction",
+           "signals_per_gpu": signals, "signal_len": SIGNAL_LEN, "n_fft": N_FFT, "hop": HOP,
+           "frames_per_gpu": signals * FRAMES, "window": "periodic_hann",
+           "sharding": f"independent signals per rank, no collective ({n_gpus} ranks)",
+           "cache": "inputs (1.07 GB) and outputs (6.4 GB) per step exceed the 126 MB L2; no flush needed"}
+    if sample_note:
+        cfg["sample"] = sample_note
+    return cfg
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+def run_ours(args, rank: int, local_rank: int, world: int):
+    import torch
+    from metalaudio_b200 import AudioDevice, Convolution, FFT, Tensor, WindowType
+    from oracle import reference_path as rp  # window table + CPU baseline only
+
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = AudioDevice(local_rank)
+    lib = dev._lib
+    stream = torch.cuda.ExternalStream(lib.ma_context_stream(dev.handle), device=torch.device("cuda", local_rank))
+    peak, peak_kind = measured_peak_gbs()
+
+    window = rp.periodic_hann(N_FFT)
+    fft = FFT(dev, FFT.Config(size=N_FFT, windowType=WindowType.hann, hopSize=HOP), window=window)
+    S = args.signals
+    sig = Tensor(dev, (S, SIGNAL_LEN))
+    spec = Tensor(dev, (S, FRAMES, KH, 2))
+    mag = Tensor(dev, (S, FRAMES, KH))
+    rec = Tensor(dev, (S, SIGNAL_LEN))
+
+    # Synthetic input: uniform[-1,1), seeded per global signal index, generated into pinned host
+    # memory (the e2e leg copies it from there every step).
+    host_in = torch.empty((S, SIGNAL_LEN), dtype=torch.float32, pin_memory=True)
+    host_out = torch.empty((S, SIGNAL_LEN), dtype=torch.float32, pin_memory=True)
+    gen = torch.Generator().manual_seed(1002 + rank)
+    host_in.uniform_(-1.0, 1.0, generator=gen)
+    sig.copyAsync(host_in.data_ptr(), sig.byteSize)
+    dev.synchronize(60)
+
+    def step():
+        fft.stftTensor(sig, spec, mag)
+        fft.istftTensor(spec, rec)
+
+    def barrier():
+        dev.synchronize(120)
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    # ---- timed region: K steps, CUDA events on the launching stream around every kernel
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = lib.ma_kernel_launch_count()
+    t_wall0 = time.perf_counter()
+    for k in range(K):
+        ev[k][0].record(stream)
+        fft.stftTensor(sig, spec, mag)
+        ev[k][1].record(stream)
+        fft.istftTensor(spec, rec)
+        ev[k][2].record(stream)
+    dev.synchronize(600)
+    torch.cuda.synchronize()
+    t_wall = time.perf_counter() - t_wall0
+    launches = int(lib.ma_kernel_launch_count() - launches0)
+    clocks = sampler.stop()
+    if dist is not None:
+        dist.barrier()
+    total_ms = ev[0][0].elapsed_time(ev[K - 1][2])
+    stft_ms = float(np.mean([ev[k][0].elapsed_time(ev[k][1]) for k in range(K)]))
+    istft_ms = float(np.mean([ev[k][1].elapsed_time(ev[k][2]) for k in range(K)]))
+    if dist is not None:
+        t = torch.tensor([total_ms, stft_ms, istft_ms], device=f"cuda:{local_rank}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, stft_ms, istft_ms = [float(v) for v in t.tolist()]
+    frames_all = S * FRAMES * world
+    value = frames_all * K / (total_ms * 1e-3)
+
+    def kernel_entry(name, ms, nbytes):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        return {"kernel": name, "ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": gbs, "frac": gbs / peak}
+
+    kernels = [kernel_entry("r2c_kernel<2048> (STFT: window + FFT + Hermitian + magnitude)", stft_ms,
+                            S * STFT_BYTES_PER_SIGNAL),
+               kernel_entry("istft_kernel<2048> (iSTFT: inverse FFT + window + overlap-add + normalise)", istft_ms,
+                            S * ISTFT_BYTES_PER_SIGNAL)]
+    dom = max(kernels, key=lambda e: e["ms"])
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        try:
+            traffic = json.load(open(tpath)).get(dom["kernel"].split(" ")[0])
+        except Exception:
+            traffic = None
+    roofline = {"bound": "hbm", "achieved": dom["achieved_gbs"], "peak": peak, "unit": "GB/s",
+                "frac": dom["frac"], "traffic": traffic, "kernel": dom["kernel"], "peak_kind": peak_kind}
+
+    # ---- e2e: pinned host -> device -> STFT -> iSTFT -> pinned host, through the Tensor API
+    e2e_steps = max(2, min(K, 5))
+
+    def e2e_step():
+        sig.copyAsync(host_in.data_ptr(), sig.byteSize)
+        fft.stftTensor(sig, spec, mag)
+        fft.istftTensor(spec, rec)
+        rec.copyToAsync(host_out.data_ptr(), rec.byteSize)
+        dev.synchronize(120)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    dev.synchronize(120)
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device=f"cuda:{local_rank}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e = {"value": frames_all * e2e_steps / (e2e_ms * 1e-3), "unit": "frames/s",
+           "h2d_bytes_per_step": sig.byteSize, "d2h_bytes_per_step": rec.byteSize, "steps": e2e_steps,
+           "ms_per_step": e2e_ms / e2e_steps}
+
+    # reconstruction sanity on the timed buffers (not part of any timed region)
+    chk = host_out[0, N_FFT:SIGNAL_LEN - N_FFT] - host_in[0, N_FFT:SIGNAL_LEN - N_FFT]
+    recon_err = float(chk.double().pow(2).mean().sqrt() / host_in[0].double().pow(2).mean().sqrt())
+
+    for tns in (spec, mag, rec, sig):
+        tns.free()
+    del host_out
+
+    extra = {}
+    if not args.no_extras:
+        extra["conv"] = bench_conv(dev, lib, torch, stream, peak)
+        extra["large_fft"] = bench_large(dev, lib, torch, stream, peak)
+
+    cpu = None
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        sample = max(16, cores)
+        x = host_in[:sample].numpy()
+        cpu_port_stft_istft(x[:cores], window, cores)
+        best = min(cpu_port_stft_istft(x, window, cores) for _ in range(3))
+        cpu = {"value": sample * FRAMES / best, "unit": "frames/s", "cores": cores, "kind": "port",
+               "sample": f"{sample} of the 256 signals ({sample * FRAMES} frames), float32 scipy.fft + numpy port of "
+                         f"the reference's stft/istft, {cores} threads, best of 3"}
+
+    if dist is not None:
+        dist.barrier()
+    if rank == 0:
+        line = {
+            "metric": "stft_istft_frames_per_s", "value": value, "unit": "frames/s", "n_gpus": world,
+            "steps": K, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / K,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": workload_config(world, signals=S),
+            "roofline": roofline, "kernels": kernels, "e2e": e2e, "cpu_baseline": cpu,
+            "gpu_launches": launches, "clocks": clocks, "reconstruction_rel_rms": recon_err,
+            "stft_frames_per_s": frames_all / (stft_ms * 1e-3), "istft_frames_per_s": frames_all / (istft_ms * 1e-3),
+            "wall_ms_per_step": 1e3 * t_wall / K,
+        }
+        line.update(extra)
+        print(json.dumps(line), flush=True)
+    fft.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def bench_conv(dev, lib, torch, stream, peak):
+    """Partitioned convolution, configuration 3 shape, as causal streaming steps: every step
+    reads the whole frequency-domain delay line of every channel once."""
+    from metalaudio_b200 import Convolution, Tensor
+    from oracle import configs
+    C, B, taps = CONV["channels"], CONV["block"], CONV["taps"]
+    steps, warm = (200, 16) if C >= 256 else (24, 8)
+    conv = Convolution(dev, Convolution.Mode.partitioned(blockSize=B), channels=C)
+    conv.setKernel(configs.c3_ir(taps))
+    x = Tensor(dev, (C, (steps + warm) * B))
+    y = Tensor(dev, (C, (steps + warm) * B))
+    host = torch.empty((C, (steps + warm) * B), dtype=torch.float32, pin_memory=True)
+    host.normal_(0.0, 0.1, generator=torch.Generator().manual_seed(1013))
+    x.copyAsync(host.data_ptr(), x.byteSize)
+    dev.synchronize(60)
+    stride = (steps + warm) * B
+
+    def do(t):
+        st = lib.ma_pconv_step_dev(conv._h, ctypes.c_void_p(x.pointer + 4 * t * B), stride,
+                                   ctypes.c_void_p(y.pointer + 4 * t * B), stride)
+        if st != 0:
+            raise RuntimeError(f"ma_pconv_step_dev failed: {st}")
+
+    for t in range(warm):
+        do(t)
+    dev.synchronize(60)
+    l0 = lib.ma_kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for t in range(warm, warm + steps):
+        do(t)
+    e1.record(stream)
+    dev.synchronize(120)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    launches = int(lib.ma_kernel_launch_count() - l0)
+    gbs = C * CONV["bytes_per_channel_block"] / (ms * 1e-3) / 1e9
+    out = {"workload": "partitioned convolution: 512 channels, shared 131072-tap IR, block 256 (FFT 512, 512 "
+                       "partitions), streaming steps",
+           "metric": "conv_channel_samples_per_s", "value": C * B / (ms * 1e-3), "unit": "channel-samples/s",
+           "ms_per_step": ms, "steps": steps, "gpu_launches": launches,
+           "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                        "algorithmic_bytes_per_channel_block": CONV["bytes_per_channel_block"],
+                        "kernel": "pconv_mac_kernel + r2c + c2r per step"}}
+    conv.close()
+    x.free()
+    y.free()
+    return out
+
+
+def bench_large(dev, lib, torch, stream, peak):
+    """65536-point forward + inverse batch (configuration 5)."""
+    from metalaudio_b200 import FFT, Tensor, WindowType
+    n, batch = LARGE["n"], LARGE["batch"]
+    fft = FFT(dev, FFT.Config(size=n, windowType=WindowType.none))
+    x = Tensor(dev, (batch, n))
+    z = Tensor(dev, (batch, n // 2 + 1, 2))
+    y = Tensor(dev, (batch, n))
+    host = torch.empty((batch, n), dtype=torch.float32, pin_memory=True)
+    host.normal_(0.0, 1.0, generator=torch.Generator().manual_seed(1005))
+    x.copyAsync(host.data_ptr(), x.byteSize)
+    dev.synchronize(60)
+
+    def pair():
+        a = lib.ma_fft_forward_dev(fft._h, ctypes.c_void_p(x.pointer), ctypes.c_void_p(z.pointer), None, None, 0,
+                                   1.0, batch, 0)
+        b = lib.ma_fft_inverse_dev(fft._h, ctypes.c_void_p(z.pointer), None, ctypes.c_void_p(y.pointer), batch, 0)
+        if a != 0 or b != 0:
+            raise RuntimeError(f"large FFT failed: {a} {b}")
+
+    for _ in range(3):
+        pair()
+    dev.synchronize(60)
+    reps = 10
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        pair()
+    e1.record(stream)
+    dev.synchronize(120)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    nbytes = 2 * batch * (n * 4 + (n // 2 + 1) * 8)
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    out = {"workload": "4096 x 65536-point real forward + inverse", "metric": "fft65536_pairs_per_s",
+           "value": batch / (ms * 1e-3), "unit": "pairs/s", "ms_per_pair_batch": ms,
+           "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                        "algorithmic_bytes": nbytes}}
+    fft.close()
+    for t in (x, y, z):
+        t.free()
+    return out
+
+
+def run_only(args, local_rank: int):
+    """One of the extra workloads alone, for profiler captures of its kernels."""
+    import torch
+    from metalaudio_b200 import AudioDevice
+    dev = AudioDevice(local_rank)
+    lib = dev._lib
+    stream = torch.cuda.ExternalStream(lib.ma_context_stream(dev.handle), device=torch.device("cuda", local_rank))
+    peak, _ = measured_peak_gbs()
+    fn = bench_conv if args.only == "conv" else bench_large
+    print(json.dumps({args.only: fn(dev, lib, torch, stream, peak)}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-extras", action="store_true", help="skip the convolution and 65536-point lines")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--signals", type=int, default=SIGNALS_PER_GPU,
+                    help="signals per GPU (default: the benchmark configuration's 256; smaller for profiler captures)")
+    ap.add_argument("--conv-channels", type=int, default=CONV["channels"])
+    ap.add_argument("--large-batch", type=int, default=LARGE["batch"])
+    ap.add_argument("--only", choices=["conv", "large"], default=None,
+                    help="run just one of the extra workloads (profiler captures)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    CONV["channels"] = args.conv_channels
+    LARGE["batch"] = args.large_batch
+    if args.only is not None:
+        run_only(args, local_rank)
+        return
+    run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -267,6 +267,16 @@ class Tensor:
                       "Tensor.toArray")
         return out
 
+    def copyAsync(self, from_ptr: int, nbytes: int) -> None:
+        """Stream-ordered host->device copy from PINNED host memory at ``from_ptr``."""
+        _raise_status(self.device._lib.ma_memcpy_h2d_async(self.device.handle, self._p, ctypes.c_void_p(from_ptr),
+                                                          nbytes), "Tensor.copyAsync")
+
+    def copyToAsync(self, to_ptr: int, nbytes: int) -> None:
+        """Stream-ordered device->host copy into PINNED host memory at ``to_ptr``."""
+        _raise_status(self.device._lib.ma_memcpy_d2h_async(self.device.handle, ctypes.c_void_p(to_ptr), self._p,
+                                                          nbytes), "Tensor.copyToAsync")
+
     def zero(self) -> None:
         _raise_status(self.device._lib.ma_buffer_zero(self.device.handle, self._p, self.byteSize), "Tensor.zero")
 
@@ -634,6 +644,27 @@ class FFT:
                                      validatedWindowFloor(), L.LAYOUT_HALF_INTERLEAVED)
         _raise_status(st, "istftBatch")
         return out
+
+    # ---- device-resident forms: Tensor in, Tensor out, nothing crosses PCIe
+    def stftTensor(self, signals: "Tensor", spectrum: "Tensor", magnitude: Optional["Tensor"] = None) -> int:
+        """STFT of a (S, L) signal Tensor into a (S, F, N/2+1, 2) spectrum Tensor (and a
+        (S, F, N/2+1) magnitude Tensor).  Queued on the device stream; returns F."""
+        s, length = signals.shape
+        f = self.frameCount(length)
+        st = self._lib.ma_stft_dev(self._h, ctypes.c_void_p(signals.pointer), length, length, s,
+                                   ctypes.c_void_p(spectrum.pointer), None,
+                                   ctypes.c_void_p(magnitude.pointer) if magnitude is not None else None,
+                                   L.MAG_MAGNITUDE, 1.0, L.LAYOUT_HALF_INTERLEAVED)
+        _raise_status(st, "stftTensor")
+        return f
+
+    def istftTensor(self, spectrum: "Tensor", output: "Tensor") -> None:
+        """Inverse of stftTensor into a (S, out_stride) Tensor with out_stride >= (F-1)*hop+N."""
+        s, f = spectrum.shape[0], spectrum.shape[1]
+        st = self._lib.ma_istft_dev(self._h, ctypes.c_void_p(spectrum.pointer), None, f, s,
+                                    ctypes.c_void_p(output.pointer), output.shape[1], validatedWindowFloor(),
+                                    L.LAYOUT_HALF_INTERLEAVED)
+        _raise_status(st, "istftTensor")
 
     def releaseGPUResources(self) -> None:
         """STFT.swift:537-542.  Device tables are a few KB; kept so the object stays usable."""

@@ -15,6 +15,10 @@ import scipy.fft as sfft
 
 F32 = np.float32
 
+# Threads scipy.fft may use (None: one).  The CPU-baseline legs of the benchmark set this to
+# the host core count; parity tests leave it alone.
+WORKERS = None
+
 # --------------------------------------------------------------------------- windows
 
 
@@ -53,7 +57,7 @@ def fft_forward(x: np.ndarray):
     Sources/MetalDSP/FFT.swift:818-855 (imaginary input zero, forward sign
     exp(-2*pi*i*k*n/N), no scaling).  ``x``: (..., N) float32."""
     x = np.ascontiguousarray(x, dtype=F32)
-    X = sfft.fft(x.astype(np.complex64), axis=-1)
+    X = sfft.fft(x.astype(np.complex64), axis=-1, workers=WORKERS)
     return np.ascontiguousarray(X.real, dtype=F32), np.ascontiguousarray(X.imag, dtype=F32)
 
 
@@ -62,7 +66,7 @@ def fft_inverse(re: np.ndarray, im: np.ndarray) -> np.ndarray:
     Sources/MetalDSP/FFT.swift:889-919 (an ``inverse: true`` object)."""
     Z = np.asarray(re, dtype=F32) + 1j * np.asarray(im, dtype=F32)
     n = Z.shape[-1]
-    z = sfft.ifft(Z.astype(np.complex64), axis=-1, norm="forward")  # unscaled
+    z = sfft.ifft(Z.astype(np.complex64), axis=-1, norm="forward", workers=WORKERS)  # unscaled
     return (z.real.astype(F32) * F32(1.0 / F32(n))).astype(F32)
 
 

@@ -1,0 +1,122 @@
+"""CPU tests: the oracle (float32 port and float64 definition) against the reference's
+golden vectors and analytic known answers, so the oracle is pinned before it checks CUDA."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from oracle import configs
+from oracle import float64 as o64
+from oracle import reference_path as rp
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_golden_forward_256():
+    d = json.load(open(os.path.join(GOLDEN, "fft_forward_256.json")))
+    x = np.array(d["input"], np.float32)
+    exp = np.array(d["expectedOutput"], np.float64)
+    assert d["parameters"]["size"] == 256 and not d["parameters"]["inverse"]
+    re, im = rp.fft_forward(x)
+    assert np.max(np.abs(np.concatenate([re, im]) - exp)) < 1e-4
+    X = o64.fft_forward(x)
+    assert np.max(np.abs(np.concatenate([X.real, X.imag]) - exp)) < 1e-4
+    assert o64.rel_rms(np.concatenate([re, im]), exp) < 1e-6
+
+
+def test_golden_roundtrip_256():
+    d = json.load(open(os.path.join(GOLDEN, "fft_roundtrip_256.json")))
+    x = np.array(d["input"], np.float32)
+    exp = np.array(d["expectedOutput"], np.float64)
+    re, im = rp.fft_forward(x)
+    y = rp.fft_inverse(re, im)
+    assert np.max(np.abs(y - exp)) < d["tolerance"]
+    assert np.max(np.abs(o64.fft_inverse(re, im) - exp)) < d["tolerance"]
+
+
+def test_known_answers():
+    n = 512
+    x = np.zeros(n, np.float32); x[0] = 1
+    re, im = rp.fft_forward(x)
+    assert np.allclose(re, 1) and np.allclose(im, 0)
+    re, im = rp.fft_forward(np.ones(n, np.float32))
+    assert abs(re[0] - n) < 1e-3 and np.max(np.abs(re[1:])) < 1e-3
+    k = 9
+    re, im = rp.fft_forward(np.sin(2 * np.pi * k * np.arange(n) / n).astype(np.float32))
+    mag = rp.magnitude(re, im)
+    assert mag.shape == (n // 2 + 1,) and int(np.argmax(mag)) == k
+    assert np.allclose(rp.power(re, im), mag * mag, rtol=1e-5, atol=1e-6)
+
+
+def test_window_is_symmetric_like_the_reference():
+    """FFTTests: w[i] == w[N-1-i] to 1e-5 at N=256 (a periodic Hann fails this), endpoints 0,
+    centre ~1, rectangular all ones, length 1 -> 1."""
+    for kind in ("hann", "hamming", "blackman"):
+        w = rp.window(kind, 256)
+        assert np.max(np.abs(w - w[::-1])) < 1e-5
+        assert np.isfinite(w).all()
+    w = rp.window("hann", 256)
+    assert w[0] == 0 and w[-1] < 1e-6 and abs(w[127] - 1) < 1e-3
+    assert np.max(np.abs(rp.periodic_hann(256) - rp.periodic_hann(256)[::-1])) > 1e-3
+    assert np.all(rp.window("none", 64) == 1) and rp.window("hann", 1)[0] == 1
+
+
+def test_window_floor_rule():
+    assert rp.window_floor(1e-8) == np.float32(1e-8)
+    assert rp.window_floor(1e-12) == np.float32(1e-6)
+    assert rp.window_floor(0.5) == np.float32(0.1)
+
+
+def test_stft_istft_port_vs_float64():
+    n, hop = 256, 64
+    x = np.random.default_rng(0).uniform(-1, 1, 5000).astype(np.float32)
+    w = rp.window("hann", n)
+    re, im = rp.stft(x, n, hop, w)
+    f = rp.stft_frame_count(5000, n, hop)
+    assert re.shape == (f, n) and f == (5000 - n) // hop + 1
+    ref = o64.stft(x, n, hop, w)
+    assert o64.rel_rms(re[:, :n // 2 + 1] + 1j * im[:, :n // 2 + 1], ref) < 1e-6
+    y = rp.istft(re, im, n, hop, w)
+    assert y.shape == ((f - 1) * hop + n,)
+    ws = rp.window_sum(f, n, hop, w, 0.0)
+    m = ws > 1e-2 * ws.max()
+    assert o64.rel_rms(y[m], x[:y.size][m]) < 1e-5
+    with pytest.raises(ValueError):
+        rp.stft_frame_count(100, 256, 64)
+
+
+def test_partitioned_port_vs_float64():
+    rng = np.random.default_rng(1)
+    for block, taps, length in [(64, 1, 256), (64, 200, 1000), (128, 1000, 3000), (16, 5, 7)]:
+        h = rng.standard_normal(taps).astype(np.float32)
+        x = rng.standard_normal(length).astype(np.float32)
+        pc = rp.PartitionedConvolution(block)
+        pc.set_kernel(h)
+        y = pc.process(x)
+        assert y.shape == (length + taps - 1,)
+        assert o64.rel_rms(y, o64.convolve_full(x, h)) < 1e-5
+    # identity kernel (ConvolutionTests): delta reproduces the input
+    pc = rp.PartitionedConvolution(64)
+    pc.set_kernel(np.array([1.0], np.float32))
+    x = np.arange(256, dtype=np.float32) / 256
+    assert np.max(np.abs(pc.process(x) - x)) < 1e-5
+    assert pc.process(np.zeros(0, np.float32)).size == 0
+
+
+def test_spot_check_matches_full_convolution():
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal(300); h = rng.standard_normal(40)
+    idx = [0, 1, 39, 40, 150, 298, 299, 338]
+    assert np.allclose(o64.convolve_spot(x, h, idx), np.convolve(x, h)[idx])
+
+
+def test_config_generators_are_seeded_and_shardable():
+    a = configs.c2_signals(4, 1000)
+    b = configs.c2_signals(2, 1000, first_signal=2)
+    assert np.array_equal(a[2:], b) and a.min() >= -1 and a.max() < 1
+    h = configs.c3_ir(4096)
+    assert abs(float(np.sum(h.astype(np.float64) ** 2)) - 1) < 1e-4
+    assert np.array_equal(configs.c3_input(3, 100)[1:], configs.c3_input(2, 100, first_channel=1))
+    assert configs.c4_irs(2, 128).shape == (2, 128) and configs.c5_batch(2, 64).shape == (2, 64)
+    assert configs.c1_frame().shape == (2048,)
