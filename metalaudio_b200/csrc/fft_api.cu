@@ -51,7 +51,14 @@ ma_status ma_fft_plan_create(ma_context* ctx, int32_t n, const float* window, in
     p->hop = hop;
     p->large = n > kMaxSmallN;
     ma_status st = MA_OK;
-    if (window != nullptr) st = upload(ctx, window, sizeof(float) * (size_t)n, (void**)&p->d_window);
+    if (window != nullptr) {
+        p->h_window.assign(window, window + n);
+        st = upload(ctx, window, sizeof(float) * (size_t)n, (void**)&p->d_window);
+    }
+    if (st == MA_OK && !p->large) {
+        cudaError_t e = cudaMalloc((void**)&p->d_norm, sizeof(float) * (size_t)hop);
+        if (e != cudaSuccess) st = cuda_fail(e);
+    }
     if (st == MA_OK && !p->large) {
         auto twM = make_twiddles(p->m, p->m);
         auto twN = make_twiddles(n, p->m / 2 + 1);
@@ -77,6 +84,7 @@ ma_status ma_fft_plan_destroy(ma_fft_plan* plan) {
     if (plan->d_window) (void)cudaFree(plan->d_window);
     if (plan->d_twM) (void)cudaFree(plan->d_twM);
     if (plan->d_twN) (void)cudaFree(plan->d_twN);
+    if (plan->d_norm) (void)cudaFree(plan->d_norm);
     (void)cudaGetLastError();
     delete plan;
     return MA_OK;

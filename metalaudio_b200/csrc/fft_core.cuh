@@ -127,6 +127,7 @@ struct FftPlan;
 #define MA_DEFINE_PLAN(M_, R_, NS_, R0, R1, R2)                                     \
     template <>                                                                     \
     struct FftPlan<M_> {                                                            \
+        static constexpr int M = M_;                                                \
         static constexpr int R = R_;                                                \
         static constexpr int T = M_ / R_;                                           \
         static constexpr int NS = NS_;                                              \
@@ -150,6 +151,31 @@ MA_DEFINE_PLAN(1024, 16, 3, 16, 8, 8)
 MA_DEFINE_PLAN(2048, 16, 3, 16, 16, 8)
 MA_DEFINE_PLAN(4096, 16, 3, 16, 16, 16)
 #undef MA_DEFINE_PLAN
+
+// The same radices in reverse order (first stage the smallest radix, possibly several
+// butterflies per thread).  Used by the inverse transforms, whose Hermitian pre-process
+// feeds a paired first stage.
+template <int M_>
+struct FftPlanRev {
+    using F = FftPlan<M_>;
+    static constexpr int M = M_;
+    static constexpr int R = F::R;
+    static constexpr int T = F::T;
+    static constexpr int NS = F::NS;
+    static constexpr __host__ __device__ int radix(int s) { return F::radix(NS - 1 - s); }
+    static constexpr __host__ __device__ int ns_before(int s) {
+        int n = 1;
+        for (int i = 0; i < s; ++i) n *= radix(i);
+        return n;
+    }
+};
+
+// True when the last forward stage (first reverse stage) runs at least two butterflies per
+// thread, which is what the paired mapping needs.
+template <int M_>
+constexpr __host__ __device__ bool plan_pairable() {
+    return FftPlan<M_>::NS >= 2 && (FftPlan<M_>::R / FftPlan<M_>::radix(FftPlan<M_>::NS - 1)) >= 2;
+}
 
 // Shared-memory addressing.  W == 1: one transform owns a contiguous region, element idx
 // lives at idx + idx/16 (float2 units).  W > 1: W transforms are interleaved, element idx
@@ -203,27 +229,41 @@ MA_HD void load_twiddles(float2* w, const float2* __restrict__ twM, int base, in
     }
 }
 
-template <int M, int W, int S>
+// Which butterfly of a stage a thread's b-th sub-butterfly is.  Natural: jv = t + b*T.
+// Paired: the thread owns butterflies in pairs (j, nbfly - j), so that element i and element
+// M - i of a stage input/output that is indexed jv + k*nbfly sit in the same thread; the two
+// self-paired butterflies 0 and nbfly/2 go to thread 0.
+template <class P, bool PAIRED>
+MA_HD int stage_jv(int t, int b, int nbfly) {
+    if constexpr (!PAIRED) {
+        (void)nbfly;
+        return t + b * P::T;
+    } else {
+        const int j = (b >> 1) * P::T + t;
+        if ((b & 1) == 0) return j;
+        return j == 0 ? (nbfly >> 1) : nbfly - j;
+    }
+}
+
+template <class P, int W, int S, bool PAIRED>
 MA_HD void stage_write(const float2* v, int t, float2* sbuf) {
-    using P = FftPlan<M>;
-    constexpr int r = P::radix(S), Ns = P::ns_before(S), NB = P::R / r, T = P::T;
+    constexpr int M = P::M, r = P::radix(S), Ns = P::ns_before(S), NB = P::R / r;
 #pragma unroll
     for (int b = 0; b < NB; ++b) {
-        const int jv = t + b * T;
+        const int jv = stage_jv<P, PAIRED>(t, b, M / r);
         const int o0 = (jv / Ns) * (Ns * r) + (jv % Ns);
 #pragma unroll
         for (int k = 0; k < r; ++k) sbuf[saddr<W>(o0 + k * Ns)] = v[b * r + k];
     }
 }
 
-template <int M, int W, int S>
+template <class P, int W, int S, bool PAIRED>
 MA_HD void stage_read_compute(float2* v, int t, const float2* sbuf,
                               const float2* __restrict__ twM) {
-    using P = FftPlan<M>;
-    constexpr int r = P::radix(S), Ns = P::ns_before(S), NB = P::R / r, T = P::T;
+    constexpr int M = P::M, r = P::radix(S), Ns = P::ns_before(S), NB = P::R / r;
 #pragma unroll
     for (int b = 0; b < NB; ++b) {
-        const int jv = t + b * T;
+        const int jv = stage_jv<P, PAIRED>(t, b, M / r);
 #pragma unroll
         for (int k = 0; k < r; ++k) v[b * r + k] = sbuf[saddr<W>(jv + k * (M / r))];
         float2 w[r];
@@ -234,33 +274,45 @@ MA_HD void stage_read_compute(float2* v, int t, const float2* sbuf,
     }
 }
 
-template <int M, int W, int S, class Cta>
+template <class P, int W, int S, bool PAIR0, bool PAIRL, class Cta>
 struct StageChain {
     static MA_HD void run(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
                           const float2* __restrict__ twM, Cta& cta) {
-        using P = FftPlan<M>;
         if constexpr (S < P::NS) {
             float2* sbuf = sbuf0 + parity * buf_stride;
-            stage_write<M, W, S - 1>(v, t, sbuf);
+            stage_write<P, W, S - 1, (S == 1) && PAIR0>(v, t, sbuf);
             cta.sync();
-            stage_read_compute<M, W, S>(v, t, sbuf, twM);
+            stage_read_compute<P, W, S, (S == P::NS - 1) && PAIRL>(v, t, sbuf, twM);
             parity ^= 1;
-            StageChain<M, W, S + 1, Cta>::run(v, t, sbuf0, buf_stride, parity, twM, cta);
+            StageChain<P, W, S + 1, PAIR0, PAIRL, Cta>::run(v, t, sbuf0, buf_stride, parity, twM, cta);
         }
     }
 };
 
-// Complex forward FFT of length M.  In: v[q] = z[t + q*T].  Out: v[q] = Z[t + q*T].
+// All stages of plan P on registers.
+// In:  v[b*r0 + k] = z[jv0(b) + k*M/r0], r0 the first radix, jv0 natural or paired (PAIR0).
+// Out: v[b*rl + k] = Z[jvl(b) + k*M/rl], rl the last radix, jvl natural or paired (PAIRL).
 // sbuf0 is the transform's exchange region (already offset by the slot when W > 1);
-// buf_stride is the distance in float2 between the two exchange buffers; parity selects
-// the buffer of the next exchange and is updated.
+// buf_stride is the distance in float2 between the two exchange buffers; parity selects the
+// buffer of the next exchange and is updated.
+template <class P, int W, bool PAIR0, bool PAIRL, class Cta>
+MA_HD void fft_run(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
+                   const float2* __restrict__ twM, Cta& cta) {
+    constexpr int r0 = P::radix(0), NB0 = P::R / r0;
+    static_assert(!(PAIRL && P::NS < 2), "a paired last stage needs at least two stages");
+#pragma unroll
+    for (int b = 0; b < NB0; ++b) Bfly<r0>::run(v + b * r0);  // stage 0: no twiddles
+    StageChain<P, W, 1, PAIR0, PAIRL, Cta>::run(v, t, sbuf0, buf_stride, parity, twM, cta);
+}
+
+// Complex forward FFT of length M in natural order.  In: v[q] = z[t + q*T].
+// Out: v[q] = Z[t + q*T].
 template <int M, int W, class Cta>
 MA_HD void fft_forward_regs(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
                             const float2* __restrict__ twM, Cta& cta) {
     using P = FftPlan<M>;
     constexpr int R = P::R;
-    Bfly<R>::run(v);  // stage 0: radix R, no twiddles
-    StageChain<M, W, 1, Cta>::run(v, t, sbuf0, buf_stride, parity, twM, cta);
+    fft_run<P, W, false, false, Cta>(v, t, sbuf0, buf_stride, parity, twM, cta);
     // After the last stage, element (b, k) of the flat array is Z[t + (b + k*NB)*T].
     constexpr int rl = P::radix(P::NS - 1), NB = R / rl;
     if constexpr (NB > 1) {

@@ -75,6 +75,64 @@ MA_HD void herm_pre(float2 a, float2 b, float2 w, float2& zk, float2& zm) {
     zm = make_float2(xe.x + xo.y, -(xe.y - xo.x));
 }
 
+// exp(-2 pi i k / R2) for R2 in {4, 8, 16} and 0 <= k < R2/2; folds to immediates once the
+// caller's loop over k is unrolled.
+template <int R2>
+MA_HD float2 root_const(int k) {
+    constexpr float kS = 0.70710678118654752440f, kC1 = 0.92387953251128675613f, kS1 = 0.38268343236508977173f;
+    switch (k * (16 / R2)) {
+        case 0: return make_float2(1.f, 0.f);
+        case 1: return make_float2(kC1, -kS1);
+        case 2: return make_float2(kS, -kS);
+        case 3: return make_float2(kS1, -kC1);
+        case 4: return make_float2(0.f, -1.f);
+        case 5: return make_float2(-kS1, -kC1);
+        case 6: return make_float2(-kS, -kS);
+        default: return make_float2(-kC1, -kS1);
+    }
+}
+
+// Stores X[k] = xk and X[M-k] = xm of frame g in the requested layout (plus magnitudes).
+template <int M>
+MA_HD void r2c_store_pair(const R2CParams& p, int64_t g, int64_t half_off, int k, float2 xk, float2 xm) {
+    constexpr int N = 2 * M;
+    (void)N;
+    const int km = M - k;
+    if (p.layout == LAYOUT_HALF_INTERLEAVED) {
+        float2* o = reinterpret_cast<float2*>(p.out_a) + half_off;
+        o[k] = xk;
+        o[km] = xm;
+    } else if (p.layout == LAYOUT_HALF_PACKED) {
+        float2* o = reinterpret_cast<float2*>(p.out_a) + half_off;
+        if (k == 0) {
+            o[0] = make_float2(xk.x, xm.x);
+        } else {
+            o[k] = xk;
+            o[km] = xm;
+        }
+    } else {
+        float* re = p.out_a + g * (int64_t)N;
+        float* im = p.out_b + g * (int64_t)N;
+        re[k] = xk.x;
+        im[k] = xk.y;
+        re[km] = xm.x;
+        im[km] = xm.y;
+        if (k > 0) {  // conjugate mirror, bins M+1 .. N-1
+            re[N - k] = xk.x;
+            im[N - k] = -xk.y;
+            if (km < M) {
+                re[N - km] = xm.x;
+                im[N - km] = -xm.y;
+            }
+        }
+    }
+    if (p.mag != nullptr) {
+        float* mg = p.mag + g * (int64_t)(M + 1);
+        mg[k] = mag_value(xk, p.mag_kind, p.db_scale);
+        mg[km] = mag_value(xm, p.mag_kind, p.db_scale);
+    }
+}
+
 // ALIGNED: every frame start is 8-byte aligned and no zero padding is requested, so
 // sample pairs are fetched with one float2 load.  Otherwise scalar guarded loads.
 template <int M, bool ALIGNED, class Cta>
@@ -130,58 +188,60 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
             }
         }
 
-        fft_forward_regs<M, 1, Cta>(v, t, sbuf0, S::BUF_STRIDE, parity, p.twM, cta);
-
-        // exchange for the Hermitian post-process
-        float2* sb = sbuf0 + parity * S::BUF_STRIDE;
-        parity ^= 1;
-#pragma unroll
-        for (int q = 0; q < R; ++q) sb[saddr<1>(t + q * T)] = v[q];
-        cta.sync();
-
         const int64_t half_off = s * p.out_signal_stride + f * p.out_frame_stride;
+        if constexpr (plan_pairable<M>()) {
+            // Last stage with paired butterflies: bins k and M-k end up in the same thread,
+            // so the Hermitian post-process needs no exchange.
+            fft_run<P, 1, false, true, Cta>(v, t, sbuf0, S::BUF_STRIDE, parity, p.twM, cta);
+            constexpr int rl = P::radix(P::NS - 1), NBL = R / rl, NL = M / rl;
 #pragma unroll
-        for (int q = 0; q <= R / 2; ++q) {
-            const int k = t + q * T;
-            if (k > M / 2 || !active) continue;
-            const float2 a = sb[saddr<1>(k)];
-            const float2 b = sb[saddr<1>((M - k) & (M - 1))];
-            const float2 w = MA_LDG(p.twN + k);
-            float2 xk, xm;
-            herm_post(a, b, w, xk, xm);
-            const int km = M - k;
-            if (p.layout == LAYOUT_HALF_INTERLEAVED) {
-                float2* o = reinterpret_cast<float2*>(p.out_a) + half_off;
-                o[k] = xk;
-                o[km] = xm;
-            } else if (p.layout == LAYOUT_HALF_PACKED) {
-                float2* o = reinterpret_cast<float2*>(p.out_a) + half_off;
-                if (k == 0) {
-                    o[0] = make_float2(xk.x, xm.x);
+            for (int c = 0; c < NBL / 2; ++c) {
+                const float2* A = v + (2 * c) * rl;
+                const float2* Bf = v + (2 * c + 1) * rl;
+                const int j = c * T + t;
+                if (j != 0) {
+                    const float2 wj = MA_LDG(p.twN + j);
+#pragma unroll
+                    for (int k = 0; k < rl; ++k) {
+                        float2 xk, xm;
+                        herm_post(A[k], Bf[rl - 1 - k], cmul(wj, root_const<2 * rl>(k)), xk, xm);
+                        if (active) r2c_store_pair<M>(p, g, half_off, j + k * NL, xk, xm);
+                    }
                 } else {
-                    o[k] = xk;
-                    o[km] = xm;
-                }
-            } else {
-                float* re = p.out_a + g * (int64_t)N;
-                float* im = p.out_b + g * (int64_t)N;
-                re[k] = xk.x;
-                im[k] = xk.y;
-                re[km] = xm.x;
-                im[km] = xm.y;
-                if (k > 0) {  // conjugate mirror, bins M+1 .. N-1
-                    re[N - k] = xk.x;
-                    im[N - k] = -xk.y;
-                    if (km < M) {
-                        re[N - km] = xm.x;
-                        im[N - km] = -xm.y;
+                    // butterfly 0 pairs with itself (bins k*NL and M - k*NL) ...
+#pragma unroll
+                    for (int k = 0; k <= rl / 2; ++k) {
+                        float2 xk, xm;
+                        herm_post(A[k], A[(rl - k) % rl], root_const<2 * rl>(k), xk, xm);
+                        if (active) r2c_store_pair<M>(p, g, half_off, k * NL, xk, xm);
+                    }
+                    // ... and so does butterfly NL/2 (bins NL/2 + k*NL).
+                    const float2 wq = MA_LDG(p.twN + NL / 2);
+#pragma unroll
+                    for (int k = 0; k < rl / 2; ++k) {
+                        float2 xk, xm;
+                        herm_post(Bf[k], Bf[rl - 1 - k], cmul(wq, root_const<2 * rl>(k)), xk, xm);
+                        if (active) r2c_store_pair<M>(p, g, half_off, NL / 2 + k * NL, xk, xm);
                     }
                 }
             }
-            if (p.mag != nullptr) {
-                float* mg = p.mag + g * (int64_t)(M + 1);
-                mg[k] = mag_value(xk, p.mag_kind, p.db_scale);
-                mg[km] = mag_value(xm, p.mag_kind, p.db_scale);
+        } else {
+            fft_forward_regs<M, 1, Cta>(v, t, sbuf0, S::BUF_STRIDE, parity, p.twM, cta);
+            // exchange for the Hermitian post-process
+            float2* sb = sbuf0 + parity * S::BUF_STRIDE;
+            parity ^= 1;
+#pragma unroll
+            for (int q = 0; q < R; ++q) sb[saddr<1>(t + q * T)] = v[q];
+            cta.sync();
+#pragma unroll
+            for (int q = 0; q <= R / 2; ++q) {
+                const int k = t + q * T;
+                if (k > M / 2 || !active) continue;
+                const float2 a = sb[saddr<1>(k)];
+                const float2 b = sb[saddr<1>((M - k) & (M - 1))];
+                float2 xk, xm;
+                herm_post(a, b, MA_LDG(p.twN + k), xk, xm);
+                r2c_store_pair<M>(p, g, half_off, k, xk, xm);
             }
         }
     }
@@ -205,6 +265,7 @@ struct C2RParams {
     int32_t n_partials;         // HALF_PACKED input: number of partial spectra to sum (>= 1)
     int64_t partial_stride;     // float2 units between partial spectra
     float* tail;                // streaming convolution step: per-signal overlap tail (N/2 floats)
+    const float* norm_mid;      // iSTFT: clamped window sums of the interior, indexed by position mod hop
     const float2* twM;
     const float2* twN;
 };
@@ -271,24 +332,68 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
                      float2* sbuf0, int buf_stride, int& parity, float2* v, Cta& cta) {
     using P = FftPlan<M>;
     constexpr int R = P::R, T = P::T;
-    float2* sb = sbuf0 + parity * buf_stride;
-    parity ^= 1;
+    if constexpr (plan_pairable<M>()) {
+        // First stage with paired butterflies (reversed radix order): the thread that loads
+        // X[i] and X[M-i] also consumes both Z[i] and Z[M-i]; no exchange for the pre-process.
+        using PR = FftPlanRev<M>;
+        constexpr int r0 = PR::radix(0), NB0 = R / r0, N0 = M / r0;
+        const float2 zero = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int q = 0; q <= R / 2; ++q) {
-        const int k = t + q * T;
-        if (k > M / 2) continue;
-        float2 a = make_float2(0.f, 0.f), b = a;
-        if (active) c2r_load_pair(p, s, f, g, k, M, a, b);
-        const float2 w = MA_LDG(p.twN + k);
-        float2 zk, zm;
-        herm_pre(a, b, w, zk, zm);
-        sb[saddr<1>(k)] = make_float2(zk.y, zk.x);
-        if (k > 0) sb[saddr<1>(M - k)] = make_float2(zm.y, zm.x);
+        for (int c = 0; c < NB0 / 2; ++c) {
+            float2* A = v + (2 * c) * r0;
+            float2* Bf = v + (2 * c + 1) * r0;
+            const int j = c * T + t;
+            if (j != 0) {
+                const float2 wj = MA_LDG(p.twN + j);
+#pragma unroll
+                for (int k = 0; k < r0; ++k) {
+                    float2 a = zero, b = zero, zk, zm;
+                    if (active) c2r_load_pair(p, s, f, g, j + k * N0, M, a, b);
+                    herm_pre(a, b, cmul(wj, root_const<2 * r0>(k)), zk, zm);
+                    A[k] = make_float2(zk.y, zk.x);
+                    Bf[r0 - 1 - k] = make_float2(zm.y, zm.x);
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k <= r0 / 2; ++k) {
+                    float2 a = zero, b = zero, zk, zm;
+                    if (active) c2r_load_pair(p, s, f, g, k * N0, M, a, b);
+                    herm_pre(a, b, root_const<2 * r0>(k), zk, zm);
+                    A[k] = make_float2(zk.y, zk.x);
+                    if (k > 0) A[r0 - k] = make_float2(zm.y, zm.x);
+                }
+                const float2 wq = MA_LDG(p.twN + N0 / 2);
+#pragma unroll
+                for (int k = 0; k < r0 / 2; ++k) {
+                    float2 a = zero, b = zero, zk, zm;
+                    if (active) c2r_load_pair(p, s, f, g, N0 / 2 + k * N0, M, a, b);
+                    herm_pre(a, b, cmul(wq, root_const<2 * r0>(k)), zk, zm);
+                    Bf[k] = make_float2(zk.y, zk.x);
+                    Bf[r0 - 1 - k] = make_float2(zm.y, zm.x);
+                }
+            }
+        }
+        fft_run<PR, 1, true, false, Cta>(v, t, sbuf0, buf_stride, parity, p.twM, cta);
+    } else {
+        float2* sb = sbuf0 + parity * buf_stride;
+        parity ^= 1;
+#pragma unroll
+        for (int q = 0; q <= R / 2; ++q) {
+            const int k = t + q * T;
+            if (k > M / 2) continue;
+            float2 a = make_float2(0.f, 0.f), b = a;
+            if (active) c2r_load_pair(p, s, f, g, k, M, a, b);
+            const float2 w = MA_LDG(p.twN + k);
+            float2 zk, zm;
+            herm_pre(a, b, w, zk, zm);
+            sb[saddr<1>(k)] = make_float2(zk.y, zk.x);
+            if (k > 0) sb[saddr<1>(M - k)] = make_float2(zm.y, zm.x);
+        }
+        cta.sync();
+#pragma unroll
+        for (int q = 0; q < R; ++q) v[q] = sb[saddr<1>(t + q * T)];
+        fft_forward_regs<M, 1, Cta>(v, t, sbuf0, buf_stride, parity, p.twM, cta);
     }
-    cta.sync();
-#pragma unroll
-    for (int q = 0; q < R; ++q) v[q] = sb[saddr<1>(t + q * T)];
-    fft_forward_regs<M, 1, Cta>(v, t, sbuf0, buf_stride, parity, p.twM, cta);
 }
 
 // Plain batched inverse: out[g][2n], out[g][2n+1].
@@ -438,7 +543,12 @@ MA_HD void istft_body(const C2RParams& p, Cta& cta, float2* smem) {
                 ring[rp] = 0.f;
                 if (emit && o < p.out_len) {
                     float r = acc;
-                    if (normalise) r = acc / window_sum_at(p.window, o, N, hop, F, p.floor);
+                    if (normalise) {
+                        // interior positions (all overlapping frames exist) share hop distinct sums
+                        const bool mid = o >= (int64_t)(N - hop) && o < F * (int64_t)hop;
+                        const float ws = mid ? MA_LDG(p.norm_mid + i) : window_sum_at(p.window, o, N, hop, F, p.floor);
+                        r = acc / ws;
+                    }
                     p.out[s * p.out_signal_stride + o] = r;
                 }
             }

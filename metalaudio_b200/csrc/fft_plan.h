@@ -1,5 +1,7 @@
 // FFT plan object and the internal launch entry points other translation units use.
 #pragma once
+#include <vector>
+
 #include "fft_kernels.cuh"
 #include "ma_internal.h"
 
@@ -12,6 +14,9 @@ struct ma_fft_plan {
     float* d_window = nullptr;  // N floats or nullptr
     float2* d_twM = nullptr;    // small path: exp(-2 pi i j/M), j < M
     float2* d_twN = nullptr;    // small path: exp(-2 pi i k/N), k <= M/2
+    std::vector<float> h_window;  // host copy of the window (empty: none)
+    float* d_norm = nullptr;    // iSTFT interior normaliser, hop floats (see launch_istft_small)
+    float norm_floor = -1.0f;   // floor the table was built for
     // large path (N = n1 * n2): see fft_large.cu
     int n1 = 0, n2 = 0;
     ma_fft_plan* sub_cols = nullptr;  // tables for the n2-point real transforms

@@ -14,19 +14,19 @@ struct DevCta {
 extern __shared__ float4 ma_dyn_smem[];
 
 template <int M, bool ALIGNED>
-__global__ void __launch_bounds__(CtaShape<M>::THREADS) r2c_kernel(const R2CParams p) {
+__global__ void __launch_bounds__(CtaShape<M>::THREADS, 512 / CtaShape<M>::THREADS) r2c_kernel(const R2CParams p) {
     DevCta cta;
     r2c_body<M, ALIGNED, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
 }
 
 template <int M>
-__global__ void __launch_bounds__(CtaShape<M>::THREADS) c2r_kernel(const C2RParams p) {
+__global__ void __launch_bounds__(CtaShape<M>::THREADS, 512 / CtaShape<M>::THREADS) c2r_kernel(const C2RParams p) {
     DevCta cta;
     c2r_body<M, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
 }
 
 template <int M>
-__global__ void __launch_bounds__(FftPlan<M>::T) istft_kernel(const C2RParams p) {
+__global__ void __launch_bounds__(FftPlan<M>::T, (512 / FftPlan<M>::T) > 16 ? 16 : (512 / FftPlan<M>::T)) istft_kernel(const C2RParams p) {
     DevCta cta;
     istft_body<M, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
 }
@@ -124,10 +124,27 @@ static ma_status launch_istft_t(ma_fft_plan* plan, C2RParams& p) {
     return after_launch(ctx);
 }
 
+// Rebuilds the interior normaliser table (host_tables.h) when the floor changes.
+static ma_status update_norm_table(ma_fft_plan* plan, int hop, float floor) {
+    if (plan->norm_floor == floor) return MA_OK;
+    const std::vector<float> tab =
+        make_norm_table(plan->h_window.empty() ? nullptr : plan->h_window.data(), plan->n, hop, floor);
+    MA_CUDA(cudaMemcpyAsync(plan->d_norm, tab.data(), sizeof(float) * (size_t)hop, cudaMemcpyHostToDevice,
+                            plan->ctx->stream));
+    MA_CUDA(cudaStreamSynchronize(plan->ctx->stream));
+    plan->norm_floor = floor;
+    return MA_OK;
+}
+
 ma_status launch_istft_small(ma_fft_plan* plan, C2RParams p) {
     p.twM = plan->d_twM;
     p.twN = plan->d_twN;
     if (p.n_signals <= 0 || p.frames_per_signal <= 0) return MA_OK;
+    if (!(p.window == nullptr && p.floor < 0.f)) {
+        if (p.hop != plan->hop) return MA_ERR_INVALID_ARGUMENT;
+        MA_TRY(update_norm_table(plan, p.hop, p.floor));
+    }
+    p.norm_mid = plan->d_norm;
     ma_status st = MA_ERR_UNSUPPORTED;
 #define RUN(MM) st = launch_istft_t<MM>(plan, p);
     MA_DISPATCH_M(plan->m, RUN)

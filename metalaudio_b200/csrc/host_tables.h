@@ -20,6 +20,26 @@ inline std::vector<float2> make_twiddles(int64_t len, int64_t count) {
     return tw;
 }
 
+// Interior window-sum table of the iSTFT normaliser: for an output position with every
+// overlapping frame present the sum of squared window depends only on the position modulo
+// hop.  Accumulated in float32 in increasing frame order (largest window offset first), as the
+// reference's sequential loop adds them, denormal sums zeroed, floor applied
+// (Sources/MetalDSP/STFT.swift:474-479, :513-520).  window == nullptr means all ones.
+inline std::vector<float> make_norm_table(const float* window, int n, int hop, float floor) {
+    std::vector<float> tab((size_t)hop);
+    for (int r = 0; r < hop; ++r) {
+        float acc = 0.f;
+        const int top = r + ((n - 1 - r) / hop) * hop;
+        for (int off = top; off >= 0; off -= hop) {
+            const float w = window ? window[off] : 1.0f;
+            acc += w * w;
+        }
+        if (acc < 1.17549435e-38f) acc = 0.f;
+        tab[(size_t)r] = acc > floor ? acc : floor;
+    }
+    return tab;
+}
+
 }  // namespace ma
 
 // Compile-time dispatch over the supported in-shared-memory complex lengths.

@@ -77,6 +77,8 @@ int emul_istft(int n, int hop, const float* in_a, const float* in_b, long long i
     p.frames_per_signal = frames; p.n_signals = n_signals; p.layout = layout; p.hop = hop;
     p.window = window; p.out = out; p.out_signal_stride = out_signal_stride; p.out_len = out_len;
     p.floor = floor; p.chunks_per_signal = chunks_per_signal;
+    auto norm = make_norm_table(window, n, hop, floor);
+    p.norm_mid = norm.data();
     p.twM = twM.data(); p.twN = twN.data();
     int rc = -1;
 #define RUN(MM)                                                                                  \
