@@ -60,9 +60,11 @@ ma_status ma_fft_plan_create(ma_context* ctx, int32_t n, const float* window, in
         if (e != cudaSuccess) st = cuda_fail(e);
     }
     if (st == MA_OK && !p->large) {
-        auto twM = make_twiddles(p->m, p->m);
+        auto twM = make_stage_tables_for(p->m, false);
+        auto twI = make_stage_tables_for(p->m, plan_pairable_rt(p->m));
         auto twN = make_twiddles(n, p->m / 2 + 1);
         st = upload(ctx, twM.data(), twM.size() * sizeof(float2), (void**)&p->d_twM);
+        if (st == MA_OK) st = upload(ctx, twI.data(), twI.size() * sizeof(float2), (void**)&p->d_twInv);
         if (st == MA_OK) st = upload(ctx, twN.data(), twN.size() * sizeof(float2), (void**)&p->d_twN);
     }
     if (st == MA_OK && p->large) st = large_plan_init(p);
@@ -83,6 +85,7 @@ ma_status ma_fft_plan_destroy(ma_fft_plan* plan) {
     large_plan_destroy(plan);
     if (plan->d_window) (void)cudaFree(plan->d_window);
     if (plan->d_twM) (void)cudaFree(plan->d_twM);
+    if (plan->d_twInv) (void)cudaFree(plan->d_twInv);
     if (plan->d_twN) (void)cudaFree(plan->d_twN);
     if (plan->d_norm) (void)cudaFree(plan->d_norm);
     (void)cudaGetLastError();

@@ -204,29 +204,26 @@ constexpr __host__ __device__ int smem_elems_per_fft() {
 }
 
 // ---------------------------------------------------------------- twiddled stages
-// Twiddles: twM[j] = exp(-2*pi*i*j/M), j in [0, M).  For a stage of radix r the thread
-// needs w^k, k = 1..r-1, with w = twM[base]; w^1..w^4 (w^1..w^3 for r <= 4) are loaded
-// exactly, the rest are products of at most two exact values times one product.
-template <int r>
-MA_HD void load_twiddles(float2* w, const float2* __restrict__ twM, int base, int M) {
-    // indices base*k stay below M because base < M/r.
-    (void)M;
-    if constexpr (r >= 2) w[1] = MA_LDG(twM + base);
-    if constexpr (r >= 4) {
-        w[2] = MA_LDG(twM + 2 * base);
-        w[3] = MA_LDG(twM + 3 * base);
-    }
-    if constexpr (r >= 8) {
-        w[4] = MA_LDG(twM + 4 * base);
-        w[5] = cmul(w[1], w[4]);
-        w[6] = cmul(w[2], w[4]);
-        w[7] = cmul(w[3], w[4]);
-    }
-    if constexpr (r >= 16) {
-        w[8] = cmul(w[4], w[4]);
+// Stage twiddles live in one table per plan, stage after stage (stage 0 has none); inside a
+// stage the layout is [k-1][j], j = jv % Ns, value exp(-2*pi*i*j*k/(Ns*r)).  Lanes run along
+// j, so every load is contiguous across a warp (a gather from a single M-point table costs an
+// L1 wavefront per distinct line), and all r-1 twiddles are exact table values.
+template <class P>
+constexpr __host__ __device__ int stage_tw_offset(int s) {
+    int off = 0;
+    for (int i = 1; i < s; ++i) off += P::ns_before(i) * (P::radix(i) - 1);
+    return off;
+}
+template <class P>
+constexpr __host__ __device__ int stage_tw_total() {
+    return stage_tw_offset<P>(P::NS);
+}
+
+template <class P, int S>
+MA_HD void load_stage_twiddles(float2* w, const float2* __restrict__ tws, int j) {
+    constexpr int r = P::radix(S), Ns = P::ns_before(S), off = stage_tw_offset<P>(S);
 #pragma unroll
-        for (int k = 1; k < 8; ++k) w[8 + k] = cmul(w[k], w[8]);
-    }
+    for (int k = 1; k < r; ++k) w[k] = MA_LDG(tws + off + (k - 1) * Ns + j);
 }
 
 // Which butterfly of a stage a thread's b-th sub-butterfly is.  Natural: jv = t + b*T.
@@ -267,7 +264,7 @@ MA_HD void stage_read_compute(float2* v, int t, const float2* sbuf,
 #pragma unroll
         for (int k = 0; k < r; ++k) v[b * r + k] = sbuf[saddr<W>(jv + k * (M / r))];
         float2 w[r];
-        load_twiddles<r>(w, twM, (jv % Ns) * (M / (Ns * r)), M);
+        load_stage_twiddles<P, S>(w, twM, jv % Ns);
 #pragma unroll
         for (int k = 1; k < r; ++k) v[b * r + k] = cmul(v[b * r + k], w[k]);
         Bfly<r>::run(v + b * r);

@@ -31,7 +31,7 @@ struct R2CParams {
     int32_t layout;
     int32_t mag_kind;
     float db_scale;             // 1/reference for MAG_DB
-    const float2* twM;          // exp(-2 pi i j / M), j < M
+    const float2* twM;          // stage twiddle tables of FftPlan<M> (fft_core.cuh layout)
     const float2* twN;          // exp(-2 pi i k / N), k <= M/2
 };
 
@@ -266,7 +266,7 @@ struct C2RParams {
     int64_t partial_stride;     // float2 units between partial spectra
     float* tail;                // streaming convolution step: per-signal overlap tail (N/2 floats)
     const float* norm_mid;      // iSTFT: clamped window sums of the interior, indexed by position mod hop
-    const float2* twM;
+    const float2* twM;          // stage tables: FftPlanRev<M> when plan_pairable<M>(), else FftPlan<M>
     const float2* twN;
 };
 

@@ -33,9 +33,9 @@ struct LargeParams {
     int n, n1, n2;
     int layout, mag_kind;
     float db_scale;
-    const float2* twM2;  // exp(-2 pi i j/M2), j < M2
+    const float2* twM2;  // stage twiddle tables of FftPlan<M2>
     const float2* twN2;  // exp(-2 pi i k/N2), k <= M2/2
-    const float2* tw1;   // exp(-2 pi i j/N1), j < N1
+    const float2* tw1;   // stage twiddle tables of FftPlan<N1>
     const float2* twL;   // exp(-2 pi i j/N),  j < N/2
 };
 
@@ -401,9 +401,15 @@ ma_status large_plan_init(ma_fft_plan* plan) {
     ma_context* ctx = plan->ctx;
     plan->n1 = s.n1;
     plan->n2 = 2 * s.m2;
-    MA_TRY(upload_tw(ctx, s.m2, s.m2, &plan->d_twM));          // column stage twiddles
+    {
+        auto tw = make_stage_tables_for(s.m2, false);  // column stage twiddles
+        MA_CUDA(cudaMalloc((void**)&plan->d_twM, tw.size() * sizeof(float2)));
+        MA_TRY(copy_h2d(ctx, plan->d_twM, tw.data(), tw.size() * sizeof(float2)));
+        auto t1 = make_stage_tables_for(s.n1, false);  // row stage twiddles
+        MA_CUDA(cudaMalloc((void**)&plan->d_tw1, t1.size() * sizeof(float2)));
+        MA_TRY(copy_h2d(ctx, plan->d_tw1, t1.data(), t1.size() * sizeof(float2)));
+    }
     MA_TRY(upload_tw(ctx, 2 * s.m2, s.m2 / 2 + 1, &plan->d_twN)); // column Hermitian twiddles
-    MA_TRY(upload_tw(ctx, s.n1, s.n1, &plan->d_tw1));
     MA_TRY(upload_tw(ctx, plan->n, plan->n / 2, &plan->d_twL));
     // Chunk size: scratch of about 48 MB stays in L2 between the passes.
     const size_t per = (size_t)(s.m2 + 1) * s.n1 * sizeof(float2);

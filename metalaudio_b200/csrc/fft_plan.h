@@ -12,7 +12,8 @@ struct ma_fft_plan {
     int hop = 0;
     bool large = false;         // N > 8192: multi-pass path
     float* d_window = nullptr;  // N floats or nullptr
-    float2* d_twM = nullptr;    // small path: exp(-2 pi i j/M), j < M
+    float2* d_twM = nullptr;    // stage twiddle tables, forward radix order (fft_core.cuh layout)
+    float2* d_twInv = nullptr;  // stage tables the inverse kernels use (reversed order when pairable)
     float2* d_twN = nullptr;    // small path: exp(-2 pi i k/N), k <= M/2
     std::vector<float> h_window;  // host copy of the window (empty: none)
     float* d_norm = nullptr;    // iSTFT interior normaliser, hop floats (see launch_istft_small)

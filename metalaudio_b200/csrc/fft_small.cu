@@ -89,7 +89,7 @@ static ma_status launch_c2r_t(ma_fft_plan* plan, const C2RParams& p) {
 }
 
 ma_status launch_c2r_small(ma_fft_plan* plan, C2RParams p) {
-    p.twM = plan->d_twM;
+    p.twM = plan->d_twInv;
     p.twN = plan->d_twN;
     if (p.n_signals * p.frames_per_signal <= 0) return MA_OK;
     ma_status st = MA_ERR_UNSUPPORTED;
@@ -137,7 +137,7 @@ static ma_status update_norm_table(ma_fft_plan* plan, int hop, float floor) {
 }
 
 ma_status launch_istft_small(ma_fft_plan* plan, C2RParams p) {
-    p.twM = plan->d_twM;
+    p.twM = plan->d_twInv;
     p.twN = plan->d_twN;
     if (p.n_signals <= 0 || p.frames_per_signal <= 0) return MA_OK;
     if (!(p.window == nullptr && p.floor < 0.f)) {

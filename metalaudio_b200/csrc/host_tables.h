@@ -7,6 +7,8 @@
 
 #include <cuda_runtime.h>
 
+#include "fft_core.cuh"
+
 namespace ma {
 
 // exp(-2*pi*i*j/len) for j in [0, count)
@@ -18,6 +20,60 @@ inline std::vector<float2> make_twiddles(int64_t len, int64_t count) {
         tw[(size_t)j] = make_float2((float)std::cos(a), (float)std::sin(a));
     }
     return tw;
+}
+
+// Stage twiddle table of plan P in the layout fft_core.cuh documents.
+template <class P>
+inline std::vector<float2> make_stage_tables() {
+    std::vector<float2> tw((size_t)(stage_tw_total<P>() > 0 ? stage_tw_total<P>() : 1), make_float2(1.f, 0.f));
+    for (int s = 1; s < P::NS; ++s) {
+        const int r = P::radix(s), ns = P::ns_before(s), off = stage_tw_offset<P>(s);
+        for (int k = 1; k < r; ++k)
+            for (int j = 0; j < ns; ++j) {
+                const double a = -2.0 * M_PI * (double)j * (double)k / ((double)ns * (double)r);
+                tw[(size_t)(off + (k - 1) * ns + j)] = make_float2((float)std::cos(a), (float)std::sin(a));
+            }
+    }
+    return tw;
+}
+
+// Stage tables for complex length m: forward radix order (rev = false) or reversed.
+inline std::vector<float2> make_stage_tables_for(int m, bool rev) {
+    std::vector<float2> out;
+#define MA_TW_CASE(MM) out = rev ? make_stage_tables<FftPlanRev<MM>>() : make_stage_tables<FftPlan<MM>>();
+    switch (m) {
+        case 1: MA_TW_CASE(1) break;
+        case 2: MA_TW_CASE(2) break;
+        case 4: MA_TW_CASE(4) break;
+        case 8: MA_TW_CASE(8) break;
+        case 16: MA_TW_CASE(16) break;
+        case 32: MA_TW_CASE(32) break;
+        case 64: MA_TW_CASE(64) break;
+        case 128: MA_TW_CASE(128) break;
+        case 256: MA_TW_CASE(256) break;
+        case 512: MA_TW_CASE(512) break;
+        case 1024: MA_TW_CASE(1024) break;
+        case 2048: MA_TW_CASE(2048) break;
+        case 4096: MA_TW_CASE(4096) break;
+        default: break;
+    }
+#undef MA_TW_CASE
+    return out;
+}
+
+// Runtime form of plan_pairable<M>().
+inline bool plan_pairable_rt(int m) {
+    switch (m) {
+        case 32: return plan_pairable<32>();
+        case 64: return plan_pairable<64>();
+        case 128: return plan_pairable<128>();
+        case 256: return plan_pairable<256>();
+        case 512: return plan_pairable<512>();
+        case 1024: return plan_pairable<1024>();
+        case 2048: return plan_pairable<2048>();
+        case 4096: return plan_pairable<4096>();
+        default: return false;
+    }
 }
 
 // Interior window-sum table of the iSTFT normaliser: for an output position with every

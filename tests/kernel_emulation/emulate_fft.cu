@@ -17,7 +17,7 @@ int emul_r2c(int n, int aligned, const float* in, long long signal_stride, long 
              const float* window, float* out_a, float* out_b, float* mag, long long out_signal_stride,
              long long out_frame_stride, int layout, int mag_kind, float db_scale, int nblocks) {
     const int M = n / 2;
-    auto twM = make_twiddles(M, M);
+    auto twM = make_stage_tables_for(M, false);
     auto twN = make_twiddles(n, M / 2 + 1);
     R2CParams p{};
     p.in = in; p.signal_stride = signal_stride; p.frames_per_signal = frames_per_signal;
@@ -45,7 +45,7 @@ int emul_c2r(int n, const float* in_a, const float* in_b, long long in_signal_st
              long long in_frame_stride, long long frames_per_signal, long long n_signals, int layout,
              float* out, int nblocks) {
     const int M = n / 2;
-    auto twM = make_twiddles(M, M);
+    auto twM = make_stage_tables_for(M, plan_pairable_rt(M));
     auto twN = make_twiddles(n, M / 2 + 1);
     C2RParams p{};
     p.in_a = in_a; p.in_b = in_b; p.in_signal_stride = in_signal_stride; p.in_frame_stride = in_frame_stride;
@@ -70,7 +70,7 @@ int emul_istft(int n, int hop, const float* in_a, const float* in_b, long long i
                const float* window, float floor, float* out, long long out_signal_stride,
                long long out_len, int chunks_per_signal, int nblocks) {
     const int M = n / 2;
-    auto twM = make_twiddles(M, M);
+    auto twM = make_stage_tables_for(M, plan_pairable_rt(M));
     auto twN = make_twiddles(n, M / 2 + 1);
     C2RParams p{};
     p.in_a = in_a; p.in_b = in_b; p.in_signal_stride = in_signal_stride; p.in_frame_stride = in_frame_stride;
