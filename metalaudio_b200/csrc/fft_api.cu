@@ -62,7 +62,7 @@ ma_status ma_fft_plan_create(ma_context* ctx, int32_t n, const float* window, in
     if (st == MA_OK && !p->large) {
         auto twM = make_stage_tables_for(p->m, false);
         auto twI = make_stage_tables_for(p->m, plan_pairable_rt(p->m));
-        auto twN = make_twiddles(n, p->m / 2 + 1);
+        auto twN = make_hermitian_table(p->m);
         st = upload(ctx, twM.data(), twM.size() * sizeof(float2), (void**)&p->d_twM);
         if (st == MA_OK) st = upload(ctx, twI.data(), twI.size() * sizeof(float2), (void**)&p->d_twInv);
         if (st == MA_OK) st = upload(ctx, twN.data(), twN.size() * sizeof(float2), (void**)&p->d_twN);

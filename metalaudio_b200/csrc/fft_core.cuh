@@ -17,9 +17,17 @@
 #define MA_HD __host__ __device__ __forceinline__
 
 #ifdef __CUDA_ARCH__
+#include <cuda_pipeline.h>
 #define MA_LDG(p) __ldg(p)
+// Asynchronous 8-byte global -> shared copy (LDGSTS): no registers, no stall until the wait.
+#define MA_ASYNC_COPY8(dst, src) __pipeline_memcpy_async((dst), (src), 8)
+#define MA_ASYNC_COMMIT() __pipeline_commit()
+#define MA_ASYNC_WAIT_ALL() __pipeline_wait_prior(0)
 #else
 #define MA_LDG(p) (*(p))
+#define MA_ASYNC_COPY8(dst, src) (*(dst) = *(src))
+#define MA_ASYNC_COMMIT() ((void)0)
+#define MA_ASYNC_WAIT_ALL() ((void)0)
 #endif
 
 namespace ma {
@@ -242,15 +250,41 @@ MA_HD int stage_jv(int t, int b, int nbfly) {
     }
 }
 
+// Padded address of element o0 + k*Ns as base(o0) + offset(k) with a compile-time offset, so
+// that the r accesses of a butterfly need one address computation.  Valid because
+// (o0 + k*Ns) >> 4 splits exactly in the three cases below (o0's low bits never carry).
+template <int W, int Ns, int r>
+struct ExchangeAddr {
+    static constexpr bool kSplit = (W != 1) || (Ns % 16 == 0) || (Ns == 1 && (r == 16 || r == 8)) ||
+                                   (Ns == 8 && r >= 2);
+    static MA_HD int base(int o0) {
+        if constexpr (W != 1) return o0 * W;
+        else return o0 + (o0 >> 4);
+    }
+    static constexpr __host__ __device__ int offset(int k) {
+        if (W != 1) return k * Ns * W;
+        if (Ns % 16 == 0) return k * Ns + k * (Ns / 16);
+        if (Ns == 1) return k;           // o0 = jv*r, r in {8, 16}: k < r never reaches bit 4 ... of o0's group
+        return k * 8 + (k >> 1);         // Ns == 8: o0 % 16 < 8, so (o0%16 + 8k) >> 4 == k >> 1
+    }
+};
+
 template <class P, int W, int S, bool PAIRED>
 MA_HD void stage_write(const float2* v, int t, float2* sbuf) {
     constexpr int M = P::M, r = P::radix(S), Ns = P::ns_before(S), NB = P::R / r;
+    using A = ExchangeAddr<W, Ns, r>;
 #pragma unroll
     for (int b = 0; b < NB; ++b) {
         const int jv = stage_jv<P, PAIRED>(t, b, M / r);
         const int o0 = (jv / Ns) * (Ns * r) + (jv % Ns);
+        if constexpr (A::kSplit) {
+            float2* dst = sbuf + A::base(o0);
 #pragma unroll
-        for (int k = 0; k < r; ++k) sbuf[saddr<W>(o0 + k * Ns)] = v[b * r + k];
+            for (int k = 0; k < r; ++k) dst[A::offset(k)] = v[b * r + k];
+        } else {
+#pragma unroll
+            for (int k = 0; k < r; ++k) sbuf[saddr<W>(o0 + k * Ns)] = v[b * r + k];
+        }
     }
 }
 
@@ -258,11 +292,19 @@ template <class P, int W, int S, bool PAIRED>
 MA_HD void stage_read_compute(float2* v, int t, const float2* sbuf,
                               const float2* __restrict__ twM) {
     constexpr int M = P::M, r = P::radix(S), Ns = P::ns_before(S), NB = P::R / r;
+    constexpr int stride = M / r;
+    using A = ExchangeAddr<W, stride, r>;
 #pragma unroll
     for (int b = 0; b < NB; ++b) {
         const int jv = stage_jv<P, PAIRED>(t, b, M / r);
+        if constexpr (W != 1 || stride % 16 == 0) {
+            const float2* src = sbuf + A::base(jv);
 #pragma unroll
-        for (int k = 0; k < r; ++k) v[b * r + k] = sbuf[saddr<W>(jv + k * (M / r))];
+            for (int k = 0; k < r; ++k) v[b * r + k] = src[A::offset(k)];
+        } else {
+#pragma unroll
+            for (int k = 0; k < r; ++k) v[b * r + k] = sbuf[saddr<W>(jv + k * stride)];
+        }
         float2 w[r];
         load_stage_twiddles<P, S>(w, twM, jv % Ns);
 #pragma unroll

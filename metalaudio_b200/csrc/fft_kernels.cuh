@@ -32,7 +32,8 @@ struct R2CParams {
     int32_t mag_kind;
     float db_scale;             // 1/reference for MAG_DB
     const float2* twM;          // stage twiddle tables of FftPlan<M> (fft_core.cuh layout)
-    const float2* twN;          // exp(-2 pi i k / N), k <= M/2
+    const float2* twN;          // Hermitian-step twiddles exp(-2 pi i k / N): [k], k <= M/2, or for
+                                // plan_pairable<M>() the table [k][j] = W_N^(j + k*NL), j <= NL/2
 };
 
 MA_HD float mag_value(float2 x, int kind, float db_scale) {
@@ -93,16 +94,19 @@ MA_HD float2 root_const(int k) {
 }
 
 // Stores X[k] = xk and X[M-k] = xm of frame g in the requested layout (plus magnitudes).
-template <int M>
+// LAYOUT >= 0 fixes the layout at compile time (-1: read p.layout); MAGK >= 0 fixes the
+// magnitude kind, -1 means no magnitude output, -2 reads p.mag / p.mag_kind.
+template <int M, int LAYOUT, int MAGK>
 MA_HD void r2c_store_pair(const R2CParams& p, int64_t g, int64_t half_off, int k, float2 xk, float2 xm) {
     constexpr int N = 2 * M;
     (void)N;
+    const int layout = LAYOUT >= 0 ? LAYOUT : p.layout;
     const int km = M - k;
-    if (p.layout == LAYOUT_HALF_INTERLEAVED) {
+    if (layout == LAYOUT_HALF_INTERLEAVED) {
         float2* o = reinterpret_cast<float2*>(p.out_a) + half_off;
         o[k] = xk;
         o[km] = xm;
-    } else if (p.layout == LAYOUT_HALF_PACKED) {
+    } else if (layout == LAYOUT_HALF_PACKED) {
         float2* o = reinterpret_cast<float2*>(p.out_a) + half_off;
         if (k == 0) {
             o[0] = make_float2(xk.x, xm.x);
@@ -126,16 +130,18 @@ MA_HD void r2c_store_pair(const R2CParams& p, int64_t g, int64_t half_off, int k
             }
         }
     }
-    if (p.mag != nullptr) {
+    if (MAGK == -1) return;
+    if (MAGK >= 0 || p.mag != nullptr) {
+        const int kind = MAGK >= 0 ? MAGK : p.mag_kind;
         float* mg = p.mag + g * (int64_t)(M + 1);
-        mg[k] = mag_value(xk, p.mag_kind, p.db_scale);
-        mg[km] = mag_value(xm, p.mag_kind, p.db_scale);
+        mg[k] = mag_value(xk, kind, p.db_scale);
+        mg[km] = mag_value(xm, kind, p.db_scale);
     }
 }
 
 // ALIGNED: every frame start is 8-byte aligned and no zero padding is requested, so
 // sample pairs are fetched with one float2 load.  Otherwise scalar guarded loads.
-template <int M, bool ALIGNED, class Cta>
+template <int M, bool ALIGNED, int LAYOUT, int MAGK, class Cta>
 MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
     using P = FftPlan<M>;
     using S = CtaShape<M>;
@@ -158,14 +164,23 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
         for (int q = 0; q < R; ++q) wreg[q] = make_float2(1.0f, 1.0f);
     }
 
+    // (signal, frame) of this thread's first frame by one division; later frames advance by the
+    // grid stride without dividing.
+    const int64_t stride_frames = (int64_t)cta.nblocks() * S::FPC;
+    int64_t g = (int64_t)cta.bid() * S::FPC + slot;
+    int64_t s = g / p.frames_per_signal;
+    int64_t f = g - s * p.frames_per_signal;
+    const int64_t ds = stride_frames / p.frames_per_signal;
+    const int64_t df = stride_frames - ds * p.frames_per_signal;
     for (int64_t base = (int64_t)cta.bid() * S::FPC; base < p.total_frames;
-         base += (int64_t)cta.nblocks() * S::FPC) {
-        const int64_t g = base + slot;
-        const bool active = g < p.total_frames;
-        const int64_t s = active ? g / p.frames_per_signal : 0;
-        const int64_t f = active ? g - s * p.frames_per_signal : 0;
+         base += stride_frames, g += stride_frames, s += ds, f += df) {
+        if (f >= p.frames_per_signal) {
+            f -= p.frames_per_signal;
+            ++s;
+        }
+        const bool active = S::FPC == 1 ? true : g < p.total_frames;
         const int64_t start = f * (int64_t)p.hop;
-        const float* src = p.in + s * p.signal_stride + start;
+        const float* src = p.in + (active ? s * p.signal_stride + start : 0);
 
         float2 v[R];
         if (ALIGNED) {
@@ -200,12 +215,11 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
                 const float2* Bf = v + (2 * c + 1) * rl;
                 const int j = c * T + t;
                 if (j != 0) {
-                    const float2 wj = MA_LDG(p.twN + j);
 #pragma unroll
                     for (int k = 0; k < rl; ++k) {
                         float2 xk, xm;
-                        herm_post(A[k], Bf[rl - 1 - k], cmul(wj, root_const<2 * rl>(k)), xk, xm);
-                        if (active) r2c_store_pair<M>(p, g, half_off, j + k * NL, xk, xm);
+                        herm_post(A[k], Bf[rl - 1 - k], MA_LDG(p.twN + k * (NL / 2 + 1) + j), xk, xm);
+                        if (active) r2c_store_pair<M, LAYOUT, MAGK>(p, g, half_off, j + k * NL, xk, xm);
                     }
                 } else {
                     // butterfly 0 pairs with itself (bins k*NL and M - k*NL) ...
@@ -213,15 +227,14 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
                     for (int k = 0; k <= rl / 2; ++k) {
                         float2 xk, xm;
                         herm_post(A[k], A[(rl - k) % rl], root_const<2 * rl>(k), xk, xm);
-                        if (active) r2c_store_pair<M>(p, g, half_off, k * NL, xk, xm);
+                        if (active) r2c_store_pair<M, LAYOUT, MAGK>(p, g, half_off, k * NL, xk, xm);
                     }
                     // ... and so does butterfly NL/2 (bins NL/2 + k*NL).
-                    const float2 wq = MA_LDG(p.twN + NL / 2);
 #pragma unroll
                     for (int k = 0; k < rl / 2; ++k) {
                         float2 xk, xm;
-                        herm_post(Bf[k], Bf[rl - 1 - k], cmul(wq, root_const<2 * rl>(k)), xk, xm);
-                        if (active) r2c_store_pair<M>(p, g, half_off, NL / 2 + k * NL, xk, xm);
+                        herm_post(Bf[k], Bf[rl - 1 - k], MA_LDG(p.twN + k * (NL / 2 + 1) + NL / 2), xk, xm);
+                        if (active) r2c_store_pair<M, LAYOUT, MAGK>(p, g, half_off, NL / 2 + k * NL, xk, xm);
                     }
                 }
             }
@@ -241,7 +254,7 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
                 const float2 b = sb[saddr<1>((M - k) & (M - 1))];
                 float2 xk, xm;
                 herm_post(a, b, MA_LDG(p.twN + k), xk, xm);
-                r2c_store_pair<M>(p, g, half_off, k, xk, xm);
+                r2c_store_pair<M, LAYOUT, MAGK>(p, g, half_off, k, xk, xm);
             }
         }
     }
@@ -344,12 +357,11 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
             float2* Bf = v + (2 * c + 1) * r0;
             const int j = c * T + t;
             if (j != 0) {
-                const float2 wj = MA_LDG(p.twN + j);
 #pragma unroll
                 for (int k = 0; k < r0; ++k) {
                     float2 a = zero, b = zero, zk, zm;
                     if (active) c2r_load_pair(p, s, f, g, j + k * N0, M, a, b);
-                    herm_pre(a, b, cmul(wj, root_const<2 * r0>(k)), zk, zm);
+                    herm_pre(a, b, MA_LDG(p.twN + k * (N0 / 2 + 1) + j), zk, zm);
                     A[k] = make_float2(zk.y, zk.x);
                     Bf[r0 - 1 - k] = make_float2(zm.y, zm.x);
                 }
@@ -362,12 +374,11 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
                     A[k] = make_float2(zk.y, zk.x);
                     if (k > 0) A[r0 - k] = make_float2(zm.y, zm.x);
                 }
-                const float2 wq = MA_LDG(p.twN + N0 / 2);
 #pragma unroll
                 for (int k = 0; k < r0 / 2; ++k) {
                     float2 a = zero, b = zero, zk, zm;
                     if (active) c2r_load_pair(p, s, f, g, N0 / 2 + k * N0, M, a, b);
-                    herm_pre(a, b, cmul(wq, root_const<2 * r0>(k)), zk, zm);
+                    herm_pre(a, b, MA_LDG(p.twN + k * (N0 / 2 + 1) + N0 / 2), zk, zm);
                     Bf[k] = make_float2(zk.y, zk.x);
                     Bf[r0 - 1 - k] = make_float2(zm.y, zm.x);
                 }
@@ -553,6 +564,209 @@ MA_HD void istft_body(const C2RParams& p, Cta& cta, float2* smem) {
                 }
             }
             cta.sync();
+        }
+    }
+}
+
+// Fast iSTFT for paired plans when hop/2 is a multiple of T (e.g. N = 4096, hop = 1024) and the
+// spectra are in a half layout.  Differences from istft_body:
+//  * the frame's bins are prefetched one frame ahead with asynchronous global->shared copies
+//    into thread-private slots (each thread copies exactly the pairs X[i], X[M-i] it will
+//    consume), so HBM latency overlaps the previous frame's transform and costs no registers;
+//  * thread t only ever touches overlap-add positions congruent to t modulo T, so the ring is
+//    thread-private too: no barrier for accumulate or emit, only the two FFT exchanges remain;
+//  * completed samples go straight from registers to HBM.
+// smem: 2 exchange buffers | staging [2*(R/2+1)][T] float2 | ring [R][T] float2.
+template <int M>
+struct IstftFastShape {
+    using P = FftPlan<M>;
+    static constexpr int ELEMS = smem_elems_per_fft<M, 1>();
+    static constexpr int NPAIR = P::R / 2 + 1;
+    static constexpr int STAGE = 2 * NPAIR * P::T;
+    static constexpr int RING = P::R * P::T;
+    static constexpr int SMEM_BYTES = (2 * ELEMS + STAGE + RING) * (int)sizeof(float2);
+};
+
+// Whether istft_fast_body serves these parameters.
+template <int M>
+inline bool istft_fast_ok(const C2RParams& p) {
+    if constexpr (!plan_pairable<M>()) {
+        (void)p;
+        return false;
+    } else {
+        constexpr int R = FftPlan<M>::R, T = FftPlan<M>::T;
+        if (p.layout != LAYOUT_HALF_INTERLEAVED && p.layout != LAYOUT_HALF_PACKED) return false;
+        if (p.n_partials > 1 || p.hop <= 0 || p.hop % (2 * T) != 0) return false;
+        const int h = p.hop / (2 * T);
+        if (h > R || R % h != 0) return false;
+        if ((reinterpret_cast<uintptr_t>(p.out) & 7) != 0 || (p.out_signal_stride & 1) != 0) return false;
+        return true;
+    }
+}
+
+template <int M, class Cta>
+MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
+    using P = FftPlan<M>;
+    using PR = FftPlanRev<M>;
+    using SH = IstftFastShape<M>;
+    constexpr int R = P::R, T = P::T, N = 2 * M;
+    constexpr int r0 = PR::radix(0), NB0 = R / r0, N0 = M / r0;
+    float2* stage = smem + 2 * SH::ELEMS;
+    float2* ring = stage + SH::STAGE;
+    const int t = cta.tid();
+    int parity = 0;
+    const float scale = 1.0f / (float)N;
+    const int hop = p.hop;
+    const int h = hop / (2 * T);  // ring slots completed per frame
+    const int64_t F = p.frames_per_signal;
+    const bool normalise = !(p.window == nullptr && p.floor < 0.f);
+    const bool packed = p.layout == LAYOUT_HALF_PACKED;
+
+    float2 wreg[R];
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+        const int n = t + q * T;
+        if (p.window != nullptr)
+            wreg[q] = make_float2(MA_LDG(p.window + 2 * n) * scale, MA_LDG(p.window + 2 * n + 1) * scale);
+        else
+            wreg[q] = make_float2(scale, scale);
+    }
+
+    // Queue the copies of one frame's bins into this thread's staging slots.
+    auto prefetch = [&](int64_t s, int64_t f) {
+        const float2* x = reinterpret_cast<const float2*>(p.in_a) + s * p.in_signal_stride + f * p.in_frame_stride;
+#pragma unroll
+        for (int c = 0; c < NB0 / 2; ++c) {
+            const int j = c * T + t;
+            if (j != 0) {
+#pragma unroll
+                for (int k = 0; k < r0; ++k) {
+                    const int i = j + k * N0;
+                    MA_ASYNC_COPY8(stage + ((c * r0 + k) * 2 + 0) * T + t, x + i);
+                    MA_ASYNC_COPY8(stage + ((c * r0 + k) * 2 + 1) * T + t, x + (M - i));
+                }
+            } else {
+#pragma unroll
+                for (int n = 0; n <= r0; ++n) {
+                    const int i = n <= r0 / 2 ? n * N0 : N0 / 2 + (n - r0 / 2 - 1) * N0;
+                    const int slot = n < r0 ? n : R / 2;
+                    MA_ASYNC_COPY8(stage + (slot * 2 + 0) * T + t, x + i);
+                    MA_ASYNC_COPY8(stage + (slot * 2 + 1) * T + t, x + (i == 0 ? (packed ? 0 : M) : M - i));
+                }
+            }
+        }
+        MA_ASYNC_COMMIT();
+    };
+
+    const int64_t n_chunks = (int64_t)p.chunks_per_signal;
+    const int64_t total_chunks = p.n_signals * n_chunks;
+    const int64_t per = (F + n_chunks - 1) / n_chunks;
+    const int reach = R / h - 1;  // earlier frames overlapping a frame start
+
+    for (int64_t c = cta.bid(); c < total_chunks; c += cta.nblocks()) {
+        const int64_t s = c / n_chunks;
+        const int64_t ci = c - s * n_chunks;
+        const int64_t f0 = ci * per;
+        int64_t f1 = f0 + per;
+        if (f1 > F) f1 = F;
+        if (f0 >= f1) continue;  // uniform across the CTA
+        int64_t fh = f0 - reach;
+        if (fh < 0) fh = 0;
+#pragma unroll
+        for (int q = 0; q < R; ++q) ring[q * T + t] = make_float2(0.f, 0.f);
+        prefetch(s, fh);
+        for (int64_t f = fh; f < f1; ++f) {
+            float2 v[R];
+            MA_ASYNC_WAIT_ALL();
+            // Hermitian pre-process out of the staging slots (same mapping as the prefetch).
+#pragma unroll
+            for (int cc = 0; cc < NB0 / 2; ++cc) {
+                float2* A = v + (2 * cc) * r0;
+                float2* Bf = v + (2 * cc + 1) * r0;
+                const int j = cc * T + t;
+                if (j != 0) {
+#pragma unroll
+                    for (int k = 0; k < r0; ++k) {
+                        const float2 a = stage[((cc * r0 + k) * 2 + 0) * T + t];
+                        const float2 b = stage[((cc * r0 + k) * 2 + 1) * T + t];
+                        float2 zk, zm;
+                        herm_pre(a, b, MA_LDG(p.twN + k * (N0 / 2 + 1) + j), zk, zm);
+                        A[k] = make_float2(zk.y, zk.x);
+                        Bf[r0 - 1 - k] = make_float2(zm.y, zm.x);
+                    }
+                } else {
+#pragma unroll
+                    for (int n = 0; n <= r0; ++n) {
+                        const int slot = n < r0 ? n : R / 2;
+                        float2 a = stage[(slot * 2 + 0) * T + t];
+                        float2 b = stage[(slot * 2 + 1) * T + t];
+                        float2 zk, zm;
+                        if (n <= r0 / 2) {  // butterfly 0: bins n*N0 and M - n*N0
+                            if (n == 0) {
+                                if (packed) {
+                                    b = make_float2(a.y, 0.f);
+                                    a = make_float2(a.x, 0.f);
+                                } else {
+                                    a.y = 0.f;
+                                    b.y = 0.f;
+                                }
+                            }
+                            herm_pre(a, b, root_const<2 * r0>(n), zk, zm);
+                            A[n] = make_float2(zk.y, zk.x);
+                            if (n > 0) A[r0 - n] = make_float2(zm.y, zm.x);
+                        } else {  // butterfly N0/2: bins N0/2 + k*N0 and their mirrors
+                            const int k = n - r0 / 2 - 1;
+                            herm_pre(a, b, MA_LDG(p.twN + k * (N0 / 2 + 1) + N0 / 2), zk, zm);
+                            Bf[k] = make_float2(zk.y, zk.x);
+                            Bf[r0 - 1 - k] = make_float2(zm.y, zm.x);
+                        }
+                    }
+                }
+            }
+            if (f + 1 < f1) prefetch(s, f + 1);  // staging slots are free again (thread-private)
+
+            fft_run<PR, 1, true, false, Cta>(v, t, smem, SH::ELEMS, parity, p.twM, cta);
+
+            // v[q] = (x[2n+1], x[2n]) * N for n = t + q*T.  Overlap-add in this thread's ring column.
+            const int64_t start = f * (int64_t)hop;
+            const int rot = (int)((f * (int64_t)h) & (R - 1));
+            const bool last = f == F - 1;
+            const bool emit = f >= f0;
+            float* out = p.out + s * p.out_signal_stride + start;
+#pragma unroll
+            for (int q = 0; q < R; ++q) {
+                float2* slot = ring + ((q + rot) & (R - 1)) * T + t;
+                float2 acc = make_float2(v[q].y * wreg[q].x, v[q].x * wreg[q].y);
+                if (q < R - h) {  // slot already holds earlier frames
+                    const float2 old = *slot;
+                    acc.x += old.x;
+                    acc.y += old.y;
+                }
+                if (q < h || last) {  // complete after this frame: emit
+                    if (emit) {
+                        const int i0 = 2 * (t + q * T);
+                        float2 r = acc;
+                        if (normalise) {
+                            const int64_t o = start + i0;
+                            float w0, w1;
+                            if (o >= (int64_t)(N - hop) && o + 1 < F * (int64_t)hop) {
+                                const float2 ws = MA_LDG(reinterpret_cast<const float2*>(p.norm_mid + i0));
+                                w0 = ws.x;
+                                w1 = ws.y;
+                            } else {
+                                w0 = window_sum_at(p.window, o, N, hop, F, p.floor);
+                                w1 = window_sum_at(p.window, o + 1, N, hop, F, p.floor);
+                            }
+                            r.x = acc.x / w0;
+                            r.y = acc.y / w1;
+                        }
+                        *reinterpret_cast<float2*>(out + i0) = r;
+                    }
+                    if (last) *slot = make_float2(0.f, 0.f);
+                } else {
+                    *slot = acc;
+                }
+            }
         }
     }
 }

@@ -13,10 +13,10 @@ struct DevCta {
 
 extern __shared__ float4 ma_dyn_smem[];
 
-template <int M, bool ALIGNED>
+template <int M, bool ALIGNED, int LAYOUT, int MAGK>
 __global__ void __launch_bounds__(CtaShape<M>::THREADS, 512 / CtaShape<M>::THREADS) r2c_kernel(const R2CParams p) {
     DevCta cta;
-    r2c_body<M, ALIGNED, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
+    r2c_body<M, ALIGNED, LAYOUT, MAGK, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
 }
 
 template <int M>
@@ -31,6 +31,13 @@ __global__ void __launch_bounds__(FftPlan<M>::T, (512 / FftPlan<M>::T) > 16 ? 16
     istft_body<M, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
 }
 
+template <int M>
+__global__ void __launch_bounds__(FftPlan<M>::T, (384 / FftPlan<M>::T) > 16 ? 16 : ((384 / FftPlan<M>::T) > 0 ? (384 / FftPlan<M>::T) : 1))
+istft_fast_kernel(const C2RParams p) {
+    DevCta cta;
+    if constexpr (plan_pairable<M>()) istft_fast_body<M, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
+}
+
 // Resident CTAs per SM for a kernel (cached per instantiation and device), after raising
 // its dynamic shared-memory limit.
 template <class K>
@@ -42,19 +49,37 @@ static ma_status occupancy(K kernel, int threads, size_t smem, int* per_sm) {
     return MA_OK;
 }
 
-template <int M, bool ALIGNED>
+template <int M, bool ALIGNED, int LAYOUT, int MAGK>
 static ma_status launch_r2c_t(ma_fft_plan* plan, const R2CParams& p) {
     using S = CtaShape<M>;
     static int per_sm[64] = {0};
     ma_context* ctx = plan->ctx;
     int& occ = per_sm[ctx->device & 63];
-    if (occ == 0) MA_TRY(occupancy(r2c_kernel<M, ALIGNED>, S::THREADS, S::SMEM_BYTES, &occ));
+    if (occ == 0) MA_TRY(occupancy(r2c_kernel<M, ALIGNED, LAYOUT, MAGK>, S::THREADS, S::SMEM_BYTES, &occ));
     int64_t want = (p.total_frames + S::FPC - 1) / S::FPC;
     int64_t cap = (int64_t)ctx->sm_count * occ;
     int grid = (int)(want < cap ? want : cap);
     if (grid < 1) return MA_OK;
-    r2c_kernel<M, ALIGNED><<<grid, S::THREADS, S::SMEM_BYTES, ctx->stream>>>(p);
+    r2c_kernel<M, ALIGNED, LAYOUT, MAGK><<<grid, S::THREADS, S::SMEM_BYTES, ctx->stream>>>(p);
     return after_launch(ctx);
+}
+
+template <int M>
+static ma_status launch_r2c_variant(ma_fft_plan* plan, const R2CParams& p, bool aligned, int magk) {
+    if constexpr (plan_pairable<M>()) {
+        if (aligned && magk != -2) {
+#define MA_R2C_CASE(L_, K_) \
+    if (p.layout == L_ && magk == K_) return launch_r2c_t<M, true, L_, K_>(plan, p);
+            MA_R2C_CASE(LAYOUT_HALF_INTERLEAVED, 0)
+            MA_R2C_CASE(LAYOUT_HALF_INTERLEAVED, -1)
+            MA_R2C_CASE(LAYOUT_HALF_PACKED, 0)
+            MA_R2C_CASE(LAYOUT_HALF_PACKED, -1)
+            MA_R2C_CASE(LAYOUT_FULL_SPLIT, 0)
+            MA_R2C_CASE(LAYOUT_FULL_SPLIT, -1)
+#undef MA_R2C_CASE
+        }
+    }
+    return aligned ? launch_r2c_t<M, true, -1, -2>(plan, p) : launch_r2c_t<M, false, -1, -2>(plan, p);
 }
 
 ma_status launch_r2c_small(ma_fft_plan* plan, R2CParams p) {
@@ -66,7 +91,10 @@ ma_status launch_r2c_small(ma_fft_plan* plan, R2CParams p) {
     const bool aligned = ((uintptr_t)p.in % 8 == 0) && (p.signal_stride % 2 == 0) && (p.hop % 2 == 0) &&
                          p.frame_valid >= n && last_end <= p.signal_len;
     ma_status st = MA_ERR_UNSUPPORTED;
-#define RUN(MM) st = aligned ? launch_r2c_t<MM, true>(plan, p) : launch_r2c_t<MM, false>(plan, p);
+    // Aligned launches of the paired plans get kernels with the layout and the magnitude kind
+    // fixed at compile time (no per-store branches); everything else decides at run time.
+    const int magk = p.mag == nullptr ? -1 : (p.mag_kind == MAG_MAGNITUDE ? 0 : -2);
+#define RUN(MM) st = launch_r2c_variant<MM>(plan, p, aligned, magk);
     MA_DISPATCH_M(plan->m, RUN)
 #undef RUN
     return st;
@@ -102,11 +130,16 @@ ma_status launch_c2r_small(ma_fft_plan* plan, C2RParams p) {
 template <int M>
 static ma_status launch_istft_t(ma_fft_plan* plan, C2RParams& p) {
     constexpr int T = FftPlan<M>::T;
-    constexpr size_t smem = 2 * smem_elems_per_fft<M, 1>() * sizeof(float2) + 2 * M * sizeof(float);
-    static int per_sm[64] = {0};
+    const bool fast = istft_fast_ok<M>(p);
+    const size_t smem = fast ? (size_t)IstftFastShape<M>::SMEM_BYTES
+                             : 2 * smem_elems_per_fft<M, 1>() * sizeof(float2) + 2 * M * sizeof(float);
+    static int per_sm[2][64] = {{0}, {0}};
     ma_context* ctx = plan->ctx;
-    int& occ = per_sm[ctx->device & 63];
-    if (occ == 0) MA_TRY(occupancy(istft_kernel<M>, T, smem, &occ));
+    int& occ = per_sm[fast ? 1 : 0][ctx->device & 63];
+    if (occ == 0) {
+        if (fast) MA_TRY(occupancy(istft_fast_kernel<M>, T, smem, &occ));
+        else MA_TRY(occupancy(istft_kernel<M>, T, smem, &occ));
+    }
     // Chunks per signal: enough CTAs to fill the device a few times over, but chunks long
     // enough that the recomputed lead-in frames stay a small fraction.
     const int64_t F = p.frames_per_signal;
@@ -120,7 +153,8 @@ static ma_status launch_istft_t(ma_fft_plan* plan, C2RParams& p) {
     const int64_t total = chunks * p.n_signals;
     int grid = (int)(total < cap ? total : cap);
     if (grid < 1) return MA_OK;
-    istft_kernel<M><<<grid, T, smem, ctx->stream>>>(p);
+    if (fast) istft_fast_kernel<M><<<grid, T, smem, ctx->stream>>>(p);
+    else istft_kernel<M><<<grid, T, smem, ctx->stream>>>(p);
     return after_launch(ctx);
 }
 

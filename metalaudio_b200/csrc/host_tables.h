@@ -61,6 +61,50 @@ inline std::vector<float2> make_stage_tables_for(int m, bool rev) {
     return out;
 }
 
+// Twiddles of the Hermitian pre/post-process, exp(-2 pi i idx / (2m)).  Pairable plans index
+// them [k][j] -> idx = j + k*NL with NL = m / (last forward radix), j <= NL/2, so that the lanes
+// of a warp (consecutive j) load contiguously; other plans use idx = k, k <= m/2.
+template <int MM>
+inline std::vector<float2> make_hermitian_table_t() {
+    const double step = -2.0 * M_PI / (2.0 * (double)MM);
+    std::vector<float2> tw;
+    if constexpr (plan_pairable<MM>()) {
+        constexpr int rl = FftPlan<MM>::radix(FftPlan<MM>::NS - 1), NL = MM / rl;
+        tw.resize((size_t)rl * (NL / 2 + 1));
+        for (int k = 0; k < rl; ++k)
+            for (int j = 0; j <= NL / 2; ++j) {
+                const double a = step * (double)(j + k * NL);
+                tw[(size_t)(k * (NL / 2 + 1) + j)] = make_float2((float)std::cos(a), (float)std::sin(a));
+            }
+    } else {
+        tw.resize((size_t)(MM / 2 + 1));
+        for (int k = 0; k <= MM / 2; ++k)
+            tw[(size_t)k] = make_float2((float)std::cos(step * k), (float)std::sin(step * k));
+    }
+    return tw;
+}
+
+inline std::vector<float2> make_hermitian_table(int m) {
+    std::vector<float2> out;
+    switch (m) {
+        case 1: out = make_hermitian_table_t<1>(); break;
+        case 2: out = make_hermitian_table_t<2>(); break;
+        case 4: out = make_hermitian_table_t<4>(); break;
+        case 8: out = make_hermitian_table_t<8>(); break;
+        case 16: out = make_hermitian_table_t<16>(); break;
+        case 32: out = make_hermitian_table_t<32>(); break;
+        case 64: out = make_hermitian_table_t<64>(); break;
+        case 128: out = make_hermitian_table_t<128>(); break;
+        case 256: out = make_hermitian_table_t<256>(); break;
+        case 512: out = make_hermitian_table_t<512>(); break;
+        case 1024: out = make_hermitian_table_t<1024>(); break;
+        case 2048: out = make_hermitian_table_t<2048>(); break;
+        case 4096: out = make_hermitian_table_t<4096>(); break;
+        default: break;
+    }
+    return out;
+}
+
 // Runtime form of plan_pairable<M>().
 inline bool plan_pairable_rt(int m) {
     switch (m) {

@@ -18,7 +18,7 @@ int emul_r2c(int n, int aligned, const float* in, long long signal_stride, long 
              long long out_frame_stride, int layout, int mag_kind, float db_scale, int nblocks) {
     const int M = n / 2;
     auto twM = make_stage_tables_for(M, false);
-    auto twN = make_twiddles(n, M / 2 + 1);
+    auto twN = make_hermitian_table(M);
     R2CParams p{};
     p.in = in; p.signal_stride = signal_stride; p.frames_per_signal = frames_per_signal;
     p.total_frames = total_frames; p.signal_len = signal_len; p.hop = hop; p.frame_valid = frame_valid;
@@ -31,8 +31,10 @@ int emul_r2c(int n, int aligned, const float* in, long long signal_stride, long 
     {                                                                                        \
         using S = CtaShape<MM>;                                                              \
         run_grid(nblocks, S::THREADS, S::SMEM_BYTES, [&](HostCta& cta, void* sm) {           \
-            if (aligned) r2c_body<MM, true, HostCta>(p, cta, (float2*)sm);                   \
-            else r2c_body<MM, false, HostCta>(p, cta, (float2*)sm);                          \
+            if (aligned && layout == 0 && mag_kind == 0 && mag != nullptr)                   \
+                r2c_body<MM, true, 0, 0, HostCta>(p, cta, (float2*)sm);                      \
+            else if (aligned) r2c_body<MM, true, -1, -2, HostCta>(p, cta, (float2*)sm);      \
+            else r2c_body<MM, false, -1, -2, HostCta>(p, cta, (float2*)sm);                  \
         });                                                                                  \
         rc = 0;                                                                              \
     }
@@ -46,7 +48,7 @@ int emul_c2r(int n, const float* in_a, const float* in_b, long long in_signal_st
              float* out, int nblocks) {
     const int M = n / 2;
     auto twM = make_stage_tables_for(M, plan_pairable_rt(M));
-    auto twN = make_twiddles(n, M / 2 + 1);
+    auto twN = make_hermitian_table(M);
     C2RParams p{};
     p.in_a = in_a; p.in_b = in_b; p.in_signal_stride = in_signal_stride; p.in_frame_stride = in_frame_stride;
     p.frames_per_signal = frames_per_signal; p.n_signals = n_signals; p.layout = layout; p.out = out;
@@ -71,7 +73,7 @@ int emul_istft(int n, int hop, const float* in_a, const float* in_b, long long i
                long long out_len, int chunks_per_signal, int nblocks) {
     const int M = n / 2;
     auto twM = make_stage_tables_for(M, plan_pairable_rt(M));
-    auto twN = make_twiddles(n, M / 2 + 1);
+    auto twN = make_hermitian_table(M);
     C2RParams p{};
     p.in_a = in_a; p.in_b = in_b; p.in_signal_stride = in_signal_stride; p.in_frame_stride = in_frame_stride;
     p.frames_per_signal = frames; p.n_signals = n_signals; p.layout = layout; p.hop = hop;
@@ -81,18 +83,25 @@ int emul_istft(int n, int hop, const float* in_a, const float* in_b, long long i
     p.norm_mid = norm.data();
     p.twM = twM.data(); p.twN = twN.data();
     int rc = -1;
+    int used_fast = 0;
 #define RUN(MM)                                                                                  \
     {                                                                                            \
         constexpr int ELEMS = smem_elems_per_fft<MM, 1>();                                       \
-        const size_t smem = 2 * ELEMS * sizeof(float2) + (size_t)n * sizeof(float);              \
+        const bool fast = istft_fast_ok<MM>(p);                                                  \
+        const size_t smem = fast ? (size_t)IstftFastShape<MM>::SMEM_BYTES                        \
+                                 : 2 * ELEMS * sizeof(float2) + (size_t)n * sizeof(float);       \
+        used_fast = fast ? 1 : 0;                                                                \
         run_grid(nblocks, FftPlan<MM>::T, smem, [&](HostCta& cta, void* sm) {                    \
+            if constexpr (plan_pairable<MM>()) {                                                 \
+                if (fast) { istft_fast_body<MM, HostCta>(p, cta, (float2*)sm); return; }         \
+            }                                                                                    \
             istft_body<MM, HostCta>(p, cta, (float2*)sm);                                        \
         });                                                                                      \
         rc = 0;                                                                                  \
     }
     MA_DISPATCH_M(M, RUN)
 #undef RUN
-    return rc;
+    return rc == 0 ? used_fast : rc;
 }
 
 }  // extern "C"

@@ -88,7 +88,9 @@ def test_zero_padded_frames(emul):
 @pytest.mark.parametrize("n,hop,length,chunks,kind", [(256, 64, 3000, 1, "hann"), (256, 64, 3000, 3, "hann"),
                                                       (512, 100, 4000, 2, "hamming"), (64, 7, 500, 4, "blackman"),
                                                       (1024, 1024, 8192, 2, "none"), (8, 2, 50, 2, "hann"),
-                                                      (4, 1, 20, 1, "hann"), (2, 1, 9, 2, "none")])
+                                                      (4, 1, 20, 1, "hann"), (2, 1, 9, 2, "none"),
+                                                      (4096, 1024, 30000, 2, "hann"), (4096, 256, 12000, 1, "hann"),
+                                                      (2048, 1024, 9000, 3, "hamming"), (64, 8, 300, 1, "hann")])
 def test_stft_istft(emul, n, hop, length, chunks, kind):
     m = n // 2
     w = rp.window(kind, n)
@@ -103,8 +105,9 @@ def test_stft_istft(emul, n, hop, length, chunks, kind):
     out_len = (f - 1) * hop + n
     y = np.zeros((2, out_len), np.float32)
     floor = float(rp.window_floor())
-    assert emul.emul_istft(n, hop, fp(spec), None, f * (m + 1), m + 1, f, 2, 0, fp(w), floor, fp(y), out_len,
-                           out_len, chunks, 3) == 0
+    rc = emul.emul_istft(n, hop, fp(spec), None, f * (m + 1), m + 1, f, 2, 0, fp(w), floor, fp(y), out_len,
+                         out_len, chunks, 3)
+    assert rc in (0, 1)  # 1: the prefetching thread-private overlap-add variant served it
     yref = o64.istft(ref, n, hop, w, floor)
     ws = rp.window_sum(f, n, hop, w, 0.0)
     msk = ws >= 1e-2 * ws.max()
