@@ -234,6 +234,41 @@ MA_HD void load_stage_twiddles(float2* w, const float2* __restrict__ tws, int j)
     for (int k = 1; k < r; ++k) w[k] = MA_LDG(tws + off + (k - 1) * Ns + j);
 }
 
+// Register-resident alternative: the twiddles of a thread's butterflies do not change from
+// frame to frame, and w^k follows from w^1 by a multiplication chain of depth <= 4, so a kernel
+// that loops over many frames keeps one base twiddle per (stage, sub-butterfly) in registers
+// and spends FMA-pipe work instead of load/store-pipe bandwidth (the scarcer resource here).
+template <class P>
+constexpr __host__ __device__ int tw_base_index(int s, int b) {
+    int idx = 0;
+    for (int i = 1; i < s; ++i) idx += P::R / P::radix(i);
+    return idx + b;
+}
+template <class P>
+constexpr __host__ __device__ int tw_base_count() {
+    return tw_base_index<P>(P::NS, 0) > 0 ? tw_base_index<P>(P::NS, 0) : 1;
+}
+
+template <int r>
+MA_HD void twiddle_powers(float2* w, float2 w1) {
+    if constexpr (r >= 2) w[1] = w1;
+    if constexpr (r >= 4) {
+        w[2] = cmul(w1, w1);
+        w[3] = cmul(w[2], w1);
+    }
+    if constexpr (r >= 8) {
+        w[4] = cmul(w[2], w[2]);
+        w[5] = cmul(w[4], w[1]);
+        w[6] = cmul(w[4], w[2]);
+        w[7] = cmul(w[4], w[3]);
+    }
+    if constexpr (r >= 16) {
+        w[8] = cmul(w[4], w[4]);
+#pragma unroll
+        for (int k = 1; k < 8; ++k) w[8 + k] = cmul(w[8], w[k]);
+    }
+}
+
 // Which butterfly of a stage a thread's b-th sub-butterfly is.  Natural: jv = t + b*T.
 // Paired: the thread owns butterflies in pairs (j, nbfly - j), so that element i and element
 // M - i of a stage input/output that is indexed jv + k*nbfly sit in the same thread; the two
@@ -288,9 +323,9 @@ MA_HD void stage_write(const float2* v, int t, float2* sbuf) {
     }
 }
 
-template <class P, int W, int S, bool PAIRED>
+template <class P, int W, int S, bool PAIRED, bool TWALU>
 MA_HD void stage_read_compute(float2* v, int t, const float2* sbuf,
-                              const float2* __restrict__ twM) {
+                              const float2* __restrict__ twM, const float2* twb) {
     constexpr int M = P::M, r = P::radix(S), Ns = P::ns_before(S), NB = P::R / r;
     constexpr int stride = M / r;
     using A = ExchangeAddr<W, stride, r>;
@@ -306,27 +341,49 @@ MA_HD void stage_read_compute(float2* v, int t, const float2* sbuf,
             for (int k = 0; k < r; ++k) v[b * r + k] = sbuf[saddr<W>(jv + k * stride)];
         }
         float2 w[r];
-        load_stage_twiddles<P, S>(w, twM, jv % Ns);
+        if constexpr (TWALU) twiddle_powers<r>(w, twb[tw_base_index<P>(S, b)]);
+        else load_stage_twiddles<P, S>(w, twM, jv % Ns);
 #pragma unroll
         for (int k = 1; k < r; ++k) v[b * r + k] = cmul(v[b * r + k], w[k]);
         Bfly<r>::run(v + b * r);
     }
 }
 
-template <class P, int W, int S, bool PAIR0, bool PAIRL, class Cta>
+template <class P, bool PAIRL, int S>
+MA_HD void tw_bases_stage(float2* twb, int t, const float2* __restrict__ tws) {
+    if constexpr (S < P::NS) {
+        constexpr int r = P::radix(S), Ns = P::ns_before(S), NB = P::R / r;
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            const int jv = stage_jv<P, (S == P::NS - 1) && PAIRL>(t, b, P::M / r);
+            twb[tw_base_index<P>(S, b)] = MA_LDG(tws + stage_tw_offset<P>(S) + (jv % Ns));
+        }
+        tw_bases_stage<P, PAIRL, S + 1>(twb, t, tws);
+    }
+}
+
+template <class P, int W, int S, bool PAIR0, bool PAIRL, bool TWALU, class Cta>
 struct StageChain {
     static MA_HD void run(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
-                          const float2* __restrict__ twM, Cta& cta) {
+                          const float2* __restrict__ twM, const float2* twb, Cta& cta) {
         if constexpr (S < P::NS) {
             float2* sbuf = sbuf0 + parity * buf_stride;
             stage_write<P, W, S - 1, (S == 1) && PAIR0>(v, t, sbuf);
             cta.sync();
-            stage_read_compute<P, W, S, (S == P::NS - 1) && PAIRL>(v, t, sbuf, twM);
+            stage_read_compute<P, W, S, (S == P::NS - 1) && PAIRL, TWALU>(v, t, sbuf, twM, twb);
             parity ^= 1;
-            StageChain<P, W, S + 1, PAIR0, PAIRL, Cta>::run(v, t, sbuf0, buf_stride, parity, twM, cta);
+            StageChain<P, W, S + 1, PAIR0, PAIRL, TWALU, Cta>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta);
         }
     }
 };
+
+// Base twiddles (k = 1 entries of the stage tables) of this thread's butterflies, for the
+// register-resident mode.
+template <class P, bool PAIRL>
+MA_HD void load_tw_bases(float2* twb, int t, const float2* __restrict__ tws) {
+    twb[0] = make_float2(1.f, 0.f);
+    tw_bases_stage<P, PAIRL, 1>(twb, t, tws);
+}
 
 // All stages of plan P on registers.
 // In:  v[b*r0 + k] = z[jv0(b) + k*M/r0], r0 the first radix, jv0 natural or paired (PAIR0).
@@ -334,14 +391,14 @@ struct StageChain {
 // sbuf0 is the transform's exchange region (already offset by the slot when W > 1);
 // buf_stride is the distance in float2 between the two exchange buffers; parity selects the
 // buffer of the next exchange and is updated.
-template <class P, int W, bool PAIR0, bool PAIRL, class Cta>
+template <class P, int W, bool PAIR0, bool PAIRL, class Cta, bool TWALU = false>
 MA_HD void fft_run(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
-                   const float2* __restrict__ twM, Cta& cta) {
+                   const float2* __restrict__ twM, Cta& cta, const float2* twb = nullptr) {
     constexpr int r0 = P::radix(0), NB0 = P::R / r0;
     static_assert(!(PAIRL && P::NS < 2), "a paired last stage needs at least two stages");
 #pragma unroll
     for (int b = 0; b < NB0; ++b) Bfly<r0>::run(v + b * r0);  // stage 0: no twiddles
-    StageChain<P, W, 1, PAIR0, PAIRL, Cta>::run(v, t, sbuf0, buf_stride, parity, twM, cta);
+    StageChain<P, W, 1, PAIR0, PAIRL, TWALU, Cta>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta);
 }
 
 // Complex forward FFT of length M in natural order.  In: v[q] = z[t + q*T].

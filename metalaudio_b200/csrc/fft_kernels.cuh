@@ -53,6 +53,9 @@ struct CtaShape {
     static constexpr int ELEMS = smem_elems_per_fft<M, 1>();      // one buffer, one frame
     static constexpr int BUF_STRIDE = ELEMS * FPC;                // float2 between buffers
     static constexpr int SMEM_BYTES = 2 * BUF_STRIDE * (int)sizeof(float2);
+    // Prefetching forward kernels add one thread-private staging slot per register point.
+    static constexpr int STAGE = FftPlan<M>::R * THREADS;
+    static constexpr int SMEM_BYTES_PREFETCH = SMEM_BYTES + STAGE * (int)sizeof(float2);
 };
 
 // Hermitian post-process of one pair: a = Z[k], b = Z[(M-k) mod M], w = exp(-2 pi i k/N).
@@ -164,6 +167,21 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
         for (int q = 0; q < R; ++q) wreg[q] = make_float2(1.0f, 1.0f);
     }
 
+    // Kernels with the layout fixed at compile time also prefetch their input.
+    constexpr bool PREFETCH = false;  // staging adds load/store-pipe traffic, the limiter; kept for reference
+    constexpr bool TWALU = ALIGNED && LAYOUT >= 0 && plan_pairable<M>();
+    float2 twb[tw_base_count<P>()];
+    float2 wherm[R / 2 + 1];
+    (void)wherm;
+    if constexpr (TWALU) {
+        load_tw_bases<P, true>(twb, t, p.twM);
+        constexpr int rl_ = P::radix(P::NS - 1), NL_ = M / rl_;
+#pragma unroll
+        for (int c = 0; c < R / rl_ / 2; ++c) wherm[c] = MA_LDG(p.twN + (c * T + t));
+        (void)NL_;
+    }
+    float2* stage = smem + 2 * S::BUF_STRIDE;
+    (void)stage;
     // (signal, frame) of this thread's first frame by one division; later frames advance by the
     // grid stride without dividing.
     const int64_t stride_frames = (int64_t)cta.nblocks() * S::FPC;
@@ -172,6 +190,14 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
     int64_t f = g - s * p.frames_per_signal;
     const int64_t ds = stride_frames / p.frames_per_signal;
     const int64_t df = stride_frames - ds * p.frames_per_signal;
+    if constexpr (PREFETCH) {
+        if (g < p.total_frames) {
+            const float2* src0 = reinterpret_cast<const float2*>(p.in + s * p.signal_stride + f * (int64_t)p.hop);
+#pragma unroll
+            for (int q = 0; q < R; ++q) MA_ASYNC_COPY8(stage + q * S::THREADS + tid, src0 + t + q * T);
+        }
+        MA_ASYNC_COMMIT();
+    }
     for (int64_t base = (int64_t)cta.bid() * S::FPC; base < p.total_frames;
          base += stride_frames, g += stride_frames, s += ds, f += df) {
         if (f >= p.frames_per_signal) {
@@ -183,7 +209,29 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
         const float* src = p.in + (active ? s * p.signal_stride + start : 0);
 
         float2 v[R];
-        if (ALIGNED) {
+        if constexpr (PREFETCH) {
+            // This frame's samples were copied asynchronously into this thread's staging slots
+            // while the previous frame was transformed; queue the next frame's right away.
+            MA_ASYNC_WAIT_ALL();
+#pragma unroll
+            for (int q = 0; q < R; ++q) {
+                const float2 x = active ? stage[q * S::THREADS + tid] : make_float2(0.f, 0.f);
+                v[q] = make_float2(x.x * wreg[q].x, x.y * wreg[q].y);
+            }
+            {
+                int64_t fn = f + df, sn = s + ds;
+                if (fn >= p.frames_per_signal) {
+                    fn -= p.frames_per_signal;
+                    ++sn;
+                }
+                if (g + stride_frames < p.total_frames) {
+                    const float2* nsrc = reinterpret_cast<const float2*>(p.in + sn * p.signal_stride + fn * (int64_t)p.hop);
+#pragma unroll
+                    for (int q = 0; q < R; ++q) MA_ASYNC_COPY8(stage + q * S::THREADS + tid, nsrc + t + q * T);
+                }
+                MA_ASYNC_COMMIT();
+            }
+        } else if (ALIGNED) {
 #pragma unroll
             for (int q = 0; q < R; ++q) {
                 const int n = t + q * T;
@@ -207,7 +255,7 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
         if constexpr (plan_pairable<M>()) {
             // Last stage with paired butterflies: bins k and M-k end up in the same thread,
             // so the Hermitian post-process needs no exchange.
-            fft_run<P, 1, false, true, Cta>(v, t, sbuf0, S::BUF_STRIDE, parity, p.twM, cta);
+            fft_run<P, 1, false, true, Cta, TWALU>(v, t, sbuf0, S::BUF_STRIDE, parity, p.twM, cta, twb);
             constexpr int rl = P::radix(P::NS - 1), NBL = R / rl, NL = M / rl;
 #pragma unroll
             for (int c = 0; c < NBL / 2; ++c) {
@@ -218,7 +266,9 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
 #pragma unroll
                     for (int k = 0; k < rl; ++k) {
                         float2 xk, xm;
-                        herm_post(A[k], Bf[rl - 1 - k], MA_LDG(p.twN + k * (NL / 2 + 1) + j), xk, xm);
+                        const float2 wk = TWALU ? cmul(wherm[c], root_const<2 * rl>(k))
+                                                : MA_LDG(p.twN + k * (NL / 2 + 1) + j);
+                        herm_post(A[k], Bf[rl - 1 - k], wk, xk, xm);
                         if (active) r2c_store_pair<M, LAYOUT, MAGK>(p, g, half_off, j + k * NL, xk, xm);
                     }
                 } else {
@@ -632,6 +682,14 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
             wreg[q] = make_float2(scale, scale);
     }
 
+    // Frame-invariant twiddles in registers: one base per butterfly for the FFT stages and
+    // W_N^j for the Hermitian pre-process.
+    float2 twb[tw_base_count<PR>()];
+    load_tw_bases<PR, false>(twb, t, p.twM);
+    float2 wherm[NB0 / 2 > 0 ? NB0 / 2 : 1];
+#pragma unroll
+    for (int cc = 0; cc < NB0 / 2; ++cc) wherm[cc] = MA_LDG(p.twN + (cc * T + t));
+
     // Queue the copies of one frame's bins into this thread's staging slots.
     auto prefetch = [&](int64_t s, int64_t f) {
         const float2* x = reinterpret_cast<const float2*>(p.in_a) + s * p.in_signal_stride + f * p.in_frame_stride;
@@ -690,7 +748,7 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
                         const float2 a = stage[((cc * r0 + k) * 2 + 0) * T + t];
                         const float2 b = stage[((cc * r0 + k) * 2 + 1) * T + t];
                         float2 zk, zm;
-                        herm_pre(a, b, MA_LDG(p.twN + k * (N0 / 2 + 1) + j), zk, zm);
+                        herm_pre(a, b, cmul(wherm[cc], root_const<2 * r0>(k)), zk, zm);
                         A[k] = make_float2(zk.y, zk.x);
                         Bf[r0 - 1 - k] = make_float2(zm.y, zm.x);
                     }
@@ -725,7 +783,7 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
             }
             if (f + 1 < f1) prefetch(s, f + 1);  // staging slots are free again (thread-private)
 
-            fft_run<PR, 1, true, false, Cta>(v, t, smem, SH::ELEMS, parity, p.twM, cta);
+            fft_run<PR, 1, true, false, Cta, true>(v, t, smem, SH::ELEMS, parity, p.twM, cta, twb);
 
             // v[q] = (x[2n+1], x[2n]) * N for n = t + q*T.  Overlap-add in this thread's ring column.
             const int64_t start = f * (int64_t)hop;

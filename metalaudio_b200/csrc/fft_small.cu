@@ -55,12 +55,13 @@ static ma_status launch_r2c_t(ma_fft_plan* plan, const R2CParams& p) {
     static int per_sm[64] = {0};
     ma_context* ctx = plan->ctx;
     int& occ = per_sm[ctx->device & 63];
-    if (occ == 0) MA_TRY(occupancy(r2c_kernel<M, ALIGNED, LAYOUT, MAGK>, S::THREADS, S::SMEM_BYTES, &occ));
+    constexpr size_t smem = S::SMEM_BYTES;
+    if (occ == 0) MA_TRY(occupancy(r2c_kernel<M, ALIGNED, LAYOUT, MAGK>, S::THREADS, smem, &occ));
     int64_t want = (p.total_frames + S::FPC - 1) / S::FPC;
     int64_t cap = (int64_t)ctx->sm_count * occ;
     int grid = (int)(want < cap ? want : cap);
     if (grid < 1) return MA_OK;
-    r2c_kernel<M, ALIGNED, LAYOUT, MAGK><<<grid, S::THREADS, S::SMEM_BYTES, ctx->stream>>>(p);
+    r2c_kernel<M, ALIGNED, LAYOUT, MAGK><<<grid, S::THREADS, smem, ctx->stream>>>(p);
     return after_launch(ctx);
 }
 

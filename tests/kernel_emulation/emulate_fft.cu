@@ -30,7 +30,7 @@ int emul_r2c(int n, int aligned, const float* in, long long signal_stride, long 
 #define RUN(MM)                                                                              \
     {                                                                                        \
         using S = CtaShape<MM>;                                                              \
-        run_grid(nblocks, S::THREADS, S::SMEM_BYTES, [&](HostCta& cta, void* sm) {           \
+        run_grid(nblocks, S::THREADS, S::SMEM_BYTES_PREFETCH, [&](HostCta& cta, void* sm) {  \
             if (aligned && layout == 0 && mag_kind == 0 && mag != nullptr)                   \
                 r2c_body<MM, true, 0, 0, HostCta>(p, cta, (float2*)sm);                      \
             else if (aligned) r2c_body<MM, true, -1, -2, HostCta>(p, cta, (float2*)sm);      \
