@@ -1,0 +1,54 @@
+// One-dimensional bulk asynchronous copies global -> shared (the TMA unit's untiled form,
+// cp.async.bulk) completed on an mbarrier.  One elected thread moves a whole frame with a single
+// instruction: no registers, and none of the load/store-pipe wavefronts a per-thread copy costs.
+// No multicast, no tensor map; source, destination and size must be multiples of 16 bytes.
+//
+// Every wait is bounded: after kBulkWaitLimit polls the waiter gives up, records the failure
+// in a device flag the host reads at the next synchronisation, and carries on (the frame's
+// output is then meaningless, but nothing hangs).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ma {
+
+constexpr int kBulkWaitLimit = 1 << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void bulk_barrier_init(uint64_t* bar) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bar)) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// Arms the barrier for `bytes` and starts the copy.  Called by one thread.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    const uint32_t b = smem_u32(bar);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(bytes) : "memory");
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(b)
+        : "memory");
+}
+
+// Waits for the phase with the given parity; false when the poll limit ran out.
+__device__ __forceinline__ bool bulk_barrier_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t b = smem_u32(bar);
+    for (int i = 0; i < kBulkWaitLimit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(b), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+}  // namespace ma

@@ -201,6 +201,10 @@ ma_status ma_context_create(int32_t device_index, size_t pinned_bytes, ma_contex
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_begin);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_end);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_sync, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&ctx->d_error_flag, sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMemset(ctx->d_error_flag, 0, sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaHostAlloc((void**)&ctx->h_error_flag, sizeof(int32_t), cudaHostAllocDefault);
+    if (e == cudaSuccess) *ctx->h_error_flag = 0;
     if (e == cudaSuccess) {
         // Keep freed stream-ordered temporaries cached instead of returning them to the OS.
         cudaMemPool_t pool;
@@ -229,6 +233,8 @@ ma_status ma_context_destroy(ma_context* ctx) {
     if (ctx->ev_end) (void)cudaEventDestroy(ctx->ev_end);
     if (ctx->ev_sync) (void)cudaEventDestroy(ctx->ev_sync);
     if (ctx->pinned) (void)cudaFreeHost(ctx->pinned);
+    if (ctx->d_error_flag) (void)cudaFree(ctx->d_error_flag);
+    if (ctx->h_error_flag) (void)cudaFreeHost(ctx->h_error_flag);
     if (ctx->copy_stream) (void)cudaStreamDestroy(ctx->copy_stream);
     if (ctx->stream) (void)cudaStreamDestroy(ctx->stream);
     (void)cudaGetLastError();
@@ -239,11 +245,20 @@ ma_status ma_context_destroy(ma_context* ctx) {
 ma_status ma_context_sync(ma_context* ctx, double timeout_s) {
     MA_TRY(enter(ctx, MA_FAULT_SYNC));
     if (timeout_s <= 0.0) timeout_s = 2.0;
+    // A kernel whose bounded wait ran out leaves a flag; fetch it behind the queued work.
+    MA_CUDA(cudaMemcpyAsync(ctx->h_error_flag, ctx->d_error_flag, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
     MA_CUDA(cudaEventRecord(ctx->ev_sync, ctx->stream));
     const auto t0 = std::chrono::steady_clock::now();
     for (;;) {
         cudaError_t e = cudaEventQuery(ctx->ev_sync);
-        if (e == cudaSuccess) return MA_OK;
+        if (e == cudaSuccess) {
+            if (*ctx->h_error_flag != 0) {
+                *ctx->h_error_flag = 0;
+                (void)cudaMemsetAsync(ctx->d_error_flag, 0, sizeof(int32_t), ctx->stream);
+                return MA_ERR_TIMEOUT;
+            }
+            return MA_OK;
+        }
         if (e != cudaErrorNotReady) return cuda_fail(e);
         const double dt = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
         if (dt > timeout_s) return MA_ERR_TIMEOUT;

@@ -56,7 +56,7 @@ ma_status ma_fft_plan_create(ma_context* ctx, int32_t n, const float* window, in
         st = upload(ctx, window, sizeof(float) * (size_t)n, (void**)&p->d_window);
     }
     if (st == MA_OK && !p->large) {
-        cudaError_t e = cudaMalloc((void**)&p->d_norm, sizeof(float) * (size_t)hop);
+        cudaError_t e = cudaMalloc((void**)&p->d_norm, 2 * sizeof(float) * (size_t)hop);
         if (e != cudaSuccess) st = cuda_fail(e);
     }
     if (st == MA_OK && !p->large) {

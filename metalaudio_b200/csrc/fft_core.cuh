@@ -362,17 +362,22 @@ MA_HD void tw_bases_stage(float2* twb, int t, const float2* __restrict__ tws) {
     }
 }
 
-template <class P, int W, int S, bool PAIR0, bool PAIRL, bool TWALU, class Cta>
+struct NoHook {
+    MA_HD void operator()() const {}
+};
+
+template <class P, int W, int S, bool PAIR0, bool PAIRL, bool TWALU, class Cta, class Hook = NoHook>
 struct StageChain {
     static MA_HD void run(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
-                          const float2* __restrict__ twM, const float2* twb, Cta& cta) {
+                          const float2* __restrict__ twM, const float2* twb, Cta& cta, const Hook& hook = Hook()) {
         if constexpr (S < P::NS) {
             float2* sbuf = sbuf0 + parity * buf_stride;
             stage_write<P, W, S - 1, (S == 1) && PAIR0>(v, t, sbuf);
             cta.sync();
+            if constexpr (S == 1) hook();  // every thread is past its reads of the frame's input
             stage_read_compute<P, W, S, (S == P::NS - 1) && PAIRL, TWALU>(v, t, sbuf, twM, twb);
             parity ^= 1;
-            StageChain<P, W, S + 1, PAIR0, PAIRL, TWALU, Cta>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta);
+            StageChain<P, W, S + 1, PAIR0, PAIRL, TWALU, Cta, Hook>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta, hook);
         }
     }
 };
@@ -391,14 +396,15 @@ MA_HD void load_tw_bases(float2* twb, int t, const float2* __restrict__ tws) {
 // sbuf0 is the transform's exchange region (already offset by the slot when W > 1);
 // buf_stride is the distance in float2 between the two exchange buffers; parity selects the
 // buffer of the next exchange and is updated.
-template <class P, int W, bool PAIR0, bool PAIRL, class Cta, bool TWALU = false>
+template <class P, int W, bool PAIR0, bool PAIRL, class Cta, bool TWALU = false, class Hook = NoHook>
 MA_HD void fft_run(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
-                   const float2* __restrict__ twM, Cta& cta, const float2* twb = nullptr) {
+                   const float2* __restrict__ twM, Cta& cta, const float2* twb = nullptr,
+                   const Hook& hook = Hook()) {
     constexpr int r0 = P::radix(0), NB0 = P::R / r0;
     static_assert(!(PAIRL && P::NS < 2), "a paired last stage needs at least two stages");
 #pragma unroll
     for (int b = 0; b < NB0; ++b) Bfly<r0>::run(v + b * r0);  // stage 0: no twiddles
-    StageChain<P, W, 1, PAIR0, PAIRL, TWALU, Cta>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta);
+    StageChain<P, W, 1, PAIR0, PAIRL, TWALU, Cta, Hook>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta, hook);
 }
 
 // Complex forward FFT of length M in natural order.  In: v[q] = z[t + q*T].

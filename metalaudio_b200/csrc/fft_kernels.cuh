@@ -32,6 +32,8 @@ struct R2CParams {
     int32_t mag_kind;
     float db_scale;             // 1/reference for MAG_DB
     const float2* twM;          // stage twiddle tables of FftPlan<M> (fft_core.cuh layout)
+    int32_t bulk_ok;            // frame starts and length are 16-byte multiples: bulk async staging allowed
+    int32_t* error_flag;        // set to 1 when a bounded wait ran out
     const float2* twN;          // Hermitian-step twiddles exp(-2 pi i k / N): [k], k <= M/2, or for
                                 // plan_pairable<M>() the table [k][j] = W_N^(j + k*NL), j <= NL/2
 };
@@ -53,9 +55,9 @@ struct CtaShape {
     static constexpr int ELEMS = smem_elems_per_fft<M, 1>();      // one buffer, one frame
     static constexpr int BUF_STRIDE = ELEMS * FPC;                // float2 between buffers
     static constexpr int SMEM_BYTES = 2 * BUF_STRIDE * (int)sizeof(float2);
-    // Prefetching forward kernels add one thread-private staging slot per register point.
+    // Prefetching forward kernels add a staging frame per slot plus one mbarrier per slot.
     static constexpr int STAGE = FftPlan<M>::R * THREADS;
-    static constexpr int SMEM_BYTES_PREFETCH = SMEM_BYTES + STAGE * (int)sizeof(float2);
+    static constexpr int SMEM_BYTES_PREFETCH = SMEM_BYTES + STAGE * (int)sizeof(float2) + 16 * FPC;
 };
 
 // Hermitian post-process of one pair: a = Z[k], b = Z[(M-k) mod M], w = exp(-2 pi i k/N).
@@ -168,8 +170,9 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
     }
 
     // Kernels with the layout fixed at compile time also prefetch their input.
-    constexpr bool PREFETCH = false;  // staging adds load/store-pipe traffic, the limiter; kept for reference
     constexpr bool TWALU = ALIGNED && LAYOUT >= 0 && plan_pairable<M>();
+    constexpr bool PREFETCH = false;  // per-thread 8-byte async copies cost more load/store-pipe wavefronts than they hide
+    constexpr bool BULK = TWALU;      // whole next frame staged by one bulk async copy (TMA unit)
     float2 twb[tw_base_count<P>()];
     float2 wherm[R / 2 + 1];
     (void)wherm;
@@ -197,6 +200,17 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
             for (int q = 0; q < R; ++q) MA_ASYNC_COPY8(stage + q * S::THREADS + tid, src0 + t + q * T);
         }
         MA_ASYNC_COMMIT();
+    }
+    // Bulk staging: slot-private frame buffer and mbarrier; thread 0 of the slot issues copies.
+    float2* stage_slot = stage + slot * M;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(stage + S::STAGE) + 2 * slot;
+    const bool bulk = BULK && p.bulk_ok != 0;
+    uint32_t phase = 0;
+    if (bulk) {
+        if (t == 0) cta.bulk_init(bar);
+        cta.sync();
+        if (t == 0 && g < p.total_frames)
+            cta.bulk_copy(stage_slot, p.in + s * p.signal_stride + f * (int64_t)p.hop, N * (uint32_t)sizeof(float), bar);
     }
     for (int64_t base = (int64_t)cta.bid() * S::FPC; base < p.total_frames;
          base += stride_frames, g += stride_frames, s += ds, f += df) {
@@ -231,6 +245,16 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
                 }
                 MA_ASYNC_COMMIT();
             }
+        } else if (bulk) {
+            if (active) {
+                if (!cta.bulk_wait(bar, phase) && p.error_flag != nullptr) *p.error_flag = 1;
+                phase ^= 1;
+            }
+#pragma unroll
+            for (int q = 0; q < R; ++q) {
+                const float2 x = active ? stage_slot[t + q * T] : make_float2(0.f, 0.f);
+                v[q] = make_float2(x.x * wreg[q].x, x.y * wreg[q].y);
+            }
         } else if (ALIGNED) {
 #pragma unroll
             for (int q = 0; q < R; ++q) {
@@ -255,7 +279,18 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
         if constexpr (plan_pairable<M>()) {
             // Last stage with paired butterflies: bins k and M-k end up in the same thread,
             // so the Hermitian post-process needs no exchange.
-            fft_run<P, 1, false, true, Cta, TWALU>(v, t, sbuf0, S::BUF_STRIDE, parity, p.twM, cta, twb);
+            auto issue_next = [&]() {
+                if (bulk && t == 0 && g + stride_frames < p.total_frames) {
+                    int64_t fn = f + df, sn = s + ds;
+                    if (fn >= p.frames_per_signal) {
+                        fn -= p.frames_per_signal;
+                        ++sn;
+                    }
+                    cta.bulk_copy(stage_slot, p.in + sn * p.signal_stride + fn * (int64_t)p.hop,
+                                  N * (uint32_t)sizeof(float), bar);
+                }
+            };
+            fft_run<P, 1, false, true, Cta, TWALU>(v, t, sbuf0, S::BUF_STRIDE, parity, p.twM, cta, twb, issue_next);
             constexpr int rl = P::radix(P::NS - 1), NBL = R / rl, NL = M / rl;
 #pragma unroll
             for (int c = 0; c < NBL / 2; ++c) {
@@ -329,15 +364,19 @@ struct C2RParams {
     int64_t partial_stride;     // float2 units between partial spectra
     float* tail;                // streaming convolution step: per-signal overlap tail (N/2 floats)
     const float* norm_mid;      // iSTFT: clamped window sums of the interior, indexed by position mod hop
+    const float* norm_mid_inv;  // iSTFT: their reciprocals
     const float2* twM;          // stage tables: FftPlanRev<M> when plan_pairable<M>(), else FftPlan<M>
     const float2* twN;
 };
 
-// Loads the pair (X[k], X[M-k]) of frame g for the inverse pre-process.
-MA_HD void c2r_load_pair(const C2RParams& p, int64_t s, int64_t f, int64_t g, int k, int M,
+// Loads the pair (X[k], X[M-k]) of frame g for the inverse pre-process.  LAYOUT >= 0 fixes the
+// layout at compile time (-1: read p.layout).  x is the frame's first bin for the half layouts.
+template <int LAYOUT>
+MA_HD void c2r_load_pair(const C2RParams& p, const float2* __restrict__ x, int64_t g, int k, int M,
                          float2& a, float2& b) {
+    const int layout = LAYOUT >= 0 ? LAYOUT : p.layout;
     const int km = M - k;
-    if (p.layout == LAYOUT_FULL_SPLIT) {
+    if (layout == LAYOUT_FULL_SPLIT) {
         const int N = 2 * M;
         const float* re = p.in_a + g * (int64_t)N;
         const float* im = p.in_b + g * (int64_t)N;
@@ -354,14 +393,12 @@ MA_HD void c2r_load_pair(const C2RParams& p, int64_t s, int64_t f, int64_t g, in
             a = make_float2(0.5f * (xa.x + xan.x), 0.5f * (xa.y - xan.y));
             b = make_float2(0.5f * (xb.x + xbn.x), 0.5f * (xb.y - xbn.y));
         }
-    } else {
-        const float2* x = reinterpret_cast<const float2*>(p.in_a) + s * p.in_signal_stride +
-                          f * p.in_frame_stride;
-        if (p.layout == LAYOUT_HALF_PACKED) {
-            // Optionally the spectrum is the sum of n_partials partial spectra (the
-            // partition-split accumulators of the convolution step).
-            float2 xa = MA_LDG(x + k);
-            float2 xb = MA_LDG(x + (k == 0 ? 0 : km));
+    } else if (layout == LAYOUT_HALF_PACKED) {
+        // Optionally the spectrum is the sum of n_partials partial spectra (the
+        // partition-split accumulators of the convolution step).
+        float2 xa = MA_LDG(x + k);
+        float2 xb = MA_LDG(x + (k == 0 ? 0 : km));
+        if (LAYOUT < 0) {
             for (int i = 1; i < p.n_partials; ++i) {
                 const float2* xi = x + (int64_t)i * p.partial_stride;
                 const float2 ya = MA_LDG(xi + k);
@@ -369,20 +406,20 @@ MA_HD void c2r_load_pair(const C2RParams& p, int64_t s, int64_t f, int64_t g, in
                 xa.x += ya.x; xa.y += ya.y;
                 xb.x += yb.x; xb.y += yb.y;
             }
-            if (k == 0) {
-                a = make_float2(xa.x, 0.f);
-                b = make_float2(xa.y, 0.f);
-            } else {
-                a = xa;
-                b = xb;
-            }
+        }
+        if (k == 0) {
+            a = make_float2(xa.x, 0.f);
+            b = make_float2(xa.y, 0.f);
         } else {
-            a = MA_LDG(x + k);
-            b = MA_LDG(x + km);
-            if (k == 0) {
-                a.y = 0.f;
-                b.y = 0.f;
-            }
+            a = xa;
+            b = xb;
+        }
+    } else {
+        a = MA_LDG(x + k);
+        b = MA_LDG(x + km);
+        if (k == 0) {
+            a.y = 0.f;
+            b.y = 0.f;
         }
     }
 }
@@ -390,11 +427,13 @@ MA_HD void c2r_load_pair(const C2RParams& p, int64_t s, int64_t f, int64_t g, in
 // Pre-process + FFT of one frame: leaves v[q] = (x[2n+1], x[2n]) * N for n = t + q*T
 // (real and imaginary parts swapped: the inverse transform is run as a forward transform
 // of the swapped spectrum).
-template <int M, class Cta>
+template <int M, int LAYOUT, bool TWALU, class Cta>
 MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int64_t g, int t,
-                     float2* sbuf0, int buf_stride, int& parity, float2* v, Cta& cta) {
+                     float2* sbuf0, int buf_stride, int& parity, float2* v, Cta& cta,
+                     const float2* twb = nullptr, const float2* wherm = nullptr) {
     using P = FftPlan<M>;
     constexpr int R = P::R, T = P::T;
+    const float2* x = reinterpret_cast<const float2*>(p.in_a) + (active ? s * p.in_signal_stride + f * p.in_frame_stride : 0);
     if constexpr (plan_pairable<M>()) {
         // First stage with paired butterflies (reversed radix order): the thread that loads
         // X[i] and X[M-i] also consumes both Z[i] and Z[M-i]; no exchange for the pre-process.
@@ -407,11 +446,20 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
             float2* Bf = v + (2 * c + 1) * r0;
             const int j = c * T + t;
             if (j != 0) {
+                // all loads first, then the arithmetic: one memory round trip per frame
+                float2 a[r0], b[r0];
 #pragma unroll
                 for (int k = 0; k < r0; ++k) {
-                    float2 a = zero, b = zero, zk, zm;
-                    if (active) c2r_load_pair(p, s, f, g, j + k * N0, M, a, b);
-                    herm_pre(a, b, MA_LDG(p.twN + k * (N0 / 2 + 1) + j), zk, zm);
+                    a[k] = zero;
+                    b[k] = zero;
+                    if (active) c2r_load_pair<LAYOUT>(p, x, g, j + k * N0, M, a[k], b[k]);
+                }
+#pragma unroll
+                for (int k = 0; k < r0; ++k) {
+                    float2 zk, zm;
+                    const float2 wk = TWALU ? cmul(wherm[c], root_const<2 * r0>(k))
+                                            : MA_LDG(p.twN + k * (N0 / 2 + 1) + j);
+                    herm_pre(a[k], b[k], wk, zk, zm);
                     A[k] = make_float2(zk.y, zk.x);
                     Bf[r0 - 1 - k] = make_float2(zm.y, zm.x);
                 }
@@ -419,7 +467,7 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
 #pragma unroll
                 for (int k = 0; k <= r0 / 2; ++k) {
                     float2 a = zero, b = zero, zk, zm;
-                    if (active) c2r_load_pair(p, s, f, g, k * N0, M, a, b);
+                    if (active) c2r_load_pair<LAYOUT>(p, x, g, k * N0, M, a, b);
                     herm_pre(a, b, root_const<2 * r0>(k), zk, zm);
                     A[k] = make_float2(zk.y, zk.x);
                     if (k > 0) A[r0 - k] = make_float2(zm.y, zm.x);
@@ -427,14 +475,14 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
 #pragma unroll
                 for (int k = 0; k < r0 / 2; ++k) {
                     float2 a = zero, b = zero, zk, zm;
-                    if (active) c2r_load_pair(p, s, f, g, N0 / 2 + k * N0, M, a, b);
+                    if (active) c2r_load_pair<LAYOUT>(p, x, g, N0 / 2 + k * N0, M, a, b);
                     herm_pre(a, b, MA_LDG(p.twN + k * (N0 / 2 + 1) + N0 / 2), zk, zm);
                     Bf[k] = make_float2(zk.y, zk.x);
                     Bf[r0 - 1 - k] = make_float2(zm.y, zm.x);
                 }
             }
         }
-        fft_run<PR, 1, true, false, Cta>(v, t, sbuf0, buf_stride, parity, p.twM, cta);
+        fft_run<PR, 1, true, false, Cta, TWALU>(v, t, sbuf0, buf_stride, parity, p.twM, cta, twb);
     } else {
         float2* sb = sbuf0 + parity * buf_stride;
         parity ^= 1;
@@ -443,7 +491,7 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
             const int k = t + q * T;
             if (k > M / 2) continue;
             float2 a = make_float2(0.f, 0.f), b = a;
-            if (active) c2r_load_pair(p, s, f, g, k, M, a, b);
+            if (active) c2r_load_pair<LAYOUT>(p, x, g, k, M, a, b);
             const float2 w = MA_LDG(p.twN + k);
             float2 zk, zm;
             herm_pre(a, b, w, zk, zm);
@@ -457,12 +505,26 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
     }
 }
 
-// Plain batched inverse: out[g][2n], out[g][2n+1].
-template <int M, class Cta>
+// Loads the frame-invariant twiddles of the register-resident mode for the inverse kernels.
+template <int M>
+MA_HD void c2r_load_tw_regs(const C2RParams& p, int t, float2* twb, float2* wherm) {
+    if constexpr (plan_pairable<M>()) {
+        using PR = FftPlanRev<M>;
+        constexpr int NB0 = PR::R / PR::radix(0);
+        load_tw_bases<PR, false>(twb, t, p.twM);
+#pragma unroll
+        for (int c = 0; c < NB0 / 2; ++c) wherm[c] = MA_LDG(p.twN + (c * PR::T + t));
+    }
+}
+
+// Plain batched inverse: out[g][2n], out[g][2n+1].  LAYOUT >= 0: layout fixed at compile time
+// and (for paired plans) twiddles kept in registers.
+template <int M, int LAYOUT, class Cta>
 MA_HD void c2r_body(const C2RParams& p, Cta& cta, float2* smem) {
     using P = FftPlan<M>;
     using S = CtaShape<M>;
     constexpr int R = P::R, T = P::T, N = 2 * M;
+    constexpr bool TWALU = LAYOUT >= 0 && plan_pairable<M>();
     const int tid = cta.tid();
     const int slot = tid / T;
     const int t = tid % T;
@@ -470,14 +532,24 @@ MA_HD void c2r_body(const C2RParams& p, Cta& cta, float2* smem) {
     int parity = 0;
     const float scale = 1.0f / (float)N;
     const int64_t total = p.n_signals * p.frames_per_signal;
+    float2 twb[tw_base_count<FftPlanRev<M>>()];
+    float2 wherm[R / 2 + 1];
+    if constexpr (TWALU) c2r_load_tw_regs<M>(p, t, twb, wherm);
+    const int64_t stride_frames = (int64_t)cta.nblocks() * S::FPC;
+    int64_t g = (int64_t)cta.bid() * S::FPC + slot;
+    int64_t s = g / p.frames_per_signal;
+    int64_t f = g - s * p.frames_per_signal;
+    const int64_t ds = stride_frames / p.frames_per_signal;
+    const int64_t df = stride_frames - ds * p.frames_per_signal;
     for (int64_t base = (int64_t)cta.bid() * S::FPC; base < total;
-         base += (int64_t)cta.nblocks() * S::FPC) {
-        const int64_t g = base + slot;
-        const bool active = g < total;
-        const int64_t s = active ? g / p.frames_per_signal : 0;
-        const int64_t f = active ? g - s * p.frames_per_signal : 0;
+         base += stride_frames, g += stride_frames, s += ds, f += df) {
+        if (f >= p.frames_per_signal) {
+            f -= p.frames_per_signal;
+            ++s;
+        }
+        const bool active = S::FPC == 1 ? true : g < total;
         float2 v[R];
-        c2r_frame<M, Cta>(p, active, s, f, g, t, sbuf0, S::BUF_STRIDE, parity, v, cta);
+        c2r_frame<M, LAYOUT, TWALU, Cta>(p, active, s, f, g, t, sbuf0, S::BUF_STRIDE, parity, v, cta, twb, wherm);
         if (active && p.tail == nullptr) {
             float2* o = reinterpret_cast<float2*>(p.out + g * (int64_t)N);
 #pragma unroll
@@ -570,7 +642,7 @@ MA_HD void istft_body(const C2RParams& p, Cta& cta, float2* smem) {
         cta.sync();
         for (int64_t f = fh; f < f1; ++f) {
             float2 v[R];
-            c2r_frame<M, Cta>(p, true, s, f, s * F + f, t, smem, ELEMS, parity, v, cta);
+            c2r_frame<M, -1, false, Cta>(p, true, s, f, s * F + f, t, smem, ELEMS, parity, v, cta);
             const int64_t start = f * (int64_t)hop;
             if ((hop & 1) == 0) {
                 float2* ring2 = reinterpret_cast<float2*>(ring);
@@ -620,21 +692,20 @@ MA_HD void istft_body(const C2RParams& p, Cta& cta, float2* smem) {
 
 // Fast iSTFT for paired plans when hop/2 is a multiple of T (e.g. N = 4096, hop = 1024) and the
 // spectra are in a half layout.  Differences from istft_body:
-//  * the frame's bins are prefetched one frame ahead with asynchronous global->shared copies
-//    into thread-private slots (each thread copies exactly the pairs X[i], X[M-i] it will
-//    consume), so HBM latency overlaps the previous frame's transform and costs no registers;
 //  * thread t only ever touches overlap-add positions congruent to t modulo T, so the ring is
-//    thread-private too: no barrier for accumulate or emit, only the two FFT exchanges remain;
-//  * completed samples go straight from registers to HBM.
-// smem: 2 exchange buffers | staging [2*(R/2+1)][T] float2 | ring [R][T] float2.
+//    thread-private: no barrier for accumulate or emit, only the two FFT exchanges remain;
+//  * completed samples go straight from registers to HBM, multiplied by the precomputed
+//    reciprocal of the interior window sum (frames near the ends of the signal take the exact
+//    per-sample path);
+//  * twiddles live in registers (power chains) and the layout is fixed at compile time.
+// OVT is the overlap count N/hop when fixed at compile time (0: read it from p.hop).
+// smem: 2 exchange buffers | ring [R][T] float2.
 template <int M>
 struct IstftFastShape {
     using P = FftPlan<M>;
     static constexpr int ELEMS = smem_elems_per_fft<M, 1>();
-    static constexpr int NPAIR = P::R / 2 + 1;
-    static constexpr int STAGE = 2 * NPAIR * P::T;
     static constexpr int RING = P::R * P::T;
-    static constexpr int SMEM_BYTES = (2 * ELEMS + STAGE + RING) * (int)sizeof(float2);
+    static constexpr int SMEM_BYTES = (2 * ELEMS + RING) * (int)sizeof(float2);
 };
 
 // Whether istft_fast_body serves these parameters.
@@ -654,23 +725,19 @@ inline bool istft_fast_ok(const C2RParams& p) {
     }
 }
 
-template <int M, class Cta>
+template <int M, int LAYOUT, int OVT, class Cta>
 MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
     using P = FftPlan<M>;
-    using PR = FftPlanRev<M>;
     using SH = IstftFastShape<M>;
     constexpr int R = P::R, T = P::T, N = 2 * M;
-    constexpr int r0 = PR::radix(0), NB0 = R / r0, N0 = M / r0;
-    float2* stage = smem + 2 * SH::ELEMS;
-    float2* ring = stage + SH::STAGE;
+    float2* ring = smem + 2 * SH::ELEMS;
     const int t = cta.tid();
     int parity = 0;
     const float scale = 1.0f / (float)N;
     const int hop = p.hop;
-    const int h = hop / (2 * T);  // ring slots completed per frame
+    const int h = OVT > 0 ? R / OVT : hop / (2 * T);  // ring slots completed per frame
     const int64_t F = p.frames_per_signal;
     const bool normalise = !(p.window == nullptr && p.floor < 0.f);
-    const bool packed = p.layout == LAYOUT_HALF_PACKED;
 
     float2 wreg[R];
 #pragma unroll
@@ -681,40 +748,9 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
         else
             wreg[q] = make_float2(scale, scale);
     }
-
-    // Frame-invariant twiddles in registers: one base per butterfly for the FFT stages and
-    // W_N^j for the Hermitian pre-process.
-    float2 twb[tw_base_count<PR>()];
-    load_tw_bases<PR, false>(twb, t, p.twM);
-    float2 wherm[NB0 / 2 > 0 ? NB0 / 2 : 1];
-#pragma unroll
-    for (int cc = 0; cc < NB0 / 2; ++cc) wherm[cc] = MA_LDG(p.twN + (cc * T + t));
-
-    // Queue the copies of one frame's bins into this thread's staging slots.
-    auto prefetch = [&](int64_t s, int64_t f) {
-        const float2* x = reinterpret_cast<const float2*>(p.in_a) + s * p.in_signal_stride + f * p.in_frame_stride;
-#pragma unroll
-        for (int c = 0; c < NB0 / 2; ++c) {
-            const int j = c * T + t;
-            if (j != 0) {
-#pragma unroll
-                for (int k = 0; k < r0; ++k) {
-                    const int i = j + k * N0;
-                    MA_ASYNC_COPY8(stage + ((c * r0 + k) * 2 + 0) * T + t, x + i);
-                    MA_ASYNC_COPY8(stage + ((c * r0 + k) * 2 + 1) * T + t, x + (M - i));
-                }
-            } else {
-#pragma unroll
-                for (int n = 0; n <= r0; ++n) {
-                    const int i = n <= r0 / 2 ? n * N0 : N0 / 2 + (n - r0 / 2 - 1) * N0;
-                    const int slot = n < r0 ? n : R / 2;
-                    MA_ASYNC_COPY8(stage + (slot * 2 + 0) * T + t, x + i);
-                    MA_ASYNC_COPY8(stage + (slot * 2 + 1) * T + t, x + (i == 0 ? (packed ? 0 : M) : M - i));
-                }
-            }
-        }
-        MA_ASYNC_COMMIT();
-    };
+    float2 twb[tw_base_count<FftPlanRev<M>>()];
+    float2 wherm[R / 2 + 1];
+    c2r_load_tw_regs<M>(p, t, twb, wherm);
 
     const int64_t n_chunks = (int64_t)p.chunks_per_signal;
     const int64_t total_chunks = p.n_signals * n_chunks;
@@ -732,64 +768,17 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
         if (fh < 0) fh = 0;
 #pragma unroll
         for (int q = 0; q < R; ++q) ring[q * T + t] = make_float2(0.f, 0.f);
-        prefetch(s, fh);
         for (int64_t f = fh; f < f1; ++f) {
             float2 v[R];
-            MA_ASYNC_WAIT_ALL();
-            // Hermitian pre-process out of the staging slots (same mapping as the prefetch).
-#pragma unroll
-            for (int cc = 0; cc < NB0 / 2; ++cc) {
-                float2* A = v + (2 * cc) * r0;
-                float2* Bf = v + (2 * cc + 1) * r0;
-                const int j = cc * T + t;
-                if (j != 0) {
-#pragma unroll
-                    for (int k = 0; k < r0; ++k) {
-                        const float2 a = stage[((cc * r0 + k) * 2 + 0) * T + t];
-                        const float2 b = stage[((cc * r0 + k) * 2 + 1) * T + t];
-                        float2 zk, zm;
-                        herm_pre(a, b, cmul(wherm[cc], root_const<2 * r0>(k)), zk, zm);
-                        A[k] = make_float2(zk.y, zk.x);
-                        Bf[r0 - 1 - k] = make_float2(zm.y, zm.x);
-                    }
-                } else {
-#pragma unroll
-                    for (int n = 0; n <= r0; ++n) {
-                        const int slot = n < r0 ? n : R / 2;
-                        float2 a = stage[(slot * 2 + 0) * T + t];
-                        float2 b = stage[(slot * 2 + 1) * T + t];
-                        float2 zk, zm;
-                        if (n <= r0 / 2) {  // butterfly 0: bins n*N0 and M - n*N0
-                            if (n == 0) {
-                                if (packed) {
-                                    b = make_float2(a.y, 0.f);
-                                    a = make_float2(a.x, 0.f);
-                                } else {
-                                    a.y = 0.f;
-                                    b.y = 0.f;
-                                }
-                            }
-                            herm_pre(a, b, root_const<2 * r0>(n), zk, zm);
-                            A[n] = make_float2(zk.y, zk.x);
-                            if (n > 0) A[r0 - n] = make_float2(zm.y, zm.x);
-                        } else {  // butterfly N0/2: bins N0/2 + k*N0 and their mirrors
-                            const int k = n - r0 / 2 - 1;
-                            herm_pre(a, b, MA_LDG(p.twN + k * (N0 / 2 + 1) + N0 / 2), zk, zm);
-                            Bf[k] = make_float2(zk.y, zk.x);
-                            Bf[r0 - 1 - k] = make_float2(zm.y, zm.x);
-                        }
-                    }
-                }
-            }
-            if (f + 1 < f1) prefetch(s, f + 1);  // staging slots are free again (thread-private)
-
-            fft_run<PR, 1, true, false, Cta, true>(v, t, smem, SH::ELEMS, parity, p.twM, cta, twb);
+            c2r_frame<M, LAYOUT, true, Cta>(p, true, s, f, s * F + f, t, smem, SH::ELEMS, parity, v, cta, twb, wherm);
 
             // v[q] = (x[2n+1], x[2n]) * N for n = t + q*T.  Overlap-add in this thread's ring column.
             const int64_t start = f * (int64_t)hop;
             const int rot = (int)((f * (int64_t)h) & (R - 1));
             const bool last = f == F - 1;
             const bool emit = f >= f0;
+            // every sample this frame completes has all its overlapping frames present
+            const bool interior = !last && start >= (int64_t)(N - hop);
             float* out = p.out + s * p.out_signal_stride + start;
 #pragma unroll
             for (int q = 0; q < R; ++q) {
@@ -805,22 +794,18 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
                         const int i0 = 2 * (t + q * T);
                         float2 r = acc;
                         if (normalise) {
-                            const int64_t o = start + i0;
-                            float w0, w1;
-                            if (o >= (int64_t)(N - hop) && o + 1 < F * (int64_t)hop) {
-                                const float2 ws = MA_LDG(reinterpret_cast<const float2*>(p.norm_mid + i0));
-                                w0 = ws.x;
-                                w1 = ws.y;
+                            if (interior) {
+                                const float2 inv = MA_LDG(reinterpret_cast<const float2*>(p.norm_mid_inv + i0));
+                                r.x = acc.x * inv.x;
+                                r.y = acc.y * inv.y;
                             } else {
-                                w0 = window_sum_at(p.window, o, N, hop, F, p.floor);
-                                w1 = window_sum_at(p.window, o + 1, N, hop, F, p.floor);
+                                const int64_t o = start + i0;
+                                r.x = acc.x / window_sum_at(p.window, o, N, hop, F, p.floor);
+                                r.y = acc.y / window_sum_at(p.window, o + 1, N, hop, F, p.floor);
                             }
-                            r.x = acc.x / w0;
-                            r.y = acc.y / w1;
                         }
                         *reinterpret_cast<float2*>(out + i0) = r;
                     }
-                    if (last) *slot = make_float2(0.f, 0.f);
                 } else {
                     *slot = acc;
                 }

@@ -1,4 +1,5 @@
 // __global__ wrappers and launchers for the in-shared-memory transforms (N <= 8192).
+#include "bulk_copy.cuh"
 #include "fft_plan.h"
 #include "host_tables.h"
 
@@ -9,6 +10,11 @@ struct DevCta {
     __device__ __forceinline__ int bid() const { return blockIdx.x; }
     __device__ __forceinline__ int nblocks() const { return gridDim.x; }
     __device__ __forceinline__ void sync() { __syncthreads(); }
+    __device__ __forceinline__ void bulk_init(uint64_t* bar) { bulk_barrier_init(bar); }
+    __device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+        bulk_copy_g2s(dst, src, bytes, bar);
+    }
+    __device__ __forceinline__ bool bulk_wait(uint64_t* bar, uint32_t parity) { return bulk_barrier_wait(bar, parity); }
 };
 
 extern __shared__ float4 ma_dyn_smem[];
@@ -19,10 +25,10 @@ __global__ void __launch_bounds__(CtaShape<M>::THREADS, 512 / CtaShape<M>::THREA
     r2c_body<M, ALIGNED, LAYOUT, MAGK, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
 }
 
-template <int M>
+template <int M, int LAYOUT>
 __global__ void __launch_bounds__(CtaShape<M>::THREADS, 512 / CtaShape<M>::THREADS) c2r_kernel(const C2RParams p) {
     DevCta cta;
-    c2r_body<M, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
+    c2r_body<M, LAYOUT, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
 }
 
 template <int M>
@@ -31,11 +37,12 @@ __global__ void __launch_bounds__(FftPlan<M>::T, (512 / FftPlan<M>::T) > 16 ? 16
     istft_body<M, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
 }
 
-template <int M>
-__global__ void __launch_bounds__(FftPlan<M>::T, (384 / FftPlan<M>::T) > 16 ? 16 : ((384 / FftPlan<M>::T) > 0 ? (384 / FftPlan<M>::T) : 1))
+template <int M, int LAYOUT, int OVT>
+__global__ void __launch_bounds__(FftPlan<M>::T, (512 / FftPlan<M>::T) > 16 ? 16 : (512 / FftPlan<M>::T))
 istft_fast_kernel(const C2RParams p) {
     DevCta cta;
-    if constexpr (plan_pairable<M>()) istft_fast_body<M, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
+    if constexpr (plan_pairable<M>())
+        istft_fast_body<M, LAYOUT, OVT, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
 }
 
 // Resident CTAs per SM for a kernel (cached per instantiation and device), after raising
@@ -55,7 +62,7 @@ static ma_status launch_r2c_t(ma_fft_plan* plan, const R2CParams& p) {
     static int per_sm[64] = {0};
     ma_context* ctx = plan->ctx;
     int& occ = per_sm[ctx->device & 63];
-    constexpr size_t smem = S::SMEM_BYTES;
+    constexpr size_t smem = (ALIGNED && LAYOUT >= 0 && plan_pairable<M>()) ? S::SMEM_BYTES_PREFETCH : S::SMEM_BYTES;
     if (occ == 0) MA_TRY(occupancy(r2c_kernel<M, ALIGNED, LAYOUT, MAGK>, S::THREADS, smem, &occ));
     int64_t want = (p.total_frames + S::FPC - 1) / S::FPC;
     int64_t cap = (int64_t)ctx->sm_count * occ;
@@ -91,6 +98,8 @@ ma_status launch_r2c_small(ma_fft_plan* plan, R2CParams p) {
     const int64_t last_end = (p.frames_per_signal - 1) * (int64_t)p.hop + n;
     const bool aligned = ((uintptr_t)p.in % 8 == 0) && (p.signal_stride % 2 == 0) && (p.hop % 2 == 0) &&
                          p.frame_valid >= n && last_end <= p.signal_len;
+    p.bulk_ok = (aligned && (uintptr_t)p.in % 16 == 0 && p.signal_stride % 4 == 0 && p.hop % 4 == 0 && n % 4 == 0) ? 1 : 0;
+    p.error_flag = plan->ctx->d_error_flag;
     ma_status st = MA_ERR_UNSUPPORTED;
     // Aligned launches of the paired plans get kernels with the layout and the magnitude kind
     // fixed at compile time (no per-store branches); everything else decides at run time.
@@ -101,20 +110,33 @@ ma_status launch_r2c_small(ma_fft_plan* plan, R2CParams p) {
     return st;
 }
 
-template <int M>
+template <int M, int LAYOUT>
 static ma_status launch_c2r_t(ma_fft_plan* plan, const C2RParams& p) {
     using S = CtaShape<M>;
     static int per_sm[64] = {0};
     ma_context* ctx = plan->ctx;
     int& occ = per_sm[ctx->device & 63];
-    if (occ == 0) MA_TRY(occupancy(c2r_kernel<M>, S::THREADS, S::SMEM_BYTES, &occ));
+    if (occ == 0) MA_TRY(occupancy(c2r_kernel<M, LAYOUT>, S::THREADS, S::SMEM_BYTES, &occ));
     const int64_t total = p.n_signals * p.frames_per_signal;
     int64_t want = (total + S::FPC - 1) / S::FPC;
     int64_t cap = (int64_t)ctx->sm_count * occ;
     int grid = (int)(want < cap ? want : cap);
     if (grid < 1) return MA_OK;
-    c2r_kernel<M><<<grid, S::THREADS, S::SMEM_BYTES, ctx->stream>>>(p);
+    c2r_kernel<M, LAYOUT><<<grid, S::THREADS, S::SMEM_BYTES, ctx->stream>>>(p);
     return after_launch(ctx);
+}
+
+template <int M>
+static ma_status launch_c2r_variant(ma_fft_plan* plan, const C2RParams& p) {
+    if constexpr (plan_pairable<M>()) {
+        // plain batched inverse of a paired plan: layout fixed at compile time
+        if (p.tail == nullptr && p.n_partials <= 1) {
+            if (p.layout == LAYOUT_HALF_INTERLEAVED) return launch_c2r_t<M, LAYOUT_HALF_INTERLEAVED>(plan, p);
+            if (p.layout == LAYOUT_HALF_PACKED) return launch_c2r_t<M, LAYOUT_HALF_PACKED>(plan, p);
+            if (p.layout == LAYOUT_FULL_SPLIT) return launch_c2r_t<M, LAYOUT_FULL_SPLIT>(plan, p);
+        }
+    }
+    return launch_c2r_t<M, -1>(plan, p);
 }
 
 ma_status launch_c2r_small(ma_fft_plan* plan, C2RParams p) {
@@ -122,7 +144,7 @@ ma_status launch_c2r_small(ma_fft_plan* plan, C2RParams p) {
     p.twN = plan->d_twN;
     if (p.n_signals * p.frames_per_signal <= 0) return MA_OK;
     ma_status st = MA_ERR_UNSUPPORTED;
-#define RUN(MM) st = launch_c2r_t<MM>(plan, p);
+#define RUN(MM) st = launch_c2r_variant<MM>(plan, p);
     MA_DISPATCH_M(plan->m, RUN)
 #undef RUN
     return st;
@@ -137,9 +159,17 @@ static ma_status launch_istft_t(ma_fft_plan* plan, C2RParams& p) {
     static int per_sm[2][64] = {{0}, {0}};
     ma_context* ctx = plan->ctx;
     int& occ = per_sm[fast ? 1 : 0][ctx->device & 63];
+    const int ov = fast ? (2 * M) / p.hop : 0;
+    const int variant = !fast ? 0 : (p.layout == LAYOUT_HALF_INTERLEAVED ? 1 : 3) + (ov == 4 ? 1 : 0);
     if (occ == 0) {
-        if (fast) MA_TRY(occupancy(istft_fast_kernel<M>, T, smem, &occ));
+        if (fast) MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_INTERLEAVED, 4>, T, smem, &occ));
         else MA_TRY(occupancy(istft_kernel<M>, T, smem, &occ));
+        if (fast) {  // the other variants share the footprint; raise their shared-memory limit too
+            int dummy;
+            MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_INTERLEAVED, 0>, T, smem, &dummy));
+            MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_PACKED, 4>, T, smem, &dummy));
+            MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_PACKED, 0>, T, smem, &dummy));
+        }
     }
     // Chunks per signal: enough CTAs to fill the device a few times over, but chunks long
     // enough that the recomputed lead-in frames stay a small fraction.
@@ -154,17 +184,24 @@ static ma_status launch_istft_t(ma_fft_plan* plan, C2RParams& p) {
     const int64_t total = chunks * p.n_signals;
     int grid = (int)(total < cap ? total : cap);
     if (grid < 1) return MA_OK;
-    if (fast) istft_fast_kernel<M><<<grid, T, smem, ctx->stream>>>(p);
-    else istft_kernel<M><<<grid, T, smem, ctx->stream>>>(p);
+    switch (variant) {
+        case 1: istft_fast_kernel<M, LAYOUT_HALF_INTERLEAVED, 0><<<grid, T, smem, ctx->stream>>>(p); break;
+        case 2: istft_fast_kernel<M, LAYOUT_HALF_INTERLEAVED, 4><<<grid, T, smem, ctx->stream>>>(p); break;
+        case 3: istft_fast_kernel<M, LAYOUT_HALF_PACKED, 0><<<grid, T, smem, ctx->stream>>>(p); break;
+        case 4: istft_fast_kernel<M, LAYOUT_HALF_PACKED, 4><<<grid, T, smem, ctx->stream>>>(p); break;
+        default: istft_kernel<M><<<grid, T, smem, ctx->stream>>>(p); break;
+    }
     return after_launch(ctx);
 }
 
 // Rebuilds the interior normaliser table (host_tables.h) when the floor changes.
 static ma_status update_norm_table(ma_fft_plan* plan, int hop, float floor) {
     if (plan->norm_floor == floor) return MA_OK;
-    const std::vector<float> tab =
+    std::vector<float> tab =
         make_norm_table(plan->h_window.empty() ? nullptr : plan->h_window.data(), plan->n, hop, floor);
-    MA_CUDA(cudaMemcpyAsync(plan->d_norm, tab.data(), sizeof(float) * (size_t)hop, cudaMemcpyHostToDevice,
+    tab.resize(2 * (size_t)hop);
+    for (int r = 0; r < hop; ++r) tab[(size_t)(hop + r)] = 1.0f / tab[(size_t)r];
+    MA_CUDA(cudaMemcpyAsync(plan->d_norm, tab.data(), 2 * sizeof(float) * (size_t)hop, cudaMemcpyHostToDevice,
                             plan->ctx->stream));
     MA_CUDA(cudaStreamSynchronize(plan->ctx->stream));
     plan->norm_floor = floor;
@@ -180,6 +217,7 @@ ma_status launch_istft_small(ma_fft_plan* plan, C2RParams p) {
         MA_TRY(update_norm_table(plan, p.hop, p.floor));
     }
     p.norm_mid = plan->d_norm;
+    p.norm_mid_inv = plan->d_norm + plan->hop;
     ma_status st = MA_ERR_UNSUPPORTED;
 #define RUN(MM) st = launch_istft_t<MM>(plan, p);
     MA_DISPATCH_M(plan->m, RUN)

@@ -21,6 +21,8 @@ struct ma_context {
     int fault_site = -1;          // host-side fault injection: next call reaching the site fails
     int fault_error = 0;
     char name[256] = {0};
+    int32_t* d_error_flag = nullptr;  // set by a kernel whose bounded wait ran out
+    int32_t* h_error_flag = nullptr;  // pinned mirror read at synchronisation
 };
 
 namespace ma {

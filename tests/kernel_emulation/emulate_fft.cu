@@ -26,6 +26,7 @@ int emul_r2c(int n, int aligned, const float* in, long long signal_stride, long 
     p.out_signal_stride = out_signal_stride; p.out_frame_stride = out_frame_stride;
     p.layout = layout; p.mag_kind = mag_kind; p.db_scale = db_scale;
     p.twM = twM.data(); p.twN = twN.data();
+    p.bulk_ok = (aligned && hop % 4 == 0 && signal_stride % 4 == 0 && n % 4 == 0) ? 1 : 0;
     int rc = -1;
 #define RUN(MM)                                                                              \
     {                                                                                        \
@@ -58,7 +59,8 @@ int emul_c2r(int n, const float* in_a, const float* in_b, long long in_signal_st
     {                                                                                        \
         using S = CtaShape<MM>;                                                              \
         run_grid(nblocks, S::THREADS, S::SMEM_BYTES, [&](HostCta& cta, void* sm) {           \
-            c2r_body<MM, HostCta>(p, cta, (float2*)sm);                                      \
+            if (layout == 0) c2r_body<MM, 0, HostCta>(p, cta, (float2*)sm);                  \
+            else c2r_body<MM, -1, HostCta>(p, cta, (float2*)sm);                             \
         });                                                                                  \
         rc = 0;                                                                              \
     }
@@ -80,7 +82,10 @@ int emul_istft(int n, int hop, const float* in_a, const float* in_b, long long i
     p.window = window; p.out = out; p.out_signal_stride = out_signal_stride; p.out_len = out_len;
     p.floor = floor; p.chunks_per_signal = chunks_per_signal;
     auto norm = make_norm_table(window, n, hop, floor);
+    norm.resize(2 * (size_t)hop);
+    for (int r = 0; r < hop; ++r) norm[(size_t)(hop + r)] = 1.0f / norm[(size_t)r];
     p.norm_mid = norm.data();
+    p.norm_mid_inv = norm.data() + hop;
     p.twM = twM.data(); p.twN = twN.data();
     int rc = -1;
     int used_fast = 0;
@@ -93,7 +98,8 @@ int emul_istft(int n, int hop, const float* in_a, const float* in_b, long long i
         used_fast = fast ? 1 : 0;                                                                \
         run_grid(nblocks, FftPlan<MM>::T, smem, [&](HostCta& cta, void* sm) {                    \
             if constexpr (plan_pairable<MM>()) {                                                 \
-                if (fast) { istft_fast_body<MM, HostCta>(p, cta, (float2*)sm); return; }         \
+                if (fast && 2 * MM / hop == 4) { istft_fast_body<MM, 0, 4, HostCta>(p, cta, (float2*)sm); return; } \
+                if (fast) { istft_fast_body<MM, 0, 0, HostCta>(p, cta, (float2*)sm); return; }   \
             }                                                                                    \
             istft_body<MM, HostCta>(p, cta, (float2*)sm);                                        \
         });                                                                                      \

@@ -4,6 +4,8 @@
 // never linked into the product library.
 #pragma once
 #include <pthread.h>
+#include <sched.h>
+#include <string.h>
 
 #include <functional>
 #include <thread>
@@ -16,6 +18,22 @@ struct HostCta {
     int bid() const { return bid_; }
     int nblocks() const { return nblocks_; }
     void sync() { pthread_barrier_wait(bar_); }
+    // Bulk asynchronous copy emulated as an immediate copy that then bumps a completion count
+    // in the barrier word.  The producer is never more than one copy ahead of the waiters, so
+    // the k-th wait (parity k & 1) is satisfied exactly when the count's low bit differs from it.
+    void bulk_init(void* bar) { __atomic_store_n((unsigned long long*)bar, 0ull, __ATOMIC_SEQ_CST); }
+    void bulk_copy(void* dst, const void* src, unsigned bytes, void* bar) {
+        memcpy(dst, src, bytes);
+        __atomic_add_fetch((unsigned long long*)bar, 1ull, __ATOMIC_SEQ_CST);
+    }
+    bool bulk_wait(void* bar, unsigned parity) {
+        for (long i = 0; i < (1L << 34); ++i) {
+            if ((__atomic_load_n((unsigned long long*)bar, __ATOMIC_SEQ_CST) & 1ull) == (unsigned long long)(parity ^ 1u))
+                return true;
+            sched_yield();
+        }
+        return false;
+    }
 };
 
 // Runs `body(cta, smem)` for every thread of every block of a 1-D grid, blocks one
