@@ -58,6 +58,9 @@ struct CtaShape {
     // Prefetching forward kernels add a staging frame per slot plus one mbarrier per slot.
     static constexpr int STAGE = FftPlan<M>::R * THREADS;
     static constexpr int SMEM_BYTES_PREFETCH = SMEM_BYTES + STAGE * (int)sizeof(float2) + 16 * FPC;
+    // Staged inverse kernels: one spectrum row (M+2 bins with the alignment slack) per slot.
+    static constexpr int ROW = M + 2;
+    static constexpr int SMEM_BYTES_STAGED = SMEM_BYTES + FPC * ROW * (int)sizeof(float2) + 16 * FPC;
 };
 
 // Hermitian post-process of one pair: a = Z[k], b = Z[(M-k) mod M], w = exp(-2 pi i k/N).
@@ -365,15 +368,16 @@ struct C2RParams {
     float* tail;                // streaming convolution step: per-signal overlap tail (N/2 floats)
     const float* norm_mid;      // iSTFT: clamped window sums of the interior, indexed by position mod hop
     const float* norm_mid_inv;  // iSTFT: their reciprocals
+    int32_t* error_flag;        // set to 1 when a bounded wait ran out
     const float2* twM;          // stage tables: FftPlanRev<M> when plan_pairable<M>(), else FftPlan<M>
     const float2* twN;
 };
 
 // Loads the pair (X[k], X[M-k]) of frame g for the inverse pre-process.  LAYOUT >= 0 fixes the
 // layout at compile time (-1: read p.layout).  x is the frame's first bin for the half layouts.
-template <int LAYOUT>
-MA_HD void c2r_load_pair(const C2RParams& p, const float2* __restrict__ x, int64_t g, int k, int M,
-                         float2& a, float2& b) {
+template <int LAYOUT, bool STAGED = false>
+MA_HD void c2r_load_pair(const C2RParams& p, const float2* x, int64_t g, int k, int M,
+                         float2& a, float2& b, const float2* xg = nullptr) {
     const int layout = LAYOUT >= 0 ? LAYOUT : p.layout;
     const int km = M - k;
     if (layout == LAYOUT_FULL_SPLIT) {
@@ -396,8 +400,8 @@ MA_HD void c2r_load_pair(const C2RParams& p, const float2* __restrict__ x, int64
     } else if (layout == LAYOUT_HALF_PACKED) {
         // Optionally the spectrum is the sum of n_partials partial spectra (the
         // partition-split accumulators of the convolution step).
-        float2 xa = MA_LDG(x + k);
-        float2 xb = MA_LDG(x + (k == 0 ? 0 : km));
+        float2 xa = STAGED ? x[k] : MA_LDG(x + k);
+        float2 xb = STAGED ? x[k == 0 ? 0 : km] : MA_LDG(x + (k == 0 ? 0 : km));
         if (LAYOUT < 0) {
             for (int i = 1; i < p.n_partials; ++i) {
                 const float2* xi = x + (int64_t)i * p.partial_stride;
@@ -415,8 +419,9 @@ MA_HD void c2r_load_pair(const C2RParams& p, const float2* __restrict__ x, int64
             b = xb;
         }
     } else {
-        a = MA_LDG(x + k);
-        b = MA_LDG(x + km);
+        a = STAGED ? x[k] : MA_LDG(x + k);
+        if (STAGED && k == 0) b = MA_LDG(xg + M);  // bin M is not staged
+        else b = STAGED ? x[km] : MA_LDG(x + km);
         if (k == 0) {
             a.y = 0.f;
             b.y = 0.f;
@@ -424,16 +429,41 @@ MA_HD void c2r_load_pair(const C2RParams& p, const float2* __restrict__ x, int64
     }
 }
 
+// A spectrum row (half layouts) prepared for a bulk copy of 16-byte granularity.  Only bins
+// 0..M-1 are staged (the thread that needs bin M reads it from HBM itself), so the copy is
+// M bins when the row starts on a 16-byte boundary and M+2 bins, beginning one bin early
+// (shift = 1), when it starts on an odd 8-byte boundary; either way it stays inside the row's
+// own neighbourhood and never runs past the end of the array.
+struct StagedRow {
+    const float2* row;   // first bin of the row (global)
+    const float2* src;   // 16-byte aligned start of the copy
+    uint32_t bytes;      // multiple of 16
+    int shift;           // bins between src and row (0 or 1)
+};
+
+template <int M>
+MA_HD StagedRow staged_row(const C2RParams& p, int64_t s, int64_t f) {
+    StagedRow r;
+    r.row = reinterpret_cast<const float2*>(p.in_a) + s * p.in_signal_stride + f * p.in_frame_stride;
+    r.shift = (int)((reinterpret_cast<uintptr_t>(r.row) >> 3) & 1);
+    r.src = r.row - r.shift;
+    r.bytes = (uint32_t)(M + 2 * r.shift) * (uint32_t)sizeof(float2);
+    return r;
+}
+
 // Pre-process + FFT of one frame: leaves v[q] = (x[2n+1], x[2n]) * N for n = t + q*T
 // (real and imaginary parts swapped: the inverse transform is run as a forward transform
 // of the swapped spectrum).
-template <int M, int LAYOUT, bool TWALU, class Cta>
+template <int M, int LAYOUT, bool TWALU, class Cta, bool STAGED = false, class Hook = NoHook>
 MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int64_t g, int t,
                      float2* sbuf0, int buf_stride, int& parity, float2* v, Cta& cta,
-                     const float2* twb = nullptr, const float2* wherm = nullptr) {
+                     const float2* twb = nullptr, const float2* wherm = nullptr,
+                     const float2* staged = nullptr, const Hook& hook = Hook(), const float2* xg = nullptr) {
     using P = FftPlan<M>;
     constexpr int R = P::R, T = P::T;
-    const float2* x = reinterpret_cast<const float2*>(p.in_a) + (active ? s * p.in_signal_stride + f * p.in_frame_stride : 0);
+    const float2* x = STAGED ? staged
+                             : reinterpret_cast<const float2*>(p.in_a) +
+                                   (active ? s * p.in_signal_stride + f * p.in_frame_stride : 0);
     if constexpr (plan_pairable<M>()) {
         // First stage with paired butterflies (reversed radix order): the thread that loads
         // X[i] and X[M-i] also consumes both Z[i] and Z[M-i]; no exchange for the pre-process.
@@ -452,7 +482,7 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
                 for (int k = 0; k < r0; ++k) {
                     a[k] = zero;
                     b[k] = zero;
-                    if (active) c2r_load_pair<LAYOUT>(p, x, g, j + k * N0, M, a[k], b[k]);
+                    if (active) c2r_load_pair<LAYOUT, STAGED>(p, x, g, j + k * N0, M, a[k], b[k], xg);
                 }
 #pragma unroll
                 for (int k = 0; k < r0; ++k) {
@@ -467,7 +497,7 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
 #pragma unroll
                 for (int k = 0; k <= r0 / 2; ++k) {
                     float2 a = zero, b = zero, zk, zm;
-                    if (active) c2r_load_pair<LAYOUT>(p, x, g, k * N0, M, a, b);
+                    if (active) c2r_load_pair<LAYOUT, STAGED>(p, x, g, k * N0, M, a, b, xg);
                     herm_pre(a, b, root_const<2 * r0>(k), zk, zm);
                     A[k] = make_float2(zk.y, zk.x);
                     if (k > 0) A[r0 - k] = make_float2(zm.y, zm.x);
@@ -475,14 +505,14 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
 #pragma unroll
                 for (int k = 0; k < r0 / 2; ++k) {
                     float2 a = zero, b = zero, zk, zm;
-                    if (active) c2r_load_pair<LAYOUT>(p, x, g, N0 / 2 + k * N0, M, a, b);
+                    if (active) c2r_load_pair<LAYOUT, STAGED>(p, x, g, N0 / 2 + k * N0, M, a, b, xg);
                     herm_pre(a, b, MA_LDG(p.twN + k * (N0 / 2 + 1) + N0 / 2), zk, zm);
                     Bf[k] = make_float2(zk.y, zk.x);
                     Bf[r0 - 1 - k] = make_float2(zm.y, zm.x);
                 }
             }
         }
-        fft_run<PR, 1, true, false, Cta, TWALU>(v, t, sbuf0, buf_stride, parity, p.twM, cta, twb);
+        fft_run<PR, 1, true, false, Cta, TWALU, Hook>(v, t, sbuf0, buf_stride, parity, p.twM, cta, twb, hook);
     } else {
         float2* sb = sbuf0 + parity * buf_stride;
         parity ^= 1;
@@ -541,6 +571,22 @@ MA_HD void c2r_body(const C2RParams& p, Cta& cta, float2* smem) {
     int64_t f = g - s * p.frames_per_signal;
     const int64_t ds = stride_frames / p.frames_per_signal;
     const int64_t df = stride_frames - ds * p.frames_per_signal;
+    // Staged variant (half layouts of paired plans): the next frame's row is brought into shared
+    // memory by one bulk asynchronous copy while this frame is transformed.
+    constexpr bool STAGED = TWALU && (LAYOUT == LAYOUT_HALF_INTERLEAVED || LAYOUT == LAYOUT_HALF_PACKED);
+    float2* stage_slot = smem + 2 * S::BUF_STRIDE + slot * S::ROW;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + 2 * S::BUF_STRIDE + S::FPC * S::ROW) + 2 * slot;
+    uint32_t phase = 0;
+    (void)stage_slot;
+    (void)bar;
+    if constexpr (STAGED) {
+        if (t == 0) cta.bulk_init(bar);
+        cta.sync();
+        if (t == 0 && g < total) {
+            const StagedRow r0 = staged_row<M>(p, s, f);
+            cta.bulk_copy(stage_slot, r0.src, r0.bytes, bar);
+        }
+    }
     for (int64_t base = (int64_t)cta.bid() * S::FPC; base < total;
          base += stride_frames, g += stride_frames, s += ds, f += df) {
         if (f >= p.frames_per_signal) {
@@ -549,7 +595,31 @@ MA_HD void c2r_body(const C2RParams& p, Cta& cta, float2* smem) {
         }
         const bool active = S::FPC == 1 ? true : g < total;
         float2 v[R];
-        c2r_frame<M, LAYOUT, TWALU, Cta>(p, active, s, f, g, t, sbuf0, S::BUF_STRIDE, parity, v, cta, twb, wherm);
+        if constexpr (STAGED) {
+            StagedRow r;
+            r.shift = 0;
+            r.row = nullptr;
+            if (active) {
+                r = staged_row<M>(p, s, f);
+                if (!cta.bulk_wait(bar, phase) && p.error_flag != nullptr) *p.error_flag = 1;
+                phase ^= 1;
+            }
+            auto issue_next = [&]() {
+                if (t == 0 && g + stride_frames < total) {
+                    int64_t fn = f + df, sn = s + ds;
+                    if (fn >= p.frames_per_signal) {
+                        fn -= p.frames_per_signal;
+                        ++sn;
+                    }
+                    const StagedRow rn = staged_row<M>(p, sn, fn);
+                    cta.bulk_copy(stage_slot, rn.src, rn.bytes, bar);
+                }
+            };
+            c2r_frame<M, LAYOUT, TWALU, Cta, true>(p, active, s, f, g, t, sbuf0, S::BUF_STRIDE, parity, v, cta, twb,
+                                                   wherm, stage_slot + r.shift, issue_next, r.row);
+        } else {
+            c2r_frame<M, LAYOUT, TWALU, Cta>(p, active, s, f, g, t, sbuf0, S::BUF_STRIDE, parity, v, cta, twb, wherm);
+        }
         if (active && p.tail == nullptr) {
             float2* o = reinterpret_cast<float2*>(p.out + g * (int64_t)N);
 #pragma unroll
@@ -699,13 +769,14 @@ MA_HD void istft_body(const C2RParams& p, Cta& cta, float2* smem) {
 //    per-sample path);
 //  * twiddles live in registers (power chains) and the layout is fixed at compile time.
 // OVT is the overlap count N/hop when fixed at compile time (0: read it from p.hop).
-// smem: 2 exchange buffers | ring [R][T] float2.
+// smem: 2 exchange buffers | ring [R][T] float2 | staged row [M+2] float2 | mbarrier.
 template <int M>
 struct IstftFastShape {
     using P = FftPlan<M>;
     static constexpr int ELEMS = smem_elems_per_fft<M, 1>();
     static constexpr int RING = P::R * P::T;
-    static constexpr int SMEM_BYTES = (2 * ELEMS + RING) * (int)sizeof(float2);
+    static constexpr int ROW = M + 2;  // staged spectrum row with the alignment slack
+    static constexpr int SMEM_BYTES = (2 * ELEMS + RING + ROW) * (int)sizeof(float2) + 16;
 };
 
 // Whether istft_fast_body serves these parameters.
@@ -731,8 +802,11 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
     using SH = IstftFastShape<M>;
     constexpr int R = P::R, T = P::T, N = 2 * M;
     float2* ring = smem + 2 * SH::ELEMS;
+    float2* stage = ring + SH::RING;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(stage + SH::ROW);
     const int t = cta.tid();
     int parity = 0;
+    uint32_t phase = 0;
     const float scale = 1.0f / (float)N;
     const int hop = p.hop;
     const int h = OVT > 0 ? R / OVT : hop / (2 * T);  // ring slots completed per frame
@@ -752,63 +826,89 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
     float2 wherm[R / 2 + 1];
     c2r_load_tw_regs<M>(p, t, twb, wherm);
 
-    const int64_t n_chunks = (int64_t)p.chunks_per_signal;
-    const int64_t total_chunks = p.n_signals * n_chunks;
-    const int64_t per = (F + n_chunks - 1) / n_chunks;
-    const int reach = R / h - 1;  // earlier frames overlapping a frame start
+    // This CTA owns the global frames [G0, G1) (frame G = signal*F + f) and the output samples
+    // they complete.  It starts up to `reach` frames early inside the same signal to rebuild the
+    // overlap (no emission for those), so no CTA depends on another and the summation order is
+    // fixed.
+    const int64_t total = p.n_signals * F;
+    const int64_t per = (total + cta.nblocks() - 1) / cta.nblocks();
+    const int64_t G0 = (int64_t)cta.bid() * per;
+    int64_t G1 = G0 + per;
+    if (G1 > total) G1 = total;
+    if (G0 >= G1) return;  // uniform across the CTA
+    const int reach = R / h - 1;
+    int64_t s = G0 / F;
+    int64_t f = G0 - s * F;
+    int64_t lead = f < reach ? f : reach;
+    f -= lead;
+    int64_t G = G0 - lead;
 
-    for (int64_t c = cta.bid(); c < total_chunks; c += cta.nblocks()) {
-        const int64_t s = c / n_chunks;
-        const int64_t ci = c - s * n_chunks;
-        const int64_t f0 = ci * per;
-        int64_t f1 = f0 + per;
-        if (f1 > F) f1 = F;
-        if (f0 >= f1) continue;  // uniform across the CTA
-        int64_t fh = f0 - reach;
-        if (fh < 0) fh = 0;
+    if (t == 0) cta.bulk_init(bar);
 #pragma unroll
-        for (int q = 0; q < R; ++q) ring[q * T + t] = make_float2(0.f, 0.f);
-        for (int64_t f = fh; f < f1; ++f) {
-            float2 v[R];
-            c2r_frame<M, LAYOUT, true, Cta>(p, true, s, f, s * F + f, t, smem, SH::ELEMS, parity, v, cta, twb, wherm);
+    for (int q = 0; q < R; ++q) ring[q * T + t] = make_float2(0.f, 0.f);
+    cta.sync();
+    if (t == 0) {
+        const StagedRow r0 = staged_row<M>(p, s, f);
+        cta.bulk_copy(stage, r0.src, r0.bytes, bar);
+    }
 
-            // v[q] = (x[2n+1], x[2n]) * N for n = t + q*T.  Overlap-add in this thread's ring column.
-            const int64_t start = f * (int64_t)hop;
-            const int rot = (int)((f * (int64_t)h) & (R - 1));
-            const bool last = f == F - 1;
-            const bool emit = f >= f0;
-            // every sample this frame completes has all its overlapping frames present
-            const bool interior = !last && start >= (int64_t)(N - hop);
-            float* out = p.out + s * p.out_signal_stride + start;
+    for (; G < G1; ++G, ++f) {
+        if (f == F) {  // next signal: nothing overlaps across signals
+            f = 0;
+            ++s;
 #pragma unroll
-            for (int q = 0; q < R; ++q) {
-                float2* slot = ring + ((q + rot) & (R - 1)) * T + t;
-                float2 acc = make_float2(v[q].y * wreg[q].x, v[q].x * wreg[q].y);
-                if (q < R - h) {  // slot already holds earlier frames
-                    const float2 old = *slot;
-                    acc.x += old.x;
-                    acc.y += old.y;
-                }
-                if (q < h || last) {  // complete after this frame: emit
-                    if (emit) {
-                        const int i0 = 2 * (t + q * T);
-                        float2 r = acc;
-                        if (normalise) {
-                            if (interior) {
-                                const float2 inv = MA_LDG(reinterpret_cast<const float2*>(p.norm_mid_inv + i0));
-                                r.x = acc.x * inv.x;
-                                r.y = acc.y * inv.y;
-                            } else {
-                                const int64_t o = start + i0;
-                                r.x = acc.x / window_sum_at(p.window, o, N, hop, F, p.floor);
-                                r.y = acc.y / window_sum_at(p.window, o + 1, N, hop, F, p.floor);
-                            }
+            for (int q = 0; q < R; ++q) ring[q * T + t] = make_float2(0.f, 0.f);
+        }
+        const StagedRow r = staged_row<M>(p, s, f);
+        if (!cta.bulk_wait(bar, phase) && p.error_flag != nullptr) *p.error_flag = 1;
+        phase ^= 1;
+        auto issue_next = [&]() {
+            if (t == 0 && G + 1 < G1) {
+                const bool wrap = f + 1 == F;
+                const StagedRow rn = staged_row<M>(p, wrap ? s + 1 : s, wrap ? 0 : f + 1);
+                cta.bulk_copy(stage, rn.src, rn.bytes, bar);
+            }
+        };
+        float2 v[R];
+        c2r_frame<M, LAYOUT, true, Cta, true>(p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm,
+                                              stage + r.shift, issue_next, r.row);
+
+        // v[q] = (x[2n+1], x[2n]) * N for n = t + q*T.  Overlap-add in this thread's ring column.
+        const int64_t start = f * (int64_t)hop;
+        const int rot = (int)((f * (int64_t)h) & (R - 1));
+        const bool last = f == F - 1;
+        const bool emit = G >= G0;
+        // every sample this frame completes has all its overlapping frames present
+        const bool interior = !last && start >= (int64_t)(N - hop);
+        float* out = p.out + s * p.out_signal_stride + start;
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            float2* slot = ring + ((q + rot) & (R - 1)) * T + t;
+            float2 acc = make_float2(v[q].y * wreg[q].x, v[q].x * wreg[q].y);
+            if (q < R - h) {  // slot already holds earlier frames
+                const float2 old = *slot;
+                acc.x += old.x;
+                acc.y += old.y;
+            }
+            if (q < h || last) {  // complete after this frame: emit
+                if (emit) {
+                    const int i0 = 2 * (t + q * T);
+                    float2 r2 = acc;
+                    if (normalise) {
+                        if (interior) {
+                            const float2 inv = MA_LDG(reinterpret_cast<const float2*>(p.norm_mid_inv + i0));
+                            r2.x = acc.x * inv.x;
+                            r2.y = acc.y * inv.y;
+                        } else {
+                            const int64_t o = start + i0;
+                            r2.x = acc.x / window_sum_at(p.window, o, N, hop, F, p.floor);
+                            r2.y = acc.y / window_sum_at(p.window, o + 1, N, hop, F, p.floor);
                         }
-                        *reinterpret_cast<float2*>(out + i0) = r;
                     }
-                } else {
-                    *slot = acc;
+                    *reinterpret_cast<float2*>(out + i0) = r2;
                 }
+            } else {
+                *slot = acc;
             }
         }
     }

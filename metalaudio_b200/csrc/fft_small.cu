@@ -116,13 +116,16 @@ static ma_status launch_c2r_t(ma_fft_plan* plan, const C2RParams& p) {
     static int per_sm[64] = {0};
     ma_context* ctx = plan->ctx;
     int& occ = per_sm[ctx->device & 63];
-    if (occ == 0) MA_TRY(occupancy(c2r_kernel<M, LAYOUT>, S::THREADS, S::SMEM_BYTES, &occ));
+    constexpr size_t smem = (plan_pairable<M>() && (LAYOUT == LAYOUT_HALF_INTERLEAVED || LAYOUT == LAYOUT_HALF_PACKED))
+                                ? S::SMEM_BYTES_STAGED
+                                : S::SMEM_BYTES;
+    if (occ == 0) MA_TRY(occupancy(c2r_kernel<M, LAYOUT>, S::THREADS, smem, &occ));
     const int64_t total = p.n_signals * p.frames_per_signal;
     int64_t want = (total + S::FPC - 1) / S::FPC;
     int64_t cap = (int64_t)ctx->sm_count * occ;
     int grid = (int)(want < cap ? want : cap);
     if (grid < 1) return MA_OK;
-    c2r_kernel<M, LAYOUT><<<grid, S::THREADS, S::SMEM_BYTES, ctx->stream>>>(p);
+    c2r_kernel<M, LAYOUT><<<grid, S::THREADS, smem, ctx->stream>>>(p);
     return after_launch(ctx);
 }
 
@@ -142,6 +145,7 @@ static ma_status launch_c2r_variant(ma_fft_plan* plan, const C2RParams& p) {
 ma_status launch_c2r_small(ma_fft_plan* plan, C2RParams p) {
     p.twM = plan->d_twInv;
     p.twN = plan->d_twN;
+    p.error_flag = plan->ctx->d_error_flag;
     if (p.n_signals * p.frames_per_signal <= 0) return MA_OK;
     ma_status st = MA_ERR_UNSUPPORTED;
 #define RUN(MM) st = launch_c2r_variant<MM>(plan, p);
@@ -181,7 +185,11 @@ static ma_status launch_istft_t(ma_fft_plan* plan, C2RParams& p) {
     if (chunks > F / min_len) chunks = F / min_len;
     if (chunks < 1) chunks = 1;
     p.chunks_per_signal = (int32_t)chunks;
-    const int64_t total = chunks * p.n_signals;
+    int64_t total = chunks * p.n_signals;
+    if (fast) {  // contiguous ranges of the global frame list, at least min_len frames each
+        total = (F * p.n_signals) / min_len;
+        if (total < 1) total = 1;
+    }
     int grid = (int)(total < cap ? total : cap);
     if (grid < 1) return MA_OK;
     switch (variant) {
@@ -218,6 +226,7 @@ ma_status launch_istft_small(ma_fft_plan* plan, C2RParams p) {
     }
     p.norm_mid = plan->d_norm;
     p.norm_mid_inv = plan->d_norm + plan->hop;
+    p.error_flag = plan->ctx->d_error_flag;
     ma_status st = MA_ERR_UNSUPPORTED;
 #define RUN(MM) st = launch_istft_t<MM>(plan, p);
     MA_DISPATCH_M(plan->m, RUN)

@@ -58,7 +58,7 @@ int emul_c2r(int n, const float* in_a, const float* in_b, long long in_signal_st
 #define RUN(MM)                                                                              \
     {                                                                                        \
         using S = CtaShape<MM>;                                                              \
-        run_grid(nblocks, S::THREADS, S::SMEM_BYTES, [&](HostCta& cta, void* sm) {           \
+        run_grid(nblocks, S::THREADS, S::SMEM_BYTES_STAGED, [&](HostCta& cta, void* sm) {    \
             if (layout == 0) c2r_body<MM, 0, HostCta>(p, cta, (float2*)sm);                  \
             else c2r_body<MM, -1, HostCta>(p, cta, (float2*)sm);                             \
         });                                                                                  \

@@ -27,7 +27,7 @@ struct HostCta {
         __atomic_add_fetch((unsigned long long*)bar, 1ull, __ATOMIC_SEQ_CST);
     }
     bool bulk_wait(void* bar, unsigned parity) {
-        for (long i = 0; i < (1L << 34); ++i) {
+        for (long i = 0; i < (1L << 21); ++i) {
             if ((__atomic_load_n((unsigned long long*)bar, __ATOMIC_SEQ_CST) & 1ull) == (unsigned long long)(parity ^ 1u))
                 return true;
             sched_yield();
