@@ -53,7 +53,8 @@ enum {
     MA_ERR_TIMEOUT = 13,               /* MetalAudioError.gpuTimeout */
     MA_ERR_DEVICE_LOST = 14,           /* MetalAudioError.deviceLost / deviceNotFound */
     MA_ERR_CUDA = 15,                  /* MetalAudioError.gpuExecutionError; see ma_last_cuda_error */
-    MA_ERR_UNSUPPORTED = 16
+    MA_ERR_UNSUPPORTED = 16,
+    MA_ERR_SCRATCH_LIMIT = 17          /* work needs more scratch than the built-in static buffer holds */
 };
 
 /* Spectrum layouts accepted / produced by the transforms (N = FFT size). */
@@ -158,6 +159,36 @@ ma_status ma_fft_forward_dev(ma_fft_plan* plan, const float* in, float* out_a, f
 ma_status ma_fft_forward_host(ma_fft_plan* plan, const float* in, float* out_a, float* out_b,
                               float* mag, int32_t mag_kind, float db_reference,
                               int64_t batch, int32_t layout);
+
+/* Size of the library's built-in scratch buffer used by ma_fft_forward_static_dev. */
+#define MA_STATIC_SCRATCH_BYTES ((size_t)8 << 20)
+
+/* Forward transform for callers that must not allocate device memory.  It has no counterpart in
+ * the reference.  Who needs it: code running where cudaMalloc is off limits - an audio render
+ * callback with a hard deadline (an allocation can block for milliseconds and synchronises the
+ * device) or a process whose device-memory budget was fixed at start-up and must not grow.  Such
+ * callers create the plan once at start-up and afterwards need every call to leave the
+ * allocator alone.
+ *
+ * Same arguments and results as ma_fft_forward_dev for plans above 8192 points (smaller plans
+ * need no scratch and are simply forwarded to ma_fft_forward_dev).  The difference: the
+ * intermediate pass data goes through a fixed buffer of MA_STATIC_SCRATCH_BYTES that is compiled
+ * into the library (a file-scope __device__ array), not through the plan's own allocation.  The
+ * call itself performs no cudaMalloc / cudaFree / stream-ordered allocation of any kind.
+ *  - Limit: one transform's intermediate data, (N2/2 + 1) * N1 * 8 bytes (about 4*N bytes), must fit
+ *    the buffer, i.e. N <= 2^20; larger plans return MA_ERR_SCRATCH_LIMIT.  Batches larger than the
+ *    buffer holds are processed in several passes.
+ *  - Every GPU that loads the library carries the buffer until the process exits.
+ *  - The first call on each device looks the buffer's device address up (one cheap runtime query,
+ *    made with that device current).  Make that first call before starting any stream capture.
+ *  - All calls, from all plans and contexts on one device, share the one buffer, and it keeps
+ *    whatever the previous call left in it.  Nothing in it has to start at zero - each pass
+ *    overwrites every element the next pass reads - so no clearing is done.  Two calls whose
+ *    kernels overlap on the GPU (different streams / contexts) would trample each other's
+ *    intermediate data: issue them on one stream, or otherwise make sure they do not overlap. */
+ma_status ma_fft_forward_static_dev(ma_fft_plan* plan, const float* in, float* out_a, float* out_b,
+                                    float* mag, int32_t mag_kind, float db_reference,
+                                    int64_t batch, int32_t layout);
 
 /* Inverse DFT with the 1/N scale fused.  Replaces FFT.inverse (FFT.swift:889-919),
  * inverseBatch (STFT.swift:327-373), inverseGPU / inverseMPSGraph / inverseAuto.

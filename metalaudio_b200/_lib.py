@@ -45,6 +45,7 @@ SIGNATURES = {
     "ma_fft_plan_scratch_bytes": (c_int32, [c_void_p, POINTER(c_size_t)]),
     "ma_fft_forward_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_float, c_int64, c_int32]),
     "ma_fft_forward_host": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_float, c_int64, c_int32]),
+    "ma_fft_forward_static_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_float, c_int64, c_int32]),
     "ma_fft_inverse_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32]),
     "ma_fft_inverse_host": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32]),
     "ma_fft_magnitude_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_float]),
@@ -71,7 +72,7 @@ MA_OK = 0
 (MA_ERR_INVALID_ARGUMENT, MA_ERR_SIZE_NOT_POW2, MA_ERR_SIZE_TOO_LARGE, MA_ERR_INVALID_HOP,
  MA_ERR_INPUT_TOO_SHORT, MA_ERR_BATCH_OVERFLOW, MA_ERR_ISTFT_OVERFLOW, MA_ERR_EMPTY_KERNEL,
  MA_ERR_KERNEL_NOT_CONFIGURED, MA_ERR_INVALID_PARTITION_STATE, MA_ERR_OUTPUT_OVERFLOW, MA_ERR_ALLOC,
- MA_ERR_TIMEOUT, MA_ERR_DEVICE_LOST, MA_ERR_CUDA, MA_ERR_UNSUPPORTED) = range(1, 17)
+ MA_ERR_TIMEOUT, MA_ERR_DEVICE_LOST, MA_ERR_CUDA, MA_ERR_UNSUPPORTED, MA_ERR_SCRATCH_LIMIT) = range(1, 18)
 LAYOUT_HALF_INTERLEAVED, LAYOUT_FULL_SPLIT, LAYOUT_HALF_PACKED = 0, 1, 2
 MAG_MAGNITUDE, MAG_POWER, MAG_DB = 0, 1, 2
 FAULT_ALLOC, FAULT_LAUNCH, FAULT_SYNC, FAULT_DEVICE_LOST = 0, 1, 2, 3

@@ -156,6 +156,7 @@ const char* ma_status_string(ma_status s) {
         case MA_ERR_DEVICE_LOST: return "no usable CUDA device (device lost or not found)";
         case MA_ERR_CUDA: return "CUDA execution error";
         case MA_ERR_UNSUPPORTED: return "unsupported configuration";
+        case MA_ERR_SCRATCH_LIMIT: return "transform needs more scratch than the built-in static buffer holds";
         default: return "unknown status";
     }
 }
