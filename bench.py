@@ -258,16 +258,16 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         gbs = nbytes / (ms * 1e-3) / 1e9
         return {"kernel": name, "ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": gbs, "frac": gbs / peak}
 
-    kernels = [kernel_entry("r2c_kernel<2048> (STFT: window + FFT + Hermitian + magnitude)", stft_ms,
+    kernels = [kernel_entry("r2c_kernel<2048,aligned,half_interleaved,magnitude> (STFT: frame gather + window + FFT + Hermitian + magnitude)", stft_ms,
                             S * STFT_BYTES_PER_SIGNAL),
-               kernel_entry("istft_kernel<2048> (iSTFT: inverse FFT + window + overlap-add + normalise)", istft_ms,
+               kernel_entry("istft_fast_kernel<2048,half_interleaved,4> (iSTFT: Hermitian + inverse FFT + window + overlap-add + normalise)", istft_ms,
                             S * ISTFT_BYTES_PER_SIGNAL)]
     dom = max(kernels, key=lambda e: e["ms"])
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
         try:
-            traffic = json.load(open(tpath)).get(dom["kernel"].split(" ")[0])
+            traffic = json.load(open(tpath)).get(dom["kernel"].split("<")[0])
         except Exception:
             traffic = None
     roofline = {"bound": "hbm", "achieved": dom["achieved_gbs"], "peak": peak, "unit": "GB/s",
