@@ -47,7 +47,7 @@ extern __shared__ float4 ma_large_smem[];
 
 // ---------------------------------------------------------------- forward pass 1
 template <int M2, int W1>
-__global__ void __launch_bounds__(W1* FftPlan<M2>::T) cols_r2c_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? 2 : 1) cols_r2c_kernel(const LargeParams p) {
     using P = FftPlan<M2>;
     constexpr int R = P::R, T = P::T;
     float2* smem = reinterpret_cast<float2*>(ma_large_smem);
@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T) rows_inv_kernel(const Larg
 
 // ---------------------------------------------------------------- inverse pass B
 template <int M2, int W1>
-__global__ void __launch_bounds__(W1* FftPlan<M2>::T) cols_c2r_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? 2 : 1) cols_c2r_kernel(const LargeParams p) {
     using P = FftPlan<M2>;
     constexpr int R = P::R, T = P::T;
     float2* smem = reinterpret_cast<float2*>(ma_large_smem);

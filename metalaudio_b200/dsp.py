@@ -277,10 +277,26 @@ class Tensor:
         _raise_status(self.device._lib.ma_memcpy_d2h_async(self.device.handle, ctypes.c_void_p(to_ptr), self._p,
                                                           nbytes), "Tensor.copyToAsync")
 
+    def rows(self, first: int, count: int, device: Optional["AudioDevice"] = None) -> "Tensor":
+        """Non-owning view of `count` leading-dimension rows starting at `first`, optionally bound to
+        another AudioDevice (stream) of the same GPU, so independent row ranges can be processed on
+        different streams."""
+        v = Tensor.__new__(Tensor)
+        v.device = device if device is not None else self.device
+        v.shape = (int(count),) + self.shape[1:]
+        v.count = int(np.prod(v.shape))
+        row_elems = int(np.prod(self.shape[1:])) if len(self.shape) > 1 else 1
+        v._p = ctypes.c_void_p(self._p.value + 4 * row_elems * int(first))
+        v._view = True
+        return v
+
     def zero(self) -> None:
         _raise_status(self.device._lib.ma_buffer_zero(self.device.handle, self._p, self.byteSize), "Tensor.zero")
 
     def free(self) -> None:
+        if getattr(self, "_view", False):
+            self._p = None
+            return
         if getattr(self, "_p", None) and self.device._h:
             self.device._lib.ma_buffer_free(self.device.handle, self._p)
         self._p = None
