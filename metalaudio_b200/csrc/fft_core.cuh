@@ -366,18 +366,22 @@ struct NoHook {
     MA_HD void operator()() const {}
 };
 
-template <class P, int W, int S, bool PAIR0, bool PAIRL, bool TWALU, class Cta, class Hook = NoHook>
+template <class P, int W, int S, bool PAIR0, bool PAIRL, bool TWALU, class Cta, class Hook = NoHook,
+          bool SINGLE = false>
 struct StageChain {
     static MA_HD void run(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
                           const float2* __restrict__ twM, const float2* twb, Cta& cta, const Hook& hook = Hook()) {
         if constexpr (S < P::NS) {
-            float2* sbuf = sbuf0 + parity * buf_stride;
+            // SINGLE: one exchange buffer only; a barrier before each write keeps it from
+            // overtaking the previous exchange's reads (costs a barrier, saves a buffer).
+            if constexpr (SINGLE) cta.sync();
+            float2* sbuf = SINGLE ? sbuf0 : sbuf0 + parity * buf_stride;
             stage_write<P, W, S - 1, (S == 1) && PAIR0>(v, t, sbuf);
             cta.sync();
             if constexpr (S == 1) hook();  // every thread is past its reads of the frame's input
             stage_read_compute<P, W, S, (S == P::NS - 1) && PAIRL, TWALU>(v, t, sbuf, twM, twb);
             parity ^= 1;
-            StageChain<P, W, S + 1, PAIR0, PAIRL, TWALU, Cta, Hook>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta, hook);
+            StageChain<P, W, S + 1, PAIR0, PAIRL, TWALU, Cta, Hook, SINGLE>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta, hook);
         }
     }
 };
@@ -396,7 +400,8 @@ MA_HD void load_tw_bases(float2* twb, int t, const float2* __restrict__ tws) {
 // sbuf0 is the transform's exchange region (already offset by the slot when W > 1);
 // buf_stride is the distance in float2 between the two exchange buffers; parity selects the
 // buffer of the next exchange and is updated.
-template <class P, int W, bool PAIR0, bool PAIRL, class Cta, bool TWALU = false, class Hook = NoHook>
+template <class P, int W, bool PAIR0, bool PAIRL, class Cta, bool TWALU = false, class Hook = NoHook,
+          bool SINGLE = false>
 MA_HD void fft_run(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
                    const float2* __restrict__ twM, Cta& cta, const float2* twb = nullptr,
                    const Hook& hook = Hook()) {
@@ -404,7 +409,7 @@ MA_HD void fft_run(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
     static_assert(!(PAIRL && P::NS < 2), "a paired last stage needs at least two stages");
 #pragma unroll
     for (int b = 0; b < NB0; ++b) Bfly<r0>::run(v + b * r0);  // stage 0: no twiddles
-    StageChain<P, W, 1, PAIR0, PAIRL, TWALU, Cta, Hook>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta, hook);
+    StageChain<P, W, 1, PAIR0, PAIRL, TWALU, Cta, Hook, SINGLE>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta, hook);
 }
 
 // Complex forward FFT of length M in natural order.  In: v[q] = z[t + q*T].

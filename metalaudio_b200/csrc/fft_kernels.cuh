@@ -61,6 +61,8 @@ struct CtaShape {
     // Staged inverse kernels: one spectrum row (M+2 bins with the alignment slack) per slot.
     static constexpr int ROW = M + 2;
     static constexpr int SMEM_BYTES_STAGED = SMEM_BYTES + FPC * ROW * (int)sizeof(float2) + 16 * FPC;
+    static_assert(SMEM_BYTES % 16 == 0 && (ROW * sizeof(float2)) % 16 == 0 && (M * sizeof(float2)) % 16 == 0 || M < 2,
+                  "bulk copy destinations must be 16-byte aligned");
 };
 
 // Hermitian post-process of one pair: a = Z[k], b = Z[(M-k) mod M], w = exp(-2 pi i k/N).
@@ -454,7 +456,7 @@ MA_HD StagedRow staged_row(const C2RParams& p, int64_t s, int64_t f) {
 // Pre-process + FFT of one frame: leaves v[q] = (x[2n+1], x[2n]) * N for n = t + q*T
 // (real and imaginary parts swapped: the inverse transform is run as a forward transform
 // of the swapped spectrum).
-template <int M, int LAYOUT, bool TWALU, class Cta, bool STAGED = false, class Hook = NoHook>
+template <int M, int LAYOUT, bool TWALU, class Cta, bool STAGED = false, class Hook = NoHook, bool SINGLE = false>
 MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int64_t g, int t,
                      float2* sbuf0, int buf_stride, int& parity, float2* v, Cta& cta,
                      const float2* twb = nullptr, const float2* wherm = nullptr,
@@ -512,7 +514,7 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
                 }
             }
         }
-        fft_run<PR, 1, true, false, Cta, TWALU, Hook>(v, t, sbuf0, buf_stride, parity, p.twM, cta, twb, hook);
+        fft_run<PR, 1, true, false, Cta, TWALU, Hook, SINGLE>(v, t, sbuf0, buf_stride, parity, p.twM, cta, twb, hook);
     } else {
         float2* sb = sbuf0 + parity * buf_stride;
         parity ^= 1;
@@ -769,14 +771,17 @@ MA_HD void istft_body(const C2RParams& p, Cta& cta, float2* smem) {
 //    per-sample path);
 //  * twiddles live in registers (power chains) and the layout is fixed at compile time.
 // OVT is the overlap count N/hop when fixed at compile time (0: read it from p.hop).
-// smem: 2 exchange buffers | ring [R][T] float2 | staged row [M+2] float2 | mbarrier.
+// smem: exchange buffer(s) | ring [R][T] float2 | staged row [M+2] float2 | mbarrier.
 template <int M>
 struct IstftFastShape {
     using P = FftPlan<M>;
     static constexpr int ELEMS = smem_elems_per_fft<M, 1>();
     static constexpr int RING = P::R * P::T;
     static constexpr int ROW = M + 2;  // staged spectrum row with the alignment slack
-    static constexpr int SMEM_BYTES = (2 * ELEMS + RING + ROW) * (int)sizeof(float2) + 16;
+    static constexpr int EXCH = 1;  // exchange buffers (1: a barrier before each write instead of a second buffer)
+    static constexpr int EXCH_ELEMS = (EXCH * ELEMS + 1) & ~1;  // keeps the staged row 16-byte aligned
+    static constexpr int SMEM_BYTES = (EXCH_ELEMS + RING + ROW) * (int)sizeof(float2) + 16;
+    static_assert(((EXCH_ELEMS + RING) * sizeof(float2)) % 16 == 0, "bulk copy destination must be 16-byte aligned");
 };
 
 // Whether istft_fast_body serves these parameters.
@@ -801,7 +806,7 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
     using P = FftPlan<M>;
     using SH = IstftFastShape<M>;
     constexpr int R = P::R, T = P::T, N = 2 * M;
-    float2* ring = smem + 2 * SH::ELEMS;
+    float2* ring = smem + SH::EXCH_ELEMS;
     float2* stage = ring + SH::RING;
     uint64_t* bar = reinterpret_cast<uint64_t*>(stage + SH::ROW);
     const int t = cta.tid();
@@ -870,8 +875,8 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
             }
         };
         float2 v[R];
-        c2r_frame<M, LAYOUT, true, Cta, true>(p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm,
-                                              stage + r.shift, issue_next, r.row);
+        c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1>(
+            p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage + r.shift, issue_next, r.row);
 
         // v[q] = (x[2n+1], x[2n]) * N for n = t + q*T.  Overlap-add in this thread's ring column.
         const int64_t start = f * (int64_t)hop;
