@@ -781,7 +781,8 @@ struct IstftFastShape {
     static constexpr int EXCH = 1;  // exchange buffers (1: a barrier before each write instead of a second buffer)
     static constexpr int EXCH_ELEMS = (EXCH * ELEMS + 1) & ~1;  // keeps the staged row 16-byte aligned
     static constexpr int SMEM_BYTES = (EXCH_ELEMS + RING + ROW) * (int)sizeof(float2) + 16;
-    static_assert(((EXCH_ELEMS + RING) * sizeof(float2)) % 16 == 0, "bulk copy destination must be 16-byte aligned");
+    static_assert(!plan_pairable<M>() || ((EXCH_ELEMS + RING) * sizeof(float2)) % 16 == 0,
+                  "bulk copy destination must be 16-byte aligned");
 };
 
 // Whether istft_fast_body serves these parameters.
