@@ -518,15 +518,50 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
     } else {
         float2* sb = sbuf0 + parity * buf_stride;
         parity ^= 1;
+        // All loads first (one memory round trip per partial spectrum, not one per bin), then the
+        // arithmetic.
+        float2 pa[R / 2 + 1], pb[R / 2 + 1];
+        const bool split_sum = LAYOUT < 0 && p.layout == LAYOUT_HALF_PACKED && p.n_partials > 1;
+#pragma unroll
+        for (int q = 0; q <= R / 2; ++q) {
+            const int k = t + q * T;
+            pa[q] = make_float2(0.f, 0.f);
+            pb[q] = pa[q];
+            if (k > M / 2 || !active) continue;
+            if (split_sum) {  // raw bins of partial spectrum 0; bin 0 is unpacked after the sum
+                pa[q] = MA_LDG(x + k);
+                pb[q] = MA_LDG(x + (k == 0 ? 0 : M - k));
+            } else {
+                c2r_load_pair<LAYOUT>(p, x, g, k, M, pa[q], pb[q]);
+            }
+        }
+        if (split_sum) {
+            for (int i = 1; i < p.n_partials; ++i) {
+                const float2* xi = x + (int64_t)i * p.partial_stride;
+#pragma unroll
+                for (int q = 0; q <= R / 2; ++q) {
+                    const int k = t + q * T;
+                    if (k > M / 2 || !active) continue;
+                    const float2 ya = MA_LDG(xi + k);
+                    const float2 yb = MA_LDG(xi + (k == 0 ? 0 : M - k));
+                    pa[q].x += ya.x;
+                    pa[q].y += ya.y;
+                    pb[q].x += yb.x;
+                    pb[q].y += yb.y;
+                }
+            }
+            if (t == 0) {  // k == 0 (q == 0): bin 0 holds (DC, Nyquist)
+                pb[0] = make_float2(pa[0].y, 0.f);
+                pa[0] = make_float2(pa[0].x, 0.f);
+            }
+        }
 #pragma unroll
         for (int q = 0; q <= R / 2; ++q) {
             const int k = t + q * T;
             if (k > M / 2) continue;
-            float2 a = make_float2(0.f, 0.f), b = a;
-            if (active) c2r_load_pair<LAYOUT>(p, x, g, k, M, a, b);
             const float2 w = MA_LDG(p.twN + k);
             float2 zk, zm;
-            herm_pre(a, b, w, zk, zm);
+            herm_pre(pa[q], pb[q], w, zk, zm);
             sb[saddr<1>(k)] = make_float2(zk.y, zk.x);
             if (k > 0) sb[saddr<1>(M - k)] = make_float2(zm.y, zm.x);
         }
