@@ -1,0 +1,111 @@
+"""Context, Tensor, timing and failure-handling slices of AudioDevice / ComputeContext / Tensor.
+Failures are injected on the host only (a test hook makes the next call reaching a site return a
+chosen error); no GPU work is disturbed and nothing is faulted or hung."""
+import ctypes
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_device_name_and_tensor_round_trip(device):
+    from metalaudio_b200 import Tensor
+    assert "NVIDIA" in device.name or len(device.name) > 0
+    t = Tensor(device, (3, 1000))
+    x = np.random.default_rng(0).standard_normal((3, 1000)).astype(np.float32)
+    t.copy(x)
+    assert np.array_equal(t.toArray(), x)
+    t.zero()
+    device.synchronize()
+    assert not t.toArray().any()
+    v = t.rows(1, 2)
+    v.copy(x[1:3])
+    assert np.array_equal(t.toArray()[1:], x[1:])
+    with pytest.raises(Exception):
+        t.copy(np.zeros(7, np.float32))
+    t.free()
+
+
+def test_timing_brackets_queued_work(device):
+    from metalaudio_b200 import FFT, WindowType
+    fft = FFT(device, FFT.Config(size=1024, windowType=WindowType.none))
+    x = np.random.default_rng(1).standard_normal((64, 1024)).astype(np.float32)
+    device.timingBegin()
+    fft.forwardBatch(x)
+    ms = device.timingEnd()
+    assert 0.0 <= ms < 5000.0
+    fft.close()
+
+
+def test_injected_faults_surface_as_reference_errors(lib):
+    """ma_test_inject_fault: allocation, launch and synchronisation failures map onto
+    bufferAllocationFailed / gpuExecutionError; the context stays usable afterwards."""
+    from metalaudio_b200 import AudioDevice, FFT, MetalAudioError, Tensor, WindowType
+    from metalaudio_b200 import _lib as L
+    dev = AudioDevice()
+    lib.ma_test_inject_fault(dev.handle, L.FAULT_ALLOC, 2)  # cudaErrorMemoryAllocation
+    with pytest.raises(MetalAudioError) as e:
+        Tensor(dev, (10,))
+    assert e.value.case == "bufferAllocationFailed"
+    t = Tensor(dev, (10,))  # next call works again
+    fft = FFT(dev, FFT.Config(size=256, windowType=WindowType.none))
+    lib.ma_test_inject_fault(dev.handle, L.FAULT_LAUNCH, 719)  # cudaErrorLaunchFailure, injected on the host
+    with pytest.raises(MetalAudioError) as e:
+        fft.forwardBatch(np.ones((2, 256), np.float32))
+    assert e.value.case == "gpuExecutionError" and lib.ma_last_cuda_error() == 719
+    re, im = fft.forwardBatch(np.ones((2, 256), np.float32))
+    assert abs(re[0, 0] - 256) < 1e-3
+    lib.ma_test_inject_fault(dev.handle, L.FAULT_SYNC, 719)
+    with pytest.raises(MetalAudioError):
+        dev.synchronize()
+    dev.synchronize()
+    # non-throwing pointer API zeroes its outputs on failure (FFT.swift:826-835)
+    lib.ma_test_inject_fault(dev.handle, L.FAULT_LAUNCH, 719)
+    r = np.ones(256, np.float32); i = np.ones(256, np.float32)
+    fft.forward(np.ones(256, np.float32), r, i)
+    assert not r.any() and not i.any()
+    fft.close(); t.free(); dev.close()
+
+
+def test_device_loss_is_an_error_not_a_reroute(lib):
+    """DeviceLossTests: markDeviceLost flips availability and every later call reports
+    deviceLost; there is no CPU fallback to reroute to."""
+    from metalaudio_b200 import AudioDevice, FFT, MetalAudioError, WindowType
+    dev = AudioDevice()
+    fft = FFT(dev, FFT.Config(size=256, windowType=WindowType.none))
+    assert dev.isDeviceAvailable
+    dev.markDeviceLost()
+    assert not dev.isDeviceAvailable
+    with pytest.raises(MetalAudioError) as e:
+        dev.ensureAvailable()
+    assert e.value.case == "deviceLost"
+    with pytest.raises(MetalAudioError) as e:
+        fft.forwardBatch(np.ones((1, 256), np.float32))
+    assert e.value.case == "deviceLost"
+    with pytest.raises(MetalAudioError):
+        FFT(dev, FFT.Config(size=512))
+    dev._lib.ma_context_destroy(dev.handle)
+    dev._h = None
+
+
+def test_two_contexts_are_independent_streams(lib):
+    """RealtimeThreadSafetyTests shape: separate objects per thread/stream do not mix results."""
+    import threading
+    from metalaudio_b200 import AudioDevice, FFT, WindowType
+    from oracle import float64 as o64
+    results = {}
+
+    def work(seed):
+        dev = AudioDevice(pinnedBytes=1 << 20)
+        fft = FFT(dev, FFT.Config(size=2048, windowType=WindowType.none))
+        x = np.random.default_rng(seed).standard_normal((50, 2048)).astype(np.float32)
+        for _ in range(5):
+            re, im = fft.forwardBatch(x)
+        results[seed] = o64.rel_rms(re + 1j * im, o64.fft_forward(x))
+        fft.close(); dev.close()
+
+    th = [threading.Thread(target=work, args=(s,)) for s in (1, 2, 3, 4)]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    assert all(v <= 1e-5 for v in results.values()) and len(results) == 4
