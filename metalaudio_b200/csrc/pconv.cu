@@ -12,6 +12,8 @@
 //                            channels that share an IR are tiled so each H element is loaded
 //                            once per tile and reused from registers
 //   c2r / istft (fft_small)  inverse transform + block overlap-add
+#include <cuda_pipeline.h>
+
 #include <new>
 #include <vector>
 
@@ -165,6 +167,125 @@ __global__ void __launch_bounds__(kMacThreads) pconv_mac_kernel(const MacParams 
             for (int v = 0; v < VEC; ++v) o[v] = acc[c][v];
         }
     }
+}
+
+// Whole-signal form of the same multiply-accumulate, tiled over time.  With every block
+// spectrum of the call already in the timeline, output blocks are independent, and TT consecutive
+// outputs of one (channel, bin) reuse the same partition spectra: a thread keeps TT accumulators
+// and a sliding window of TT timeline values in registers, and per partition takes ONE new
+// timeline value and ONE partition value for TT complex multiply-accumulates (4*TT FMAs).
+// A CTA is 4 warps = 4 consecutive time tiles of one channel and 32 bins (lanes along bins).
+// Its warps need the same partition rows and overlapping timeline rows, so both are staged in
+// shared memory by 16-byte asynchronous copies, a chunk of TT partitions ahead: the timeline
+// rows in a ring of 128 rows (each row enters once per CTA), the partition rows double-buffered.
+// That leaves about 0.25 byte of L2 traffic per complex multiply-accumulate and makes the FMA
+// pipe the limiter.  One barrier per chunk (1024 FMAs per thread apart).
+template <int TT>
+__global__ void __launch_bounds__(128) pconv_mac_tiled_kernel(const MacParams q, int t_total, int64_t tl_len) {
+    constexpr int RING = 128;  // >= 4*TT - 1 + 2*TT rows in flight
+    static_assert(4 * TT - 1 + 2 * TT <= RING, "timeline ring too small");
+    __shared__ __align__(16) float2 xs[RING][32];
+    __shared__ __align__(16) float2 hs[2][TT][32];
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int B = q.block, P = q.partitions;
+    const int bin_tiles = B >> 5;
+    const int bt = blockIdx.x % bin_tiles;
+    const int c = blockIdx.x / bin_tiles;
+    const bool dc = (bt == 0 && lane == 0);
+    const int t0_cta = blockIdx.y * 4 * TT;
+    if (t0_cta >= t_total) return;
+    const float2* xc = q.x + (int64_t)c * q.x_chan_stride + bt * 32;
+    const float2* hc = q.h + (int64_t)__ldg(q.ch2ir + c) * P * B + bt * 32;
+    const int64_t base0 = (int64_t)(P - 1) + t0_cta;     // timeline row of the CTA's first output at p = 0
+    const int64_t base = base0 + warp * TT;              // ... of this warp's first output
+
+    // 16-byte copies: a row of 32 bins is 16 segments
+    auto load_x_rows = [&](int64_t first, int count) {
+        for (int idx = tid; idx < count * 16; idx += 128) {
+            const int64_t row = first + (idx >> 4);
+            const int seg = idx & 15;
+            int64_t src = row > tl_len - 1 ? tl_len - 1 : row;  // rows past the end feed outputs that are never stored
+            __pipeline_memcpy_async(&xs[row & (RING - 1)][seg * 2], xc + src * B + seg * 2, 16);
+        }
+    };
+    auto load_h_rows = [&](int buf, int p0) {
+        for (int idx = tid; idx < TT * 16; idx += 128) {
+            const int pr = p0 + (idx >> 4);
+            const int seg = idx & 15;
+            if (pr < P) __pipeline_memcpy_async(&hs[buf][idx >> 4][seg * 2], hc + (int64_t)pr * B + seg * 2, 16);
+        }
+    };
+
+    load_x_rows(base0 - TT + 1, 4 * TT - 1 + TT);  // rows of chunk 0: [base0-TT+1, base0+4TT-1]
+    load_h_rows(0, 0);
+    __pipeline_commit();
+    __pipeline_wait_prior(0);
+    __syncthreads();
+
+    float2 acc[TT], xw[TT];
+#pragma unroll
+    for (int i = 0; i < TT; ++i) {
+        acc[i] = make_float2(0.f, 0.f);
+        xw[i] = xs[(base + i) & (RING - 1)][lane];
+    }
+    int buf = 0;
+    for (int p0 = 0; p0 < P; p0 += TT) {
+        if (p0 + TT < P) {  // stage the next chunk while this one is consumed
+            load_x_rows(base0 - p0 - 2 * TT + 1, TT);
+            load_h_rows(buf ^ 1, p0 + TT);
+        }
+        __pipeline_commit();
+#pragma unroll
+        for (int j = 0; j < TT; ++j) {
+            const int p = p0 + j;
+            if (p < P) {
+                // slot (i - j) mod TT holds timeline row base + i - p; the row base - p enters at i = 0
+                if (p > 0) xw[(TT - j) % TT] = xs[(base - p) & (RING - 1)][lane];
+                const float2 h = hs[buf][j][lane];
+                const float ha = dc ? 0.f : h.y;   // bin 0 carries (DC, Nyquist): component-wise product
+                const float hb = dc ? h.y : h.x;
+#pragma unroll
+                for (int i = 0; i < TT; ++i) {
+                    const float2 xv = xw[(i - j + TT) % TT];
+                    acc[i].x = fmaf(xv.x, h.x, acc[i].x);
+                    acc[i].x = fmaf(-xv.y, ha, acc[i].x);
+                    acc[i].y = fmaf(xv.x, ha, acc[i].y);
+                    acc[i].y = fmaf(xv.y, hb, acc[i].y);
+                }
+            }
+        }
+        __pipeline_wait_prior(0);
+        __syncthreads();
+        buf ^= 1;
+    }
+    const int t0 = t0_cta + warp * TT;
+    float2* o = q.out + (int64_t)c * q.out_chan_stride + (int64_t)t0 * q.out_t_stride + bt * 32 + lane;
+#pragma unroll
+    for (int i = 0; i < TT; ++i)
+        if (t0 + i < t_total) o[(int64_t)i * q.out_t_stride] = acc[i];
+}
+
+static ma_status launch_mac_tiled(ma_pconv* pc, const MacParams& q, int64_t t_count, int64_t tl_len) {
+    constexpr int TT = 16;
+    ma_context* ctx = pc->ctx;
+    const int bin_tiles = pc->block >> 5;
+    const int64_t t_ctas = (t_count + 4 * TT - 1) / (4 * TT);
+    int64_t done = 0;
+    while (done < t_ctas) {  // grid.y limit
+        int64_t ny = t_ctas - done;
+        if (ny > 32768) ny = 32768;
+        MacParams qq = q;
+        const int64_t t_first = done * 4 * TT;
+        qq.out = q.out + t_first * q.out_t_stride;
+        qq.x = q.x + t_first * pc->block;  // shifts the timeline origin by t_first rows
+        dim3 grid((unsigned)(bin_tiles * pc->channels), (unsigned)ny, 1);
+        pconv_mac_tiled_kernel<TT><<<grid, 128, 0, ctx->stream>>>(qq, (int)(t_count - t_first), tl_len - t_first);
+        MA_TRY(after_launch(ctx));
+        done += ny;
+    }
+    return MA_OK;
 }
 
 template <int CT, int VEC, bool STREAM>
@@ -488,7 +609,8 @@ ma_status ma_pconv_process_dev(ma_pconv* pc, const float* in, int64_t len, int64
         q.wrap = 0;
         q.splits = 1;
         q.p_per_split = P;
-        MA_TRY(launch_mac(pc, q, false, T));
+        if (B >= 32 && T < (int64_t)1 << 30) MA_TRY(launch_mac_tiled(pc, q, T, tl_len));
+        else MA_TRY(launch_mac(pc, q, false, T));
     }
     // 4. inverse transform + block overlap-add, truncated at len + taps - 1
     {
