@@ -39,6 +39,26 @@ struct LargeParams {
     const float2* twL;   // exp(-2 pi i j/N),  j < N/2
 };
 
+// w[q] = base * step^q for q < n (n <= 17), products of depth <= 3 from step, step^4, step^8, step^12, step^16.
+template <int n>
+__device__ __forceinline__ void geometric_twiddles(float2* w, float2 base, float2 step) {
+    const float2 s2 = cmul(step, step), s3 = cmul(s2, step), s4 = cmul(s2, s2);
+    const float2 s8 = cmul(s4, s4), s12 = cmul(s8, s4), s16 = cmul(s8, s8);
+#pragma unroll
+    for (int q = 0; q < n; ++q) {
+        const int lo = q & 3, hi = q >> 2;
+        float2 v = base;
+        if (lo == 1) v = cmul(v, step);
+        else if (lo == 2) v = cmul(v, s2);
+        else if (lo == 3) v = cmul(v, s3);
+        if (hi == 1) v = cmul(v, s4);
+        else if (hi == 2) v = cmul(v, s8);
+        else if (hi == 3) v = cmul(v, s12);
+        else if (hi == 4) v = cmul(v, s16);
+        w[q] = v;
+    }
+}
+
 struct DevCtaL {
     __device__ __forceinline__ void sync() { __syncthreads(); }
 };
@@ -73,6 +93,12 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
         for (int q = 0; q < R; ++q) sb[saddr<W1>(t + q * T)] = v[q];
         cta.sync();
         float2* c = p.scratch + b * (int64_t)(M2 + 1) * p.n1 + n1;
+        // pass twiddles exp(-2 pi i n1 k / N) for k = t + q*T as a geometric sequence from three
+        // table values (a gather per output would cost an L1 wavefront per lane)
+        float2 wk[R / 2 + 1];
+        geometric_twiddles<R / 2 + 1>(wk, __ldg(p.twL + (int64_t)n1 * t), __ldg(p.twL + (int64_t)n1 * T));
+        const float2 wtop = __ldg(p.twL + (int64_t)n1 * (M2 / 2));
+        const float2 wm2 = cmul(wtop, wtop);  // exp(-2 pi i n1 M2 / N); index n1*M2 may reach N/2, the table's end
 #pragma unroll
         for (int q = 0; q <= R / 2; ++q) {
             const int k = t + q * T;
@@ -82,8 +108,8 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
             float2 xk, xm;
             herm_post(a, bb, __ldg(p.twN2 + k), xk, xm);
             const int km = M2 - k;
-            c[(int64_t)k * p.n1] = cmul(xk, __ldg(p.twL + (int64_t)n1 * k));
-            c[(int64_t)km * p.n1] = cmul(xm, __ldg(p.twL + (int64_t)n1 * km));
+            c[(int64_t)k * p.n1] = cmul(xk, wk[q]);
+            c[(int64_t)km * p.n1] = cmul(xm, cmul(wm2, cconj(wk[q])));
         }
         cta.sync();  // the exchange buffers are reused by the next tile
     }
@@ -210,13 +236,49 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T) rows_inv_kernel(const Larg
         const int64_t b = blk / tiles;
         const int r0 = (int)(blk - b * tiles) * W2;
         float2* tile = smem;
-        for (int idx = threadIdx.x; idx < N1 * W2; idx += THREADS) {
-            const int s = idx % W2;
-            const int k1 = idx / W2;
+        // All of a thread's loads are issued before the first use: one memory latency per tile
+        // instead of one per element.
+        {
+            static_assert(THREADS % W2 == 0 && (N1 * W2) % THREADS == 0, "tile load shape");
+            constexpr int ITER = N1 * W2 / THREADS, KSTEP = THREADS / W2;
+            const int s = threadIdx.x % W2;
+            const int k1base = threadIdx.x / W2;
             const int kk2 = r0 + s;
-            float2 x = make_float2(0.f, 0.f);
-            if (kk2 <= m2) x = load_bin(p, b, (int64_t)k1 * p.n2 + kk2);
-            tile[k1 * (W2 + 1) + s] = make_float2(x.y, x.x);  // swapped: inverse as forward
+            const bool live = kk2 <= m2;
+            const int64_t n = p.n, half = n / 2;
+            float2 x[ITER];
+            if (p.layout == LAYOUT_FULL_SPLIT) {
+                const float* re = p.in + b * n;
+                const float* im = p.in_b + b * n;
+#pragma unroll
+                for (int it = 0; it < ITER; ++it) {
+                    const int64_t k = live ? (int64_t)(k1base + it * KSTEP) * p.n2 + kk2 : 0;
+                    x[it] = make_float2(__ldg(re + k), __ldg(im + k));
+                    if (k == 0 || k == half) x[it].y = 0.f;
+                }
+            } else {
+                const bool packed = p.layout == LAYOUT_HALF_PACKED;
+                const float2* src = reinterpret_cast<const float2*>(p.in) + b * (packed ? half : half + 1);
+#pragma unroll
+                for (int it = 0; it < ITER; ++it) {
+                    const int64_t k = live ? (int64_t)(k1base + it * KSTEP) * p.n2 + kk2 : 0;
+                    const int64_t idx = k > half ? n - k : k;
+                    x[it] = __ldg(src + ((packed && idx == half) ? 0 : idx));
+                }
+#pragma unroll
+                for (int it = 0; it < ITER; ++it) {
+                    const int64_t k = live ? (int64_t)(k1base + it * KSTEP) * p.n2 + kk2 : 0;
+                    const int64_t idx = k > half ? n - k : k;
+                    if (idx == 0) x[it].y = 0.f;
+                    else if (idx == half) x[it] = make_float2(packed ? x[it].y : x[it].x, 0.f);
+                    else if (k > half) x[it].y = -x[it].y;
+                }
+            }
+#pragma unroll
+            for (int it = 0; it < ITER; ++it) {
+                const float2 val = live ? x[it] : make_float2(0.f, 0.f);
+                tile[(k1base + it * KSTEP) * (W2 + 1) + s] = make_float2(val.y, val.x);  // swapped: inverse as forward
+            }
         }
         cta.sync();
         float2 v[R];
@@ -228,11 +290,12 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T) rows_inv_kernel(const Larg
         const int k2 = r0 + slot;
         if (k2 <= m2) {
             float2* row = p.scratch + (b * (int64_t)(m2 + 1) + k2) * N1;
+            float2 wq[R];
+            geometric_twiddles<R>(wq, __ldg(p.twL + (int64_t)k2 * t), __ldg(p.twL + (int64_t)k2 * T));
 #pragma unroll
             for (int q = 0; q < R; ++q) {
                 const int n1 = t + q * T;
-                const float2 w = __ldg(p.twL + (int64_t)n1 * k2);
-                row[n1] = cmul(make_float2(v[q].y, v[q].x), cconj(w));
+                row[n1] = cmul(make_float2(v[q].y, v[q].x), cconj(wq[q]));
             }
         }
         cta.sync();
@@ -258,12 +321,20 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
         float2* sbuf0 = smem + i;
         float2* sb = sbuf0 + parity * (M2 * W1);
         parity ^= 1;
+        float2 ra[R / 2 + 1], rb[R / 2 + 1];
+#pragma unroll
+        for (int q = 0; q <= R / 2; ++q) {  // every load in flight before the first use
+            const int k = t + q * T;
+            const int kc = k > M2 / 2 ? M2 / 2 : k;
+            ra[q] = d[(int64_t)kc * p.n1];
+            rb[q] = d[(int64_t)(M2 - kc) * p.n1];
+        }
 #pragma unroll
         for (int q = 0; q <= R / 2; ++q) {
             const int k = t + q * T;
             if (k > M2 / 2) continue;
-            float2 a = d[(int64_t)k * p.n1];
-            float2 bb = d[(int64_t)(M2 - k) * p.n1];
+            float2 a = ra[q];
+            float2 bb = rb[q];
             if (k == 0) {
                 a.y = 0.f;
                 bb.y = 0.f;
