@@ -152,6 +152,50 @@ __device__ __forceinline__ void store_bin(const LargeParams& p, int64_t b, int64
     if (p.mag != nullptr && interior && n - k <= half) p.mag[b * (half + 1) + (n - k)] = mag_value(v, p.mag_kind, p.db_scale);
 }
 
+// Stores a transposed tile (rows r0 .. r0+W2-1 of the second pass, all N1 columns) into a half
+// spectrum.  Bin k = k1*n2 + kk2 lies in the lower half for k1 < N1/2 and is stored as is; for
+// k1 >= N1/2 its conjugate is bin n-k of the lower half (stored for interior rows only, the edge
+// rows' mirrors being produced directly).  Which case applies is known per unrolled iteration.
+template <int N1, int W2, int THREADS, bool PACKED>
+__device__ __forceinline__ void store_half_tile(const LargeParams& p, int64_t b, int r0, const float2* tile) {
+    static_assert(THREADS % W2 == 0 && (N1 * W2) % THREADS == 0, "tile shape");
+    constexpr int ITER = N1 * W2 / THREADS, KSTEP = THREADS / W2;
+    static_assert(ITER % 2 == 0 && (N1 / 2) % KSTEP == 0, "the halves must split between iterations");
+    const int s = threadIdx.x % W2;
+    const int k1base = threadIdx.x / W2;
+    const int kk2 = r0 + s;
+    const int m2 = p.n2 / 2;
+    if (kk2 > m2) return;
+    const int n = (int)p.n, half = n / 2;
+    const bool interior = kk2 > 0 && kk2 < m2;
+    float2* o = reinterpret_cast<float2*>(p.out_a) + b * (int64_t)(PACKED ? half : half + 1);
+    float* mg = p.mag != nullptr ? p.mag + b * (int64_t)(half + 1) : nullptr;
+#pragma unroll
+    for (int it = 0; it < ITER / 2; ++it) {
+        const int k1 = k1base + it * KSTEP;
+        const int k = k1 * p.n2 + kk2;
+        const float2 v = tile[k1 * (W2 + 1) + s];
+        if (PACKED && k == 0) o[0].x = v.x;
+        else o[k] = v;
+        if (mg != nullptr) mg[k] = mag_value(v, p.mag_kind, p.db_scale);
+    }
+#pragma unroll
+    for (int it = ITER / 2; it < ITER; ++it) {
+        const int k1 = k1base + it * KSTEP;
+        const int k = k1 * p.n2 + kk2;
+        float2 v = tile[k1 * (W2 + 1) + s];
+        if (k == half) {
+            if (PACKED) o[0].y = v.x;
+            else o[half] = v;
+            if (mg != nullptr) mg[half] = mag_value(v, p.mag_kind, p.db_scale);
+        } else if (interior) {
+            v.y = -v.y;
+            o[n - k] = v;
+            if (mg != nullptr) mg[n - k] = mag_value(v, p.mag_kind, p.db_scale);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- forward pass 2
 template <int N1, int W2>
 __global__ void __launch_bounds__(W2* FftPlan<N1>::T) rows_fwd_kernel(const LargeParams p) {
@@ -182,12 +226,18 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T) rows_fwd_kernel(const Larg
 #pragma unroll
         for (int q = 0; q < R; ++q) tile[(t + q * T) * (W2 + 1) + slot] = v[q];
         cta.sync();
-        for (int idx = threadIdx.x; idx < N1 * W2; idx += THREADS) {
-            const int s = idx % W2;
-            const int k1 = idx / W2;
-            const int kk2 = r0 + s;
-            if (kk2 > m2) continue;
-            store_bin(p, b, (int64_t)k1 * p.n2 + kk2, kk2, tile[k1 * (W2 + 1) + s]);
+        if (p.layout == LAYOUT_FULL_SPLIT) {
+            for (int idx = threadIdx.x; idx < N1 * W2; idx += THREADS) {
+                const int s = idx % W2;
+                const int k1 = idx / W2;
+                const int kk2 = r0 + s;
+                if (kk2 > m2) continue;
+                store_bin(p, b, (int64_t)k1 * p.n2 + kk2, kk2, tile[k1 * (W2 + 1) + s]);
+            }
+        } else if (p.layout == LAYOUT_HALF_PACKED) {
+            store_half_tile<N1, W2, THREADS, true>(p, b, r0, tile);
+        } else {
+            store_half_tile<N1, W2, THREADS, false>(p, b, r0, tile);
         }
         cta.sync();
     }
@@ -220,7 +270,7 @@ __device__ __forceinline__ float2 load_bin(const LargeParams& p, int64_t b, int6
 
 // ---------------------------------------------------------------- inverse pass A
 template <int N1, int W2>
-__global__ void __launch_bounds__(W2* FftPlan<N1>::T) rows_inv_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 256 ? 3 : 1) rows_inv_kernel(const LargeParams p) {
     using P = FftPlan<N1>;
     constexpr int R = P::R, T = P::T;
     constexpr int ELEMS = smem_elems_per_fft<N1, 1>();
@@ -257,22 +307,24 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T) rows_inv_kernel(const Larg
                     if (k == 0 || k == half) x[it].y = 0.f;
                 }
             } else {
+                static_assert(ITER % 2 == 0 && (N1 / 2) % KSTEP == 0, "the halves must split between iterations");
                 const bool packed = p.layout == LAYOUT_HALF_PACKED;
                 const float2* src = reinterpret_cast<const float2*>(p.in) + b * (packed ? half : half + 1);
+                const int nn = (int)n, hh = (int)half;
+                // lower half (k1 < N1/2): bin k itself; upper half: the conjugate of bin n-k
 #pragma unroll
                 for (int it = 0; it < ITER; ++it) {
-                    const int64_t k = live ? (int64_t)(k1base + it * KSTEP) * p.n2 + kk2 : 0;
-                    const int64_t idx = k > half ? n - k : k;
-                    x[it] = __ldg(src + ((packed && idx == half) ? 0 : idx));
+                    const int k = live ? (k1base + it * KSTEP) * p.n2 + kk2 : (it < ITER / 2 ? 0 : hh);
+                    int idx = it < ITER / 2 ? k : nn - k;
+                    if (packed && idx == hh) idx = 0;
+                    x[it] = __ldg(src + idx);
+                }
+                if (kk2 == 0 && k1base == 0) {  // the two real bins
+                    x[0].y = 0.f;
+                    x[ITER / 2] = make_float2(packed ? x[ITER / 2].y : x[ITER / 2].x, 0.f);
                 }
 #pragma unroll
-                for (int it = 0; it < ITER; ++it) {
-                    const int64_t k = live ? (int64_t)(k1base + it * KSTEP) * p.n2 + kk2 : 0;
-                    const int64_t idx = k > half ? n - k : k;
-                    if (idx == 0) x[it].y = 0.f;
-                    else if (idx == half) x[it] = make_float2(packed ? x[it].y : x[it].x, 0.f);
-                    else if (k > half) x[it].y = -x[it].y;
-                }
+                for (int it = ITER / 2; it < ITER; ++it) x[it].y = -x[it].y;
             }
 #pragma unroll
             for (int it = 0; it < ITER; ++it) {
@@ -409,7 +461,8 @@ static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse)
 template <int N1, int W2>
 static ma_status run_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse) {
     constexpr int threads = W2 * FftPlan<N1>::T;
-    constexpr size_t smem = 2 * (size_t)smem_elems_per_fft<N1, 1>() * W2 * sizeof(float2);
+    // plans with a single exchange (two stages) never touch the second exchange buffer
+    constexpr size_t smem = (FftPlan<N1>::NS > 2 ? 2 : 1) * (size_t)smem_elems_per_fft<N1, 1>() * W2 * sizeof(float2);
     static_assert((size_t)N1 * (W2 + 1) * sizeof(float2) <= smem, "transposed tile must fit the exchange buffers");
     ma_context* ctx = plan->ctx;
     auto kf = rows_fwd_kernel<N1, W2>;
