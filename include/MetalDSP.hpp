@@ -69,6 +69,13 @@ struct ConvolutionError : std::runtime_error {
         return ConvolutionError("fftNotInitialized",
                                 "FFT resources failed to initialize. This may indicate a Metal device error.");
     }
+    static ConvolutionError inputSizeMismatch(int64_t inputSize, int64_t expectedMaxSize, int64_t fftSize) {
+        return ConvolutionError("inputSizeMismatch",
+                                "Convolution input size " + std::to_string(inputSize) + " exceeds expected maximum " +
+                                    std::to_string(expectedMaxSize) + " (FFT size: " + std::to_string(fftSize) +
+                                    "). This would cause circular convolution artifacts. Call setKernel() with a larger "
+                                    "expectedInputSize parameter.");
+    }
     static ConvolutionError outputSizeOverflow(int64_t inputSize, int64_t kernelSize) {
         return ConvolutionError("outputSizeOverflow", "Output size would overflow: input (" + std::to_string(inputSize) +
                                                           ") + kernel (" + std::to_string(kernelSize) +
@@ -374,20 +381,39 @@ private:
 // ------------------------------------------------------------------------------ convolution
 class Convolution {
 public:
-    struct Mode {  // Convolution.swift:112-125; only .partitioned is served
+    struct Mode {  // Convolution.swift:112-125; .fft and .partitioned are served, .direct is not
+        enum Kind { kFFT, kPartitioned } kind;
         int blockSize;
         bool useMPSGraphFFT;
-        static Mode partitioned(int blockSize, bool useMPSGraphFFT = false) { return Mode{blockSize, useMPSGraphFFT}; }
+        static Mode fft() { return Mode{kFFT, 0, false}; }
+        static Mode partitioned(int blockSize, bool useMPSGraphFFT = false) { return Mode{kPartitioned, blockSize, useMPSGraphFFT}; }
     };
 
-    Convolution(AudioDevice& device, Mode mode, int channels = 1) : device_(device), mode_(mode), channels_(channels) {}
-    ~Convolution() { ma_pconv_destroy(pc_); }
+    explicit Convolution(AudioDevice& device, Mode mode = Mode::fft(), int channels = 1)
+        : device_(device), mode_(mode), channels_(channels) {}
+    ~Convolution() {
+        ma_pconv_destroy(pc_);
+        ma_fftconv_destroy(fc_);
+    }
     Convolution(const Convolution&) = delete;
     Convolution& operator=(const Convolution&) = delete;
 
-    // Convolution.swift:188-208 -> :250-322
-    void setKernel(const std::vector<float>& kernel) {
+    // Convolution.swift:188-208 -> :210-248 (.fft) or :250-322 (.partitioned).  expectedInputSize
+    // (.fft only) defaults to the kernel length, as in the reference.
+    void setKernel(const std::vector<float>& kernel, int64_t expectedInputSize = -1) {
         if (kernel.empty()) throw ConvolutionError::emptyKernel();
+        if (mode_.kind == Mode::kFFT) {
+            const int64_t expected = expectedInputSize < 0 ? (int64_t)kernel.size() : expectedInputSize;
+            ma_fftconv_destroy(fc_);
+            fc_ = nullptr;
+            const ma_status st = ma_fftconv_create(device_.handle(), kernel.data(), (int64_t)kernel.size(), expected, channels_, &fc_);
+            if (st == MA_ERR_SIZE_TOO_LARGE) throw FFTError::sizeTooLarge(expected + (int64_t)kernel.size() - 1, 1 << 24);
+            throwStatus(st, "setKernel");
+            ma_fftconv_fft_size(fc_, &fftSize_);
+            expected_ = expected;
+            taps_ = (int64_t)kernel.size();
+            return;
+        }
         if (mode_.blockSize <= 0)
             throw MetalAudioError("invalidConfiguration", "Block size must be positive, got " + std::to_string(mode_.blockSize));
         if ((mode_.blockSize & (mode_.blockSize - 1)) != 0) throw FFTError::sizeNotPowerOf2(2 * mode_.blockSize);
@@ -397,17 +423,28 @@ public:
     }
     int64_t kernelTailLength() const { return taps_ > 0 ? taps_ - 1 : 0; }
     int64_t expectedOutputSize(int64_t inputSize) const { return taps_ > 0 ? inputSize + taps_ - 1 : inputSize; }
-    int64_t maxInputSize() const { return 0; }
+    int64_t maxInputSize() const { return mode_.kind == Mode::kFFT ? expected_ : 0; }  // Convolution.swift:377-383
+    int64_t fftSize() const { return fftSize_; }
     int partitionCount() const {
         int32_t p = 0;
         if (pc_) ma_pconv_partition_count(pc_, &p);
         return p;
     }
 
-    // Convolution.swift:336-352 -> :529-758: channels x L in, channels x (L+K-1) out (row-major).
+    // Convolution.swift:336-352.  .partitioned (-> :529-758): channels x L in, channels x (L+K-1)
+    // out (row-major).  .fft (-> :437-493): fftSize samples per signal, a smaller output is
+    // replaced, a larger one keeps its tail.
     void process(const std::vector<float>& input, std::vector<float>& output) {
         if (input.empty()) {
             output.clear();
+            return;
+        }
+        if (mode_.kind == Mode::kFFT) {
+            if (fc_ == nullptr) throw ConvolutionError::fftNotInitialized();
+            const int64_t len = (int64_t)input.size() / channels_;
+            if (len > expected_) throw ConvolutionError::inputSizeMismatch(len, expected_, fftSize_);
+            if ((int64_t)output.size() < fftSize_ * channels_) output.assign((size_t)(fftSize_ * channels_), 0.f);
+            throwStatus(ma_fftconv_process_host(fc_, input.data(), len, len, channels_, output.data()), "process");
             return;
         }
         if (pc_ == nullptr) throw ConvolutionError::fftNotInitialized();
@@ -425,8 +462,9 @@ private:
     AudioDevice& device_;
     Mode mode_;
     int channels_;
-    int64_t taps_ = 0;
+    int64_t taps_ = 0, expected_ = 0, fftSize_ = 0;
     ma_pconv* pc_ = nullptr;
+    ma_fftconv* fc_ = nullptr;
 };
 
 }  // namespace metalaudio

@@ -54,7 +54,8 @@ enum {
     MA_ERR_DEVICE_LOST = 14,           /* MetalAudioError.deviceLost / deviceNotFound */
     MA_ERR_CUDA = 15,                  /* MetalAudioError.gpuExecutionError; see ma_last_cuda_error */
     MA_ERR_UNSUPPORTED = 16,
-    MA_ERR_SCRATCH_LIMIT = 17          /* work needs more scratch than the built-in static buffer holds */
+    MA_ERR_SCRATCH_LIMIT = 17,         /* work needs more scratch than the built-in static buffer holds */
+    MA_ERR_INPUT_SIZE_MISMATCH = 18    /* ConvolutionError.inputSizeMismatch */
 };
 
 /* Spectrum layouts accepted / produced by the transforms (N = FFT size). */
@@ -62,8 +63,16 @@ enum {
     MA_LAYOUT_HALF_INTERLEAVED = 0, /* N/2+1 interleaved complex bins per frame (re,im pairs) */
     MA_LAYOUT_FULL_SPLIT = 1,       /* the reference's layout: real[N] and imag[N] per frame,
                                        bins N/2+1..N-1 the conjugate mirror (FFT.swift:799-802) */
-    MA_LAYOUT_HALF_PACKED = 2       /* N/2 interleaved complex bins, bin 0 = (DC, Nyquist);
+    MA_LAYOUT_HALF_PACKED = 2,      /* N/2 interleaved complex bins, bin 0 = (DC, Nyquist);
                                        internal format of the convolution delay line */
+    MA_LAYOUT_HALF_POLAR = 3        /* array a = magnitude[N/2+1], array b = phase[N/2+1] (radians,
+                                       atan2(im, re)) per frame: the magnitude / phase split and
+                                       the polar -> complex rebuild that the reference's one STFT
+                                       consumer does on the host around stft / istft
+                                       (Sources/MetalNN/HTDemucs.swift:726-741, :795-812; shader
+                                       forms compute_phase / polar_to_complex,
+                                       Shaders/DSP.metal:806-834), fused into the transforms.
+                                       Plans up to 8192 points. */
 };
 
 /* Magnitude kinds (FFT.swift:1780-1847). */
@@ -75,6 +84,7 @@ enum { MA_FAULT_ALLOC = 0, MA_FAULT_LAUNCH = 1, MA_FAULT_SYNC = 2, MA_FAULT_DEVI
 typedef struct ma_context ma_context;
 typedef struct ma_fft_plan ma_fft_plan;
 typedef struct ma_pconv ma_pconv;
+typedef struct ma_fftconv ma_fftconv;
 
 /* ------------------------------------------------------------------ library */
 
@@ -206,6 +216,19 @@ ma_status ma_fft_magnitude_dev(ma_fft_plan* plan, const float* re, const float* 
 ma_status ma_fft_magnitude_host(ma_fft_plan* plan, const float* re, const float* im, float* out,
                                 int64_t batch, int32_t kind, float db_reference);
 
+/* ------------------------------------------------------------------ spectrum glue
+ * Elementwise steps of the reference's shader library on device arrays, stream-ordered:
+ * compute_magnitude + compute_phase in one pass over `count` interleaved complex bins
+ * (Shaders/DSP.metal:784-813; either output may be NULL), polar_to_complex (:821-834) and the
+ * in-place to_decibels with its 1e-10 ratio clamp, min_db floor and reference <= 0 fallback
+ * (:861-881).  The transforms produce and consume the same quantities directly with
+ * MA_LAYOUT_HALF_POLAR; these serve spectra that already exist. */
+ma_status ma_spectrum_to_polar_dev(ma_context* ctx, const float* spectrum, float* magnitude, float* phase,
+                                   int64_t count);
+ma_status ma_polar_to_spectrum_dev(ma_context* ctx, const float* magnitude, const float* phase, float* spectrum,
+                                   int64_t count);
+ma_status ma_to_decibels_dev(ma_context* ctx, float* data, int64_t count, float reference, float min_db);
+
 /* ------------------------------------------------------------------ STFT / iSTFT */
 
 /* Frame count (L - N)/hop + 1 for a signal of `length` (STFT.swift:45-49);
@@ -271,6 +294,27 @@ ma_status ma_pconv_step_dev(ma_pconv* pc, const float* in_block, int64_t in_stri
                             float* out_block, int64_t out_stride);
 /* Zero the delay line, the write index and the overlap tail (Convolution.reset). */
 ma_status ma_pconv_reset(ma_pconv* pc);
+
+/* ------------------------------------------------------------------ one-shot FFT convolution
+ * Replaces Convolution(device:mode: .fft) + setKernel(_:expectedInputSize:) + process
+ * (Convolution.swift:188-208, :210-248, :437-493) for up to `max_signals` signals that share one
+ * kernel.  fft_size is the next power of two >= expected_input + taps - 1 (at least 2);
+ * MA_ERR_EMPTY_KERNEL for taps == 0, MA_ERR_SIZE_TOO_LARGE above 2^24.  The kernel (host memory)
+ * is transformed once here; every work buffer is allocated here. */
+ma_status ma_fftconv_create(ma_context* ctx, const float* kernel, int64_t taps, int64_t expected_input,
+                            int32_t max_signals, ma_fftconv** out);
+ma_status ma_fftconv_destroy(ma_fftconv* fc);
+ma_status ma_fftconv_fft_size(ma_fftconv* fc, int64_t* fft_size);
+/* Signal s (len samples at in + s*in_stride) is zero-padded to fft_size, transformed, multiplied
+ * by the kernel spectrum and transformed back: out receives n_signals contiguous rows of fft_size
+ * samples, the linear convolution in the first len + taps - 1 of them (the reference returns the
+ * same fft_size samples).  len > expected_input would wrap around and is refused with
+ * MA_ERR_INPUT_SIZE_MISMATCH (Convolution.swift:461-467); n_signals > max_signals gives
+ * MA_ERR_BATCH_OVERFLOW.  The _dev form allocates nothing. */
+ma_status ma_fftconv_process_dev(ma_fftconv* fc, const float* in, int64_t len, int64_t in_stride,
+                                 int32_t n_signals, float* out);
+ma_status ma_fftconv_process_host(ma_fftconv* fc, const float* in, int64_t len, int64_t in_stride,
+                                  int32_t n_signals, float* out);
 
 #ifdef __cplusplus
 }

@@ -65,6 +65,14 @@ SIGNATURES = {
     "ma_pconv_process_host": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64]),
     "ma_pconv_step_dev": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64]),
     "ma_pconv_reset": (c_int32, [c_void_p]),
+    "ma_spectrum_to_polar_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64]),
+    "ma_polar_to_spectrum_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64]),
+    "ma_to_decibels_dev": (c_int32, [c_void_p, c_void_p, c_int64, c_float, c_float]),
+    "ma_fftconv_create": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int32, POINTER(c_void_p)]),
+    "ma_fftconv_destroy": (c_int32, [c_void_p]),
+    "ma_fftconv_fft_size": (c_int32, [c_void_p, POINTER(c_int64)]),
+    "ma_fftconv_process_dev": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p]),
+    "ma_fftconv_process_host": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p]),
 }
 
 # Status codes and enums (include/metalaudio_cuda.h).
@@ -72,8 +80,9 @@ MA_OK = 0
 (MA_ERR_INVALID_ARGUMENT, MA_ERR_SIZE_NOT_POW2, MA_ERR_SIZE_TOO_LARGE, MA_ERR_INVALID_HOP,
  MA_ERR_INPUT_TOO_SHORT, MA_ERR_BATCH_OVERFLOW, MA_ERR_ISTFT_OVERFLOW, MA_ERR_EMPTY_KERNEL,
  MA_ERR_KERNEL_NOT_CONFIGURED, MA_ERR_INVALID_PARTITION_STATE, MA_ERR_OUTPUT_OVERFLOW, MA_ERR_ALLOC,
- MA_ERR_TIMEOUT, MA_ERR_DEVICE_LOST, MA_ERR_CUDA, MA_ERR_UNSUPPORTED, MA_ERR_SCRATCH_LIMIT) = range(1, 18)
-LAYOUT_HALF_INTERLEAVED, LAYOUT_FULL_SPLIT, LAYOUT_HALF_PACKED = 0, 1, 2
+ MA_ERR_TIMEOUT, MA_ERR_DEVICE_LOST, MA_ERR_CUDA, MA_ERR_UNSUPPORTED, MA_ERR_SCRATCH_LIMIT,
+ MA_ERR_INPUT_SIZE_MISMATCH) = range(1, 19)
+LAYOUT_HALF_INTERLEAVED, LAYOUT_FULL_SPLIT, LAYOUT_HALF_PACKED, LAYOUT_HALF_POLAR = 0, 1, 2, 3
 MAG_MAGNITUDE, MAG_POWER, MAG_DB = 0, 1, 2
 FAULT_ALLOC, FAULT_LAUNCH, FAULT_SYNC, FAULT_DEVICE_LOST = 0, 1, 2, 3
 

@@ -157,6 +157,7 @@ const char* ma_status_string(ma_status s) {
         case MA_ERR_CUDA: return "CUDA execution error";
         case MA_ERR_UNSUPPORTED: return "unsupported configuration";
         case MA_ERR_SCRATCH_LIMIT: return "transform needs more scratch than the built-in static buffer holds";
+        case MA_ERR_INPUT_SIZE_MISMATCH: return "convolution input exceeds the expected size (circular wrap-around)";
         default: return "unknown status";
     }
 }

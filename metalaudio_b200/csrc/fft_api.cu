@@ -20,13 +20,17 @@ static ma_status upload(ma_context* ctx, const void* host, size_t bytes, void** 
 }
 
 static bool valid_layout(int layout) {
-    return layout == MA_LAYOUT_HALF_INTERLEAVED || layout == MA_LAYOUT_FULL_SPLIT || layout == MA_LAYOUT_HALF_PACKED;
+    return layout == MA_LAYOUT_HALF_INTERLEAVED || layout == MA_LAYOUT_FULL_SPLIT || layout == MA_LAYOUT_HALF_PACKED ||
+           layout == MA_LAYOUT_HALF_POLAR;
 }
+// Layouts that use the second array.
+static bool two_arrays(int layout) { return layout == MA_LAYOUT_FULL_SPLIT || layout == MA_LAYOUT_HALF_POLAR; }
 
 // Output floats per frame in array a / b for a layout.
 static int64_t floats_a(int n, int layout) {
     if (layout == MA_LAYOUT_FULL_SPLIT) return n;
     if (layout == MA_LAYOUT_HALF_PACKED) return n;  // N/2 complex
+    if (layout == MA_LAYOUT_HALF_POLAR) return n / 2 + 1;
     return 2 * (int64_t)(n / 2 + 1);
 }
 static int64_t complex_per_frame(int n, int layout) {
@@ -105,11 +109,12 @@ ma_status ma_fft_forward_dev(ma_fft_plan* plan, const float* in, float* out_a, f
     MA_TRY(enter(plan->ctx, MA_FAULT_LAUNCH));
     if (batch == 0) return MA_OK;  // empty batch is a no-op (STFT.swift:99-100)
     if (batch < 0 || !valid_layout(layout) || in == nullptr || out_a == nullptr) return MA_ERR_INVALID_ARGUMENT;
-    if (layout == MA_LAYOUT_FULL_SPLIT && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (two_arrays(layout) && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
     if (mag != nullptr && (mag_kind < MA_MAG_MAGNITUDE || mag_kind > MA_MAG_DB)) return MA_ERR_INVALID_ARGUMENT;
     int64_t total;
     if (mul_overflow(batch, plan->n, &total)) return MA_ERR_BATCH_OVERFLOW;
     const float db_scale = 1.0f / db_reference;
+    if (plan->large && layout == MA_LAYOUT_HALF_POLAR) return MA_ERR_UNSUPPORTED;
     if (plan->large) return launch_r2c_large(plan, in, out_a, out_b, mag, mag_kind, db_scale, batch, layout);
     R2CParams p{};
     p.in = in;
@@ -137,9 +142,10 @@ ma_status ma_fft_inverse_dev(ma_fft_plan* plan, const float* in_a, const float* 
     MA_TRY(enter(plan->ctx, MA_FAULT_LAUNCH));
     if (batch == 0) return MA_OK;
     if (batch < 0 || !valid_layout(layout) || in_a == nullptr || out == nullptr) return MA_ERR_INVALID_ARGUMENT;
-    if (layout == MA_LAYOUT_FULL_SPLIT && in_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (two_arrays(layout) && in_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
     int64_t total;
     if (mul_overflow(batch, plan->n, &total)) return MA_ERR_BATCH_OVERFLOW;
+    if (plan->large && layout == MA_LAYOUT_HALF_POLAR) return MA_ERR_UNSUPPORTED;
     if (plan->large) return launch_c2r_large(plan, in_a, in_b, out, batch, layout);
     C2RParams p{};
     p.in_a = in_a;
@@ -188,7 +194,7 @@ ma_status ma_stft_dev(ma_fft_plan* plan, const float* signals, int64_t length, i
     MA_TRY(enter(plan->ctx, MA_FAULT_LAUNCH));
     if (n_signals == 0) return MA_OK;
     if (n_signals < 0 || !valid_layout(layout) || signals == nullptr || out_a == nullptr) return MA_ERR_INVALID_ARGUMENT;
-    if (layout == MA_LAYOUT_FULL_SPLIT && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (two_arrays(layout) && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
     if (mag != nullptr && (mag_kind < MA_MAG_MAGNITUDE || mag_kind > MA_MAG_DB)) return MA_ERR_INVALID_ARGUMENT;
     int64_t frames;
     MA_TRY(ma_stft_frame_count(plan, length, &frames));
@@ -224,7 +230,7 @@ ma_status ma_istft_dev(ma_fft_plan* plan, const float* in_a, const float* in_b, 
     if (frames == 0 || n_signals == 0) return MA_OK;  // frameCount == 0 -> empty output (STFT.swift:389)
     if (frames < 0 || n_signals < 0 || !valid_layout(layout) || in_a == nullptr || out == nullptr)
         return MA_ERR_INVALID_ARGUMENT;
-    if (layout == MA_LAYOUT_FULL_SPLIT && in_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (two_arrays(layout) && in_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
     if (!(floor > 0.f)) return MA_ERR_INVALID_ARGUMENT;
     int64_t out_len;
     MA_TRY(ma_istft_output_length(plan, frames, &out_len));
@@ -259,13 +265,13 @@ ma_status ma_fft_forward_host(ma_fft_plan* plan, const float* in, float* out_a, 
     MA_TRY(enter(ctx, MA_FAULT_LAUNCH));
     if (batch == 0) return MA_OK;
     if (batch < 0 || !valid_layout(layout) || in == nullptr || out_a == nullptr) return MA_ERR_INVALID_ARGUMENT;
-    if (layout == MA_LAYOUT_FULL_SPLIT && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (two_arrays(layout) && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
     int64_t total;
     if (mul_overflow(batch, plan->n, &total) || total > (int64_t)(std::numeric_limits<int64_t>::max() / 16))
         return MA_ERR_BATCH_OVERFLOW;
     const size_t in_b_ = (size_t)total * sizeof(float);
     const size_t a_b = (size_t)(batch * floats_a(plan->n, layout)) * sizeof(float);
-    const size_t b_b = layout == MA_LAYOUT_FULL_SPLIT ? a_b : 0;
+    const size_t b_b = two_arrays(layout) ? a_b : 0;
     const size_t m_b = mag ? (size_t)(batch * (plan->n / 2 + 1)) * sizeof(float) : 0;
     float *d_in = nullptr, *d_a = nullptr, *d_b = nullptr, *d_m = nullptr;
     ma_status st = temp_alloc(ctx, in_b_, (void**)&d_in);
@@ -291,12 +297,12 @@ ma_status ma_fft_inverse_host(ma_fft_plan* plan, const float* in_a, const float*
     MA_TRY(enter(ctx, MA_FAULT_LAUNCH));
     if (batch == 0) return MA_OK;
     if (batch < 0 || !valid_layout(layout) || in_a == nullptr || out == nullptr) return MA_ERR_INVALID_ARGUMENT;
-    if (layout == MA_LAYOUT_FULL_SPLIT && in_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (two_arrays(layout) && in_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
     int64_t total;
     if (mul_overflow(batch, plan->n, &total) || total > (int64_t)(std::numeric_limits<int64_t>::max() / 16))
         return MA_ERR_BATCH_OVERFLOW;
     const size_t a_b = (size_t)(batch * floats_a(plan->n, layout)) * sizeof(float);
-    const size_t b_b = layout == MA_LAYOUT_FULL_SPLIT ? a_b : 0;
+    const size_t b_b = two_arrays(layout) ? a_b : 0;
     const size_t o_b = (size_t)total * sizeof(float);
     float *d_a = nullptr, *d_b = nullptr, *d_o = nullptr;
     ma_status st = temp_alloc(ctx, a_b, (void**)&d_a);
@@ -347,7 +353,7 @@ ma_status ma_stft_host(ma_fft_plan* plan, const float* signals, int64_t length, 
     MA_TRY(enter(ctx, MA_FAULT_LAUNCH));
     if (n_signals == 0) return MA_OK;
     if (n_signals < 0 || !valid_layout(layout) || signals == nullptr || out_a == nullptr) return MA_ERR_INVALID_ARGUMENT;
-    if (layout == MA_LAYOUT_FULL_SPLIT && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (two_arrays(layout) && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
     int64_t frames;
     MA_TRY(ma_stft_frame_count(plan, length, &frames));
     if (n_signals > 1 && signal_stride < length) return MA_ERR_INVALID_ARGUMENT;
@@ -357,7 +363,7 @@ ma_status ma_stft_host(ma_fft_plan* plan, const float* signals, int64_t length, 
     // Device copy of the signals is dense: signal s at s*dlen (dlen even keeps pairs aligned).
     const int64_t dlen = length + (length & 1);
     const size_t a_b = (size_t)(total * floats_a(plan->n, layout)) * sizeof(float);
-    const size_t b_b = layout == MA_LAYOUT_FULL_SPLIT ? a_b : 0;
+    const size_t b_b = two_arrays(layout) ? a_b : 0;
     const size_t m_b = mag ? (size_t)(total * (plan->n / 2 + 1)) * sizeof(float) : 0;
     float *d_in = nullptr, *d_a = nullptr, *d_b = nullptr, *d_m = nullptr;
     ma_status st = temp_alloc(ctx, (size_t)(dlen * n_signals) * sizeof(float), (void**)&d_in);
@@ -392,7 +398,7 @@ ma_status ma_istft_host(ma_fft_plan* plan, const float* in_a, const float* in_b,
     if (frames == 0 || n_signals == 0) return MA_OK;
     if (frames < 0 || n_signals < 0 || !valid_layout(layout) || in_a == nullptr || out == nullptr)
         return MA_ERR_INVALID_ARGUMENT;
-    if (layout == MA_LAYOUT_FULL_SPLIT && in_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (two_arrays(layout) && in_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
     int64_t out_len;
     MA_TRY(ma_istft_output_length(plan, frames, &out_len));
     if (n_signals > 1 && out_stride < out_len) return MA_ERR_INVALID_ARGUMENT;
@@ -400,7 +406,7 @@ ma_status ma_istft_host(ma_fft_plan* plan, const float* in_a, const float* in_b,
     if (mul_overflow(frames, n_signals, &total) || mul_overflow(total, 4 * (int64_t)plan->n, &total_in))
         return MA_ERR_BATCH_OVERFLOW;
     const size_t a_b = (size_t)(total * floats_a(plan->n, layout)) * sizeof(float);
-    const size_t b_b = layout == MA_LAYOUT_FULL_SPLIT ? a_b : 0;
+    const size_t b_b = two_arrays(layout) ? a_b : 0;
     float *d_a = nullptr, *d_b = nullptr, *d_o = nullptr;
     ma_status st = temp_alloc(ctx, a_b, (void**)&d_a);
     if (st == MA_OK && b_b) st = temp_alloc(ctx, b_b, (void**)&d_b);

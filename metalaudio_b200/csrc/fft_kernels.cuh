@@ -11,7 +11,7 @@
 
 namespace ma {
 
-enum : int { LAYOUT_HALF_INTERLEAVED = 0, LAYOUT_FULL_SPLIT = 1, LAYOUT_HALF_PACKED = 2 };
+enum : int { LAYOUT_HALF_INTERLEAVED = 0, LAYOUT_FULL_SPLIT = 1, LAYOUT_HALF_PACKED = 2, LAYOUT_HALF_POLAR = 3 };
 enum : int { MAG_NONE = -1, MAG_MAGNITUDE = 0, MAG_POWER = 1, MAG_DB = 2 };
 
 struct R2CParams {
@@ -124,6 +124,13 @@ MA_HD void r2c_store_pair(const R2CParams& p, int64_t g, int64_t half_off, int k
             o[k] = xk;
             o[km] = xm;
         }
+    } else if (layout == LAYOUT_HALF_POLAR) {
+        float* mg = p.out_a + g * (int64_t)(M + 1);
+        float* ph = p.out_b + g * (int64_t)(M + 1);
+        mg[k] = sqrtf(xk.x * xk.x + xk.y * xk.y);
+        ph[k] = atan2f(xk.y, xk.x);
+        mg[km] = sqrtf(xm.x * xm.x + xm.y * xm.y);
+        ph[km] = atan2f(xm.y, xm.x);
     } else {
         float* re = p.out_a + g * (int64_t)N;
         float* im = p.out_b + g * (int64_t)N;
@@ -420,6 +427,15 @@ MA_HD void c2r_load_pair(const C2RParams& p, const float2* x, int64_t g, int k, 
             a = xa;
             b = xb;
         }
+    } else if (layout == LAYOUT_HALF_POLAR) {
+        const float* mg = p.in_a + g * (int64_t)(M + 1);
+        const float* ph = p.in_b + g * (int64_t)(M + 1);
+        float sa, ca, sb, cb;
+        sincosf(MA_LDG(ph + k), &sa, &ca);
+        sincosf(MA_LDG(ph + km), &sb, &cb);
+        const float ma = MA_LDG(mg + k), mb = MA_LDG(mg + km);
+        a = make_float2(ma * ca, k == 0 ? 0.f : ma * sa);
+        b = make_float2(mb * cb, k == 0 ? 0.f : mb * sb);
     } else {
         a = STAGED ? x[k] : MA_LDG(x + k);
         if (STAGED && k == 0) b = MA_LDG(xg + M);  // bin M is not staged

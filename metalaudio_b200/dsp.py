@@ -661,6 +661,36 @@ class FFT:
         _raise_status(st, "istftBatch")
         return out
 
+    def stftPolar(self, signals: np.ndarray):
+        """STFT of (S, L) signals straight to magnitude and phase, float32 (S, F, N/2+1) each:
+        the split HTDemucs does on the host after stft (HTDemucs.swift:726-741), fused into the
+        transform so the complex spectrum never reaches memory."""
+        x = _f32(signals)
+        s, length = x.shape
+        f = self.frameCount(length)
+        kh = self.size // 2 + 1
+        mag = np.empty((s, f, kh), np.float32)
+        phase = np.empty((s, f, kh), np.float32)
+        st = self._lib.ma_stft_host(self._h, _ptr(x), length, length, s, _ptr(mag), _ptr(phase), None,
+                                    L.MAG_MAGNITUDE, 1.0, L.LAYOUT_HALF_POLAR)
+        _raise_status(st, "stftPolar")
+        return mag, phase
+
+    def istftPolar(self, magnitude: np.ndarray, phase: np.ndarray) -> np.ndarray:
+        """iSTFT from magnitude and phase (S, F, N/2+1): the polar -> complex rebuild with its
+        conjugate mirror (HTDemucs.swift:795-812) fused into the inverse transform."""
+        m = _f32(magnitude)
+        ph = _f32(phase)
+        if m.shape != ph.shape or m.ndim != 3:
+            raise MetalAudioError.invalidConfiguration("magnitude and phase must both be (S, F, N/2+1)")
+        s, f, kh = m.shape
+        out_len = (f - 1) * self.config.hopSize + self.size
+        out = np.empty((s, out_len), np.float32)
+        st = self._lib.ma_istft_host(self._h, _ptr(m), _ptr(ph), f, s, _ptr(out), out_len,
+                                     validatedWindowFloor(), L.LAYOUT_HALF_POLAR)
+        _raise_status(st, "istftPolar")
+        return out
+
     # ---- device-resident forms: Tensor in, Tensor out, nothing crosses PCIe
     def stftTensor(self, signals: "Tensor", spectrum: "Tensor", magnitude: Optional["Tensor"] = None) -> int:
         """STFT of a (S, L) signal Tensor into a (S, F, N/2+1, 2) spectrum Tensor (and a
@@ -704,8 +734,35 @@ class FFT:
 
 # --------------------------------------------------------------------------- convolution
 
+def spectrumToPolar(device: "AudioDevice", spectrum: "Tensor", magnitude: Optional["Tensor"],
+                    phase: Optional["Tensor"]) -> None:
+    """compute_magnitude + compute_phase (DSP.metal:784-813) over a Tensor of interleaved complex
+    bins (last dimension 2); either output may be None."""
+    st = device._lib.ma_spectrum_to_polar_dev(device.handle, ctypes.c_void_p(spectrum.pointer),
+                                              ctypes.c_void_p(magnitude.pointer) if magnitude is not None else None,
+                                              ctypes.c_void_p(phase.pointer) if phase is not None else None,
+                                              spectrum.count // 2)
+    _raise_status(st, "spectrumToPolar")
+
+
+def polarToSpectrum(device: "AudioDevice", magnitude: "Tensor", phase: "Tensor", spectrum: "Tensor") -> None:
+    """polar_to_complex (DSP.metal:821-834)."""
+    st = device._lib.ma_polar_to_spectrum_dev(device.handle, ctypes.c_void_p(magnitude.pointer),
+                                              ctypes.c_void_p(phase.pointer), ctypes.c_void_p(spectrum.pointer),
+                                              magnitude.count)
+    _raise_status(st, "polarToSpectrum")
+
+
+def toDecibels(device: "AudioDevice", data: "Tensor", reference: float = 1.0, minDB: float = -100.0) -> None:
+    """to_decibels in place (DSP.metal:861-881)."""
+    st = device._lib.ma_to_decibels_dev(device.handle, ctypes.c_void_p(data.pointer), data.count, float(reference),
+                                        float(minDB))
+    _raise_status(st, "toDecibels")
+
+
 class Convolution:
-    """Convolution.swift:176.  Only ``Mode.partitioned`` is served by this backend."""
+    """Convolution.swift:176.  ``Mode.partitioned`` and ``Mode.fft`` are served by this backend;
+    ``Mode.direct`` (vDSP cross-correlation semantics, Convolution.swift:400-434) is not."""
 
     class Mode:
         """Convolution.swift:112-125."""
@@ -719,17 +776,27 @@ class Convolution:
         def partitioned(blockSize: int, useMPSGraphFFT: bool = False) -> "Convolution.Mode":
             return Convolution.Mode("partitioned", blockSize, useMPSGraphFFT)
 
-    def __init__(self, device: AudioDevice, mode: "Convolution.Mode", channels: int = 1):
+        @staticmethod
+        def fft() -> "Convolution.Mode":
+            return Convolution.Mode("fft")
+
+    def __init__(self, device: AudioDevice, mode: Optional["Convolution.Mode"] = None, channels: int = 1):
         """``channels`` > 1 runs that many independent channels through one object (the
-        reference holds one object per channel)."""
-        if mode.kind != "partitioned":
-            raise MetalAudioError.invalidConfiguration("only .partitioned mode is served by the CUDA backend")
+        reference holds one object per channel).  The default mode is ``.fft``
+        (Convolution.swift:176)."""
+        if mode is None:
+            mode = Convolution.Mode.fft()
+        if mode.kind not in ("partitioned", "fft"):
+            raise MetalAudioError.invalidConfiguration("only .partitioned and .fft modes are served by the CUDA backend")
         self.device = device
         self.mode = mode
         self.channels = int(channels)
         self.kernel = np.zeros(0, np.float32)
         self._lib = device._lib
         self._h = None
+        self._fc = None           # .fft mode handle
+        self.fftSize = 0
+        self._expected = 0
 
     def setKernel(self, kernel: np.ndarray, expectedInputSize: Optional[int] = None,
                   channelToKernel: Optional[Sequence[int]] = None) -> None:
@@ -738,6 +805,8 @@ class Convolution:
         k = _f32(kernel)
         if k.size == 0:
             raise ConvolutionError.emptyKernel()
+        if self.mode.kind == "fft":
+            return self._setup_fft(k, expectedInputSize)
         b = int(self.mode.blockSize)
         if b <= 0:
             raise MetalAudioError.invalidConfiguration(f"Block size must be positive, got {b}")
@@ -757,6 +826,49 @@ class Convolution:
         st = self._lib.ma_pconv_set_kernels(self._h, _ptr(k2), self._taps, int(k2.shape[0]), _ptr(cmap))
         _raise_status(st, "Convolution.setKernel")
 
+    def _setup_fft(self, k: np.ndarray, expectedInputSize: Optional[int]) -> None:
+        """Convolution.swift:210-248: FFT size = next power of two >= expected + taps - 1."""
+        if k.ndim != 1:
+            raise MetalAudioError.invalidConfiguration(".fft mode takes one kernel")
+        expected = int(k.size if expectedInputSize is None else expectedInputSize)
+        if expected + k.size - 1 > (1 << 24):
+            raise FFTError.sizeTooLarge(expected + int(k.size) - 1, 1 << 24)
+        if self._fc is not None:
+            self._lib.ma_fftconv_destroy(self._fc)
+            self._fc = None
+        h = ctypes.c_void_p()
+        st = self._lib.ma_fftconv_create(self.device.handle, _ptr(k), int(k.size), expected, self.channels,
+                                         ctypes.byref(h))
+        _raise_status(st, "Convolution.setKernel")
+        self._fc = h
+        self.kernel = k
+        self._taps = int(k.size)
+        self._expected = expected
+        n = ctypes.c_int64(0)
+        self._lib.ma_fftconv_fft_size(h, ctypes.byref(n))
+        self.fftSize = int(n.value)
+
+    def _process_fft(self, x: np.ndarray, output: Optional[np.ndarray]) -> np.ndarray:
+        """Convolution.swift:437-493: fftSize samples per signal, the linear convolution in the
+        first len + taps - 1 of them."""
+        if self._fc is None:
+            raise ConvolutionError.fftNotInitialized()
+        single = x.ndim == 1
+        x2 = x.reshape(1, -1) if single else x
+        if x2.shape[0] > self.channels:
+            raise MetalAudioError.invalidConfiguration(f"expected at most {self.channels} signals, got {x2.shape[0]}")
+        length = x2.shape[1]
+        if length > self._expected:
+            raise ConvolutionError.inputSizeMismatch(length, self._expected, self.fftSize)
+        out = np.empty((x2.shape[0], self.fftSize), np.float32)
+        st = self._lib.ma_fftconv_process_host(self._fc, _ptr(x2), length, length, x2.shape[0], _ptr(out))
+        _raise_status(st, "Convolution.process")
+        res = out[0] if single else out
+        if output is not None and single and output.size >= self.fftSize:
+            output[:self.fftSize] = res  # the inverse writes fftSize samples into the caller's array
+            return output
+        return res
+
     @property
     def partitionCount(self) -> int:
         v = ctypes.c_int32(0)
@@ -767,14 +879,15 @@ class Convolution:
 
     @property
     def kernelTailLength(self) -> int:
-        return 0 if self._h is None else self._taps - 1
+        return 0 if (self._h is None and self._fc is None) else self._taps - 1
 
     def expectedOutputSize(self, forInputSize: int) -> int:
-        return forInputSize if self._h is None else forInputSize + self._taps - 1
+        return forInputSize if (self._h is None and self._fc is None) else forInputSize + self._taps - 1
 
     @property
     def maxInputSize(self) -> int:
-        return 0
+        """Convolution.swift:377-383: the expected input size in .fft mode, 0 (no limit) otherwise."""
+        return self._expected if self.mode.kind == "fft" else 0
 
     def process(self, input: np.ndarray, output: Optional[np.ndarray] = None) -> np.ndarray:
         """Convolution.swift:336-352 -> :529-758.  (L,) for one channel or (channels, L);
@@ -783,6 +896,8 @@ class Convolution:
         x = _f32(input)
         if x.size == 0:
             return np.zeros(0, np.float32)
+        if self.mode.kind == "fft":
+            return self._process_fft(x, output)
         if self._h is None:
             raise ConvolutionError.fftNotInitialized()
         single = x.ndim == 1
@@ -815,6 +930,9 @@ class Convolution:
         if getattr(self, "_h", None) and self.device._h:
             self._lib.ma_pconv_destroy(self._h)
         self._h = None
+        if getattr(self, "_fc", None) and self.device._h:
+            self._lib.ma_fftconv_destroy(self._fc)
+        self._fc = None
 
     def __del__(self):
         try:

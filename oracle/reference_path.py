@@ -231,3 +231,68 @@ class PartitionedConvolution:
             out[lo:lo + n] += y
             self.write_index = (self.write_index + 1) % p_count
         return out[:full].copy()
+
+
+# ----------------------------------------------------------- one-shot FFT convolution
+
+
+class FFTConvolution:
+    """The `.fft` mode, following Convolution.swift:210-248 (set-up) and :437-493 (process):
+    ``fftSize = 1 << ceil(log2(expected + K - 1))``, full-size float32 complex transforms of the
+    zero-padded kernel (once) and input, bin-by-bin complex product, inverse scaled by 1/fftSize;
+    the result has ``fftSize`` samples.  Inputs longer than ``expected`` are refused
+    (ConvolutionError.inputSizeMismatch, :461-467)."""
+
+    def __init__(self, kernel: np.ndarray, expected_input_size=None):
+        kernel = np.asarray(kernel, dtype=F32)
+        if kernel.size == 0:
+            raise ValueError("Convolution kernel cannot be empty")
+        self.kernel = kernel
+        self.expected = int(kernel.size if expected_input_size is None else expected_input_size)
+        min_size = self.expected + kernel.size - 1
+        self.fft_size = 1 << int(np.ceil(np.log2(float(min_size))))
+        padded = np.zeros(self.fft_size, dtype=F32)
+        padded[:kernel.size] = kernel
+        self.h = sfft.fft(padded.astype(np.complex64))
+
+    def process(self, x: np.ndarray) -> np.ndarray:
+        x = np.asarray(x, dtype=F32)
+        if x.size == 0:
+            return np.zeros(0, dtype=F32)
+        if x.size > self.expected:
+            raise ValueError(f"input size {x.size} exceeds expected maximum {self.expected} (FFT size: {self.fft_size})")
+        padded = np.zeros(self.fft_size, dtype=F32)
+        padded[:x.size] = x
+        spec = sfft.fft(padded.astype(np.complex64))
+        re = spec.real * self.h.real - spec.imag * self.h.imag       # the reference's scalar loop (:476-480)
+        im = spec.real * self.h.imag + spec.imag * self.h.real
+        y = sfft.ifft((re + 1j * im).astype(np.complex64), norm="forward").real.astype(F32)
+        return (y * F32(1.0 / F32(self.fft_size))).astype(F32)
+
+
+# ----------------------------------------------------------- magnitude / phase glue
+
+
+def to_polar(re: np.ndarray, im: np.ndarray):
+    """Magnitude and phase per bin as the STFT's consumer computes them in float32
+    (HTDemucs.swift:735-738; shader forms DSP.metal:784-813): sqrt(re^2 + im^2), atan2(im, re)."""
+    re = np.asarray(re, dtype=F32)
+    im = np.asarray(im, dtype=F32)
+    return np.sqrt(re * re + im * im).astype(F32), np.arctan2(im, re).astype(F32)
+
+
+def from_polar(mag: np.ndarray, phase: np.ndarray):
+    """mag*cos(phase), mag*sin(phase) in float32 (HTDemucs.swift:803-804; DSP.metal:821-834)."""
+    mag = np.asarray(mag, dtype=F32)
+    phase = np.asarray(phase, dtype=F32)
+    return (mag * np.cos(phase)).astype(F32), (mag * np.sin(phase)).astype(F32)
+
+
+def to_decibels(data: np.ndarray, reference: float, min_db: float) -> np.ndarray:
+    """DSP.metal:861-881: 20*log10(max(x/reference, 1e-10)) floored at min_db; a reference <= 0
+    yields min_db everywhere."""
+    data = np.asarray(data, dtype=F32)
+    if reference <= 0:
+        return np.full(data.shape, F32(min_db), dtype=F32)
+    ratio = np.maximum(data / F32(reference), F32(1e-10))
+    return np.maximum(F32(20.0) * np.log10(ratio), F32(min_db)).astype(F32)

@@ -145,6 +145,23 @@ static void gpu_tests() {
         threw = e.errorCase == "emptyKernel";
     }
     CHECK(threw);
+    // .fft mode (the default): an impulse returns the kernel; oversize input is refused
+    // (ConvolutionTests testFFTConvolutionImpulseResponse / InputSizeMismatchThrows)
+    Convolution fc(dev);
+    const std::vector<float> k4 = {1.0f, 0.5f, 0.25f, 0.125f};
+    fc.setKernel(k4);
+    std::vector<float> o4;
+    fc.process({1.0f, 0.0f, 0.0f, 0.0f}, o4);
+    CHECK(o4.size() == 8 && fc.fftSize() == 8 && fc.maxInputSize() == 4);
+    for (int i = 0; i < 4; ++i) CHECK(std::fabs(o4[i] - k4[i]) < 1e-5f);
+    fc.setKernel(k4, 64);
+    threw = false;
+    try {
+        fc.process(std::vector<float>(128, 1.0f), o4);
+    } catch (const ConvolutionError& e) {
+        threw = e.errorCase == "inputSizeMismatch" && std::string(e.what()).find("circular convolution") != std::string::npos;
+    }
+    CHECK(threw);
     dev.markDeviceLost();
     threw = false;
     try {

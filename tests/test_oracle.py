@@ -104,6 +104,30 @@ def test_partitioned_port_vs_float64():
     assert pc.process(np.zeros(0, np.float32)).size == 0
 
 
+def test_fft_convolution_port_vs_float64():
+    """The `.fft` mode port: known answers of ConvolutionTests.swift:94-140 and parity with the
+    float64 linear convolution (the tail beyond len + taps - 1 is zero padding)."""
+    rng = np.random.default_rng(3)
+    for taps, expected, length in [(4, None, 4), (4, 64, 64), (33, 100, 77), (1000, 3000, 3000), (1, 1, 1)]:
+        h = rng.standard_normal(taps).astype(np.float32)
+        x = rng.standard_normal(length).astype(np.float32)
+        fc = rp.FFTConvolution(h, expected)
+        n = fc.fft_size
+        assert n & (n - 1) == 0 and n >= (expected or taps) + taps - 1 and (n == 1 or n // 2 < (expected or taps) + taps - 1)
+        y = fc.process(x)
+        assert y.shape == (n,)
+        full = o64.convolve_full(x, h)
+        assert o64.rel_rms(y[:full.size], full) < 1e-5
+        assert np.max(np.abs(y[full.size:]), initial=0.0) < 1e-4 * np.sqrt(np.mean(full ** 2))
+    fc = rp.FFTConvolution(np.array([1.0, 0.0, 0.0, 0.0], np.float32))
+    assert np.allclose(fc.process(np.array([1.0, 2.0, 3.0, 4.0], np.float32))[:4], [1, 2, 3, 4], atol=1e-5)
+    k = np.array([1.0, 0.5, 0.25, 0.125], np.float32)
+    assert np.allclose(rp.FFTConvolution(k).process(np.array([1.0, 0, 0, 0], np.float32))[:4], k, atol=1e-5)
+    with pytest.raises(ValueError):
+        rp.FFTConvolution(k, 64).process(np.ones(128, np.float32))
+    assert rp.FFTConvolution(k, 128).process(np.ones(128, np.float32)).size == 256
+
+
 def test_spot_check_matches_full_convolution():
     rng = np.random.default_rng(2)
     x = rng.standard_normal(300); h = rng.standard_normal(40)
