@@ -51,6 +51,21 @@ CONV = dict(channels=512, block=256, taps=131072, bytes_per_channel_block=105883
 LARGE = dict(n=65536, batch=4096)
 
 
+def periodic_hann(n: int) -> np.ndarray:
+    """0.5(1 - cos(2 pi k/n)), computed in float64: the window the benchmark configuration names."""
+    k = np.arange(n, dtype=np.float64)
+    return (0.5 * (1.0 - np.cos(2.0 * np.pi * k / float(n)))).astype(np.float32)
+
+
+def decaying_ir(taps: int, seed: int = 1003) -> np.ndarray:
+    """Synthetic room response: Gaussian noise with an exponential decay reaching -60 dB after 1.5 s
+    at 48 kHz, scaled to unit energy."""
+    g = np.random.Generator(np.random.PCG64(seed))
+    k = np.arange(taps, dtype=np.float64)
+    h = g.standard_normal(taps) * np.exp(-6.907755278982137 * k / (1.5 * 48000.0))
+    return (h / np.sqrt(np.sum(h * h))).astype(np.float32)
+
+
 def measured_peak_gbs():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -139,7 +154,7 @@ def run_reference(args, rank: int, world: int):
     cores = os.cpu_count() or 1
     sample = max(cores, 16)
     x = configs.c2_signals(n_signals=sample, length=SIGNAL_LEN)
-    w = rp.periodic_hann(N_FFT)
+    w = periodic_hann(N_FFT)
     for _ in range(min(args.warmup, 1)):
         cpu_port_stft_istft(x[:cores], w, cores)
     times = [cpu_port_stft_istft(x, w, cores) for _ in range(args.steps)]
@@ -179,7 +194,6 @@ def workload_config(n_gpus: int, sample_note: str | None = None, signals: int = 
 def run_ours(args, rank: int, local_rank: int, world: int):
     import torch
     from metalaudio_b200 import AudioDevice, Convolution, FFT, Tensor, WindowType
-    from oracle import reference_path as rp  # window table + CPU baseline only
 
     dist = None
     if world > 1:
@@ -192,7 +206,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     stream = torch.cuda.ExternalStream(lib.ma_context_stream(dev.handle), device=torch.device("cuda", local_rank))
     peak, peak_kind = measured_peak_gbs()
 
-    window = rp.periodic_hann(N_FFT)
+    window = periodic_hann(N_FFT)
     fft = FFT(dev, FFT.Config(size=N_FFT, windowType=WindowType.hann, hopSize=HOP), window=window)
     S = args.signals
     sig = Tensor(dev, (S, SIGNAL_LEN))
@@ -335,6 +349,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     if not args.no_extras:
         extra["conv"] = bench_conv(dev, lib, torch, stream, peak)
         extra["large_fft"] = bench_large(dev, lib, torch, stream, peak)
+        extra["next_rows"] = bench_next_rows(dev, lib, torch, stream, peak)
 
     cpu = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
@@ -371,11 +386,10 @@ def bench_conv(dev, lib, torch, stream, peak):
     """Partitioned convolution, configuration 3 shape, as causal streaming steps: every step
     reads the whole frequency-domain delay line of every channel once."""
     from metalaudio_b200 import Convolution, Tensor
-    from oracle import configs
     C, B, taps = CONV["channels"], CONV["block"], CONV["taps"]
     steps, warm = (200, 16) if C >= 256 else (24, 8)
     conv = Convolution(dev, Convolution.Mode.partitioned(blockSize=B), channels=C)
-    conv.setKernel(configs.c3_ir(taps))
+    conv.setKernel(decaying_ir(taps))
     x = Tensor(dev, (C, (steps + warm) * B))
     y = Tensor(dev, (C, (steps + warm) * B))
     host = torch.empty((C, (steps + warm) * B), dtype=torch.float32, pin_memory=True)
@@ -494,6 +508,79 @@ def bench_large(dev, lib, torch, stream, peak):
     return out
 
 
+def bench_next_rows(dev, lib, torch, stream, peak):
+    """The callers either side of the hot path: STFT / iSTFT through the magnitude + phase layout
+    (64 signals of configuration 2's shape) and the one-shot FFT convolution (32 signals, 131072-tap
+    kernel, 2^20-point transforms).  Device-resident, CUDA-event timed, best of 5 after a warm-up."""
+    from metalaudio_b200 import FFT, WindowType
+    device = torch.device("cuda", dev.deviceIndex)
+
+    def timed(fn, reps=5):
+        best = None
+        for i in range(reps + 1):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            st = fn()
+            e1.record(stream)
+            dev.synchronize(120)
+            torch.cuda.synchronize()
+            if st != 0:
+                raise RuntimeError(f"next-row workload failed: status {st}")
+            if i > 0:
+                ms = e0.elapsed_time(e1)
+                best = ms if best is None else min(best, ms)
+        return best
+
+    def ptr(t):
+        return ctypes.c_void_p(t.data_ptr())
+
+    out = {}
+    # --- magnitude / phase layout
+    S, L, n, hop = 64, SIGNAL_LEN, N_FFT, HOP
+    frames = (L - n) // hop + 1
+    kh = n // 2 + 1
+    fft = FFT(dev, FFT.Config(size=n, windowType=WindowType.hann, hopSize=hop), window=periodic_hann(n))
+    x = torch.empty((S, L), dtype=torch.float32, device=device).uniform_(-1.0, 1.0)
+    mag = torch.empty((S, frames, kh), dtype=torch.float32, device=device)
+    ph = torch.empty_like(mag)
+    y = torch.empty((S, L), dtype=torch.float32, device=device)
+    torch.cuda.synchronize()
+    ms_f = timed(lambda: lib.ma_stft_dev(fft._h, ptr(x), L, L, S, ptr(mag), ptr(ph), None, 0, 1.0, 3))
+    ms_i = timed(lambda: lib.ma_istft_dev(fft._h, ptr(mag), ptr(ph), frames, S, ptr(y), L, 1e-8, 3))
+    keep = slice(n, L - n)
+    err = float((y[:, keep] - x[:, keep]).pow(2).mean().sqrt() / x[:, keep].pow(2).mean().sqrt())
+    bytes_f = S * (4 * L + frames * 8 * kh)
+    out["polar_stft_istft"] = {
+        "workload": f"{S} signals x 2^20 samples, N={n}, hop={hop}: STFT to magnitude+phase, iSTFT from them",
+        "stft_ms": ms_f, "istft_ms": ms_i, "frames_per_s": S * frames / ((ms_f + ms_i) * 1e-3),
+        "stft_frac_of_hbm_peak": bytes_f / (ms_f * 1e-3) / 1e9 / peak,
+        "istft_frac_of_hbm_peak": bytes_f / (ms_i * 1e-3) / 1e9 / peak,
+        "algorithmic_bytes_each": bytes_f, "reconstruction_rel_rms": err}
+    fft.close()
+    del x, mag, ph, y
+    # --- one-shot FFT convolution
+    sig, taps, nfft = 32, 131072, 1 << 20
+    length = nfft - taps + 1
+    h = decaying_ir(taps)
+    fc = ctypes.c_void_p()
+    st = lib.ma_fftconv_create(dev.handle, h.ctypes.data_as(ctypes.c_void_p), taps, length, sig, ctypes.byref(fc))
+    if st != 0:
+        raise RuntimeError(f"ma_fftconv_create failed: {st}")
+    xs = torch.empty((sig, length), dtype=torch.float32, device=device).normal_(0.0, 0.1)
+    ys = torch.empty((sig, nfft), dtype=torch.float32, device=device)
+    torch.cuda.synchronize()
+    ms_c = timed(lambda: lib.ma_fftconv_process_dev(fc, ptr(xs), length, length, sig, ptr(ys)))
+    bytes_c = sig * 4 * (length + nfft)
+    out["fft_convolution"] = {
+        "workload": f"{sig} signals x {length} samples, one {taps}-tap kernel, {nfft}-point transforms",
+        "ms": ms_c, "value": sig * length / (ms_c * 1e-3), "unit": "signal-samples/s",
+        "frac_of_hbm_peak": bytes_c / (ms_c * 1e-3) / 1e9 / peak, "algorithmic_bytes": bytes_c,
+        "note": "pad, forward, multiply, inverse as separate passes through L2-sized chunks: several times "
+                "the compulsory traffic"}
+    lib.ma_fftconv_destroy(fc)
+    return out
+
+
 def run_only(args, local_rank: int):
     """One of the extra workloads alone, for profiler captures of its kernels."""
     import torch
@@ -502,7 +589,7 @@ def run_only(args, local_rank: int):
     lib = dev._lib
     stream = torch.cuda.ExternalStream(lib.ma_context_stream(dev.handle), device=torch.device("cuda", local_rank))
     peak, _ = measured_peak_gbs()
-    fn = bench_conv if args.only == "conv" else bench_large
+    fn = {"conv": bench_conv, "large": bench_large, "next": bench_next_rows}[args.only]
     print(json.dumps({args.only: fn(dev, lib, torch, stream, peak)}), flush=True)
 
 
@@ -518,7 +605,7 @@ def main():
                     help="signals per GPU (default: the benchmark configuration's 256; smaller for profiler captures)")
     ap.add_argument("--conv-channels", type=int, default=CONV["channels"])
     ap.add_argument("--large-batch", type=int, default=LARGE["batch"])
-    ap.add_argument("--only", choices=["conv", "large"], default=None,
+    ap.add_argument("--only", choices=["conv", "large", "next"], default=None,
                     help="run just one of the extra workloads (profiler captures)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

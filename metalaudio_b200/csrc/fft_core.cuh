@@ -42,6 +42,45 @@ MA_HD float2 cconj(float2 a) { return make_float2(a.x, -a.y); }
 // a * (-i)
 MA_HD float2 cmul_mi(float2 a) { return make_float2(a.y, -a.x); }
 
+// atan2 for finite arguments, about 4e-7 rad maximum error: odd polynomial in min/max (degree 15,
+// near-minimax on [0, 1]) with the octant folded back afterwards.  Signed zeros of x count as +0.
+MA_HD float fast_atan2(float y, float x) {
+#ifdef __CUDA_ARCH__
+    const float ax = fabsf(x), ay = fabsf(y);
+    const float mx = fmaxf(ax, ay), mn = fminf(ax, ay);
+    const float a = mx > 0.f ? __fdividef(mn, mx) : 0.f;
+    const float s = a * a;
+    float r = -0.004668773151934147f;
+    r = fmaf(r, s, 0.02416618913412094f);
+    r = fmaf(r, s, -0.0593671016395092f);
+    r = fmaf(r, s, 0.09906096756458282f);
+    r = fmaf(r, s, -0.14016585052013397f);
+    r = fmaf(r, s, 0.19969235360622406f);
+    r = fmaf(r, s, -0.33331960439682007f);
+    r = fmaf(r, s, 0.9999998807907104f);
+    r *= a;
+    if (ay > ax) r = 1.5707963705062866f - r;
+    if (x < 0.f) r = 3.1415927410125732f - r;
+    return copysignf(r, y);
+#else
+    return atan2f(y, x);
+#endif
+}
+
+// sin and cos with an explicit two-constant reduction by 2*pi followed by the hardware
+// approximations: absolute error below 5e-7 for |x| up to about 1e4 rad.
+MA_HD void fast_sincos(float x, float* sn, float* cs) {
+#ifdef __CUDA_ARCH__
+    const float k = rintf(x * 0.15915494309189535f);
+    float r = fmaf(-k, 6.2831854820251465f, x);
+    r = fmaf(k, 1.7484555e-7f, r);  // 2*pi = 6.2831854820251465 - 1.7484555e-7
+    *sn = __sinf(r);
+    *cs = __cosf(r);
+#else
+    sincosf(x, sn, cs);
+#endif
+}
+
 // Multiply by W_R^K = exp(-2*pi*i*K/R) with the trivial cases resolved at compile time.
 template <int R, int K>
 MA_HD float2 mul_wconst(float2 v) {

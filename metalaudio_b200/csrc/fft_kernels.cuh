@@ -128,9 +128,9 @@ MA_HD void r2c_store_pair(const R2CParams& p, int64_t g, int64_t half_off, int k
         float* mg = p.out_a + g * (int64_t)(M + 1);
         float* ph = p.out_b + g * (int64_t)(M + 1);
         mg[k] = sqrtf(xk.x * xk.x + xk.y * xk.y);
-        ph[k] = atan2f(xk.y, xk.x);
+        ph[k] = fast_atan2(xk.y, xk.x);
         mg[km] = sqrtf(xm.x * xm.x + xm.y * xm.y);
-        ph[km] = atan2f(xm.y, xm.x);
+        ph[km] = fast_atan2(xm.y, xm.x);
     } else {
         float* re = p.out_a + g * (int64_t)N;
         float* im = p.out_b + g * (int64_t)N;
@@ -431,8 +431,8 @@ MA_HD void c2r_load_pair(const C2RParams& p, const float2* x, int64_t g, int k, 
         const float* mg = p.in_a + g * (int64_t)(M + 1);
         const float* ph = p.in_b + g * (int64_t)(M + 1);
         float sa, ca, sb, cb;
-        sincosf(MA_LDG(ph + k), &sa, &ca);
-        sincosf(MA_LDG(ph + km), &sb, &cb);
+        fast_sincos(MA_LDG(ph + k), &sa, &ca);
+        fast_sincos(MA_LDG(ph + km), &sb, &cb);
         const float ma = MA_LDG(mg + k), mb = MA_LDG(mg + km);
         a = make_float2(ma * ca, k == 0 ? 0.f : ma * sa);
         b = make_float2(mb * cb, k == 0 ? 0.f : mb * sb);
@@ -844,7 +844,7 @@ inline bool istft_fast_ok(const C2RParams& p) {
         return false;
     } else {
         constexpr int R = FftPlan<M>::R, T = FftPlan<M>::T;
-        if (p.layout != LAYOUT_HALF_INTERLEAVED && p.layout != LAYOUT_HALF_PACKED) return false;
+        if (p.layout != LAYOUT_HALF_INTERLEAVED && p.layout != LAYOUT_HALF_PACKED && p.layout != LAYOUT_HALF_POLAR) return false;
         if (p.n_partials > 1 || p.hop <= 0 || p.hop % (2 * T) != 0) return false;
         const int h = p.hop / (2 * T);
         if (h > R || R % h != 0) return false;
@@ -858,6 +858,9 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
     using P = FftPlan<M>;
     using SH = IstftFastShape<M>;
     constexpr int R = P::R, T = P::T, N = 2 * M;
+    // The complex layouts stage each spectrum row with a bulk copy; magnitude + phase rows (two
+    // arrays, 4-byte granularity) are read with plain loads.
+    constexpr bool STAGED = LAYOUT != LAYOUT_HALF_POLAR;
     float2* ring = smem + SH::EXCH_ELEMS;
     float2* stage = ring + SH::RING;
     uint64_t* bar = reinterpret_cast<uint64_t*>(stage + SH::ROW);
@@ -900,11 +903,11 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
     f -= lead;
     int64_t G = G0 - lead;
 
-    if (t == 0) cta.bulk_init(bar);
+    if (STAGED && t == 0) cta.bulk_init(bar);
 #pragma unroll
     for (int q = 0; q < R; ++q) ring[q * T + t] = make_float2(0.f, 0.f);
     cta.sync();
-    if (t == 0) {
+    if (STAGED && t == 0) {
         const StagedRow r0 = staged_row<M>(p, s, f);
         cta.bulk_copy(stage, r0.src, r0.bytes, bar);
     }
@@ -916,19 +919,24 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
 #pragma unroll
             for (int q = 0; q < R; ++q) ring[q * T + t] = make_float2(0.f, 0.f);
         }
-        const StagedRow r = staged_row<M>(p, s, f);
-        if (!cta.bulk_wait(bar, phase) && p.error_flag != nullptr) *p.error_flag = 1;
-        phase ^= 1;
-        auto issue_next = [&]() {
-            if (t == 0 && G + 1 < G1) {
-                const bool wrap = f + 1 == F;
-                const StagedRow rn = staged_row<M>(p, wrap ? s + 1 : s, wrap ? 0 : f + 1);
-                cta.bulk_copy(stage, rn.src, rn.bytes, bar);
-            }
-        };
         float2 v[R];
-        c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1>(
-            p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage + r.shift, issue_next, r.row);
+        if constexpr (STAGED) {
+            const StagedRow r = staged_row<M>(p, s, f);
+            if (!cta.bulk_wait(bar, phase) && p.error_flag != nullptr) *p.error_flag = 1;
+            phase ^= 1;
+            auto issue_next = [&]() {
+                if (t == 0 && G + 1 < G1) {
+                    const bool wrap = f + 1 == F;
+                    const StagedRow rn = staged_row<M>(p, wrap ? s + 1 : s, wrap ? 0 : f + 1);
+                    cta.bulk_copy(stage, rn.src, rn.bytes, bar);
+                }
+            };
+            c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1>(
+                p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage + r.shift, issue_next, r.row);
+        } else {
+            c2r_frame<M, LAYOUT, true, Cta, false, NoHook, SH::EXCH == 1>(p, true, s, f, G, t, smem, SH::ELEMS, parity,
+                                                                         v, cta, twb, wherm);
+        }
 
         // v[q] = (x[2n+1], x[2n]) * N for n = t + q*T.  Overlap-add in this thread's ring column.
         const int64_t start = f * (int64_t)hop;

@@ -84,6 +84,7 @@ static ma_status launch_r2c_variant(ma_fft_plan* plan, const R2CParams& p, bool 
             MA_R2C_CASE(LAYOUT_HALF_PACKED, -1)
             MA_R2C_CASE(LAYOUT_FULL_SPLIT, 0)
             MA_R2C_CASE(LAYOUT_FULL_SPLIT, -1)
+            MA_R2C_CASE(LAYOUT_HALF_POLAR, -1)
 #undef MA_R2C_CASE
         }
     }
@@ -164,7 +165,9 @@ static ma_status launch_istft_t(ma_fft_plan* plan, C2RParams& p) {
     ma_context* ctx = plan->ctx;
     int& occ = per_sm[fast ? 1 : 0][ctx->device & 63];
     const int ov = fast ? (2 * M) / p.hop : 0;
-    const int variant = !fast ? 0 : (p.layout == LAYOUT_HALF_INTERLEAVED ? 1 : 3) + (ov == 4 ? 1 : 0);
+    const int variant = !fast ? 0
+                              : (p.layout == LAYOUT_HALF_INTERLEAVED ? 1 : (p.layout == LAYOUT_HALF_PACKED ? 3 : 5)) +
+                                    (ov == 4 ? 1 : 0);
     if (occ == 0) {
         if (fast) MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_INTERLEAVED, 4>, T, smem, &occ));
         else MA_TRY(occupancy(istft_kernel<M>, T, smem, &occ));
@@ -173,6 +176,8 @@ static ma_status launch_istft_t(ma_fft_plan* plan, C2RParams& p) {
             MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_INTERLEAVED, 0>, T, smem, &dummy));
             MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_PACKED, 4>, T, smem, &dummy));
             MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_PACKED, 0>, T, smem, &dummy));
+            MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_POLAR, 4>, T, smem, &dummy));
+            MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_POLAR, 0>, T, smem, &dummy));
         }
     }
     // Chunks per signal: enough CTAs to fill the device a few times over, but chunks long
@@ -197,6 +202,8 @@ static ma_status launch_istft_t(ma_fft_plan* plan, C2RParams& p) {
         case 2: istft_fast_kernel<M, LAYOUT_HALF_INTERLEAVED, 4><<<grid, T, smem, ctx->stream>>>(p); break;
         case 3: istft_fast_kernel<M, LAYOUT_HALF_PACKED, 0><<<grid, T, smem, ctx->stream>>>(p); break;
         case 4: istft_fast_kernel<M, LAYOUT_HALF_PACKED, 4><<<grid, T, smem, ctx->stream>>>(p); break;
+        case 5: istft_fast_kernel<M, LAYOUT_HALF_POLAR, 0><<<grid, T, smem, ctx->stream>>>(p); break;
+        case 6: istft_fast_kernel<M, LAYOUT_HALF_POLAR, 4><<<grid, T, smem, ctx->stream>>>(p); break;
         default: istft_kernel<M><<<grid, T, smem, ctx->stream>>>(p); break;
     }
     return after_launch(ctx);
