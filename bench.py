@@ -578,6 +578,32 @@ def bench_next_rows(dev, lib, torch, stream, peak):
         "note": "pad, forward, multiply, inverse as separate passes through L2-sized chunks: several times "
                 "the compulsory traffic"}
     lib.ma_fftconv_destroy(fc)
+    del xs, ys
+    # --- multichannel biquad: 512 channels x 2^20 samples, one low-pass section, then a 4-section cascade
+    C, L = 512, SIGNAL_LEN
+    xb = torch.empty((C, L), dtype=torch.float32, device=device).normal_(0.0, 0.1)
+    yb = torch.empty_like(xb)
+    torch.cuda.synchronize()
+    w = 2.0 * np.pi * 1000.0 / 48000.0
+    al = np.sin(w) / (2.0 * 0.7071067811865476)
+    lp = (np.array([(1 - np.cos(w)) / 2, 1 - np.cos(w), (1 - np.cos(w)) / 2, -2 * np.cos(w), 1 - al]) / (1 + al)).astype(np.float32)
+    res = {}
+    for sections in (1, 4):
+        bq = ctypes.c_void_p()
+        st = lib.ma_biquad_create(dev.handle, C, sections, ctypes.byref(bq))
+        coeffs = np.ascontiguousarray(np.tile(lp, (sections, 1)))
+        st = st or lib.ma_biquad_set_coefficients(bq, coeffs.ctypes.data_as(ctypes.c_void_p), 1, None)
+        if st != 0:
+            raise RuntimeError(f"biquad set-up failed: {st}")
+        ms_b = timed(lambda: lib.ma_biquad_process_dev(bq, ptr(xb), L, ptr(yb), L, L))
+        res[sections] = ms_b
+        lib.ma_biquad_destroy(bq)
+    bytes_b = C * L * 8
+    out["biquad"] = {
+        "workload": f"{C} channels x 2^20 samples, Direct Form II Transposed low-pass sections, state in double",
+        "ms_1_section": res[1], "ms_4_sections": res[4], "value": C * L / (res[1] * 1e-3), "unit": "channel-samples/s",
+        "frac_of_hbm_peak_1_section": bytes_b / (res[1] * 1e-3) / 1e9 / peak,
+        "frac_of_hbm_peak_4_sections": bytes_b / (res[4] * 1e-3) / 1e9 / peak, "algorithmic_bytes": bytes_b}
     return out
 
 

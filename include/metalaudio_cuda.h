@@ -85,6 +85,7 @@ typedef struct ma_context ma_context;
 typedef struct ma_fft_plan ma_fft_plan;
 typedef struct ma_pconv ma_pconv;
 typedef struct ma_fftconv ma_fftconv;
+typedef struct ma_biquad ma_biquad;
 
 /* ------------------------------------------------------------------ library */
 
@@ -315,6 +316,36 @@ ma_status ma_fftconv_process_dev(ma_fftconv* fc, const float* in, int64_t len, i
                                  int32_t n_signals, float* out);
 ma_status ma_fftconv_process_host(ma_fftconv* fc, const float* in, int64_t len, int64_t in_stride,
                                   int32_t n_signals, float* out);
+
+/* ------------------------------------------------------------------ biquad cascades
+ * Replaces the biquad_filter_multichannel shader (Shaders/DSP.metal:697-744) and the processing
+ * loops of BiquadFilter / FilterBank (Filters.swift:515-660, :845-868): `n_channels` independent
+ * channels in [channel][sample] layout, each a cascade of `n_sections` (<= 32) Direct Form II
+ * Transposed sections, y = b0 x + z1; z1 = b1 x - a1 y + z2; z2 = b2 x - a2 y, with the (z1, z2)
+ * state of every channel and section kept in the object between calls.  Coefficient design
+ * (Filters.swift:226-345) stays on the host. */
+ma_status ma_biquad_create(ma_context* ctx, int32_t n_channels, int32_t n_sections, ma_biquad** out);
+ma_status ma_biquad_destroy(ma_biquad* bq);
+/* coeffs: n_sets x n_sections x (b0, b1, b2, a1, a2), host memory, a0 already divided out.
+ * Channel c uses set channel_to_set[c]; NULL means one set shared by all channels. */
+ma_status ma_biquad_set_coefficients(ma_biquad* bq, const float* coeffs, int32_t n_sets,
+                                     const int32_t* channel_to_set);
+/* Filters `samples` samples of every channel (row c at in + c*in_stride, out + c*out_stride) and
+ * advances the states.  in_stride == 0 feeds one signal to every channel (a parallel filter
+ * bank).  The _dev form allocates nothing. */
+ma_status ma_biquad_process_dev(ma_biquad* bq, const float* in, int64_t in_stride, float* out,
+                                int64_t out_stride, int64_t samples);
+ma_status ma_biquad_process_host(ma_biquad* bq, const float* in, int64_t in_stride, float* out,
+                                 int64_t out_stride, int64_t samples);
+/* BiquadFilter.reset (Filters.swift:662-672); state exchange with the host as
+ * n_channels x n_sections x (z1, z2). */
+ma_status ma_biquad_reset(ma_biquad* bq);
+ma_status ma_biquad_get_state(ma_biquad* bq, float* state);
+ma_status ma_biquad_set_state(ma_biquad* bq, const float* state);
+/* out[n] = scale * sum over channels of in[c*stride + n], summed in channel order: the mix step of
+ * FilterBank.processParallel (Filters.swift:854-868). */
+ma_status ma_channel_mix_dev(ma_context* ctx, const float* in, int32_t n_channels, int64_t stride,
+                             int64_t samples, float scale, float* out);
 
 #ifdef __cplusplus
 }

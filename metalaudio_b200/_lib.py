@@ -68,6 +68,15 @@ SIGNATURES = {
     "ma_spectrum_to_polar_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64]),
     "ma_polar_to_spectrum_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64]),
     "ma_to_decibels_dev": (c_int32, [c_void_p, c_void_p, c_int64, c_float, c_float]),
+    "ma_biquad_create": (c_int32, [c_void_p, c_int32, c_int32, POINTER(c_void_p)]),
+    "ma_biquad_destroy": (c_int32, [c_void_p]),
+    "ma_biquad_set_coefficients": (c_int32, [c_void_p, c_void_p, c_int32, c_void_p]),
+    "ma_biquad_process_dev": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64]),
+    "ma_biquad_process_host": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64]),
+    "ma_biquad_reset": (c_int32, [c_void_p]),
+    "ma_biquad_get_state": (c_int32, [c_void_p, c_void_p]),
+    "ma_biquad_set_state": (c_int32, [c_void_p, c_void_p]),
+    "ma_channel_mix_dev": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_float, c_void_p]),
     "ma_fftconv_create": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int32, POINTER(c_void_p)]),
     "ma_fftconv_destroy": (c_int32, [c_void_p]),
     "ma_fftconv_fft_size": (c_int32, [c_void_p, POINTER(c_int64)]),

@@ -939,3 +939,326 @@ class Convolution:
             self.close()
         except Exception:
             pass
+
+
+# --------------------------------------------------------------------------- filters
+
+class FilterError(Exception):
+    """Sources/MetalDSP/Filters.swift:14-26."""
+
+    def __init__(self, case: str, description: str, **payload):
+        self.case = case
+        self.errorDescription = description
+        self.__dict__.update(payload)
+        super().__init__(description)
+
+    @staticmethod
+    def unstable(reason: str) -> "FilterError":
+        return FilterError("unstable", f"Filter is unstable: {reason}", reason=reason)
+
+    @staticmethod
+    def invalidParameter(name: str, value: float, requirement: str) -> "FilterError":
+        return FilterError("invalidParameter", f"Invalid parameter '{name}' with value {value}: {requirement}",
+                           name=name, value=value, requirement=requirement)
+
+
+class BiquadFilter:
+    """Filters.swift:65.  Coefficient design (RBJ forms, float64 then rounded to float32,
+    Filters.swift:226-345) and its validation (:346-490) run on the host exactly as in the
+    reference; every sample is filtered on the GPU (``ma_biquad_process_*``), whatever the buffer
+    size.  ``channels`` > 1 filters that many independent rows with the same coefficients."""
+
+    class FilterType:
+        """Filters.swift:68-77."""
+
+        def __init__(self, kind: str, gainDB: float = 0.0):
+            self.kind = kind
+            self.gainDB = float(gainDB)
+
+    for _k in ("lowpass", "highpass", "bandpass", "notch", "allpass"):
+        setattr(FilterType, _k, FilterType(_k))
+    FilterType.peaking = staticmethod(lambda gainDB: BiquadFilter.FilterType("peaking", gainDB))
+    FilterType.lowshelf = staticmethod(lambda gainDB: BiquadFilter.FilterType("lowshelf", gainDB))
+    FilterType.highshelf = staticmethod(lambda gainDB: BiquadFilter.FilterType("highshelf", gainDB))
+    del _k
+
+    class Coefficients:
+        """Filters.swift:80-96: b0, b1, b2, a1, a2 (a0 divided out); identity by default."""
+
+        def __init__(self, b0: float = 1.0, b1: float = 0.0, b2: float = 0.0, a1: float = 0.0, a2: float = 0.0):
+            self.b0, self.b1, self.b2, self.a1, self.a2 = (np.float32(v) for v in (b0, b1, b2, a1, a2))
+
+        def asArray(self) -> np.ndarray:
+            return np.array([self.b0, self.b1, self.b2, self.a1, self.a2], np.float32)
+
+    def __init__(self, device: AudioDevice, channels: int = 1):
+        self.device = device
+        self.channels = int(channels)
+        self._lib = device._lib
+        self.coefficients = BiquadFilter.Coefficients()
+        h = ctypes.c_void_p()
+        _raise_status(self._lib.ma_biquad_create(device.handle, self.channels, 1, ctypes.byref(h)), "BiquadFilter()")
+        self._h = h
+        self._upload()
+
+    gpuEnabled = True
+
+    def _upload(self) -> None:
+        c = self.coefficients.asArray()
+        _raise_status(self._lib.ma_biquad_set_coefficients(self._h, _ptr(c), 1, None), "BiquadFilter.configure")
+
+    @staticmethod
+    def design(type: "BiquadFilter.FilterType", frequency: float, sampleRate: float,
+               q: float = 0.7071067811865476) -> "BiquadFilter.Coefficients":
+        """Validated coefficients for the parameters, or FilterError (Filters.swift:346-482)."""
+        frequency, sampleRate, q = np.float32(frequency), np.float32(sampleRate), np.float32(q)
+        if not sampleRate > 0:
+            raise FilterError.invalidParameter("sampleRate", float(sampleRate), "must be > 0")
+        nyquist = np.float32(sampleRate / np.float32(2.0))
+        if not (frequency > 0 and frequency < nyquist):
+            raise FilterError.invalidParameter("frequency", float(frequency), f"must be > 0 and < {float(nyquist)} Hz (Nyquist)")
+        if not q > 0:
+            raise FilterError.invalidParameter("q", float(q), "must be > 0")
+        if not (np.isfinite(frequency) and np.isfinite(sampleRate) and np.isfinite(q)):
+            raise FilterError.invalidParameter("input", 0.0, "parameters must not be NaN or Infinite")
+        omega = 2.0 * math.pi * float(frequency) / float(sampleRate)
+        sn, cs = math.sin(omega), math.cos(omega)
+        alpha = sn / (2.0 * float(q))
+        k = type.kind
+        if k == "lowpass":
+            b = ((1.0 - cs) / 2.0, 1.0 - cs, (1.0 - cs) / 2.0)
+            a = (1.0 + alpha, -2.0 * cs, 1.0 - alpha)
+        elif k == "highpass":
+            b = ((1.0 + cs) / 2.0, -(1.0 + cs), (1.0 + cs) / 2.0)
+            a = (1.0 + alpha, -2.0 * cs, 1.0 - alpha)
+        elif k == "bandpass":
+            b = (alpha, 0.0, -alpha)
+            a = (1.0 + alpha, -2.0 * cs, 1.0 - alpha)
+        elif k == "notch":
+            b = (1.0, -2.0 * cs, 1.0)
+            a = (1.0 + alpha, -2.0 * cs, 1.0 - alpha)
+        elif k == "allpass":
+            b = (1.0 - alpha, -2.0 * cs, 1.0 + alpha)
+            a = (1.0 + alpha, -2.0 * cs, 1.0 - alpha)
+        elif k == "peaking":
+            A = math.pow(10.0, float(np.float32(type.gainDB)) / 40.0)
+            b = (1.0 + alpha * A, -2.0 * cs, 1.0 - alpha * A)
+            a = (1.0 + alpha / A, -2.0 * cs, 1.0 - alpha / A)
+        elif k in ("lowshelf", "highshelf"):
+            A = math.pow(10.0, float(np.float32(type.gainDB)) / 40.0)
+            rt = 2.0 * math.sqrt(A) * alpha
+            sg = 1.0 if k == "lowshelf" else -1.0      # the two shelves mirror the cos terms
+            b = (A * ((A + 1.0) - sg * (A - 1.0) * cs + rt),
+                 sg * 2.0 * A * ((A - 1.0) - sg * (A + 1.0) * cs),
+                 A * ((A + 1.0) - sg * (A - 1.0) * cs - rt))
+            a = ((A + 1.0) + sg * (A - 1.0) * cs + rt,
+                 -sg * 2.0 * ((A - 1.0) + sg * (A + 1.0) * cs),
+                 (A + 1.0) + sg * (A - 1.0) * cs - rt)
+        else:
+            raise MetalAudioError.invalidConfiguration(f"unknown filter type {k}")
+        a0f = np.float32(a[0])
+        if not abs(a0f) > np.float32(1e-6):
+            raise FilterError.invalidParameter("a0 (computed)", float(a0f),
+                                               "denominator coefficient a0 must not be near zero (|a0| > 1e-6). This "
+                                               "typically indicates frequency near 0 Hz or Nyquist, or extreme Q values")
+        with np.errstate(over="ignore", invalid="ignore"):
+            nb = [np.float32(v / a[0]) for v in b]
+            na = [np.float32(v / a[0]) for v in a[1:]]
+        if not all(np.isfinite(v) for v in nb + na):
+            raise FilterError.invalidParameter("coefficients", 0.0,
+                                               "normalized coefficients must not be NaN or Infinite. This typically "
+                                               "indicates extreme parameter combinations (very high Q, frequency near "
+                                               "0 or Nyquist)")
+        if not abs(na[1]) < 1.0:
+            raise FilterError.invalidParameter("a2 (stability)", float(na[1]),
+                                               f"|a2| must be < 1 for filter stability. Current |a2| = {abs(float(na[1]))}. "
+                                               "Try reducing Q or adjusting frequency.")
+        if not abs(na[0]) < np.float32(1.0) + na[1]:
+            raise FilterError.invalidParameter("a1 (stability)", float(na[0]),
+                                               f"|a1| must be < 1 + a2 for filter stability. Current |a1| = "
+                                               f"{abs(float(na[0]))}, 1 + a2 = {float(np.float32(1.0) + na[1])}. Try reducing Q.")
+        return BiquadFilter.Coefficients(nb[0], nb[1], nb[2], na[0], na[1])
+
+    def configure(self, type: "BiquadFilter.FilterType", frequency: float, sampleRate: float,
+                  q: float = 0.7071067811865476) -> None:
+        """Filters.swift:346-490: the object keeps its previous coefficients when validation fails."""
+        self.coefficients = BiquadFilter.design(type, frequency, sampleRate, q)
+        self._upload()
+
+    def setCoefficients(self, coefficients: "BiquadFilter.Coefficients") -> None:
+        self.coefficients = coefficients
+        self._upload()
+
+    @property
+    def currentCoefficients(self) -> "BiquadFilter.Coefficients":
+        return self.coefficients
+
+    def process(self, input=None, sample: Optional[float] = None):
+        """``process(input:)`` (Filters.swift:555-593) for a (L,) array or (channels, L) rows;
+        ``process(sample=...)`` (:515-537) for one sample.  State carries over between calls."""
+        if sample is not None:
+            return float(self.process(np.array([sample], np.float32))[0])
+        x = _f32(input)
+        if x.size == 0:
+            return np.zeros(x.shape, np.float32)
+        single = x.ndim == 1
+        x2 = x.reshape(1, -1) if single else x
+        if x2.shape[0] != self.channels:
+            raise MetalAudioError.invalidConfiguration(f"expected {self.channels} channels, got {x2.shape[0]}")
+        out = np.empty_like(x2)
+        n = x2.shape[1]
+        _raise_status(self._lib.ma_biquad_process_host(self._h, _ptr(x2), n, _ptr(out), n, n), "BiquadFilter.process")
+        return out[0] if single else out
+
+    def processTensor(self, input: "Tensor", output: "Tensor") -> None:
+        """Device-resident form: (channels, L) Tensors, queued on the device stream."""
+        n = input.shape[-1]
+        st = self._lib.ma_biquad_process_dev(self._h, ctypes.c_void_p(input.pointer), n,
+                                             ctypes.c_void_p(output.pointer), output.shape[-1], n)
+        _raise_status(st, "BiquadFilter.processTensor")
+
+    def reset(self) -> None:
+        """Filters.swift:662-672."""
+        _raise_status(self._lib.ma_biquad_reset(self._h), "BiquadFilter.reset")
+
+    @property
+    def delays(self) -> np.ndarray:
+        """(channels, 2) array of (z1, z2)."""
+        st = np.empty((self.channels, 1, 2), np.float32)
+        _raise_status(self._lib.ma_biquad_get_state(self._h, _ptr(st)), "BiquadFilter.delays")
+        return st[:, 0, :]
+
+    def validateStability(self) -> None:
+        """Filters.swift:688-716."""
+        a1, a2 = self.coefficients.a1, self.coefficients.a2
+        if not (np.isfinite(a1) and np.isfinite(a2)):
+            raise FilterError.unstable("coefficients contain NaN or Infinite values, filter is in invalid state")
+        if not abs(a2) < 1.0:
+            raise FilterError.unstable(f"a2 coefficient magnitude ({abs(float(a2))}) >= 1, poles outside unit circle")
+        if not abs(a1) < np.float32(1.0) + a2:
+            raise FilterError.unstable(f"a1 coefficient ({float(a1)}) violates stability condition |a1| < 1 + a2 = "
+                                       f"{float(np.float32(1.0) + a2)}")
+
+    @property
+    def isStable(self) -> bool:
+        a1, a2 = self.coefficients.a1, self.coefficients.a2
+        return bool(np.isfinite(a1) and np.isfinite(a2) and abs(a2) < 1.0 and abs(a1) < np.float32(1.0) + a2)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) and self.device._h:
+            self._lib.ma_biquad_destroy(self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class FilterBank:
+    """Filters.swift:736.  ``processSeries`` runs the bands as one cascade of sections on the GPU;
+    ``processParallel`` feeds one signal to every band (one channel per band) and mixes them with
+    1/bandCount (:845-868)."""
+
+    def __init__(self, device: AudioDevice, bandCount: int):
+        self.device = device
+        self.bandCount = int(bandCount)
+        self._lib = device._lib
+        self._coeffs = [BiquadFilter.Coefficients() for _ in range(max(self.bandCount, 0))]
+        self._series = None
+        self._parallel = None
+        self._dirty = True
+
+    gpuEnabled = True
+
+    def _handles(self):
+        if self.bandCount <= 0:
+            return
+        if self._series is None:
+            hs, hp = ctypes.c_void_p(), ctypes.c_void_p()
+            _raise_status(self._lib.ma_biquad_create(self.device.handle, 1, self.bandCount, ctypes.byref(hs)), "FilterBank")
+            _raise_status(self._lib.ma_biquad_create(self.device.handle, self.bandCount, 1, ctypes.byref(hp)), "FilterBank")
+            self._series, self._parallel = hs, hp
+        if self._dirty:
+            c = np.stack([k.asArray() for k in self._coeffs])
+            _raise_status(self._lib.ma_biquad_set_coefficients(self._series, _ptr(c), 1, None), "FilterBank")
+            cmap = np.arange(self.bandCount, dtype=np.int32)
+            _raise_status(self._lib.ma_biquad_set_coefficients(self._parallel, _ptr(c), self.bandCount, _ptr(cmap)), "FilterBank")
+            self._dirty = False
+
+    def configureAsEQ(self, lowFreq: float, highFreq: float, sampleRate: float, q: float = 1.414) -> None:
+        """Logarithmically spaced 0 dB peaking bands (Filters.swift:768-812)."""
+        if self.bandCount < 2:
+            raise FilterError.invalidParameter("bandCount", float(self.bandCount), "must be >= 2 for logarithmic band spacing")
+        lowFreq, highFreq = np.float32(lowFreq), np.float32(highFreq)
+        if not lowFreq > 0:
+            raise FilterError.invalidParameter("lowFreq", float(lowFreq),
+                                               f"must be > 0 (got {float(lowFreq)}, log10 requires positive values)")
+        if not (highFreq > 0 and highFreq > lowFreq):
+            raise FilterError.invalidParameter("highFreq", float(highFreq), f"must be > 0 and > lowFreq ({float(lowFreq)})")
+        log_low, log_high = np.log10(lowFreq), np.log10(highFreq)
+        step = np.float32((log_high - log_low) / np.float32(self.bandCount - 1))
+        new = []
+        for i in range(self.bandCount):
+            freq = np.power(np.float32(10.0), np.float32(log_low + np.float32(i) * step))
+            new.append(BiquadFilter.design(BiquadFilter.FilterType.peaking(0.0), freq, sampleRate, q))
+            # the reference configures band by band: earlier bands keep their new settings if a later one throws
+            self._coeffs[i] = new[-1]
+            self._dirty = True
+
+    def setBandGain(self, band: int, gainDB: float, frequency: float, sampleRate: float, q: float = 1.414) -> None:
+        """Filters.swift:822-842."""
+        if not (0 <= band < self.bandCount):
+            raise FilterError.invalidParameter("band", float(band), f"must be in range 0..<{self.bandCount}")
+        self._coeffs[band] = BiquadFilter.design(BiquadFilter.FilterType.peaking(gainDB), frequency, sampleRate, q)
+        self._dirty = True
+
+    def processSeries(self, input) -> np.ndarray:
+        x = _f32(input)
+        if x.size == 0 or self.bandCount <= 0:
+            return x.copy()
+        self._handles()
+        out = np.empty_like(x)
+        _raise_status(self._lib.ma_biquad_process_host(self._series, _ptr(x), x.size, _ptr(out), x.size, x.size),
+                      "FilterBank.processSeries")
+        return out
+
+    def processParallel(self, input) -> np.ndarray:
+        x = _f32(input)
+        if x.size == 0 or self.bandCount <= 0:
+            return np.zeros_like(x)
+        self._handles()
+        n = x.size
+        dev = self.device
+        tin, bands, mix = Tensor(dev, (n,)), Tensor(dev, (self.bandCount, n)), Tensor(dev, (n,))
+        try:
+            tin.copy(x)
+            st = self._lib.ma_biquad_process_dev(self._parallel, ctypes.c_void_p(tin.pointer), 0,
+                                                 ctypes.c_void_p(bands.pointer), n, n)
+            _raise_status(st, "FilterBank.processParallel")
+            scale = float(np.float32(1.0) / np.float32(self.bandCount))
+            st = self._lib.ma_channel_mix_dev(dev.handle, ctypes.c_void_p(bands.pointer), self.bandCount, n, n, scale,
+                                              ctypes.c_void_p(mix.pointer))
+            _raise_status(st, "FilterBank.processParallel")
+            return mix.toArray()
+        finally:
+            for t in (tin, bands, mix):
+                t.free()
+
+    def reset(self) -> None:
+        for h in (self._series, self._parallel):
+            if h is not None:
+                _raise_status(self._lib.ma_biquad_reset(h), "FilterBank.reset")
+
+    def close(self) -> None:
+        for h in (getattr(self, "_series", None), getattr(self, "_parallel", None)):
+            if h is not None and self.device._h:
+                self._lib.ma_biquad_destroy(h)
+        self._series = self._parallel = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

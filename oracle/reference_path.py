@@ -296,3 +296,58 @@ def to_decibels(data: np.ndarray, reference: float, min_db: float) -> np.ndarray
         return np.full(data.shape, F32(min_db), dtype=F32)
     ratio = np.maximum(data / F32(reference), F32(1e-10))
     return np.maximum(F32(20.0) * np.log10(ratio), F32(min_db)).astype(F32)
+
+
+# ----------------------------------------------------------- biquad filters
+
+
+def biquad_coefficients(kind: str, frequency: float, sample_rate: float, q: float = 0.7071067811865476,
+                        gain_db: float = 0.0) -> np.ndarray:
+    """(b0, b1, b2, a1, a2) in float32 as BiquadFilter.configure derives them
+    (Filters.swift:226-345, :386-437): float32 parameters widened to float64, the cookbook forms,
+    division by a0, rounding to float32.  Validation is not restated here."""
+    f, sr, qq = (float(F32(v)) for v in (frequency, sample_rate, q))
+    w = 2.0 * np.pi * f / sr
+    sn, cs = np.sin(w), np.cos(w)
+    al = sn / (2.0 * qq)
+    amp = 10.0 ** (float(F32(gain_db)) / 40.0)
+    if kind == "lowpass":
+        b, a = [(1 - cs) / 2, 1 - cs, (1 - cs) / 2], [1 + al, -2 * cs, 1 - al]
+    elif kind == "highpass":
+        b, a = [(1 + cs) / 2, -(1 + cs), (1 + cs) / 2], [1 + al, -2 * cs, 1 - al]
+    elif kind == "bandpass":
+        b, a = [al, 0.0, -al], [1 + al, -2 * cs, 1 - al]
+    elif kind == "notch":
+        b, a = [1.0, -2 * cs, 1.0], [1 + al, -2 * cs, 1 - al]
+    elif kind == "allpass":
+        b, a = [1 - al, -2 * cs, 1 + al], [1 + al, -2 * cs, 1 - al]
+    elif kind == "peaking":
+        b, a = [1 + al * amp, -2 * cs, 1 - al * amp], [1 + al / amp, -2 * cs, 1 - al / amp]
+    elif kind == "lowshelf":
+        r = 2 * np.sqrt(amp) * al
+        b = [amp * ((amp + 1) - (amp - 1) * cs + r), 2 * amp * ((amp - 1) - (amp + 1) * cs),
+             amp * ((amp + 1) - (amp - 1) * cs - r)]
+        a = [(amp + 1) + (amp - 1) * cs + r, -2 * ((amp - 1) + (amp + 1) * cs), (amp + 1) + (amp - 1) * cs - r]
+    elif kind == "highshelf":
+        r = 2 * np.sqrt(amp) * al
+        b = [amp * ((amp + 1) + (amp - 1) * cs + r), -2 * amp * ((amp - 1) + (amp + 1) * cs),
+             amp * ((amp + 1) + (amp - 1) * cs - r)]
+        a = [(amp + 1) - (amp - 1) * cs + r, 2 * ((amp - 1) - (amp + 1) * cs), (amp + 1) - (amp - 1) * cs - r]
+    else:
+        raise ValueError(kind)
+    return np.array([b[0] / a[0], b[1] / a[0], b[2] / a[0], a[1] / a[0], a[2] / a[0]]).astype(F32)
+
+
+def biquad_process(x: np.ndarray, coeffs: np.ndarray, state=None, dtype=F32):
+    """Direct Form II Transposed recurrence of BiquadFilter.process(sample:) (Filters.swift:515-537)
+    and the biquad_filter_multichannel shader (DSP.metal:727-735) over the last axis of x, in
+    `dtype` arithmetic; returns (y, final (z1, z2)).  scipy.signal.lfilter implements exactly this
+    structure, with `zi` holding (z1, z2)."""
+    import scipy.signal as ssig
+    x = np.asarray(x, dtype=dtype)
+    c = np.asarray(coeffs, dtype=dtype)
+    b = c[:3]
+    a = np.concatenate([np.ones(1, dtype=dtype), c[3:5]])
+    zi = np.zeros(x.shape[:-1] + (2,), dtype=dtype) if state is None else np.asarray(state, dtype=dtype)
+    y, zf = ssig.lfilter(b, a, x, axis=-1, zi=zi)
+    return y.astype(dtype), zf.astype(dtype)

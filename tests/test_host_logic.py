@@ -145,3 +145,34 @@ def test_product_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "import oracle" not in text and "from oracle" not in text, f
+
+
+def test_biquad_design_matches_port_and_validation():
+    """Coefficient design and its validation order (Filters.swift:346-490) need no device."""
+    from metalaudio_b200.dsp import BiquadFilter, FilterError
+    from oracle import reference_path as rp
+    T = BiquadFilter.FilterType
+    cases = [(T.lowpass, "lowpass", 0.0), (T.highpass, "highpass", 0.0), (T.bandpass, "bandpass", 0.0),
+             (T.notch, "notch", 0.0), (T.allpass, "allpass", 0.0), (T.peaking(6.0), "peaking", 6.0),
+             (T.lowshelf(-12.0), "lowshelf", -12.0), (T.highshelf(3.0), "highshelf", 3.0)]
+    for t, kind, g in cases:
+        for fr, sr, q in [(1000.0, 44100.0, 0.707), (50.0, 48000.0, 12.0), (15000.0, 44100.0, 0.5)]:
+            c = BiquadFilter.design(t, fr, sr, q).asArray()
+            assert np.array_equal(c, rp.biquad_coefficients(kind, fr, sr, q, g))
+            assert abs(c[4]) < 1 and abs(c[3]) < 1 + c[4]
+    lp = BiquadFilter.design(T.lowpass, 1000.0, 44100.0).asArray().astype(np.float64)
+    assert abs((lp[0] + lp[1] + lp[2]) / (1 + lp[3] + lp[4]) - 1.0) < 1e-4        # unity gain at DC
+    hp = BiquadFilter.design(T.highpass, 1000.0, 44100.0).asArray().astype(np.float64)
+    assert abs(hp[0] + hp[1] + hp[2]) < 1e-6                                      # zero at DC
+    pk = BiquadFilter.design(T.peaking(0.0), 1000.0, 44100.0).asArray()
+    assert np.allclose(pk[:3], [1.0, pk[3], pk[4]], atol=1e-7)                    # 0 dB peaking = identity
+    for args, name in [((T.lowpass, 1000.0, 0.0), "sampleRate"), ((T.lowpass, 0.0, 44100.0), "frequency"),
+                       ((T.lowpass, 30000.0, 44100.0), "frequency"), ((T.lowpass, 1000.0, 44100.0, 0.0), "q"),
+                       ((T.lowpass, 1000.0, 44100.0, -1.0), "q")]:
+        with pytest.raises(FilterError) as e:
+            BiquadFilter.design(*args)
+        assert e.value.case == "invalidParameter" and e.value.name == name
+    assert "Invalid parameter 'q'" in FilterError.invalidParameter("q", 0.0, "must be > 0").errorDescription
+    assert FilterError.unstable("x").errorDescription == "Filter is unstable: x"
+    d = BiquadFilter.Coefficients()
+    assert (d.b0, d.b1, d.b2, d.a1, d.a2) == (1, 0, 0, 0, 0)
