@@ -508,7 +508,7 @@ def bench_large(dev, lib, torch, stream, peak):
     return out
 
 
-def bench_next_rows(dev, lib, torch, stream, peak):
+def bench_next_rows(dev, lib, torch, stream, peak, small=False):
     """The callers either side of the hot path: STFT / iSTFT through the magnitude + phase layout
     (64 signals of configuration 2's shape) and the one-shot FFT convolution (32 signals, 131072-tap
     kernel, 2^20-point transforms).  Device-resident, CUDA-event timed, best of 5 after a warm-up."""
@@ -536,7 +536,7 @@ def bench_next_rows(dev, lib, torch, stream, peak):
 
     out = {}
     # --- magnitude / phase layout
-    S, L, n, hop = 64, SIGNAL_LEN, N_FFT, HOP
+    S, L, n, hop = (16 if small else 64), SIGNAL_LEN, N_FFT, HOP
     frames = (L - n) // hop + 1
     kh = n // 2 + 1
     fft = FFT(dev, FFT.Config(size=n, windowType=WindowType.hann, hopSize=hop), window=periodic_hann(n))
@@ -559,7 +559,7 @@ def bench_next_rows(dev, lib, torch, stream, peak):
     fft.close()
     del x, mag, ph, y
     # --- one-shot FFT convolution
-    sig, taps, nfft = 32, 131072, 1 << 20
+    sig, taps, nfft = (8 if small else 32), 131072, 1 << 20
     length = nfft - taps + 1
     h = decaying_ir(taps)
     fc = ctypes.c_void_p()
@@ -575,12 +575,13 @@ def bench_next_rows(dev, lib, torch, stream, peak):
         "workload": f"{sig} signals x {length} samples, one {taps}-tap kernel, {nfft}-point transforms",
         "ms": ms_c, "value": sig * length / (ms_c * 1e-3), "unit": "signal-samples/s",
         "frac_of_hbm_peak": bytes_c / (ms_c * 1e-3) / 1e9 / peak, "algorithmic_bytes": bytes_c,
-        "note": "pad, forward, multiply, inverse as separate passes through L2-sized chunks: several times "
-                "the compulsory traffic"}
+        "note": "three passes per chunk (columns forward, rows forward * kernel spectrum + inverse in place, "
+                "columns inverse) on L2-resident pass data: HBM sees input and output once; the passes "
+                "themselves are latency / issue bound at this transform size"}
     lib.ma_fftconv_destroy(fc)
     del xs, ys
     # --- multichannel biquad: 512 channels x 2^20 samples, one low-pass section, then a 4-section cascade
-    C, L = 512, SIGNAL_LEN
+    C, L = (128 if small else 512), SIGNAL_LEN
     xb = torch.empty((C, L), dtype=torch.float32, device=device).normal_(0.0, 0.1)
     yb = torch.empty_like(xb)
     torch.cuda.synchronize()
@@ -615,8 +616,11 @@ def run_only(args, local_rank: int):
     lib = dev._lib
     stream = torch.cuda.ExternalStream(lib.ma_context_stream(dev.handle), device=torch.device("cuda", local_rank))
     peak, _ = measured_peak_gbs()
-    fn = {"conv": bench_conv, "large": bench_large, "next": bench_next_rows}[args.only]
-    print(json.dumps({args.only: fn(dev, lib, torch, stream, peak)}), flush=True)
+    if args.only == "next":
+        res = bench_next_rows(dev, lib, torch, stream, peak, small=args.small)
+    else:
+        res = {"conv": bench_conv, "large": bench_large}[args.only](dev, lib, torch, stream, peak)
+    print(json.dumps({args.only: res}), flush=True)
 
 
 def main():
@@ -631,6 +635,7 @@ def main():
                     help="signals per GPU (default: the benchmark configuration's 256; smaller for profiler captures)")
     ap.add_argument("--conv-channels", type=int, default=CONV["channels"])
     ap.add_argument("--large-batch", type=int, default=LARGE["batch"])
+    ap.add_argument("--small", action="store_true", help="with --only next: a quarter-size case for profiler captures")
     ap.add_argument("--only", choices=["conv", "large", "next"], default=None,
                     help="run just one of the extra workloads (profiler captures)")
     args = ap.parse_args()

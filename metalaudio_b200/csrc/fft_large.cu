@@ -37,6 +37,9 @@ struct LargeParams {
     const float2* twN2;  // exp(-2 pi i k/N2), k <= M2/2
     const float2* tw1;   // stage twiddle tables of FftPlan<N1>
     const float2* twL;   // exp(-2 pi i j/N),  j < N/2
+    int64_t in_stride;   // forward pass 1: floats between consecutive transforms' inputs
+    int64_t valid;       // forward pass 1: samples present per transform, the rest reads as zero
+    float2* spec_rows;   // convolution: kernel spectrum in pass-2 row order [N2/2+1][N1]
 };
 
 // w[q] = base * step^q for q < n (n <= 17), products of depth <= 3 from step, step^4, step^8, step^12, step^16.
@@ -67,7 +70,7 @@ extern __shared__ float4 ma_large_smem[];
 
 // ---------------------------------------------------------------- forward pass 1
 template <int M2, int W1>
-__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? 2 : 1) cols_r2c_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? 3 : 1) cols_r2c_kernel(const LargeParams p) {
     using P = FftPlan<M2>;
     constexpr int R = P::R, T = P::T;
     float2* smem = reinterpret_cast<float2*>(ma_large_smem);
@@ -78,12 +81,21 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
     for (int64_t blk = blockIdx.x; blk < p.batch * tiles; blk += gridDim.x) {
         const int64_t b = blk / tiles;
         const int n1 = (int)(blk - b * tiles) * W1 + i;
-        const float* x = p.in + b * (int64_t)p.n + n1;
+        const float* x = p.in + b * p.in_stride + n1;
         float2 v[R];
+        if (p.valid >= p.n) {
 #pragma unroll
-        for (int q = 0; q < R; ++q) {
-            const int64_t j = t + q * T;
-            v[q] = make_float2(__ldcs(x + (2 * j) * p.n1), __ldcs(x + (2 * j + 1) * p.n1));
+            for (int q = 0; q < R; ++q) {
+                const int64_t j = t + q * T;
+                v[q] = make_float2(__ldcs(x + (2 * j) * p.n1), __ldcs(x + (2 * j + 1) * p.n1));
+            }
+        } else {  // zero-padded input (the convolution's transforms): samples at and beyond `valid` read as 0
+#pragma unroll
+            for (int q = 0; q < R; ++q) {
+                const int64_t j = t + q * T;
+                const int64_t i0 = (2 * j) * p.n1, i1 = (2 * j + 1) * p.n1;
+                v[q] = make_float2(n1 + i0 < p.valid ? __ldcs(x + i0) : 0.f, n1 + i1 < p.valid ? __ldcs(x + i1) : 0.f);
+            }
         }
         int parity = 0;
         float2* sbuf0 = smem + i;
@@ -198,7 +210,7 @@ __device__ __forceinline__ void store_half_tile(const LargeParams& p, int64_t b,
 
 // ---------------------------------------------------------------- forward pass 2
 template <int N1, int W2>
-__global__ void __launch_bounds__(W2* FftPlan<N1>::T) rows_fwd_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 256 ? 4 : 1) rows_fwd_kernel(const LargeParams p) {
     using P = FftPlan<N1>;
     constexpr int R = P::R, T = P::T;
     constexpr int ELEMS = smem_elems_per_fft<N1, 1>();
@@ -354,9 +366,66 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
     }
 }
 
+// ---------------------------------------------------------------- convolution pass 2
+// Both row passes of a transform pair with the bin-by-bin product in between, on the scratch rows
+// in place: C[k2][.] -> forward N1-point transform -> times the kernel spectrum's row k2 ->
+// inverse transform -> times exp(+2 pi i n1 k2 / N) -> D[k2][.].  The spectrum of the signal
+// never leaves the registers.  STORE_SPECTRUM: stop after the forward transform and write the row
+// to p.spec_rows (how the kernel's own spectrum is prepared).
+template <int N1, int W2, bool STORE_SPECTRUM>
+__global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 256 ? 3 : 1) rows_mul_kernel(const LargeParams p) {
+    using P = FftPlan<N1>;
+    constexpr int R = P::R, T = P::T;
+    constexpr int ELEMS = smem_elems_per_fft<N1, 1>();
+    constexpr int BUF = ELEMS * W2;
+    float2* smem = reinterpret_cast<float2*>(ma_large_smem);
+    const int slot = threadIdx.x / T;
+    const int t = threadIdx.x % T;
+    const int m2 = p.n2 / 2;
+    const int tiles = (m2 + 1 + W2 - 1) / W2;
+    DevCtaL cta;
+    for (int64_t blk = blockIdx.x; blk < p.batch * tiles; blk += gridDim.x) {
+        const int64_t b = blk / tiles;
+        const int k2 = (int)(blk - b * tiles) * W2 + slot;
+        const bool active = k2 <= m2;
+        float2* row = p.scratch + (b * (int64_t)(m2 + 1) + (active ? k2 : 0)) * N1;
+        const float2* hrow = p.spec_rows + (int64_t)(active ? k2 : 0) * N1;
+        float2 v[R], h[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q) v[q] = active ? row[t + q * T] : make_float2(0.f, 0.f);
+        if constexpr (!STORE_SPECTRUM) {
+#pragma unroll
+            for (int q = 0; q < R; ++q) h[q] = __ldg(hrow + t + q * T);
+        }
+        int parity = 0;
+        fft_forward_regs<N1, 1, DevCtaL>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
+        if constexpr (STORE_SPECTRUM) {
+            if (active) {
+#pragma unroll
+                for (int q = 0; q < R; ++q) p.spec_rows[(int64_t)k2 * N1 + t + q * T] = v[q];
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < R; ++q) {
+                const float2 y = cmul(v[q], h[q]);
+                v[q] = make_float2(y.y, y.x);  // swapped: the inverse runs as a forward transform
+            }
+            cta.sync();  // the first transform's exchange reads are done before the buffers are rewritten
+            fft_forward_regs<N1, 1, DevCtaL>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
+            if (active) {
+                float2 wq[R];
+                geometric_twiddles<R>(wq, __ldg(p.twL + (int64_t)k2 * t), __ldg(p.twL + (int64_t)k2 * T));
+#pragma unroll
+                for (int q = 0; q < R; ++q) row[t + q * T] = cmul(make_float2(v[q].y, v[q].x), cconj(wq[q]));
+            }
+        }
+        cta.sync();
+    }
+}
+
 // ---------------------------------------------------------------- inverse pass B
 template <int M2, int W1>
-__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? 2 : 1) cols_c2r_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? 3 : 1) cols_c2r_kernel(const LargeParams p) {
     using P = FftPlan<M2>;
     constexpr int R = P::R, T = P::T;
     float2* smem = reinterpret_cast<float2*>(ma_large_smem);
@@ -489,6 +558,48 @@ static ma_status run_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse)
     return after_launch(ctx);
 }
 
+// Raises a kernel's dynamic shared-memory limit and returns its resident CTAs per SM (cached in occ).
+template <typename K>
+static ma_status kernel_occupancy(K kernel, int threads, size_t smem, int* occ) {
+    if (*occ == 0) {
+        int n = 0;
+        MA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        MA_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem));
+        *occ = n > 0 ? n : 1;
+    }
+    return MA_OK;
+}
+
+template <int N1, int W2>
+static ma_status run_rows_mul(ma_fft_plan* plan, const LargeParams& p, bool store_spectrum) {
+    constexpr int threads = W2 * FftPlan<N1>::T;
+    constexpr size_t smem = 2 * (size_t)smem_elems_per_fft<N1, 1>() * W2 * sizeof(float2);
+    ma_context* ctx = plan->ctx;
+    static int occ[2][64] = {};
+    int* o = &occ[store_spectrum ? 1 : 0][ctx->device & 63];
+    if (store_spectrum) MA_TRY(kernel_occupancy(rows_mul_kernel<N1, W2, true>, threads, smem, o));
+    else MA_TRY(kernel_occupancy(rows_mul_kernel<N1, W2, false>, threads, smem, o));
+    const int m2 = p.n2 / 2;
+    const int64_t work = p.batch * ((m2 + 1 + W2 - 1) / W2);
+    const int64_t cap = (int64_t)ctx->sm_count * *o;
+    const int grid = (int)(work < cap ? work : cap);
+    if (store_spectrum) rows_mul_kernel<N1, W2, true><<<grid, threads, smem, ctx->stream>>>(p);
+    else rows_mul_kernel<N1, W2, false><<<grid, threads, smem, ctx->stream>>>(p);
+    return after_launch(ctx);
+}
+
+static ma_status dispatch_rows_mul(ma_fft_plan* plan, const LargeParams& p, bool store_spectrum) {
+    switch (p.n1) {
+        case 128: return run_rows_mul<128, 16>(plan, p, store_spectrum);
+        case 256: return run_rows_mul<256, 16>(plan, p, store_spectrum);
+        case 512: return run_rows_mul<512, 16>(plan, p, store_spectrum);
+        case 1024: return run_rows_mul<1024, 8>(plan, p, store_spectrum);
+        case 2048: return run_rows_mul<2048, 4>(plan, p, store_spectrum);
+        case 4096: return run_rows_mul<4096, 2>(plan, p, store_spectrum);
+        default: return MA_ERR_UNSUPPORTED;
+    }
+}
+
 static ma_status dispatch_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse) {
     switch (p.n2 / 2) {
         case 64: return run_cols<64, 32>(plan, p, inverse);
@@ -562,6 +673,8 @@ static void fill_tables(ma_fft_plan* plan, LargeParams& p) {
     p.twN2 = plan->d_twN;
     p.tw1 = plan->d_tw1;
     p.twL = plan->d_twL;
+    p.in_stride = plan->n;
+    p.valid = plan->n;
 }
 
 ma_status launch_r2c_large(ma_fft_plan* plan, const float* in, float* out_a, float* out_b, float* mag,
@@ -604,6 +717,42 @@ ma_status launch_c2r_large(ma_fft_plan* plan, const float* in_a, const float* in
         }
         p.out_a = out + done * n;
         MA_TRY(dispatch_rows(plan, p, true));
+        MA_TRY(dispatch_cols(plan, p, true));
+    }
+    return MA_OK;
+}
+
+// Spectrum of one real signal of `valid` samples (zero-padded to N) in pass-2 row order, for
+// launch_conv_large.  spec_rows holds (N2/2+1) * N1 complex values.
+ma_status launch_spec_rows_large(ma_fft_plan* plan, const float* in, int64_t valid, float2* spec_rows) {
+    LargeParams p{};
+    fill_tables(plan, p);
+    p.batch = 1;
+    p.in = in;
+    p.valid = valid;
+    p.spec_rows = spec_rows;
+    MA_TRY(dispatch_cols(plan, p, false));
+    return dispatch_rows_mul(plan, p, true);
+}
+
+// out[b][0..N) = inverse(forward(zero-padded in[b][0..valid)) * spectrum) for `batch` signals: three
+// passes per chunk (columns forward, rows forward-multiply-inverse in place, columns inverse), the
+// intermediate data staying in the L2-sized scratch.
+ma_status launch_conv_large(ma_fft_plan* plan, const float* in, int64_t valid, int64_t in_stride,
+                            const float2* spec_rows, float* out, int64_t batch) {
+    const int64_t n = plan->n;
+    for (int64_t done = 0; done < batch; done += plan->scratch_batch) {
+        LargeParams p{};
+        fill_tables(plan, p);
+        p.batch = batch - done < plan->scratch_batch ? batch - done : plan->scratch_batch;
+        p.in = in + done * in_stride;
+        p.in_stride = in_stride;
+        p.valid = valid;
+        p.spec_rows = const_cast<float2*>(spec_rows);
+        p.out_a = out + done * n;
+        p.layout = LAYOUT_HALF_INTERLEAVED;
+        MA_TRY(dispatch_cols(plan, p, false));
+        MA_TRY(dispatch_rows_mul(plan, p, false));
         MA_TRY(dispatch_cols(plan, p, true));
     }
     return MA_OK;

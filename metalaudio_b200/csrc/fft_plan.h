@@ -44,5 +44,9 @@ ma_status launch_r2c_large(ma_fft_plan* plan, const float* in, float* out_a, flo
                            int mag_kind, float db_scale, int64_t batch, int layout);
 ma_status launch_c2r_large(ma_fft_plan* plan, const float* in_a, const float* in_b, float* out,
                            int64_t batch, int layout);
+// Convolution through a large plan with the spectrum kept on chip (fft_large.cu).
+ma_status launch_spec_rows_large(ma_fft_plan* plan, const float* in, int64_t valid, float2* spec_rows);
+ma_status launch_conv_large(ma_fft_plan* plan, const float* in, int64_t valid, int64_t in_stride,
+                            const float2* spec_rows, float* out, int64_t batch);
 
 }  // namespace ma

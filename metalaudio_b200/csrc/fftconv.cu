@@ -4,11 +4,14 @@
 //   fft_size = next power of two >= expected_input + taps - 1
 //   y = IFFT( FFT(zero-padded x) * FFT(zero-padded h) ),  fft_size samples per signal
 //
-// Built on the library's real-input transforms: the input rows are zero-padded into a work
-// buffer, transformed to half spectra, multiplied bin by bin with the kernel's half spectrum
-// (both are spectra of real signals, so the product's upper half is the conjugate mirror and never
-// has to exist), and transformed back with the 1/N scale.  All work buffers are sized at creation
-// for `max_signals`; the process calls allocate nothing.
+// Built on the library's real-input transforms.  Up to 8192 points the input rows are zero-padded
+// into a work buffer, transformed to half spectra, multiplied bin by bin with the kernel's half
+// spectrum (both are spectra of real signals, so the product's upper half is the conjugate mirror
+// and never has to exist), and transformed back with the 1/N scale.  Above 8192 points the
+// two-pass transforms are fused around the product: columns forward (zero padding applied by the
+// loader), then one kernel that runs the row transform, the product and the inverse row transform
+// in place on the L2-resident pass data, then columns inverse; HBM sees the input and the output
+// only.  All work buffers are sized at creation; the process calls allocate nothing.
 #include <new>
 
 #include "fft_plan.h"
@@ -21,7 +24,8 @@ struct ma_fftconv {
     int32_t max_signals = 0;
     float* d_padded = nullptr;   // [max_signals][n]
     float2* d_spec = nullptr;    // [max_signals][n/2+1]
-    float2* d_kernel = nullptr;  // [n/2+1]
+    float2* d_kernel = nullptr;  // [n/2+1], or for large plans the spectrum in pass-2 row order
+    bool large = false;
 };
 
 namespace ma {
@@ -53,6 +57,7 @@ static ma_status fftconv_run(ma_fftconv* fc, const float* d_in, int64_t len, int
                              float* d_out) {
     ma_context* ctx = fc->ctx;
     const int64_t n = fc->n, bins = n / 2 + 1;
+    if (fc->large) return launch_conv_large(fc->plan, d_in, len, in_stride, fc->d_kernel, d_out, n_signals);
     fftconv_pad_kernel<<<grid_for(ctx, n * n_signals), 256, 0, ctx->stream>>>(d_in, len, in_stride, fc->d_padded, n,
                                                                                n * n_signals);
     MA_TRY(after_launch(ctx));
@@ -92,26 +97,31 @@ ma_status ma_fftconv_create(ma_context* ctx, const float* kernel, int64_t taps, 
     fc->max_signals = max_signals;
     const int64_t bins = n / 2 + 1;
     ma_status st = ma_fft_plan_create(ctx, (int32_t)n, nullptr, (int32_t)n, &fc->plan);
+    fc->large = st == MA_OK && fc->plan->large;
+    // large plans keep the kernel spectrum in pass-2 row order: (N2/2+1) rows of N1 values
+    const int64_t kernel_elems = fc->large ? (int64_t)(fc->plan->n2 / 2 + 1) * fc->plan->n1 : bins;
     if (st == MA_OK) {
-        cudaError_t e = cudaMalloc((void**)&fc->d_padded, sizeof(float) * (size_t)n * max_signals);
-        if (e == cudaSuccess) e = cudaMalloc((void**)&fc->d_spec, sizeof(float2) * (size_t)bins * max_signals);
-        if (e == cudaSuccess) e = cudaMalloc((void**)&fc->d_kernel, sizeof(float2) * (size_t)bins);
+        cudaError_t e = cudaMalloc((void**)&fc->d_kernel, sizeof(float2) * (size_t)kernel_elems);
+        if (e == cudaSuccess && !fc->large) {
+            e = cudaMalloc((void**)&fc->d_padded, sizeof(float) * (size_t)n * max_signals);
+            if (e == cudaSuccess) e = cudaMalloc((void**)&fc->d_spec, sizeof(float2) * (size_t)bins * max_signals);
+        }
         if (e != cudaSuccess) st = cuda_fail(e);
     }
-    // kernel spectrum: the taps staged through the output-sized scratch row, transformed once
     float* d_taps = nullptr;
     if (st == MA_OK) {
         cudaError_t e = cudaMalloc((void**)&d_taps, sizeof(float) * (size_t)taps);
         if (e != cudaSuccess) st = cuda_fail(e);
     }
     if (st == MA_OK) st = copy_h2d(ctx, d_taps, kernel, sizeof(float) * (size_t)taps);
-    if (st == MA_OK) {
+    if (st == MA_OK && fc->large) st = launch_spec_rows_large(fc->plan, d_taps, taps, fc->d_kernel);
+    if (st == MA_OK && !fc->large) {
         fftconv_pad_kernel<<<grid_for(ctx, n), 256, 0, ctx->stream>>>(d_taps, taps, taps, fc->d_padded, n, n);
         st = after_launch(ctx);
+        if (st == MA_OK)
+            st = ma_fft_forward_dev(fc->plan, fc->d_padded, reinterpret_cast<float*>(fc->d_kernel), nullptr, nullptr, 0,
+                                    1.f, 1, MA_LAYOUT_HALF_INTERLEAVED);
     }
-    if (st == MA_OK)
-        st = ma_fft_forward_dev(fc->plan, fc->d_padded, reinterpret_cast<float*>(fc->d_kernel), nullptr, nullptr, 0, 1.f,
-                                1, MA_LAYOUT_HALF_INTERLEAVED);
     if (st == MA_OK) st = ma_context_sync(ctx, 30.0);
     if (d_taps != nullptr) (void)cudaFree(d_taps);
     if (st != MA_OK) {
