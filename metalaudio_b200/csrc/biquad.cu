@@ -15,7 +15,10 @@
 // host-built table) and a short serial pass over the 8 warps, which gives every thread the true
 // state in front of its samples; it then runs the recurrence again from that state and keeps the
 // outputs.  States and recurrences are double precision (see biquad_kernel), data is float32.  Cascaded sections run back to back on the registers.  Loads and stores of a tile are
-// contiguous; the tile is re-indexed through padded shared memory.
+// contiguous; the tile is re-indexed through swizzled shared memory, and the next tile is fetched
+// asynchronously while the current one is filtered.
+#include <cuda_pipeline.h>
+
 #include <cmath>
 #include <new>
 #include <vector>
@@ -46,7 +49,14 @@ __device__ __forceinline__ double2 mat_vec(const double* m, double2 v) {
     return make_double2(fma(m[0], v.x, m[1] * v.y), fma(m[2], v.x, m[3] * v.y));
 }
 
-__device__ __forceinline__ int padded(int i) { return i + (i >> 5); }
+// Tile layout in shared memory: 16-byte chunks of four samples; chunk c of row r (a row is one
+// thread's 32 samples) sits at column c ^ (r & 7).  Both access patterns are then conflict-free
+// with 16-byte accesses: a thread walking its own row, and consecutive threads touching
+// consecutive chunks of the signal.
+__device__ __forceinline__ int swizzled(int i) {
+    const int g = i >> 2, r = g >> 3;
+    return (((r << 3) | ((g & 7) ^ (r & 7))) << 2) | (i & 3);
+}
 
 // Why double precision inside: a thread restarts the recurrence every 32 samples.  In float32 the
 // rounding drift of one block and the freshly computed state of the next do not line up, which
@@ -56,11 +66,11 @@ __device__ __forceinline__ int padded(int i) { return i + (i >> 5); }
 // in double the steps vanish and every section's output is the exact filter's, rounded once to
 // float32 (the precision sections exchange data in, as the reference's float arrays do).
 __global__ void __launch_bounds__(kBqThreads, 2) biquad_kernel(const BiquadLaunch p) {
-    extern __shared__ double bq_smem[];
+    extern __shared__ __align__(16) double bq_smem[];
     double* tab = bq_smem;                                              // n_sections * kBqTable
     double2* warp_end = reinterpret_cast<double2*>(tab + p.n_sections * kBqTable);  // [2][kBqWarps]
     double2* carry = warp_end + 2 * kBqWarps;                           // [2][n_sections]: read one, write the other
-    float* tile = reinterpret_cast<float*>(carry + 2 * p.n_sections);   // kBqTile + kBqTile/32 floats
+    float* tiles = reinterpret_cast<float*>(carry + 2 * p.n_sections);  // two tiles: one in use, one being filled
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t ch = blockIdx.x;
     const int set = p.channel_to_set != nullptr ? p.channel_to_set[ch] : 0;
@@ -76,32 +86,54 @@ __global__ void __launch_bounds__(kBqThreads, 2) biquad_kernel(const BiquadLaunc
     const bool vec_out = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     __syncthreads();
 
+    constexpr int kTileFloats = kBqTile;
+    // Full, 16-byte aligned tiles are fetched one iteration ahead with asynchronous 16-byte copies
+    // (global -> shared without passing through registers), so the load latency of tile i+1 is
+    // spent while tile i is filtered.
+    auto prefetch = [&](int64_t base, float* dst) {
+#pragma unroll
+        for (int k = 0; k < kBqPer / 4; ++k) {
+            const int i = 4 * (tid + k * kBqThreads);
+            __pipeline_memcpy_async(dst + swizzled(i), in + base + i, 16);
+        }
+        __pipeline_commit();
+    };
+    auto full_tile = [&](int64_t base) { return vec_in && base + kBqTile <= p.samples; };
+    bool fetched = false;
+    if (p.samples > 0 && full_tile(0)) {
+        prefetch(0, tiles);
+        fetched = true;
+    }
     int par = 0;
     for (int64_t base = 0; base < p.samples; base += kBqTile, par ^= 1) {
+        float* tile = tiles + par * kTileFloats;
         const double2* carry_in = carry + par * p.n_sections;
         double2* carry_out = carry + (par ^ 1) * p.n_sections;
         const int64_t left = p.samples - base;
         const int valid = left < kBqTile ? (int)left : kBqTile;
-        // ---- contiguous load into the padded tile (zeros beyond the end of the signal)
-        if (vec_in && valid == kBqTile) {
-#pragma unroll
-            for (int k = 0; k < kBqPer / 4; ++k) {
-                const int i = 4 * (tid + k * kBqThreads);
-                const float4 v = __ldcs(reinterpret_cast<const float4*>(in + base + i));
-                float* d = tile + padded(i);  // four consecutive samples never straddle a pad
-                d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
-            }
+        // ---- this tile: already on its way, or loaded here (ragged / unaligned: zeros beyond the end)
+        if (fetched) {
+            __pipeline_wait_prior(0);
         } else {
 #pragma unroll 4
             for (int k = 0; k < kBqPer; ++k) {
                 const int i = tid + k * kBqThreads;
-                tile[padded(i)] = i < valid ? __ldcs(in + base + i) : 0.f;
+                tile[swizzled(i)] = i < valid ? __ldcs(in + base + i) : 0.f;
             }
+        }
+        // ---- next tile: start it now (its buffer was last read two iterations ago, before the barriers since)
+        fetched = false;
+        if (base + kBqTile < p.samples && full_tile(base + kBqTile)) {
+            prefetch(base + kBqTile, tiles + (par ^ 1) * kTileFloats);
+            fetched = true;
         }
         __syncthreads();
         float x[kBqPer];
 #pragma unroll
-        for (int j = 0; j < kBqPer; ++j) x[j] = tile[padded(tid * kBqPer) + j];
+        for (int k = 0; k < kBqPer / 4; ++k) {
+            const float4 v = reinterpret_cast<const float4*>(tile)[tid * (kBqPer / 4) + (k ^ (tid & 7))];
+            x[4 * k] = v.x; x[4 * k + 1] = v.y; x[4 * k + 2] = v.z; x[4 * k + 3] = v.w;
+        }
         const bool last_tile = left <= kBqTile;
         const int last_local = valid - 1 - tid * kBqPer;  // index of the signal's last sample in this thread
         const bool owns_last = last_tile && last_local >= 0 && last_local < kBqPer;
@@ -168,22 +200,23 @@ __global__ void __launch_bounds__(kBqThreads, 2) biquad_kernel(const BiquadLaunc
             // carry for the next tile: the state the last thread ends in
             if (!last_tile && tid == kBqThreads - 1) carry_out[s] = make_double2(s1, s2);
         }
-        // ---- contiguous store
+        // ---- contiguous store through the same tile
 #pragma unroll
-        for (int j = 0; j < kBqPer; ++j) tile[padded(tid * kBqPer) + j] = x[j];
+        for (int k = 0; k < kBqPer / 4; ++k)
+            reinterpret_cast<float4*>(tile)[tid * (kBqPer / 4) + (k ^ (tid & 7))] =
+                make_float4(x[4 * k], x[4 * k + 1], x[4 * k + 2], x[4 * k + 3]);
         __syncthreads();
         if (vec_out && valid == kBqTile) {
 #pragma unroll
             for (int k = 0; k < kBqPer / 4; ++k) {
                 const int i = 4 * (tid + k * kBqThreads);
-                const float* d = tile + padded(i);
-                __stcs(reinterpret_cast<float4*>(out + base + i), make_float4(d[0], d[1], d[2], d[3]));
+                __stcs(reinterpret_cast<float4*>(out + base + i), *reinterpret_cast<const float4*>(tile + swizzled(i)));
             }
         } else {
 #pragma unroll 4
             for (int k = 0; k < kBqPer; ++k) {
                 const int i = tid + k * kBqThreads;
-                if (i < valid) __stcs(out + base + i, tile[padded(i)]);
+                if (i < valid) __stcs(out + base + i, tile[swizzled(i)]);
             }
         }
         __syncthreads();  // the tile and the carries are reused by the next iteration
@@ -235,7 +268,7 @@ struct ma_biquad {
 };
 
 static size_t biquad_smem(int sections) {
-    return sizeof(float) * (size_t)(kBqTile + kBqTile / 32) + sizeof(double) * (size_t)(sections * kBqTable) +
+    return sizeof(float) * (size_t)(2 * kBqTile) + sizeof(double) * (size_t)(sections * kBqTable) +
            sizeof(double2) * (size_t)(2 * kBqWarps + 2 * sections);
 }
 

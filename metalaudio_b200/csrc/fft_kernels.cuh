@@ -34,6 +34,7 @@ struct R2CParams {
     const float2* twM;          // stage twiddle tables of FftPlan<M> (fft_core.cuh layout)
     int32_t bulk_ok;            // frame starts and length are 16-byte multiples: bulk async staging allowed
     int32_t* error_flag;        // set to 1 when a bounded wait ran out
+    int32_t dependent_launch;   // launched with programmatic stream serialization (see fft_small.cu)
     const float2* twN;          // Hermitian-step twiddles exp(-2 pi i k / N): [k], k <= M/2, or for
                                 // plan_pairable<M>() the table [k][j] = W_N^(j + k*NL), j <= NL/2
 };
@@ -378,6 +379,7 @@ struct C2RParams {
     const float* norm_mid;      // iSTFT: clamped window sums of the interior, indexed by position mod hop
     const float* norm_mid_inv;  // iSTFT: their reciprocals
     int32_t* error_flag;        // set to 1 when a bounded wait ran out
+    int32_t dependent_launch;   // launched with programmatic stream serialization (see fft_small.cu)
     const float2* twM;          // stage tables: FftPlanRev<M> when plan_pairable<M>(), else FftPlan<M>
     const float2* twN;
 };

@@ -19,15 +19,51 @@ struct DevCta {
 
 extern __shared__ float4 ma_dyn_smem[];
 
+// Programmatic dependent launch, used by the convolution's streaming step (r2c -> multiply-
+// accumulate -> c2r, every block).  A kernel launched with the programmatic-stream-serialization
+// attribute may become resident once every CTA of the kernel before it has executed
+// launch_dependents; it must execute wait before it touches (or, for r2c, before it completes
+// ahead of) anything the earlier kernel produces.  Without the attribute both are no-ops.
+//   c2r: wait, then launch_dependents - the next step's r2c starts while this c2r still runs
+//        (they share no data), but never before the multiply-accumulate that reads the delay line
+//        slot r2c is about to overwrite has completed;
+//   r2c: launch_dependents at once, wait only at the very end - so it completes after the c2r
+//        before it, and everything later in the stream stays ordered after that c2r as well.
+__device__ __forceinline__ void dependents_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// cudaLaunchKernelEx with the attribute (dependent != 0) or a plain launch.
+template <typename K, typename P>
+static void launch_maybe_dependent(K kernel, int grid, int threads, size_t smem, cudaStream_t stream, const P& p,
+                                   int dependent) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent ? 1 : 0;
+    (void)cudaLaunchKernelEx(&cfg, kernel, p);  // an error is picked up by after_launch
+}
+
 template <int M, bool ALIGNED, int LAYOUT, int MAGK>
 __global__ void __launch_bounds__(CtaShape<M>::THREADS, 512 / CtaShape<M>::THREADS) r2c_kernel(const R2CParams p) {
     DevCta cta;
+    if (p.dependent_launch) dependents_launch();
     r2c_body<M, ALIGNED, LAYOUT, MAGK, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
+    if (p.dependent_launch) dependency_wait();
 }
 
 template <int M, int LAYOUT>
 __global__ void __launch_bounds__(CtaShape<M>::THREADS, 512 / CtaShape<M>::THREADS) c2r_kernel(const C2RParams p) {
     DevCta cta;
+    if (p.dependent_launch) {
+        dependency_wait();
+        dependents_launch();
+    }
     c2r_body<M, LAYOUT, DevCta>(p, cta, reinterpret_cast<float2*>(ma_dyn_smem));
 }
 
@@ -68,7 +104,7 @@ static ma_status launch_r2c_t(ma_fft_plan* plan, const R2CParams& p) {
     int64_t cap = (int64_t)ctx->sm_count * occ;
     int grid = (int)(want < cap ? want : cap);
     if (grid < 1) return MA_OK;
-    r2c_kernel<M, ALIGNED, LAYOUT, MAGK><<<grid, S::THREADS, smem, ctx->stream>>>(p);
+    launch_maybe_dependent(r2c_kernel<M, ALIGNED, LAYOUT, MAGK>, grid, S::THREADS, smem, ctx->stream, p, p.dependent_launch);
     return after_launch(ctx);
 }
 
@@ -126,7 +162,7 @@ static ma_status launch_c2r_t(ma_fft_plan* plan, const C2RParams& p) {
     int64_t cap = (int64_t)ctx->sm_count * occ;
     int grid = (int)(want < cap ? want : cap);
     if (grid < 1) return MA_OK;
-    c2r_kernel<M, LAYOUT><<<grid, S::THREADS, smem, ctx->stream>>>(p);
+    launch_maybe_dependent(c2r_kernel<M, LAYOUT>, grid, S::THREADS, smem, ctx->stream, p, p.dependent_launch);
     return after_launch(ctx);
 }
 

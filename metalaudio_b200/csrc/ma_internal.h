@@ -23,6 +23,10 @@ struct ma_context {
     char name[256] = {0};
     int32_t* d_error_flag = nullptr;  // set by a kernel whose bounded wait ran out
     int32_t* h_error_flag = nullptr;  // pinned mirror read at synchronisation
+    // Output rows of the latest convolution streaming step on this context (any object): the next
+    // step's first kernel may overlap that step's last one unless it reads these rows.
+    const float* step_out = nullptr;
+    const float* step_out_end = nullptr;
 };
 
 namespace ma {

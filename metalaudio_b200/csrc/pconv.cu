@@ -58,6 +58,7 @@ struct MacParams {
     int p_per_split;
     int bin_tiles;
     int bpt;         // threads covering one spectrum tile (power of two <= 128)
+    int dependent_launch;  // streaming step: launched with programmatic stream serialization
 };
 
 constexpr int kMacThreads = 128;
@@ -77,6 +78,10 @@ template <int CT, int VEC, bool STREAM>
 __global__ void __launch_bounds__(kMacThreads) pconv_mac_kernel(const MacParams q) {
     using V = typename VecT<VEC>::type;
     __shared__ float2 red[kMacThreads * CT * VEC];
+    if (q.dependent_launch) {  // streaming step: the new delay-line slot comes from the kernel before this one
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     const int tid = threadIdx.x;
     const int bpt = q.bpt;
     const int kb = tid & (bpt - 1);
@@ -298,7 +303,16 @@ static ma_status launch_mac_t(ma_context* ctx, const MacParams& q, int chan_tile
         qq.w0 = q.w0 + (int)done;
         qq.out = q.out + done * q.out_t_stride;
         dim3 grid((unsigned)(chan_tiles * q.bin_tiles * q.splits), (unsigned)ny, 1);
-        pconv_mac_kernel<CT, VEC, STREAM><<<grid, kMacThreads, 0, ctx->stream>>>(qq);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(kMacThreads);
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = q.dependent_launch ? 1 : 0;
+        (void)cudaLaunchKernelEx(&cfg, pconv_mac_kernel<CT, VEC, STREAM>, qq);  // an error is picked up by after_launch
         MA_TRY(after_launch(ctx));
         done += ny;
     }
@@ -685,9 +699,15 @@ ma_status ma_pconv_step_dev(ma_pconv* pc, const float* in_block, int64_t in_stri
     if (C > 1 && (in_stride < B || out_stride < B)) return MA_ERR_INVALID_ARGUMENT;
     if (pc->write_index < 0 || pc->write_index >= P) return MA_ERR_INVALID_PARTITION_STATE;
     const int w = pc->write_index;
+    // The three kernels are chained by programmatic dependent launch: this step's r2c may run
+    // beside the previous step's c2r (see fft_small.cu).  They share no data unless the caller
+    // feeds the previous step's output block straight back in; then r2c is launched plainly.
+    const float* in_end = in_block + (int64_t)(C - 1) * in_stride + B;
+    const bool feeds_back = ctx->step_out != nullptr && in_block < ctx->step_out_end && ctx->step_out < in_end;
     // 1. this block's spectrum into ring slot w
     {
         R2CParams p{};
+        p.dependent_launch = feeds_back ? 0 : 1;
         p.in = in_block;
         p.signal_stride = in_stride;
         p.frames_per_signal = 1;
@@ -719,6 +739,7 @@ ma_status ma_pconv_step_dev(ma_pconv* pc, const float* in_block, int64_t in_stri
         q.wrap = P;
         q.splits = pc->splits;
         q.p_per_split = (P + pc->splits - 1) / pc->splits;
+        q.dependent_launch = 1;
         MA_TRY(launch_mac(pc, q, true, 1));
     }
     // 3. sum the partials, inverse transform, add the kept tail, keep the new one
@@ -735,8 +756,11 @@ ma_status ma_pconv_step_dev(ma_pconv* pc, const float* in_block, int64_t in_stri
         p.out = out_block;
         p.out_signal_stride = out_stride;
         p.tail = pc->d_tail;
+        p.dependent_launch = 1;
         MA_TRY(launch_c2r_small(pc->plan, p));
     }
+    ctx->step_out = out_block;
+    ctx->step_out_end = out_block + (int64_t)(C - 1) * out_stride + B;
     pc->write_index = (w + 1) % P;
     return MA_OK;
 }
