@@ -348,6 +348,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     extra = {}
     if not args.no_extras:
         extra["conv"] = bench_conv(dev, lib, torch, stream, peak)
+        extra["conv_low_latency"] = bench_conv4(dev, lib, torch, stream, peak)
         extra["large_fft"] = bench_large(dev, lib, torch, stream, peak)
         extra["next_rows"] = bench_next_rows(dev, lib, torch, stream, peak)
 
@@ -460,6 +461,63 @@ def bench_conv(dev, lib, torch, stream, peak):
             "note": "time-tiled multiply-accumulate: delay-line spectra reused on chip, FMA-bound "
                     "(1.24e12 FP32 FMAs), so the HBM-streaming byte count is exceeded by design"}
         del xs, ys
+    conv.close()
+    return out
+
+
+def bench_conv4(dev, lib, torch, stream, peak, channels=1024):
+    """Low-latency partitioned convolution, configuration 4 shape, as causal streaming steps: 1024
+    channels, block 64 (FFT 128), 262144-tap impulse response per channel pair (512 distinct ones,
+    4096 partitions): the per-pair spectra cannot be shared beyond two channels."""
+    from metalaudio_b200 import Convolution, Tensor
+    C, B, taps = channels, 64, 262144
+    n_irs = C // 2
+    bytes_per_channel_block = 4 * B + 4 * B + 8 * (B + 1) * (1 + taps // B + taps // B // 2)   # 3 195 912
+    steps, warm = 40, 8
+    g = np.random.Generator(np.random.PCG64(1004))
+    decay = np.exp(-6.907755278982137 * np.arange(taps, dtype=np.float64) / (1.5 * 48000.0)).astype(np.float32)
+    irs = g.standard_normal((n_irs, taps), dtype=np.float32) * decay
+    irs /= np.sqrt(np.sum(irs.astype(np.float64) ** 2, axis=1, keepdims=True)).astype(np.float32)
+    conv = Convolution(dev, Convolution.Mode.partitioned(blockSize=B), channels=C)
+    conv.setKernel(irs, channelToKernel=[c // 2 for c in range(C)])
+    del irs
+    x = Tensor(dev, (C, (steps + warm) * B))
+    y = Tensor(dev, (C, (steps + warm) * B))
+    host = torch.empty((C, (steps + warm) * B), dtype=torch.float32, pin_memory=True)
+    host.normal_(0.0, 0.1, generator=torch.Generator().manual_seed(1014))
+    x.copyAsync(host.data_ptr(), x.byteSize)
+    dev.synchronize(60)
+    stride = (steps + warm) * B
+
+    def do(t):
+        st = lib.ma_pconv_step_dev(conv._h, ctypes.c_void_p(x.pointer + 4 * t * B), stride,
+                                   ctypes.c_void_p(y.pointer + 4 * t * B), stride)
+        if st != 0:
+            raise RuntimeError(f"ma_pconv_step_dev failed: {st}")
+
+    for t in range(warm):
+        do(t)
+    dev.synchronize(60)
+    l0 = lib.ma_kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for t in range(warm, warm + steps):
+        do(t)
+    e1.record(stream)
+    dev.synchronize(120)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    launches = int(lib.ma_kernel_launch_count() - l0)
+    gbs = C * bytes_per_channel_block / (ms * 1e-3) / 1e9
+    out = {"workload": f"partitioned convolution: {C} channels, {n_irs} impulse responses of 262144 taps (one per "
+                       "channel pair), block 64 (FFT 128, 4096 partitions), streaming steps",
+           "metric": "conv_channel_samples_per_s", "value": C * B / (ms * 1e-3), "unit": "channel-samples/s",
+           "ms_per_step": ms, "steps": steps, "gpu_launches": launches,
+           "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                        "algorithmic_bytes_per_channel_block": bytes_per_channel_block,
+                        "kernel": "pconv_mac_kernel + r2c + c2r per step"}}
+    x.free()
+    y.free()
     conv.close()
     return out
 
@@ -618,6 +676,8 @@ def run_only(args, local_rank: int):
     peak, _ = measured_peak_gbs()
     if args.only == "next":
         res = bench_next_rows(dev, lib, torch, stream, peak, small=args.small)
+    elif args.only == "conv4":
+        res = bench_conv4(dev, lib, torch, stream, peak, channels=256 if args.small else 1024)
     else:
         res = {"conv": bench_conv, "large": bench_large}[args.only](dev, lib, torch, stream, peak)
     print(json.dumps({args.only: res}), flush=True)
@@ -636,7 +696,7 @@ def main():
     ap.add_argument("--conv-channels", type=int, default=CONV["channels"])
     ap.add_argument("--large-batch", type=int, default=LARGE["batch"])
     ap.add_argument("--small", action="store_true", help="with --only next: a quarter-size case for profiler captures")
-    ap.add_argument("--only", choices=["conv", "large", "next"], default=None,
+    ap.add_argument("--only", choices=["conv", "conv4", "large", "next"], default=None,
                     help="run just one of the extra workloads (profiler captures)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
