@@ -346,7 +346,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     del host_out
 
     extra = {}
-    if not args.no_extras:
+    if not args.no_extras and rank == 0:  # single-GPU side measurements: rank 0 only, the others wait at the barrier
         extra["conv"] = bench_conv(dev, lib, torch, stream, peak)
         extra["conv_low_latency"] = bench_conv4(dev, lib, torch, stream, peak)
         extra["large_fft"] = bench_large(dev, lib, torch, stream, peak)
