@@ -241,7 +241,10 @@ ma_status ma_istft_output_length(ma_fft_plan* plan, int64_t frames, int64_t* len
 /* STFT of `n_signals` signals of `length` samples, signal s starting at
  * signals + s*signal_stride: frames at i*hop, analysis window, forward DFT.
  * Replaces FFT.stft (STFT.swift:40-81) run over a set of signals.  Outputs are indexed
- * by global frame g = s*F + f with the layouts of ma_fft_forward_dev; `mag` optional. */
+ * by global frame g = s*F + f with the layouts of ma_fft_forward_dev; `mag` optional.
+ * Plans above 8192 points read the frames straight from the signal (window applied by the
+ * loader) through the two-pass transforms; their inverse (ma_istft_*) passes the frames through
+ * a plan-owned buffer that is allocated on the first such call. */
 ma_status ma_stft_dev(ma_fft_plan* plan, const float* signals, int64_t length,
                       int64_t signal_stride, int64_t n_signals, float* out_a, float* out_b,
                       float* mag, int32_t mag_kind, float db_reference, int32_t layout);

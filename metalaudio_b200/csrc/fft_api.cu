@@ -202,7 +202,11 @@ ma_status ma_stft_dev(ma_fft_plan* plan, const float* signals, int64_t length, i
     int64_t total, total_out;
     if (mul_overflow(frames, n_signals, &total) || mul_overflow(total, plan->n, &total_out))
         return MA_ERR_BATCH_OVERFLOW;
-    if (plan->large) return MA_ERR_UNSUPPORTED;  // STFT frames above 8192 points are not served
+    if (plan->large) {
+        if (layout == MA_LAYOUT_HALF_POLAR) return MA_ERR_UNSUPPORTED;
+        return launch_stft_large(plan, signals, signal_stride, frames, n_signals, out_a, out_b, mag, mag_kind,
+                                 1.0f / db_reference, layout);
+    }
     R2CParams p{};
     p.in = signals;
     p.signal_stride = signal_stride;
@@ -238,7 +242,10 @@ ma_status ma_istft_dev(ma_fft_plan* plan, const float* in_a, const float* in_b, 
     int64_t total, total_in;
     if (mul_overflow(frames, n_signals, &total) || mul_overflow(total, plan->n, &total_in))
         return MA_ERR_BATCH_OVERFLOW;
-    if (plan->large) return MA_ERR_UNSUPPORTED;
+    if (plan->large) {
+        if (layout == MA_LAYOUT_HALF_POLAR) return MA_ERR_UNSUPPORTED;
+        return launch_istft_large(plan, in_a, in_b, frames, n_signals, out, out_stride, out_len, floor, layout);
+    }
     C2RParams p{};
     p.in_a = in_a;
     p.in_b = in_b;

@@ -40,6 +40,7 @@ struct LargeParams {
     int64_t in_stride;   // forward pass 1: floats between consecutive transforms' inputs
     int64_t valid;       // forward pass 1: samples present per transform, the rest reads as zero
     float2* spec_rows;   // convolution: kernel spectrum in pass-2 row order [N2/2+1][N1]
+    const float* window; // forward pass 1: analysis window applied by the loader (STFT), or nullptr
 };
 
 // w[q] = base * step^q for q < n (n <= 17), products of depth <= 3 from step, step^4, step^8, step^12, step^16.
@@ -95,6 +96,15 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
                 const int64_t j = t + q * T;
                 const int64_t i0 = (2 * j) * p.n1, i1 = (2 * j + 1) * p.n1;
                 v[q] = make_float2(n1 + i0 < p.valid ? __ldcs(x + i0) : 0.f, n1 + i1 < p.valid ? __ldcs(x + i1) : 0.f);
+            }
+        }
+        if (p.window != nullptr) {  // STFT: frames overlap in the signal, the window table stays in L2
+            const float* w = p.window + n1;
+#pragma unroll
+            for (int q = 0; q < R; ++q) {
+                const int64_t j = t + q * T;
+                v[q].x *= __ldg(w + (2 * j) * p.n1);
+                v[q].y *= __ldg(w + (2 * j + 1) * p.n1);
             }
         }
         int parity = 0;
@@ -658,6 +668,8 @@ ma_status large_plan_init(ma_fft_plan* plan) {
 void large_plan_destroy(ma_fft_plan* plan) {
     if (plan->d_tw1) (void)cudaFree(plan->d_tw1);
     if (plan->d_twL) (void)cudaFree(plan->d_twL);
+    if (plan->d_frames) (void)cudaFree(plan->d_frames);
+    plan->d_frames = nullptr;
     if (plan->d_scratch) (void)cudaFree(plan->d_scratch);
     plan->d_tw1 = nullptr;
     plan->d_twL = nullptr;
@@ -718,6 +730,95 @@ ma_status launch_c2r_large(ma_fft_plan* plan, const float* in_a, const float* in
         p.out_a = out + done * n;
         MA_TRY(dispatch_rows(plan, p, true));
         MA_TRY(dispatch_cols(plan, p, true));
+    }
+    return MA_OK;
+}
+
+// Overlap-add of `count` inverse frames (frame f0 + i at frames[i*n]) into one signal's output:
+// out[o] += sum over those frames covering o of frame[o - f*hop] * window[o - f*hop], frames taken
+// in increasing order (the reference's loop order).  One thread per output sample of the span.
+__global__ void __launch_bounds__(256) ola_add_kernel(const float* __restrict__ frames, int64_t count, int64_t f0, int n,
+                                                      int hop, const float* __restrict__ window, float* __restrict__ out) {
+    const int64_t span = (count - 1) * hop + n;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < span; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t lo = i >= n ? (i - n) / hop + 1 : 0;
+        int64_t hi = i / hop;
+        if (hi > count - 1) hi = count - 1;
+        float acc = 0.f;
+        for (int64_t f = lo; f <= hi; ++f) {
+            const int64_t k = i - f * hop;
+            const float v = __ldcs(frames + f * n + k);
+            acc += window != nullptr ? v * __ldg(window + k) : v;
+        }
+        out[f0 * hop + i] += acc;
+    }
+}
+
+// out[o] /= max(sum of window^2 over the frames covering o, floor)   (STFT.swift:491-522)
+__global__ void __launch_bounds__(256) ola_normalise_kernel(float* __restrict__ out, int64_t out_len, const float* __restrict__ window,
+                                                            int n, int hop, int64_t frames, float floor) {
+    for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < out_len; o += (int64_t)gridDim.x * blockDim.x)
+        out[o] = out[o] / window_sum_at(window, o, n, hop, frames, floor);
+}
+
+static int stream_grid(ma_context* ctx, int64_t total) {
+    const int64_t want = (total + 255) / 256, cap = (int64_t)ctx->sm_count * 8;
+    return (int)(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
+ma_status launch_stft_large(ma_fft_plan* plan, const float* signals, int64_t signal_stride, int64_t frames,
+                            int64_t n_signals, float* out_a, float* out_b, float* mag, int mag_kind,
+                            float db_scale, int layout) {
+    const int64_t n = plan->n, half = n / 2;
+    for (int64_t s = 0; s < n_signals; ++s) {
+        for (int64_t f0 = 0; f0 < frames; f0 += plan->scratch_batch) {
+            const int64_t g = s * frames + f0;  // global frame index of the chunk's first frame
+            LargeParams p{};
+            fill_tables(plan, p);
+            p.batch = frames - f0 < plan->scratch_batch ? frames - f0 : plan->scratch_batch;
+            p.in = signals + s * signal_stride + f0 * plan->hop;
+            p.in_stride = plan->hop;
+            p.window = plan->d_window;
+            p.layout = layout;
+            p.mag_kind = mag_kind;
+            p.db_scale = db_scale;
+            if (layout == LAYOUT_FULL_SPLIT) {
+                p.out_a = out_a + g * n;
+                p.out_b = out_b + g * n;
+            } else {
+                p.out_a = out_a + g * 2 * (layout == LAYOUT_HALF_PACKED ? half : half + 1);
+            }
+            p.mag = mag ? mag + g * (half + 1) : nullptr;
+            MA_TRY(dispatch_cols(plan, p, false));
+            MA_TRY(dispatch_rows(plan, p, false));
+        }
+    }
+    return MA_OK;
+}
+
+ma_status launch_istft_large(ma_fft_plan* plan, const float* in_a, const float* in_b, int64_t frames,
+                             int64_t n_signals, float* out, int64_t out_stride, int64_t out_len, float floor,
+                             int layout) {
+    ma_context* ctx = plan->ctx;
+    const int64_t n = plan->n, half = n / 2;
+    if (plan->d_frames == nullptr)  // first overlap-add through this plan
+        MA_CUDA(cudaMalloc((void**)&plan->d_frames, sizeof(float) * (size_t)n * (size_t)plan->scratch_batch));
+    const int64_t per_frame = layout == LAYOUT_FULL_SPLIT ? n : 2 * (layout == LAYOUT_HALF_PACKED ? half : half + 1);
+    for (int64_t s = 0; s < n_signals; ++s) {
+        float* row = out + s * out_stride;
+        MA_CUDA(cudaMemsetAsync(row, 0, sizeof(float) * (size_t)out_len, ctx->stream));
+        for (int64_t f0 = 0; f0 < frames; f0 += plan->scratch_batch) {
+            const int64_t count = frames - f0 < plan->scratch_batch ? frames - f0 : plan->scratch_batch;
+            const int64_t g = s * frames + f0;
+            MA_TRY(launch_c2r_large(plan, in_a + g * per_frame, in_b ? in_b + g * per_frame : nullptr, plan->d_frames,
+                                    count, layout));
+            ola_add_kernel<<<stream_grid(ctx, (count - 1) * plan->hop + n), 256, 0, ctx->stream>>>(
+                plan->d_frames, count, f0, (int)n, plan->hop, plan->d_window, row);
+            MA_TRY(after_launch(ctx));
+        }
+        ola_normalise_kernel<<<stream_grid(ctx, out_len), 256, 0, ctx->stream>>>(row, out_len, plan->d_window, (int)n,
+                                                                                 plan->hop, frames, floor);
+        MA_TRY(after_launch(ctx));
     }
     return MA_OK;
 }

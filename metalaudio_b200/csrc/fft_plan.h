@@ -25,6 +25,7 @@ struct ma_fft_plan {
     float2* d_twL = nullptr;          // exp(-2 pi i j/N),  j < N (pass twiddles)
     float2* d_scratch = nullptr;      // (n2/2+1) x n1 complex per transform in a pass
     int64_t scratch_batch = 0;        // transforms the scratch holds
+    float* d_frames = nullptr;        // iSTFT above 8192 points: scratch_batch inverse frames (allocated on first use)
 };
 
 namespace ma {
@@ -44,6 +45,15 @@ ma_status launch_r2c_large(ma_fft_plan* plan, const float* in, float* out_a, flo
                            int mag_kind, float db_scale, int64_t batch, int layout);
 ma_status launch_c2r_large(ma_fft_plan* plan, const float* in_a, const float* in_b, float* out,
                            int64_t batch, int layout);
+// STFT / iSTFT above 8192 points (fft_large.cu): frames are read straight from the signal with
+// the window applied by the loader; inverse frames pass through d_frames and are overlap-added in
+// frame order, then normalised.
+ma_status launch_stft_large(ma_fft_plan* plan, const float* signals, int64_t signal_stride, int64_t frames,
+                            int64_t n_signals, float* out_a, float* out_b, float* mag, int mag_kind,
+                            float db_scale, int layout);
+ma_status launch_istft_large(ma_fft_plan* plan, const float* in_a, const float* in_b, int64_t frames,
+                             int64_t n_signals, float* out, int64_t out_stride, int64_t out_len, float floor,
+                             int layout);
 // Convolution through a large plan with the spectrum kept on chip (fft_large.cu).
 ma_status launch_spec_rows_large(ma_fft_plan* plan, const float* in, int64_t valid, float2* spec_rows);
 ma_status launch_conv_large(ma_fft_plan* plan, const float* in, int64_t valid, int64_t in_stride,

@@ -20,7 +20,10 @@ def interior(frames, n, hop, win, frac=1e-2):
 CASES = [(256, 64, 4000, "hann"), (512, 100, 5000, "hamming"), (64, 7, 700, "blackman"),
          (1024, 1024, 8192, "none"), (2048, 512, 40000, "hann"), (4096, 1024, 70000, "hann"),
          (8192, 2048, 70000, "hann"), (8, 2, 50, "hann"), (4, 1, 21, "hann"), (2, 1, 9, "none"),
-         (256, 255, 3001, "hann")]
+         (256, 255, 3001, "hann"),
+         # above 8192 points: the two-pass transforms with the window in the loader and a separate overlap-add
+         (16384, 4096, 100000, "hann"), (32768, 8192, 140000, "hamming"), (65536, 65536, 200000, "none"),
+         (16384, 1000, 60001, "blackman")]
 
 
 @pytest.mark.parametrize("n,hop,length,kind", CASES)
@@ -95,3 +98,26 @@ def test_stft_bit_stable(device):
     a = fft.istft(fft.stft(x))
     b = fft.istft(fft.stft(x))
     assert np.array_equal(a, b)
+
+
+def test_large_frames_many_signals_half_layout(device):
+    """More frames than one scratch chunk holds (16384-point frames: 760 per chunk) over two signals,
+    half-spectrum layout with magnitudes, through the batched API."""
+    from metalaudio_b200 import FFT, WindowType
+    n, hop, length = 16384, 2048, 2048 * 900 + 16384
+    rng = np.random.default_rng(12)
+    x = rng.uniform(-1, 1, (2, length)).astype(np.float32)
+    fft = FFT(device, FFT.Config(size=n, windowType=WindowType.hann, hopSize=hop))
+    spec, mag = fft.stftBatch(x, magnitude=True)
+    frames = (length - n) // hop + 1
+    assert spec.shape == (2, frames, n // 2 + 1) and frames > 760
+    w = rp.window("hann", n)
+    pick = [0, 1, 759, 760, 761, frames - 1]
+    for s_ in range(2):
+        fr = x[s_][np.array(pick)[:, None] * hop + np.arange(n)[None, :]].astype(np.float64) * w
+        ref = np.fft.rfft(fr, axis=-1)
+        assert o64.rel_rms(spec[s_, pick], ref) <= TOL
+        assert o64.rel_rms(mag[s_, pick], np.abs(ref)) <= TOL
+    y = fft.istftBatch(spec)
+    m = interior(frames, n, hop, w)
+    assert o64.rel_rms(y[:, m], x[:, :y.shape[1]][:, m]) <= TOL
