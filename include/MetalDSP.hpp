@@ -8,7 +8,9 @@
 //   Tensor                              Sources/MetalAudioKit/Buffers/Tensor.swift:59, :272, :325
 //   FFT, FFT::Config, WindowType, COLA  Sources/MetalDSP/FFT.swift:12-55, :155-348, :441-495, :818-919, :1780-1847
 //   FFT::stft / istft / batches         Sources/MetalDSP/STFT.swift:10-22, :40-128, :327-527
-//   Convolution (.partitioned)          Sources/MetalDSP/Convolution.swift:8-47, :112-125, :176-383, :529-775
+//   Convolution (.fft, .partitioned)    Sources/MetalDSP/Convolution.swift:8-47, :112-125, :176-383, :437-493, :529-775
+//   BiquadFilter, FilterBank            Sources/MetalDSP/Filters.swift:14-26, :65-96, :226-490, :515-716, :736-873
+//   stftPolar / istftPolar              the magnitude / phase split and rebuild of Sources/MetalNN/HTDemucs.swift:726-741, :795-812
 // Swift `throws` becomes C++ exceptions carrying the Swift case name and the same description.
 // There is one backend (CUDA) and no CPU fallback.
 #pragma once
@@ -348,6 +350,36 @@ public:
         return out;
     }
 
+    // STFT straight to magnitude and phase, frames x (N/2+1) each, row-major: the split the
+    // reference's STFT consumer does on the host (HTDemucs.swift:726-741), fused into the transform.
+    void stftPolar(const std::vector<float>& input, std::vector<float>& magnitude, std::vector<float>& phase) {
+        const int64_t f = frameCount((int64_t)input.size());
+        const size_t count = (size_t)f * (size_t)(config_.size / 2 + 1);
+        magnitude.resize(count);
+        phase.resize(count);
+        throwStatus(ma_stft_host(plan_, input.data(), (int64_t)input.size(), (int64_t)input.size(), 1, magnitude.data(),
+                                 phase.data(), nullptr, 0, 1.0f, MA_LAYOUT_HALF_POLAR),
+                    "stftPolar");
+    }
+
+    // iSTFT from magnitude and phase (polar rebuild + conjugate mirror of HTDemucs.swift:795-812, fused).
+    std::vector<float> istftPolar(const std::vector<float>& magnitude, const std::vector<float>& phase,
+                                  float windowFloorEpsilon = 1e-8f) {
+        const int64_t kh = config_.size / 2 + 1;
+        const int64_t f = (int64_t)magnitude.size() / kh;
+        if (f == 0) return {};
+        if (phase.size() != magnitude.size()) throw MetalAudioError("invalidConfiguration", "magnitude and phase sizes differ");
+        int64_t outLen = 0;
+        if (ma_istft_output_length(plan_, f, &outLen) != MA_OK) throw FFTError::istftOutputOverflow(f, config_.hopSize, config_.size);
+        std::vector<float> out((size_t)outLen);
+        float floor = windowFloorEpsilon;
+        if (floor < 1e-10f) floor = 1e-6f;
+        else if (floor > 0.1f) floor = 0.1f;
+        throwStatus(ma_istft_host(plan_, magnitude.data(), phase.data(), f, 1, out.data(), outLen, floor, MA_LAYOUT_HALF_POLAR),
+                    "istftPolar");
+        return out;
+    }
+
     // STFT.swift:94-128 / :327-373 on flat row-major batches.
     void forwardBatch(const std::vector<float>& inputs, int batch, std::vector<float>& outReal, std::vector<float>& outImag) {
         const int n = config_.size;
@@ -465,6 +497,211 @@ private:
     int64_t taps_ = 0, expected_ = 0, fftSize_ = 0;
     ma_pconv* pc_ = nullptr;
     ma_fftconv* fc_ = nullptr;
+};
+
+// ------------------------------------------------------------------------------ filters
+
+struct FilterError : std::runtime_error {  // Filters.swift:14-26
+    std::string errorCase, name;
+    float value = 0.f;
+    FilterError(std::string c, const std::string& msg, std::string n = "", float v = 0.f)
+        : std::runtime_error(msg), errorCase(std::move(c)), name(std::move(n)), value(v) {}
+    static FilterError unstable(const std::string& reason) { return FilterError("unstable", "Filter is unstable: " + reason); }
+    static FilterError invalidParameter(const std::string& name, float value, const std::string& requirement) {
+        return FilterError("invalidParameter",
+                           "Invalid parameter '" + name + "' with value " + std::to_string(value) + ": " + requirement, name, value);
+    }
+};
+
+class BiquadFilter {
+public:
+    enum class Kind { lowpass, highpass, bandpass, notch, allpass, peaking, lowshelf, highshelf };
+    struct FilterType {  // Filters.swift:68-77
+        Kind kind;
+        float gainDB;
+        static FilterType lowpass() { return {Kind::lowpass, 0.f}; }
+        static FilterType highpass() { return {Kind::highpass, 0.f}; }
+        static FilterType bandpass() { return {Kind::bandpass, 0.f}; }
+        static FilterType notch() { return {Kind::notch, 0.f}; }
+        static FilterType allpass() { return {Kind::allpass, 0.f}; }
+        static FilterType peaking(float gainDB) { return {Kind::peaking, gainDB}; }
+        static FilterType lowshelf(float gainDB) { return {Kind::lowshelf, gainDB}; }
+        static FilterType highshelf(float gainDB) { return {Kind::highshelf, gainDB}; }
+    };
+    struct Coefficients {  // Filters.swift:80-96: a0 divided out, identity by default
+        float b0 = 1.f, b1 = 0.f, b2 = 0.f, a1 = 0.f, a2 = 0.f;
+    };
+
+    explicit BiquadFilter(AudioDevice& device, int channels = 1) : device_(device), channels_(channels) {
+        throwStatus(ma_biquad_create(device.handle(), channels, 1, &bq_), "BiquadFilter");
+        upload();
+    }
+    ~BiquadFilter() { ma_biquad_destroy(bq_); }
+    BiquadFilter(const BiquadFilter&) = delete;
+    BiquadFilter& operator=(const BiquadFilter&) = delete;
+
+    // Coefficient design and validation in the order of Filters.swift:346-482 (double precision
+    // cookbook forms, rounded to float after the division by a0).
+    static Coefficients design(FilterType type, float frequency, float sampleRate, float q = 0.7071067811865476f) {
+        if (!(sampleRate > 0)) throw FilterError::invalidParameter("sampleRate", sampleRate, "must be > 0");
+        const float nyquist = sampleRate / 2.0f;
+        if (!(frequency > 0 && frequency < nyquist))
+            throw FilterError::invalidParameter("frequency", frequency, "must be > 0 and < " + std::to_string(nyquist) + " Hz (Nyquist)");
+        if (!(q > 0)) throw FilterError::invalidParameter("q", q, "must be > 0");
+        if (!std::isfinite(frequency) || !std::isfinite(sampleRate) || !std::isfinite(q))
+            throw FilterError::invalidParameter("input", 0.f, "parameters must not be NaN or Infinite");
+        const double pi = 3.14159265358979323846;
+        const double w = 2.0 * pi * (double)frequency / (double)sampleRate, sn = std::sin(w), cs = std::cos(w);
+        const double al = sn / (2.0 * (double)q);
+        const double A = std::pow(10.0, (double)type.gainDB / 40.0), rt = 2.0 * std::sqrt(A) * al;
+        double b[3], a[3];
+        auto set = [](double* d, double x, double y, double z) { d[0] = x; d[1] = y; d[2] = z; };
+        switch (type.kind) {
+            case Kind::lowpass: set(b, (1 - cs) / 2, 1 - cs, (1 - cs) / 2); set(a, 1 + al, -2 * cs, 1 - al); break;
+            case Kind::highpass: set(b, (1 + cs) / 2, -(1 + cs), (1 + cs) / 2); set(a, 1 + al, -2 * cs, 1 - al); break;
+            case Kind::bandpass: set(b, al, 0, -al); set(a, 1 + al, -2 * cs, 1 - al); break;
+            case Kind::notch: set(b, 1, -2 * cs, 1); set(a, 1 + al, -2 * cs, 1 - al); break;
+            case Kind::allpass: set(b, 1 - al, -2 * cs, 1 + al); set(a, 1 + al, -2 * cs, 1 - al); break;
+            case Kind::peaking: set(b, 1 + al * A, -2 * cs, 1 - al * A); set(a, 1 + al / A, -2 * cs, 1 - al / A); break;
+            case Kind::lowshelf:
+                set(b, A * ((A + 1) - (A - 1) * cs + rt), 2 * A * ((A - 1) - (A + 1) * cs), A * ((A + 1) - (A - 1) * cs - rt));
+                set(a, (A + 1) + (A - 1) * cs + rt, -2 * ((A - 1) + (A + 1) * cs), (A + 1) + (A - 1) * cs - rt);
+                break;
+            case Kind::highshelf:
+                set(b, A * ((A + 1) + (A - 1) * cs + rt), -2 * A * ((A - 1) + (A + 1) * cs), A * ((A + 1) + (A - 1) * cs - rt));
+                set(a, (A + 1) - (A - 1) * cs + rt, 2 * ((A - 1) - (A + 1) * cs), (A + 1) - (A - 1) * cs - rt);
+                break;
+        }
+        const float a0f = (float)a[0];
+        if (!(std::fabs(a0f) > 1e-6f))
+            throw FilterError::invalidParameter("a0 (computed)", a0f, "denominator coefficient a0 must not be near zero (|a0| > 1e-6)");
+        Coefficients c;
+        c.b0 = (float)(b[0] / a[0]); c.b1 = (float)(b[1] / a[0]); c.b2 = (float)(b[2] / a[0]);
+        c.a1 = (float)(a[1] / a[0]); c.a2 = (float)(a[2] / a[0]);
+        if (!std::isfinite(c.b0) || !std::isfinite(c.b1) || !std::isfinite(c.b2) || !std::isfinite(c.a1) || !std::isfinite(c.a2))
+            throw FilterError::invalidParameter("coefficients", 0.f, "normalized coefficients must not be NaN or Infinite");
+        if (!(std::fabs(c.a2) < 1.0f)) throw FilterError::invalidParameter("a2 (stability)", c.a2, "|a2| must be < 1 for filter stability");
+        if (!(std::fabs(c.a1) < 1.0f + c.a2))
+            throw FilterError::invalidParameter("a1 (stability)", c.a1, "|a1| must be < 1 + a2 for filter stability");
+        return c;
+    }
+
+    // Filters.swift:346-490: a failed validation leaves the previous coefficients in place.
+    void configure(FilterType type, float frequency, float sampleRate, float q = 0.7071067811865476f) {
+        coefficients_ = design(type, frequency, sampleRate, q);
+        upload();
+    }
+    const Coefficients& currentCoefficients() const { return coefficients_; }
+    bool isStable() const {
+        return std::isfinite(coefficients_.a1) && std::isfinite(coefficients_.a2) && std::fabs(coefficients_.a2) < 1.0f &&
+               std::fabs(coefficients_.a1) < 1.0f + coefficients_.a2;
+    }
+    void validateStability() const {  // Filters.swift:688-716
+        if (!std::isfinite(coefficients_.a1) || !std::isfinite(coefficients_.a2))
+            throw FilterError::unstable("coefficients contain NaN or Infinite values, filter is in invalid state");
+        if (!(std::fabs(coefficients_.a2) < 1.0f)) throw FilterError::unstable("a2 coefficient magnitude >= 1, poles outside unit circle");
+        if (!(std::fabs(coefficients_.a1) < 1.0f + coefficients_.a2)) throw FilterError::unstable("a1 coefficient violates stability condition |a1| < 1 + a2");
+    }
+
+    // process(input:) (Filters.swift:555-593): channels x L row-major in, same shape out; state carries over.
+    std::vector<float> process(const std::vector<float>& input) {
+        std::vector<float> out(input.size());
+        if (input.empty()) return out;
+        const int64_t len = (int64_t)input.size() / channels_;
+        throwStatus(ma_biquad_process_host(bq_, input.data(), len, out.data(), len, len), "process");
+        return out;
+    }
+    float process(float sample) {  // Filters.swift:515-537
+        float y = 0.f;
+        throwStatus(ma_biquad_process_host(bq_, &sample, 1, &y, 1, 1), "process");
+        return y;
+    }
+    void reset() { throwStatus(ma_biquad_reset(bq_), "reset"); }
+
+private:
+    void upload() {
+        const float c[5] = {coefficients_.b0, coefficients_.b1, coefficients_.b2, coefficients_.a1, coefficients_.a2};
+        throwStatus(ma_biquad_set_coefficients(bq_, c, 1, nullptr), "configure");
+    }
+    AudioDevice& device_;
+    int channels_;
+    Coefficients coefficients_;
+    ma_biquad* bq_ = nullptr;
+};
+
+class FilterBank {  // Filters.swift:736-873
+public:
+    FilterBank(AudioDevice& device, int bandCount) : device_(device), bands_(bandCount), coeffs_((size_t)(bandCount > 0 ? bandCount : 0)) {}
+    ~FilterBank() {
+        ma_biquad_destroy(series_);
+        ma_biquad_destroy(parallel_);
+    }
+    FilterBank(const FilterBank&) = delete;
+    FilterBank& operator=(const FilterBank&) = delete;
+
+    void configureAsEQ(float lowFreq, float highFreq, float sampleRate, float q = 1.414f) {
+        if (bands_ < 2) throw FilterError::invalidParameter("bandCount", (float)bands_, "must be >= 2 for logarithmic band spacing");
+        if (!(lowFreq > 0)) throw FilterError::invalidParameter("lowFreq", lowFreq, "must be > 0");
+        if (!(highFreq > 0 && highFreq > lowFreq)) throw FilterError::invalidParameter("highFreq", highFreq, "must be > 0 and > lowFreq");
+        const float logLow = std::log10(lowFreq), logHigh = std::log10(highFreq), step = (logHigh - logLow) / (float)(bands_ - 1);
+        for (int i = 0; i < bands_; ++i) {
+            coeffs_[(size_t)i] = BiquadFilter::design(BiquadFilter::FilterType::peaking(0.f), std::pow(10.0f, logLow + (float)i * step), sampleRate, q);
+            dirty_ = true;
+        }
+    }
+    void setBandGain(int band, float gainDB, float frequency, float sampleRate, float q = 1.414f) {
+        if (band < 0 || band >= bands_) throw FilterError::invalidParameter("band", (float)band, "must be in range 0..<" + std::to_string(bands_));
+        coeffs_[(size_t)band] = BiquadFilter::design(BiquadFilter::FilterType::peaking(gainDB), frequency, sampleRate, q);
+        dirty_ = true;
+    }
+    std::vector<float> processSeries(const std::vector<float>& input) {  // one cascade of bandCount sections
+        if (input.empty() || bands_ <= 0) return input;
+        prepare();
+        std::vector<float> out(input.size());
+        throwStatus(ma_biquad_process_host(series_, input.data(), (int64_t)input.size(), out.data(), (int64_t)input.size(), (int64_t)input.size()), "processSeries");
+        return out;
+    }
+    std::vector<float> processParallel(const std::vector<float>& input) {  // every band on the same input, mixed with 1/bandCount
+        std::vector<float> out(input.size(), 0.f);
+        if (input.empty() || bands_ <= 0) return out;
+        prepare();
+        const int64_t n = (int64_t)input.size();
+        Tensor in(device_, {n}), bands(device_, {(int64_t)bands_, n}), mix(device_, {n});
+        in.copy(input);
+        throwStatus(ma_biquad_process_dev(parallel_, in.devicePointer(), 0, bands.devicePointer(), n, n), "processParallel");
+        throwStatus(ma_channel_mix_dev(device_.handle(), bands.devicePointer(), bands_, n, n, 1.0f / (float)bands_, mix.devicePointer()), "processParallel");
+        return mix.toArray();
+    }
+    void reset() {
+        if (series_) throwStatus(ma_biquad_reset(series_), "reset");
+        if (parallel_) throwStatus(ma_biquad_reset(parallel_), "reset");
+    }
+
+private:
+    void prepare() {
+        if (series_ == nullptr) {
+            throwStatus(ma_biquad_create(device_.handle(), 1, bands_, &series_), "FilterBank");
+            throwStatus(ma_biquad_create(device_.handle(), bands_, 1, &parallel_), "FilterBank");
+        }
+        if (!dirty_) return;
+        std::vector<float> c((size_t)bands_ * 5);
+        std::vector<int32_t> map((size_t)bands_);
+        for (int i = 0; i < bands_; ++i) {
+            const auto& k = coeffs_[(size_t)i];
+            const float v[5] = {k.b0, k.b1, k.b2, k.a1, k.a2};
+            std::copy(v, v + 5, c.begin() + 5 * i);
+            map[(size_t)i] = i;
+        }
+        throwStatus(ma_biquad_set_coefficients(series_, c.data(), 1, nullptr), "FilterBank");
+        throwStatus(ma_biquad_set_coefficients(parallel_, c.data(), bands_, map.data()), "FilterBank");
+        dirty_ = false;
+    }
+    AudioDevice& device_;
+    int bands_;
+    std::vector<BiquadFilter::Coefficients> coeffs_;
+    ma_biquad* series_ = nullptr;
+    ma_biquad* parallel_ = nullptr;
+    bool dirty_ = true;
 };
 
 }  // namespace metalaudio

@@ -887,6 +887,13 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
     float2 twb[tw_base_count<FftPlanRev<M>>()];
     float2 wherm[R / 2 + 1];
     c2r_load_tw_regs<M>(p, t, twb, wherm);
+    // reciprocal window sums of the samples an interior frame completes (positions modulo hop)
+    constexpr int HN = OVT > 0 ? R / OVT : 1;
+    float2 ninv[HN];
+#pragma unroll
+    for (int q = 0; q < HN; ++q)
+        ninv[q] = (OVT > 0 && normalise) ? MA_LDG(reinterpret_cast<const float2*>(p.norm_mid_inv + 2 * (t + q * T)))
+                                         : make_float2(1.f, 1.f);
 
     // This CTA owns the global frames [G0, G1) (frame G = signal*F + f) and the output samples
     // they complete.  It starts up to `reach` frames early inside the same signal to rebuild the
@@ -948,6 +955,27 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
         // every sample this frame completes has all its overlapping frames present
         const bool interior = !last && start >= (int64_t)(N - hop);
         float* out = p.out + s * p.out_signal_stride + start;
+        if (OVT > 0 && emit && interior && normalise) {
+            // The common frame (all overlapping frames present, inside this CTA's range): no
+            // per-slot decisions, reciprocals of the window sum already in registers.
+            constexpr int H = OVT > 0 ? R / OVT : 1;
+#pragma unroll
+            for (int q = 0; q < R; ++q) {
+                float2* slot = ring + ((q + rot) & (R - 1)) * T + t;
+                float2 acc = make_float2(v[q].y * wreg[q].x, v[q].x * wreg[q].y);
+                if (q < R - H) {  // slot already holds earlier frames
+                    const float2 old = *slot;
+                    acc.x += old.x;
+                    acc.y += old.y;
+                }
+                if (q < H) {  // complete after this frame
+                    *reinterpret_cast<float2*>(out + 2 * (t + q * T)) = make_float2(acc.x * ninv[q].x, acc.y * ninv[q].y);
+                } else {
+                    *slot = acc;
+                }
+            }
+            continue;
+        }
 #pragma unroll
         for (int q = 0; q < R; ++q) {
             float2* slot = ring + ((q + rot) & (R - 1)) * T + t;

@@ -41,6 +41,22 @@ static void host_logic() {
     CHECK(std::string(FFTError::sizeNotPowerOf2(300).what()).find("300") != std::string::npos);
     CHECK(FFTError::invalidHopSize(0, 256).errorCase == "invalidHopSize");
     CHECK(ConvolutionError::emptyKernel().errorCase == "emptyKernel");
+    // biquad coefficient design needs no device: DC gain 1 for a low-pass, zero at DC for a high-pass,
+    // 0 dB peaking is an identity; validation errors name the parameter
+    const auto lp = BiquadFilter::design(BiquadFilter::FilterType::lowpass(), 1000.f, 44100.f);
+    CHECK(std::fabs((lp.b0 + lp.b1 + lp.b2) / (1.0 + lp.a1 + lp.a2) - 1.0) < 1e-4);
+    const auto hp = BiquadFilter::design(BiquadFilter::FilterType::highpass(), 1000.f, 44100.f);
+    CHECK(std::fabs(hp.b0 + hp.b1 + hp.b2) < 1e-6);
+    const auto pk = BiquadFilter::design(BiquadFilter::FilterType::peaking(0.f), 1000.f, 44100.f);
+    CHECK(std::fabs(pk.b0 - 1.f) < 1e-6f && std::fabs(pk.b1 - pk.a1) < 1e-6f && std::fabs(pk.b2 - pk.a2) < 1e-6f);
+    bool caught = false;
+    try {
+        BiquadFilter::design(BiquadFilter::FilterType::lowpass(), 1000.f, 44100.f, 0.f);
+    } catch (const FilterError& e) {
+        caught = e.errorCase == "invalidParameter" && e.name == "q";
+    }
+    CHECK(caught);
+    CHECK(std::string(FilterError::unstable("x").what()) == "Filter is unstable: x");
 }
 
 static void no_device() {
@@ -162,6 +178,50 @@ static void gpu_tests() {
         threw = e.errorCase == "inputSizeMismatch" && std::string(e.what()).find("circular convolution") != std::string::npos;
     }
     CHECK(threw);
+    // magnitude / phase STFT and its inverse reproduce the signal away from the ends
+    {
+        FFT pf(dev, FFT::Config(1024, false, WindowType::hann, 256));
+        std::vector<float> sig(16384), mg, ph;
+        for (auto& v : sig) v = nd(rng);
+        pf.stftPolar(sig, mg, ph);
+        CHECK(mg.size() == (size_t)((16384 - 1024) / 256 + 1) * 513 && ph.size() == mg.size());
+        const std::vector<float> back = pf.istftPolar(mg, ph);
+        double err = 0, ref = 0;
+        for (size_t i = 1024; i + 1024 < back.size(); ++i) {
+            err += (back[i] - sig[i]) * (double)(back[i] - sig[i]);
+            ref += sig[i] * (double)sig[i];
+        }
+        CHECK(std::sqrt(err / ref) < 1e-5);
+    }
+    // biquad: unity DC gain of a low-pass, streaming equals one call, filter bank of 0 dB bands is an identity
+    {
+        BiquadFilter lp(dev);
+        lp.configure(BiquadFilter::FilterType::lowpass(), 1000.0f, 44100.0f, 0.707f);
+        const std::vector<float> ones(20000, 1.0f);
+        const std::vector<float> y = lp.process(ones);
+        CHECK(std::fabs(y.back() - 1.0f) < 1e-4f && lp.isStable());
+        lp.reset();
+        std::vector<float> parts = lp.process(std::vector<float>(ones.begin(), ones.begin() + 9000));
+        const std::vector<float> rest = lp.process(std::vector<float>(ones.begin() + 9000, ones.end()));
+        parts.insert(parts.end(), rest.begin(), rest.end());
+        for (size_t i = 0; i < y.size(); i += 97) CHECK(std::fabs(parts[i] - y[i]) < 1e-5f);
+        threw = false;
+        try {
+            lp.configure(BiquadFilter::FilterType::lowpass(), 30000.0f, 44100.0f);
+        } catch (const FilterError& e) {
+            threw = e.errorCase == "invalidParameter" && e.name == "frequency";
+        }
+        CHECK(threw);
+        FilterBank bank(dev, 5);
+        bank.configureAsEQ(100.0f, 10000.0f, 44100.0f);
+        std::vector<float> noise(5000);
+        for (auto& v : noise) v = nd(rng);
+        const std::vector<float> flat = bank.processSeries(noise), par = bank.processParallel(noise);
+        for (size_t i = 0; i < noise.size(); i += 13) {
+            CHECK(std::fabs(flat[i] - noise[i]) < 1e-4f);
+            CHECK(std::fabs(par[i] - noise[i]) < 1e-4f);
+        }
+    }
     dev.markDeviceLost();
     threw = false;
     try {
