@@ -34,6 +34,19 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32
         : "memory");
 }
 
+// Several copies on one phase: one thread arms the barrier once for the total and then starts each
+// copy with bulk_copy_part.
+__device__ __forceinline__ void bulk_barrier_expect(uint64_t* bar, uint32_t total_bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(total_bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_part(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
 // Waits for the phase with the given parity; false when the poll limit ran out.
 __device__ __forceinline__ bool bulk_barrier_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t b = smem_u32(bar);

@@ -380,6 +380,7 @@ struct C2RParams {
     const float* norm_mid_inv;  // iSTFT: their reciprocals
     int32_t* error_flag;        // set to 1 when a bounded wait ran out
     int32_t dependent_launch;   // launched with programmatic stream serialization (see fft_small.cu)
+    const float2* mul;          // HALF_INTERLEAVED input only: every bin is multiplied by mul[k] on load (N/2+1 values), or nullptr
     const float2* twM;          // stage tables: FftPlanRev<M> when plan_pairable<M>(), else FftPlan<M>
     const float2* twN;
 };
@@ -432,16 +433,36 @@ MA_HD void c2r_load_pair(const C2RParams& p, const float2* x, int64_t g, int k, 
     } else if (layout == LAYOUT_HALF_POLAR) {
         const float* mg = p.in_a + g * (int64_t)(M + 1);
         const float* ph = p.in_b + g * (int64_t)(M + 1);
+        float ma, pa, mb, pb;
+        if (STAGED) {
+            // x: M staged magnitudes followed by M staged phases, each copied from the 16-byte
+            // boundary at or below its row (rows of M+1 floats start 4*(g mod 4) bytes past one),
+            // so bin i sits at [i + shift] and the last shift bins plus bin M come from HBM.
+            const float* sm = reinterpret_cast<const float*>(x);
+            const int shift = (int)(g & 3), lim = M - shift;
+            ma = k < lim ? sm[k + shift] : MA_LDG(mg + k);
+            pa = k < lim ? sm[M + k + shift] : MA_LDG(ph + k);
+            mb = km < lim ? sm[km + shift] : MA_LDG(mg + km);
+            pb = km < lim ? sm[M + km + shift] : MA_LDG(ph + km);
+        } else {
+            ma = MA_LDG(mg + k);
+            pa = MA_LDG(ph + k);
+            mb = MA_LDG(mg + km);
+            pb = MA_LDG(ph + km);
+        }
         float sa, ca, sb, cb;
-        fast_sincos(MA_LDG(ph + k), &sa, &ca);
-        fast_sincos(MA_LDG(ph + km), &sb, &cb);
-        const float ma = MA_LDG(mg + k), mb = MA_LDG(mg + km);
+        fast_sincos(pa, &sa, &ca);
+        fast_sincos(pb, &sb, &cb);
         a = make_float2(ma * ca, k == 0 ? 0.f : ma * sa);
         b = make_float2(mb * cb, k == 0 ? 0.f : mb * sb);
     } else {
         a = STAGED ? x[k] : MA_LDG(x + k);
         if (STAGED && k == 0) b = MA_LDG(xg + M);  // bin M is not staged
         else b = STAGED ? x[km] : MA_LDG(x + km);
+        if (LAYOUT < 0 && p.mul != nullptr) {  // frequency-domain product fused into the inverse (FFT convolution)
+            a = cmul(a, MA_LDG(p.mul + k));
+            b = cmul(b, MA_LDG(p.mul + km));
+        }
         if (k == 0) {
             a.y = 0.f;
             b.y = 0.f;
@@ -847,6 +868,9 @@ inline bool istft_fast_ok(const C2RParams& p) {
     } else {
         constexpr int R = FftPlan<M>::R, T = FftPlan<M>::T;
         if (p.layout != LAYOUT_HALF_INTERLEAVED && p.layout != LAYOUT_HALF_PACKED && p.layout != LAYOUT_HALF_POLAR) return false;
+        // staged magnitude / phase rows are copied from 16-byte boundaries: the arrays must start on one
+        if (p.layout == LAYOUT_HALF_POLAR && (M % 4 != 0 || ((reinterpret_cast<uintptr_t>(p.in_a) | reinterpret_cast<uintptr_t>(p.in_b)) & 15) != 0))
+            return false;
         if (p.n_partials > 1 || p.hop <= 0 || p.hop % (2 * T) != 0) return false;
         const int h = p.hop / (2 * T);
         if (h > R || R % h != 0) return false;
@@ -860,12 +884,26 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
     using P = FftPlan<M>;
     using SH = IstftFastShape<M>;
     constexpr int R = P::R, T = P::T, N = 2 * M;
-    // The complex layouts stage each spectrum row with a bulk copy; magnitude + phase rows (two
-    // arrays, 4-byte granularity) are read with plain loads.
-    constexpr bool STAGED = LAYOUT != LAYOUT_HALF_POLAR;
+    // Every layout stages the next frame's spectrum row(s) with bulk copies: one copy of the complex
+    // row, or one each of the magnitude and the phase row.
+    constexpr bool STAGED = true;
+    constexpr bool POLAR = LAYOUT == LAYOUT_HALF_POLAR;
     float2* ring = smem + SH::EXCH_ELEMS;
     float2* stage = ring + SH::RING;
     uint64_t* bar = reinterpret_cast<uint64_t*>(stage + SH::ROW);
+    auto start_copy = [&](int64_t s_, int64_t f_) {  // called by thread 0
+        if constexpr (POLAR) {
+            const int64_t g_ = s_ * p.frames_per_signal + f_;
+            const int shift = (int)(g_ & 3);
+            float* dst = reinterpret_cast<float*>(stage);
+            cta.bulk_expect(bar, 2u * M * (uint32_t)sizeof(float));
+            cta.bulk_part(dst, p.in_a + g_ * (int64_t)(M + 1) - shift, M * (uint32_t)sizeof(float), bar);
+            cta.bulk_part(dst + M, p.in_b + g_ * (int64_t)(M + 1) - shift, M * (uint32_t)sizeof(float), bar);
+        } else {
+            const StagedRow r_ = staged_row<M>(p, s_, f_);
+            cta.bulk_copy(stage, r_.src, r_.bytes, bar);
+        }
+    };
     const int t = cta.tid();
     int parity = 0;
     uint32_t phase = 0;
@@ -916,10 +954,7 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
 #pragma unroll
     for (int q = 0; q < R; ++q) ring[q * T + t] = make_float2(0.f, 0.f);
     cta.sync();
-    if (STAGED && t == 0) {
-        const StagedRow r0 = staged_row<M>(p, s, f);
-        cta.bulk_copy(stage, r0.src, r0.bytes, bar);
-    }
+    if (STAGED && t == 0) start_copy(s, f);
 
     for (; G < G1; ++G, ++f) {
         if (f == F) {  // next signal: nothing overlaps across signals
@@ -930,18 +965,22 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
         }
         float2 v[R];
         if constexpr (STAGED) {
-            const StagedRow r = staged_row<M>(p, s, f);
             if (!cta.bulk_wait(bar, phase) && p.error_flag != nullptr) *p.error_flag = 1;
             phase ^= 1;
             auto issue_next = [&]() {
                 if (t == 0 && G + 1 < G1) {
                     const bool wrap = f + 1 == F;
-                    const StagedRow rn = staged_row<M>(p, wrap ? s + 1 : s, wrap ? 0 : f + 1);
-                    cta.bulk_copy(stage, rn.src, rn.bytes, bar);
+                    start_copy(wrap ? s + 1 : s, wrap ? 0 : f + 1);
                 }
             };
-            c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1>(
-                p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage + r.shift, issue_next, r.row);
+            if constexpr (POLAR) {
+                c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1>(
+                    p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage, issue_next, nullptr);
+            } else {
+                const StagedRow r = staged_row<M>(p, s, f);
+                c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1>(
+                    p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage + r.shift, issue_next, r.row);
+            }
         } else {
             c2r_frame<M, LAYOUT, true, Cta, false, NoHook, SH::EXCH == 1>(p, true, s, f, G, t, smem, SH::ELEMS, parity,
                                                                          v, cta, twb, wherm);

@@ -14,6 +14,10 @@ struct DevCta {
     __device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
         bulk_copy_g2s(dst, src, bytes, bar);
     }
+    __device__ __forceinline__ void bulk_expect(uint64_t* bar, uint32_t total_bytes) { bulk_barrier_expect(bar, total_bytes); }
+    __device__ __forceinline__ void bulk_part(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+        bulk_copy_part(dst, src, bytes, bar);
+    }
     __device__ __forceinline__ bool bulk_wait(uint64_t* bar, uint32_t parity) { return bulk_barrier_wait(bar, parity); }
 };
 
@@ -170,7 +174,7 @@ template <int M>
 static ma_status launch_c2r_variant(ma_fft_plan* plan, const C2RParams& p) {
     if constexpr (plan_pairable<M>()) {
         // plain batched inverse of a paired plan: layout fixed at compile time
-        if (p.tail == nullptr && p.n_partials <= 1) {
+        if (p.tail == nullptr && p.n_partials <= 1 && p.mul == nullptr) {
             if (p.layout == LAYOUT_HALF_INTERLEAVED) return launch_c2r_t<M, LAYOUT_HALF_INTERLEAVED>(plan, p);
             if (p.layout == LAYOUT_HALF_PACKED) return launch_c2r_t<M, LAYOUT_HALF_PACKED>(plan, p);
             if (p.layout == LAYOUT_FULL_SPLIT) return launch_c2r_t<M, LAYOUT_FULL_SPLIT>(plan, p);

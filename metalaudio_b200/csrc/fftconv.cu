@@ -4,10 +4,11 @@
 //   fft_size = next power of two >= expected_input + taps - 1
 //   y = IFFT( FFT(zero-padded x) * FFT(zero-padded h) ),  fft_size samples per signal
 //
-// Built on the library's real-input transforms.  Up to 8192 points the input rows are zero-padded
-// into a work buffer, transformed to half spectra, multiplied bin by bin with the kernel's half
-// spectrum (both are spectra of real signals, so the product's upper half is the conjugate mirror
-// and never has to exist), and transformed back with the 1/N scale.  Above 8192 points the
+// Built on the library's real-input transforms.  Up to 8192 points one kernel transforms the input
+// rows to half spectra (zero padding applied by its loader) and a second one transforms back with
+// the bin-by-bin product by the kernel's half spectrum fused into its loads (both are spectra of
+// real signals, so the product's upper half is the conjugate mirror and never has to exist) and
+// the 1/N scale.  Above 8192 points the
 // two-pass transforms are fused around the product: columns forward (zero padding applied by the
 // loader), then one kernel that runs the row transform, the product and the inverse row transform
 // in place on the L2-resident pass data, then columns inverse; HBM sees the input and the output
@@ -22,7 +23,7 @@ struct ma_fftconv {
     ma_fft_plan* plan = nullptr;
     int64_t taps = 0, expected = 0, n = 0;
     int32_t max_signals = 0;
-    float* d_padded = nullptr;   // [max_signals][n]
+    float* d_padded = nullptr;   // [n]: the zero-padded kernel, small plans only
     float2* d_spec = nullptr;    // [max_signals][n/2+1]
     float2* d_kernel = nullptr;  // [n/2+1], or for large plans the spectrum in pass-2 row order
     bool large = false;
@@ -39,15 +40,6 @@ __global__ void __launch_bounds__(256) fftconv_pad_kernel(const float* __restric
     }
 }
 
-// spec[s][k] *= kernel[k] for the n/2+1 bins of every signal.
-__global__ void __launch_bounds__(256) fftconv_multiply_kernel(float2* __restrict__ spec, const float2* __restrict__ kernel,
-                                                               int64_t bins, int64_t total) {
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const float2 a = spec[i], b = __ldg(kernel + i % bins);
-        spec[i] = make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
-    }
-}
-
 static int grid_for(ma_context* ctx, int64_t total) {
     const int64_t want = (total + 255) / 256, cap = (int64_t)ctx->sm_count * 8;
     return (int)(want < cap ? (want > 0 ? want : 1) : cap);
@@ -58,16 +50,34 @@ static ma_status fftconv_run(ma_fftconv* fc, const float* d_in, int64_t len, int
     ma_context* ctx = fc->ctx;
     const int64_t n = fc->n, bins = n / 2 + 1;
     if (fc->large) return launch_conv_large(fc->plan, d_in, len, in_stride, fc->d_kernel, d_out, n_signals);
-    fftconv_pad_kernel<<<grid_for(ctx, n * n_signals), 256, 0, ctx->stream>>>(d_in, len, in_stride, fc->d_padded, n,
-                                                                               n * n_signals);
-    MA_TRY(after_launch(ctx));
-    MA_TRY(ma_fft_forward_dev(fc->plan, fc->d_padded, reinterpret_cast<float*>(fc->d_spec), nullptr, nullptr, 0, 1.f,
-                              n_signals, MA_LAYOUT_HALF_INTERLEAVED));
-    fftconv_multiply_kernel<<<grid_for(ctx, bins * n_signals), 256, 0, ctx->stream>>>(fc->d_spec, fc->d_kernel, bins,
-                                                                                      bins * n_signals);
-    MA_TRY(after_launch(ctx));
-    return ma_fft_inverse_dev(fc->plan, reinterpret_cast<const float*>(fc->d_spec), nullptr, d_out, n_signals,
-                              MA_LAYOUT_HALF_INTERLEAVED);
+    // forward transforms with the zero padding applied by the loader, straight from the caller's rows
+    R2CParams f{};
+    f.in = d_in;
+    f.signal_stride = in_stride;
+    f.frames_per_signal = 1;
+    f.total_frames = n_signals;
+    f.signal_len = len;
+    f.hop = (int32_t)n;
+    f.frame_valid = (int32_t)(len < n ? len : n);
+    f.out_a = reinterpret_cast<float*>(fc->d_spec);
+    f.out_signal_stride = bins;
+    f.out_frame_stride = 0;
+    f.layout = LAYOUT_HALF_INTERLEAVED;
+    f.mag_kind = MAG_NONE;
+    MA_TRY(launch_r2c_small(fc->plan, f));
+    // inverse transforms with the product by the kernel spectrum fused into their loads
+    C2RParams c{};
+    c.in_a = reinterpret_cast<const float*>(fc->d_spec);
+    c.in_frame_stride = bins;
+    c.in_signal_stride = 0;
+    c.frames_per_signal = n_signals;
+    c.n_signals = 1;
+    c.layout = LAYOUT_HALF_INTERLEAVED;
+    c.hop = (int32_t)n;
+    c.out = d_out;
+    c.out_signal_stride = 0;
+    c.mul = fc->d_kernel;
+    return launch_c2r_small(fc->plan, c);
 }
 
 }  // namespace ma
@@ -103,7 +113,7 @@ ma_status ma_fftconv_create(ma_context* ctx, const float* kernel, int64_t taps, 
     if (st == MA_OK) {
         cudaError_t e = cudaMalloc((void**)&fc->d_kernel, sizeof(float2) * (size_t)kernel_elems);
         if (e == cudaSuccess && !fc->large) {
-            e = cudaMalloc((void**)&fc->d_padded, sizeof(float) * (size_t)n * max_signals);
+            e = cudaMalloc((void**)&fc->d_padded, sizeof(float) * (size_t)n);
             if (e == cudaSuccess) e = cudaMalloc((void**)&fc->d_spec, sizeof(float2) * (size_t)bins * max_signals);
         }
         if (e != cudaSuccess) st = cuda_fail(e);

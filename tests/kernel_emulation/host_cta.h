@@ -26,6 +26,18 @@ struct HostCta {
         memcpy(dst, src, bytes);
         __atomic_add_fetch((unsigned long long*)bar, 1ull, __ATOMIC_SEQ_CST);
     }
+    // Several copies on one phase: the parts are copied at once and the count is bumped when the
+    // bytes announced by bulk_expect have all arrived (one thread issues them, in program order).
+    unsigned pending_ = 0;
+    void bulk_expect(void* bar, unsigned total_bytes) {
+        (void)bar;
+        pending_ = total_bytes;
+    }
+    void bulk_part(void* dst, const void* src, unsigned bytes, void* bar) {
+        memcpy(dst, src, bytes);
+        pending_ -= bytes;
+        if (pending_ == 0) __atomic_add_fetch((unsigned long long*)bar, 1ull, __ATOMIC_SEQ_CST);
+    }
     bool bulk_wait(void* bar, unsigned parity) {
         for (long i = 0; i < (1L << 21); ++i) {
             if ((__atomic_load_n((unsigned long long*)bar, __ATOMIC_SEQ_CST) & 1ull) == (unsigned long long)(parity ^ 1u))

@@ -133,3 +133,37 @@ def test_standalone_glue_kernels(device):
     t.copy(vals)
     toDecibels(device, t, reference=0.0, minDB=-60.0)
     assert np.all(t.toArray() == -60.0)
+
+
+def test_istft_polar_unaligned_arrays_take_the_plain_path(device, lib):
+    """Magnitude / phase arrays that do not start on a 16-byte boundary cannot be staged with bulk
+    copies; the result must not depend on which kernel served the call."""
+    import ctypes
+    import torch
+    from metalaudio_b200 import _lib as L
+    rng = np.random.default_rng(21)
+    n, hop, sig = 4096, 1024, 3
+    x = (rng.random((sig, 40000)) * 2 - 1).astype(np.float32)
+    fft = make_fft(device, n, hop)
+    mag, phase = fft.stftPolar(x)
+    frames, kh = mag.shape[1], mag.shape[2]
+    out_len = (frames - 1) * hop + n
+    count = sig * frames * kh
+    outs = []
+    for off in (0, 1, 2, 3):        # element offsets: 0 is aligned, the others are not
+        dm = torch.zeros(count + 4, device="cuda"); dp = torch.zeros(count + 4, device="cuda")
+        dm[off:off + count] = torch.from_numpy(mag.ravel()).cuda()
+        dp[off:off + count] = torch.from_numpy(phase.ravel()).cuda()
+        dy = torch.empty((sig, out_len), device="cuda")
+        torch.cuda.synchronize()
+        st = lib.ma_istft_dev(fft._h, ctypes.c_void_p(dm.data_ptr() + 4 * off), ctypes.c_void_p(dp.data_ptr() + 4 * off),
+                              frames, sig, ctypes.c_void_p(dy.data_ptr()), out_len, 1e-8, L.LAYOUT_HALF_POLAR)
+        assert st == 0
+        device.synchronize(10)
+        outs.append(dy.cpu().numpy())
+    win = rp.window("hann", n)
+    ws = rp.window_sum(frames, n, hop, win, 0.0)
+    keep = ws > 1e-3 * ws.max()
+    for y in outs[1:]:
+        assert o64.rel_rms(y[:, keep], outs[0][:, keep]) < 1e-6
+    assert o64.rel_rms(outs[0][:, keep], x[:, :out_len][:, keep]) < TOL
