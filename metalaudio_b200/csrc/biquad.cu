@@ -31,6 +31,7 @@ constexpr int kBqThreads = 256, kBqPer = 32, kBqTile = kBqThreads * kBqPer, kBqW
 constexpr int kBqMaxSections = 32;
 // Table of one (coefficient set, section), doubles:
 //   [0..4]     b0 b1 b2 a1 a2 (the float32 coefficients, widened)
+//   [5..6]     c1 = b1 - a1*b0, c2 = b2 - a2*b0 (the state update with the output substituted)
 //   [8..135]   A^(32*l) row-major 2x2, l < 32
 //   [136..139] A^1024
 constexpr int kBqCoef = 0, kBqPl = 8, kBqPw = 136, kBqTable = 140;
@@ -140,15 +141,19 @@ __global__ void __launch_bounds__(kBqThreads, 2) biquad_kernel(const BiquadLaunc
 
         for (int s = 0; s < p.n_sections; ++s) {
             const double* T = tab + s * kBqTable;
-            const double b0 = T[0], b1 = T[1], b2 = T[2], a1 = T[3], a2 = T[4];
+            // With y = b0*x + z1 substituted, the state update is
+            //     z1' = -a1*z1 + (z2 + c1*x),   z2' = -a2*z1 + c2*x,
+            // one dependent multiply-add per sample instead of two (the output is off the chain).
+            // In double precision the rearrangement changes nothing at float32 output level.
+            const double b0 = T[0], a1 = T[3], a2 = T[4], c1 = T[5], c2 = T[6];
             // ---- zero-state pass over this thread's samples: only its end state is kept
             double z1 = 0.0, z2 = 0.0;
 #pragma unroll
             for (int j = 0; j < kBqPer; ++j) {
                 const double xv = (double)x[j];
-                const double yv = fma(b0, xv, z1);
-                z1 = fma(-a1, yv, fma(b1, xv, z2));
-                z2 = fma(-a2, yv, b2 * xv);
+                const double z1n = fma(-a1, z1, fma(c1, xv, z2));
+                z2 = fma(-a2, z1, c2 * xv);
+                z1 = z1n;
             }
             // ---- inclusive scan of the end states across the warp: E_l = P*E_{l-1} + e_l, P = A^32
             double2 e = make_double2(z1, z2);
@@ -182,8 +187,9 @@ __global__ void __launch_bounds__(kBqThreads, 2) biquad_kernel(const BiquadLaunc
             for (int j = 0; j < kBqPer; ++j) {
                 const double xv = (double)x[j];
                 const double yv = fma(b0, xv, s1);
-                s1 = fma(-a1, yv, fma(b1, xv, s2));
-                s2 = fma(-a2, yv, b2 * xv);
+                const double s1n = fma(-a1, s1, fma(c1, xv, s2));
+                s2 = fma(-a2, s1, c2 * xv);
+                s1 = s1n;
                 x[j] = (float)yv;  // input of the next section
                 if (j == last_local) {
                     f1 = s1;
@@ -238,6 +244,8 @@ static void build_table(const float* c, double* t) {
     for (int i = 0; i < kBqTable; ++i) t[i] = 0.0;
     for (int i = 0; i < 5; ++i) t[kBqCoef + i] = (double)c[i];
     const double a1 = c[3], a2 = c[4];
+    t[5] = (double)c[1] - a1 * (double)c[0];
+    t[6] = (double)c[2] - a2 * (double)c[0];
     auto mul = [](const double* a, const double* b, double* r) {
         const double r0 = a[0] * b[0] + a[1] * b[2], r1 = a[0] * b[1] + a[1] * b[3];
         const double r2 = a[2] * b[0] + a[3] * b[2], r3 = a[2] * b[1] + a[3] * b[3];
