@@ -9,8 +9,8 @@ float32 scalars the generator's plain ``json.dump`` cannot serialise; the genera
 ``save_reference`` is therefore called through a ``json.dump`` that converts numpy scalars
 with ``float()``.  The values are exactly what the generator computed.
 
-Usage (in a container where the reference is mounted):
-    python tests/golden/make_golden.py [/path/to/reference]
+Usage (where a checkout of the reference exists):
+    python tests/golden/make_golden.py /path/to/reference
 """
 import importlib.util
 import json  # noqa: F401  (the generator's module-level json is patched below)
@@ -18,7 +18,9 @@ import os
 import sys
 
 here = os.path.dirname(os.path.abspath(__file__))
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py /path/to/reference")
+ref_root = sys.argv[1]
 path = os.path.join(ref_root, "scripts", "generate_references.py")
 spec = importlib.util.spec_from_file_location("reference_generate_references", path)
 mod = importlib.util.module_from_spec(spec)
