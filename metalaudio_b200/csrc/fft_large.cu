@@ -12,8 +12,9 @@
 //                                transform over k1, times exp(+2 pi i n1 k2 / N) -> D[k2][n1]
 //            pass B (cols_c2r):  N2-point real inverse over k2 -> x[n1 + N1*n2] / N
 //
-// A batch is cut into chunks whose scratch (about 4*N bytes per transform) stays resident in
-// the 126 MB L2 between the two passes, so HBM sees each transform's input and output once.
+// A batch is cut into chunks of about 192 MB of pass data (about 4*N bytes per transform).  Up to
+// roughly 100 MB that scratch stays in the 126 MB L2 between the two passes; larger batches let it
+// spill to HBM, which the passes - bound by instruction issue and latency, not by HBM - do not feel.
 // Plain loads and stores only: no TMA, no multicast.
 #include <new>
 
@@ -656,9 +657,11 @@ ma_status large_plan_init(ma_fft_plan* plan) {
     }
     MA_TRY(upload_tw(ctx, 2 * s.m2, s.m2 / 2 + 1, &plan->d_twN)); // column Hermitian twiddles
     MA_TRY(upload_tw(ctx, plan->n, plan->n / 2, &plan->d_twL));
-    // Chunk size: scratch of about 48 MB stays in L2 between the passes.
+    // Chunk size: about 192 MB of pass data.  An L2-sized chunk (48 MB) keeps the scratch out of HBM,
+    // but the passes are issue- and latency-bound rather than HBM-bound, and fewer, longer launches
+    // measured 9 % faster for 4096 transforms of 65536 points although the scratch then crosses HBM.
     const size_t per = (size_t)(s.m2 + 1) * s.n1 * sizeof(float2);
-    int64_t chunk = (int64_t)(((size_t)48 << 20) / per);
+    int64_t chunk = (int64_t)(((size_t)192 << 20) / per);
     if (chunk < 1) chunk = 1;
     plan->scratch_batch = chunk;
     MA_CUDA(cudaMalloc((void**)&plan->d_scratch, per * (size_t)chunk));

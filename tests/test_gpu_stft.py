@@ -101,18 +101,18 @@ def test_stft_bit_stable(device):
 
 
 def test_large_frames_many_signals_half_layout(device):
-    """More frames than one scratch chunk holds (16384-point frames: 760 per chunk) over two signals,
+    """More frames than one scratch chunk holds (16384-point frames: 3027 per chunk) over two signals,
     half-spectrum layout with magnitudes, through the batched API."""
     from metalaudio_b200 import FFT, WindowType
-    n, hop, length = 16384, 2048, 2048 * 900 + 16384
+    n, hop, length = 16384, 2048, 2048 * 3100 + 16384
     rng = np.random.default_rng(12)
     x = rng.uniform(-1, 1, (2, length)).astype(np.float32)
     fft = FFT(device, FFT.Config(size=n, windowType=WindowType.hann, hopSize=hop))
     spec, mag = fft.stftBatch(x, magnitude=True)
     frames = (length - n) // hop + 1
-    assert spec.shape == (2, frames, n // 2 + 1) and frames > 760
+    assert spec.shape == (2, frames, n // 2 + 1) and frames > 3027
     w = rp.window("hann", n)
-    pick = [0, 1, 759, 760, 761, frames - 1]
+    pick = [0, 1, 3026, 3027, 3028, frames - 1]
     for s_ in range(2):
         fr = x[s_][np.array(pick)[:, None] * hop + np.arange(n)[None, :]].astype(np.float64) * w
         ref = np.fft.rfft(fr, axis=-1)
