@@ -532,7 +532,8 @@ static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse)
     }
     const int64_t work = p.batch * (p.n1 / W1);
     const int64_t cap = (int64_t)ctx->sm_count * occ;
-    const int grid = (int)(work < cap ? work : cap);
+    // forward passes: one CTA per tile (measured 5 % faster than persistent CTAs); inverse passes: persistent
+    const int grid = !inverse ? (int)work : (int)(work < cap ? work : cap);
     if (inverse) ki<<<grid, threads, smem, ctx->stream>>>(p);
     else kf<<<grid, threads, smem, ctx->stream>>>(p);
     return after_launch(ctx);
@@ -563,7 +564,8 @@ static ma_status run_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse)
     const int m2 = p.n2 / 2;
     const int64_t work = p.batch * ((m2 + 1 + W2 - 1) / W2);
     const int64_t cap = (int64_t)ctx->sm_count * occ;
-    const int grid = (int)(work < cap ? work : cap);
+    // forward passes: one CTA per tile (measured 5 % faster than persistent CTAs); inverse passes: persistent
+    const int grid = !inverse ? (int)work : (int)(work < cap ? work : cap);
     if (inverse) ki<<<grid, threads, smem, ctx->stream>>>(p);
     else kf<<<grid, threads, smem, ctx->stream>>>(p);
     return after_launch(ctx);
