@@ -383,7 +383,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         dist.destroy_process_group()
 
 
-def bench_conv(dev, lib, torch, stream, peak):
+def bench_conv(dev, lib, torch, stream, peak, whole_signal=None):
     """Partitioned convolution, configuration 3 shape, as causal streaming steps: every step
     reads the whole frequency-domain delay line of every channel once."""
     from metalaudio_b200 import Convolution, Tensor
@@ -431,7 +431,7 @@ def bench_conv(dev, lib, torch, stream, peak):
     # Whole-signal call (the reference's process(input:output:)): 2^20 samples per channel, full
     # L+K-1 output.  All block spectra exist up front, so the multiply-accumulate is tiled over
     # time and becomes FMA-bound; its rate is quoted against the same streaming byte count.
-    if C >= 256:
+    if (C >= 256) if whole_signal is None else whole_signal:
         L = 1 << 20
         full = L + taps - 1
         st = lib.ma_pconv_reset(conv._h)
@@ -455,7 +455,7 @@ def bench_conv(dev, lib, torch, stream, peak):
         pms = min(times[1:])
         stream_bytes = C * (L // B) * CONV["bytes_per_channel_block"]
         out["whole_signal"] = {
-            "workload": "process(): 512 channels x 2^20 samples, full L+K-1 output (4608 blocks per channel)",
+            "workload": f"process(): {C} channels x 2^20 samples, full L+K-1 output (4608 blocks per channel)",
             "value": C * L / (pms * 1e-3), "unit": "channel-samples/s", "ms": pms,
             "times_streaming_roofline": stream_bytes / (pms * 1e-3) / 1e9 / peak,
             "note": "time-tiled multiply-accumulate: delay-line spectra reused on chip, FMA-bound "
@@ -678,8 +678,10 @@ def run_only(args, local_rank: int):
         res = bench_next_rows(dev, lib, torch, stream, peak, small=args.small)
     elif args.only == "conv4":
         res = bench_conv4(dev, lib, torch, stream, peak, channels=256 if args.small else 1024)
+    elif args.only == "conv":
+        res = bench_conv(dev, lib, torch, stream, peak, whole_signal=True if args.small else None)
     else:
-        res = {"conv": bench_conv, "large": bench_large}[args.only](dev, lib, torch, stream, peak)
+        res = bench_large(dev, lib, torch, stream, peak)
     print(json.dumps({args.only: res}), flush=True)
 
 
@@ -695,7 +697,8 @@ def main():
                     help="signals per GPU (default: the benchmark configuration's 256; smaller for profiler captures)")
     ap.add_argument("--conv-channels", type=int, default=CONV["channels"])
     ap.add_argument("--large-batch", type=int, default=LARGE["batch"])
-    ap.add_argument("--small", action="store_true", help="with --only next: a quarter-size case for profiler captures")
+    ap.add_argument("--small", action="store_true", help="with --only next / conv4: a quarter-size case for profiler captures; with --only conv: run the "
+                         "whole-signal call at any channel count")
     ap.add_argument("--only", choices=["conv", "conv4", "large", "next"], default=None,
                     help="run just one of the extra workloads (profiler captures)")
     args = ap.parse_args()
