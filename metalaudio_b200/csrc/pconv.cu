@@ -15,6 +15,7 @@
 #include <cuda_pipeline.h>
 
 #include <new>
+#include <type_traits>
 #include <vector>
 
 #include "fft_plan.h"
@@ -242,25 +243,32 @@ __global__ void __launch_bounds__(128) pconv_mac_tiled_kernel(const MacParams q,
             load_h_rows(buf ^ 1, p0 + TT);
         }
         __pipeline_commit();
+        // one chunk of TT partitions; FULL: all of them exist, so no per-partition test
+        auto chunk = [&](auto full) {
+            constexpr bool FULL = decltype(full)::value;
+            const float2* hrow = &hs[buf][0][lane];
 #pragma unroll
-        for (int j = 0; j < TT; ++j) {
-            const int p = p0 + j;
-            if (p < P) {
-                // slot (i - j) mod TT holds timeline row base + i - p; the row base - p enters at i = 0
-                if (p > 0) xw[(TT - j) % TT] = xs[(base - p) & (RING - 1)][lane];
-                const float2 h = hs[buf][j][lane];
-                const float ha = dc ? 0.f : h.y;   // bin 0 carries (DC, Nyquist): component-wise product
-                const float hb = dc ? h.y : h.x;
+            for (int j = 0; j < TT; ++j) {
+                const int p = p0 + j;
+                if (FULL || p < P) {
+                    // slot (i - j) mod TT holds timeline row base + i - p; the row base - p enters at i = 0
+                    if (j > 0 || p0 > 0) xw[(TT - j) % TT] = xs[(base - p) & (RING - 1)][lane];
+                    const float2 h = hrow[j * 32];
+                    const float ha = dc ? 0.f : h.y;   // bin 0 carries (DC, Nyquist): component-wise product
+                    const float hb = dc ? h.y : h.x;
 #pragma unroll
-                for (int i = 0; i < TT; ++i) {
-                    const float2 xv = xw[(i - j + TT) % TT];
-                    acc[i].x = fmaf(xv.x, h.x, acc[i].x);
-                    acc[i].x = fmaf(-xv.y, ha, acc[i].x);
-                    acc[i].y = fmaf(xv.x, ha, acc[i].y);
-                    acc[i].y = fmaf(xv.y, hb, acc[i].y);
+                    for (int i = 0; i < TT; ++i) {
+                        const float2 xv = xw[(i - j + TT) % TT];
+                        acc[i].x = fmaf(xv.x, h.x, acc[i].x);
+                        acc[i].x = fmaf(-xv.y, ha, acc[i].x);
+                        acc[i].y = fmaf(xv.x, ha, acc[i].y);
+                        acc[i].y = fmaf(xv.y, hb, acc[i].y);
+                    }
                 }
             }
-        }
+        };
+        if (p0 + TT <= P) chunk(std::true_type{});
+        else chunk(std::false_type{});
         __pipeline_wait_prior(0);
         __syncthreads();
         buf ^= 1;
