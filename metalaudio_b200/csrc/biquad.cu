@@ -14,13 +14,15 @@
 // zero state to get e0, the end states are combined by a warp scan (powers of A^32 from a
 // host-built table) and a short serial pass over the 8 warps, which gives every thread the true
 // state in front of its samples; it then runs the recurrence again from that state and keeps the
-// outputs.  States and recurrences are double precision (see biquad_kernel), data is float32.  Cascaded sections run back to back on the registers.  Loads and stores of a tile are
-// contiguous; the tile is re-indexed through swizzled shared memory, and the next tile is fetched
+// outputs.  States and recurrences are double precision (see biquad_kernel), data is float32.
+// Cascaded sections run back to back on the registers.  Loads and stores of a tile are contiguous;
+// the tile is re-indexed through swizzled shared memory, and the next tile is fetched
 // asynchronously while the current one is filtered.
 #include <cuda_pipeline.h>
 
 #include <cmath>
 #include <new>
+#include <type_traits>
 #include <vector>
 
 #include "ma_internal.h"
@@ -183,19 +185,25 @@ __global__ void __launch_bounds__(kBqThreads, 2) biquad_kernel(const BiquadLaunc
             // that holds the signal's last sample also records the state after it
             double s1 = prev.x + pc.x, s2 = prev.y + pc.y;
             double f1 = 0.0, f2 = 0.0;
+            // CAPTURE (the signal's last tile only): remember the state right after sample last_local
+            auto second_pass = [&](auto capture) {
+                constexpr bool CAPTURE = decltype(capture)::value;
 #pragma unroll
-            for (int j = 0; j < kBqPer; ++j) {
-                const double xv = (double)x[j];
-                const double yv = fma(b0, xv, s1);
-                const double s1n = fma(-a1, s1, fma(c1, xv, s2));
-                s2 = fma(-a2, s1, c2 * xv);
-                s1 = s1n;
-                x[j] = (float)yv;  // input of the next section
-                if (j == last_local) {
-                    f1 = s1;
-                    f2 = s2;
+                for (int j = 0; j < kBqPer; ++j) {
+                    const double xv = (double)x[j];
+                    const double yv = fma(b0, xv, s1);
+                    const double s1n = fma(-a1, s1, fma(c1, xv, s2));
+                    s2 = fma(-a2, s1, c2 * xv);
+                    s1 = s1n;
+                    x[j] = (float)yv;  // input of the next section
+                    if (CAPTURE && j == last_local) {
+                        f1 = s1;
+                        f2 = s2;
+                    }
                 }
-            }
+            };
+            if (last_tile) second_pass(std::true_type{});
+            else second_pass(std::false_type{});
             if (owns_last) {
                 // results below the smallest normal are stored as zero (DSP.metal:736-740)
                 float g1 = (float)f1, g2 = (float)f2;
