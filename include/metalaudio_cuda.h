@@ -127,6 +127,12 @@ ma_status ma_timing_end(ma_context* ctx, float* milliseconds);
 /* Test hook, host side only: the next call that reaches `site` fails with
  * `cuda_error` (no GPU work is disturbed). */
 ma_status ma_test_inject_fault(ma_context* ctx, int32_t site, int32_t cuda_error);
+/* Test hook for the device-side timeout path (the reference's gpuTimeout,
+ * ComputeContext.swift:176-208): queues a one-thread kernel that waits, with the same bounded
+ * wait the transform kernels use for their staged copies, on a barrier nothing will complete;
+ * after `polls` polls (1..65536) it gives up and raises the context's error flag, which the next
+ * ma_context_sync reports as MA_ERR_TIMEOUT and clears.  Nothing faults or hangs. */
+ma_status ma_test_bounded_wait(ma_context* ctx, int32_t polls);
 
 /* ------------------------------------------------------------------ buffers
  * Backing store of Tensor (Sources/MetalAudioKit/Buffers/Tensor.swift:59, :272, :325,
@@ -209,6 +215,15 @@ ma_status ma_fft_inverse_dev(ma_fft_plan* plan, const float* in_a, const float* 
                              int64_t batch, int32_t layout);
 ma_status ma_fft_inverse_host(ma_fft_plan* plan, const float* in_a, const float* in_b, float* out,
                               int64_t batch, int32_t layout);
+
+/* Complex-input transform of `batch` sequences of N interleaved (re, im) pairs, in and out
+ * (2N floats per sequence, 8-byte aligned for the _dev form): the full complex DFT, forward
+ * unscaled (inverse == 0) or inverse with the 1/N scale (inverse != 0).  Replaces the
+ * explicit-backend calls FFT.forwardGPU / inverseGPU (FFT.swift:945-1107, :1176-1315), whose
+ * data format this is, for every plan size.  Runs as split -> batched real transform -> combine
+ * through a plan-owned work buffer that is allocated on the first such call. */
+ma_status ma_fft_complex_dev(ma_fft_plan* plan, const float* in, float* out, int64_t batch, int32_t inverse);
+ma_status ma_fft_complex_host(ma_fft_plan* plan, const float* in, float* out, int64_t batch, int32_t inverse);
 
 /* Magnitude / power / dB over bins 0..N/2 of caller-supplied FULL_SPLIT spectra.
  * Replaces FFT.magnitude / power / magnitudeDB (FFT.swift:1780-1847). */
@@ -293,7 +308,13 @@ ma_status ma_pconv_process_host(ma_pconv* pc, const float* in, int64_t len, int6
  * in_stride), one block of B output samples out; the block's second half is kept in the
  * object and added to the next step's output.  Every step reads the whole delay line:
  * this is the HBM-streaming kernel.  No reference counterpart call (the reference loops
- * blocks inside process()); the arithmetic per block is Convolution.swift:580-757. */
+ * blocks inside process()); the arithmetic per block is Convolution.swift:580-757.
+ * Back-to-back steps on one context overlap the start of a step with the end of the previous one;
+ * the library detects by itself when anything else of its own was queued in between or when a
+ * step's output is fed back as the next input.  A caller that fills in_block with a kernel of its
+ * OWN on the context's stream (ma_context_stream) must keep one other stream operation of this
+ * library (for instance ma_buffer_zero of a scratch word) or a stream/event wait between that
+ * kernel and the step. */
 ma_status ma_pconv_step_dev(ma_pconv* pc, const float* in_block, int64_t in_stride,
                             float* out_block, int64_t out_stride);
 /* Zero the delay line, the write index and the overlap tail (Convolution.reset). */

@@ -31,6 +31,7 @@ SIGNATURES = {
     "ma_timing_begin": (c_int32, [c_void_p]),
     "ma_timing_end": (c_int32, [c_void_p, c_float_p]),
     "ma_test_inject_fault": (c_int32, [c_void_p, c_int32, c_int32]),
+    "ma_test_bounded_wait": (c_int32, [c_void_p, c_int32]),
     "ma_buffer_alloc": (c_int32, [c_void_p, c_size_t, POINTER(c_void_p)]),
     "ma_buffer_free": (c_int32, [c_void_p, c_void_p]),
     "ma_buffer_zero": (c_int32, [c_void_p, c_void_p, c_size_t]),
@@ -48,6 +49,8 @@ SIGNATURES = {
     "ma_fft_forward_static_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_float, c_int64, c_int32]),
     "ma_fft_inverse_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32]),
     "ma_fft_inverse_host": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32]),
+    "ma_fft_complex_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int32]),
+    "ma_fft_complex_host": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int32]),
     "ma_fft_magnitude_dev": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_float]),
     "ma_fft_magnitude_host": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_float]),
     "ma_stft_frame_count": (c_int32, [c_void_p, c_int64, c_int64_p]),

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libmetalaudio_cuda.so")
 
-SOURCES = ["context.cu", "fft_small.cu", "fft_large.cu", "fft_api.cu", "pconv.cu", "fftconv.cu", "spectral_glue.cu", "biquad.cu"]
+SOURCES = ["context.cu", "fft_small.cu", "fft_large.cu", "fft_api.cu", "fft_complex.cu", "pconv.cu", "fftconv.cu", "spectral_glue.cu", "biquad.cu"]
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3",

@@ -301,7 +301,7 @@ ma_status ma_biquad_create(ma_context* ctx, int32_t n_channels, int32_t n_sectio
     bq->channels = n_channels;
     bq->sections = n_sections;
     cudaError_t e = cudaMalloc((void**)&bq->d_state, sizeof(float2) * (size_t)n_channels * n_sections);
-    if (e == cudaSuccess) e = cudaMemset(bq->d_state, 0, sizeof(float2) * (size_t)n_channels * n_sections);
+    if (e == cudaSuccess) e = cudaMemsetAsync(bq->d_state, 0, sizeof(float2) * (size_t)n_channels * n_sections, ctx->stream);  // ordered before the first kernel of the context
     if (e != cudaSuccess) {
         ma_biquad_destroy(bq);
         return cuda_fail(e);

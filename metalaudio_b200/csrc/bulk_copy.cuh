@@ -48,9 +48,9 @@ __device__ __forceinline__ void bulk_copy_part(void* dst, const void* src, uint3
 }
 
 // Waits for the phase with the given parity; false when the poll limit ran out.
-__device__ __forceinline__ bool bulk_barrier_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool bulk_barrier_wait(uint64_t* bar, uint32_t parity, int limit = kBulkWaitLimit) {
     const uint32_t b = smem_u32(bar);
-    for (int i = 0; i < kBulkWaitLimit; ++i) {
+    for (int i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"

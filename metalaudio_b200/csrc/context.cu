@@ -5,6 +5,7 @@
 #include <new>
 #include <thread>
 
+#include "bulk_copy.cuh"
 #include "ma_internal.h"
 
 namespace ma {
@@ -43,7 +44,7 @@ ma_status enter(ma_context* ctx, int site) {
 }
 
 ma_status after_launch(ma_context* ctx) {
-    (void)ctx;
+    if (ctx != nullptr) ++ctx->launch_seq;
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e);
@@ -131,6 +132,15 @@ void temp_free(ma_context* ctx, void* dptr) {
     if (dptr != nullptr) (void)cudaFreeAsync(dptr, ctx->stream);
 }
 
+// One thread waits, with the kernels' bounded wait, on a barrier that no copy will ever complete,
+// gives up after `polls` polls and raises the context's error flag - the path a transform kernel
+// takes when a staged copy does not arrive.  Nothing faults and nothing hangs.
+__global__ void bounded_wait_probe_kernel(int32_t* error_flag, int polls) {
+    __shared__ uint64_t bar;
+    bulk_barrier_init(&bar);
+    if (!bulk_barrier_wait(&bar, 0, polls)) *error_flag = 1;
+}
+
 }  // namespace ma
 
 using namespace ma;
@@ -204,7 +214,7 @@ ma_status ma_context_create(int32_t device_index, size_t pinned_bytes, ma_contex
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_end);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_sync, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaMalloc((void**)&ctx->d_error_flag, sizeof(int32_t));
-    if (e == cudaSuccess) e = cudaMemset(ctx->d_error_flag, 0, sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMemsetAsync(ctx->d_error_flag, 0, sizeof(int32_t), ctx->stream);  // ordered before every kernel of the context
     if (e == cudaSuccess) e = cudaHostAlloc((void**)&ctx->h_error_flag, sizeof(int32_t), cudaHostAllocDefault);
     if (e == cudaSuccess) *ctx->h_error_flag = 0;
     if (e == cudaSuccess) {
@@ -311,6 +321,13 @@ ma_status ma_test_inject_fault(ma_context* ctx, int32_t site, int32_t cuda_error
     ctx->fault_site = site;
     ctx->fault_error = cuda_error;
     return MA_OK;
+}
+
+ma_status ma_test_bounded_wait(ma_context* ctx, int32_t polls) {
+    MA_TRY(enter(ctx, MA_FAULT_LAUNCH));
+    if (polls < 1 || polls > (1 << 16)) return MA_ERR_INVALID_ARGUMENT;
+    bounded_wait_probe_kernel<<<1, 1, 0, ctx->stream>>>(ctx->d_error_flag, polls);
+    return after_launch(ctx);
 }
 
 ma_status ma_buffer_alloc(ma_context* ctx, size_t bytes, void** dptr) {

@@ -37,6 +37,19 @@ static int64_t complex_per_frame(int n, int layout) {
     return layout == MA_LAYOUT_HALF_PACKED ? n / 2 : n / 2 + 1;
 }
 
+namespace ma {
+ma_status check_forward_args(ma_fft_plan* plan, const float* in, const float* out_a, const float* out_b,
+                             const float* mag, int mag_kind, int64_t batch, int layout) {
+    if (batch < 0 || !valid_layout(layout) || in == nullptr || out_a == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (two_arrays(layout) && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (mag != nullptr && (mag_kind < MA_MAG_MAGNITUDE || mag_kind > MA_MAG_DB)) return MA_ERR_INVALID_ARGUMENT;
+    int64_t total;
+    if (mul_overflow(batch, plan->n, &total)) return MA_ERR_BATCH_OVERFLOW;
+    if (plan->large && layout == MA_LAYOUT_HALF_POLAR) return MA_ERR_UNSUPPORTED;
+    return MA_OK;
+}
+}  // namespace ma
+
 extern "C" {
 
 ma_status ma_fft_plan_create(ma_context* ctx, int32_t n, const float* window, int32_t hop, ma_fft_plan** out) {
@@ -92,6 +105,7 @@ ma_status ma_fft_plan_destroy(ma_fft_plan* plan) {
     if (plan->d_twInv) (void)cudaFree(plan->d_twInv);
     if (plan->d_twN) (void)cudaFree(plan->d_twN);
     if (plan->d_norm) (void)cudaFree(plan->d_norm);
+    if (plan->d_cwork) (void)cudaFree(plan->d_cwork);
     (void)cudaGetLastError();
     delete plan;
     return MA_OK;
@@ -108,13 +122,9 @@ ma_status ma_fft_forward_dev(ma_fft_plan* plan, const float* in, float* out_a, f
     if (plan == nullptr) return MA_ERR_INVALID_ARGUMENT;
     MA_TRY(enter(plan->ctx, MA_FAULT_LAUNCH));
     if (batch == 0) return MA_OK;  // empty batch is a no-op (STFT.swift:99-100)
-    if (batch < 0 || !valid_layout(layout) || in == nullptr || out_a == nullptr) return MA_ERR_INVALID_ARGUMENT;
-    if (two_arrays(layout) && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
-    if (mag != nullptr && (mag_kind < MA_MAG_MAGNITUDE || mag_kind > MA_MAG_DB)) return MA_ERR_INVALID_ARGUMENT;
-    int64_t total;
-    if (mul_overflow(batch, plan->n, &total)) return MA_ERR_BATCH_OVERFLOW;
+    MA_TRY(check_forward_args(plan, in, out_a, out_b, mag, mag_kind, batch, layout));
+    const int64_t total = batch * plan->n;
     const float db_scale = 1.0f / db_reference;
-    if (plan->large && layout == MA_LAYOUT_HALF_POLAR) return MA_ERR_UNSUPPORTED;
     if (plan->large) return launch_r2c_large(plan, in, out_a, out_b, mag, mag_kind, db_scale, batch, layout);
     R2CParams p{};
     p.in = in;

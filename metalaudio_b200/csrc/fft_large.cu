@@ -695,12 +695,15 @@ static void fill_tables(ma_fft_plan* plan, LargeParams& p) {
 }
 
 ma_status launch_r2c_large(ma_fft_plan* plan, const float* in, float* out_a, float* out_b, float* mag,
-                           int mag_kind, float db_scale, int64_t batch, int layout) {
+                           int mag_kind, float db_scale, int64_t batch, int layout, float2* scratch,
+                           int64_t scratch_batch) {
     const int64_t n = plan->n, half = n / 2;
-    for (int64_t done = 0; done < batch; done += plan->scratch_batch) {
+    const int64_t chunk = scratch != nullptr ? scratch_batch : plan->scratch_batch;
+    for (int64_t done = 0; done < batch; done += chunk) {
         LargeParams p{};
         fill_tables(plan, p);
-        p.batch = batch - done < plan->scratch_batch ? batch - done : plan->scratch_batch;
+        if (scratch != nullptr) p.scratch = scratch;  // caller-provided pass buffer instead of the plan's
+        p.batch = batch - done < chunk ? batch - done : chunk;
         p.in = in + done * n;
         p.layout = layout;
         p.mag_kind = mag_kind;
@@ -877,18 +880,21 @@ ma_status launch_conv_large(ma_fft_plan* plan, const float* in, int64_t valid, i
 static __device__ __align__(256) unsigned char g_static_scratch[MA_STATIC_SCRATCH_BYTES];
 
 namespace {
-float2* g_static_scratch_addr[64] = {nullptr};
+std::atomic<float2*> g_static_scratch_addr[64];  // zero-initialised; one slot per device ordinal
 
-// Device address of the static scratch on the current device (which must be `device`).
+// Device address of the static scratch on the current device (which must be `device`).  Threads
+// that race on the first call all store the same address.
 ma_status static_scratch_address(int device, float2** out) {
     if (device < 0 || device >= 64) return MA_ERR_INVALID_ARGUMENT;
-    if (g_static_scratch_addr[device] == nullptr) {
+    float2* addr = g_static_scratch_addr[device].load(std::memory_order_acquire);
+    if (addr == nullptr) {
         void* ptr = nullptr;
         const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
         if (e != cudaSuccess) return ma::cuda_fail(e);
-        g_static_scratch_addr[device] = static_cast<float2*>(ptr);
+        addr = static_cast<float2*>(ptr);
+        g_static_scratch_addr[device].store(addr, std::memory_order_release);
     }
-    *out = g_static_scratch_addr[device];
+    *out = addr;
     return MA_OK;
 }
 }  // namespace
@@ -902,36 +908,11 @@ extern "C" ma_status ma_fft_forward_static_dev(ma_fft_plan* plan, const float* i
         return ma_fft_forward_dev(plan, in, out_a, out_b, mag, mag_kind, db_reference, batch, layout);
     MA_TRY(enter(plan->ctx, MA_FAULT_LAUNCH));  // makes the context's device current
     if (batch == 0) return MA_OK;
-    if (batch < 0 || in == nullptr || out_a == nullptr) return MA_ERR_INVALID_ARGUMENT;
-    if (layout != LAYOUT_HALF_INTERLEAVED && layout != LAYOUT_FULL_SPLIT && layout != LAYOUT_HALF_PACKED)
-        return MA_ERR_INVALID_ARGUMENT;
-    if (layout == LAYOUT_FULL_SPLIT && out_b == nullptr) return MA_ERR_INVALID_ARGUMENT;
-    if (mag != nullptr && (mag_kind < MA_MAG_MAGNITUDE || mag_kind > MA_MAG_DB)) return MA_ERR_INVALID_ARGUMENT;
+    MA_TRY(check_forward_args(plan, in, out_a, out_b, mag, mag_kind, batch, layout));  // same checks as ma_fft_forward_dev
     const size_t per = (size_t)(plan->n2 / 2 + 1) * (size_t)plan->n1 * sizeof(float2);
     if (per > MA_STATIC_SCRATCH_BYTES) return MA_ERR_SCRATCH_LIMIT;
-    const int64_t chunk = (int64_t)(MA_STATIC_SCRATCH_BYTES / per);
     float2* scratch = nullptr;
     MA_TRY(static_scratch_address(plan->ctx->device, &scratch));
-    const int64_t n = plan->n, half = n / 2;
-    const float db_scale = 1.0f / db_reference;
-    for (int64_t done = 0; done < batch; done += chunk) {
-        LargeParams p{};
-        fill_tables(plan, p);
-        p.scratch = scratch;  // the static buffer instead of the plan's allocation
-        p.batch = batch - done < chunk ? batch - done : chunk;
-        p.in = in + done * n;
-        p.layout = layout;
-        p.mag_kind = mag_kind;
-        p.db_scale = db_scale;
-        if (layout == LAYOUT_FULL_SPLIT) {
-            p.out_a = out_a + done * n;
-            p.out_b = out_b + done * n;
-        } else {
-            p.out_a = out_a + done * 2 * (layout == LAYOUT_HALF_PACKED ? half : half + 1);
-        }
-        p.mag = mag ? mag + done * (half + 1) : nullptr;
-        MA_TRY(dispatch_cols(plan, p, false));
-        MA_TRY(dispatch_rows(plan, p, false));
-    }
-    return MA_OK;
+    return launch_r2c_large(plan, in, out_a, out_b, mag, mag_kind, 1.0f / db_reference, batch, layout, scratch,
+                            (int64_t)(MA_STATIC_SCRATCH_BYTES / per));
 }

@@ -26,6 +26,7 @@ struct ma_fft_plan {
     float2* d_scratch = nullptr;      // (n2/2+1) x n1 complex per transform in a pass
     int64_t scratch_batch = 0;        // transforms the scratch holds
     float* d_frames = nullptr;        // iSTFT above 8192 points: scratch_batch inverse frames (allocated on first use)
+    float* d_cwork = nullptr;         // complex-input transforms: real rows + half spectra of one chunk (allocated on first use)
 };
 
 namespace ma {
@@ -41,8 +42,15 @@ ma_status launch_istft_small(ma_fft_plan* plan, C2RParams p);
 // Large path (N > 8192), contiguous frames only.
 ma_status large_plan_init(ma_fft_plan* plan);
 void large_plan_destroy(ma_fft_plan* plan);
+// `scratch` != nullptr: pass data goes through that buffer, `scratch_batch` transforms at a time,
+// instead of the plan's own allocation.
 ma_status launch_r2c_large(ma_fft_plan* plan, const float* in, float* out_a, float* out_b, float* mag,
-                           int mag_kind, float db_scale, int64_t batch, int layout);
+                           int mag_kind, float db_scale, int64_t batch, int layout, float2* scratch = nullptr,
+                           int64_t scratch_batch = 0);
+// Argument checks of the batched forward transform (batch > 0), shared by every entry point that
+// runs it: pointers, layout, magnitude kind, batch * N overflow, layouts the large path lacks.
+ma_status check_forward_args(ma_fft_plan* plan, const float* in, const float* out_a, const float* out_b,
+                             const float* mag, int mag_kind, int64_t batch, int layout);
 ma_status launch_c2r_large(ma_fft_plan* plan, const float* in_a, const float* in_b, float* out,
                            int64_t batch, int layout);
 // STFT / iSTFT above 8192 points (fft_large.cu): frames are read straight from the signal with

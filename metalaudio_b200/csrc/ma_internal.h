@@ -27,6 +27,10 @@ struct ma_context {
     // step's first kernel may overlap that step's last one unless it reads these rows.
     const float* step_out = nullptr;
     const float* step_out_end = nullptr;
+    // Kernels this context has queued, and the count right after the latest streaming step's last
+    // kernel: equal when nothing else of the library was queued on the stream since that step.
+    uint64_t launch_seq = 0;
+    uint64_t step_end_seq = UINT64_MAX;
 };
 
 namespace ma {

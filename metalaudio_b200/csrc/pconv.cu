@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "fft_plan.h"
+#include "pconv_tiling.h"
 
 struct ma_pconv {
     ma_context* ctx = nullptr;
@@ -186,10 +187,15 @@ __global__ void __launch_bounds__(kMacThreads) pconv_mac_kernel(const MacParams 
 // rows in a ring of 128 rows (each row enters once per CTA), the partition rows double-buffered.
 // That leaves about 0.25 byte of L2 traffic per complex multiply-accumulate and makes the FMA
 // pipe the limiter.  One barrier per chunk (1024 FMAs per thread apart).
-template <int TT>
+// TWO_LEVEL: every kFlushChunks chunks the running sums are added into a second set of
+// accumulators and cleared, so no float32 sum runs over more than TT*kFlushChunks partitions
+// (blocked summation: the rounding error of thousands of partitions grows with the block
+// length, not with the partition count).
+constexpr int kFlushChunks = 16;
+template <int TT, bool TWO_LEVEL>
 __global__ void __launch_bounds__(128) pconv_mac_tiled_kernel(const MacParams q, int t_total, int64_t tl_len) {
-    constexpr int RING = 128;  // >= 4*TT - 1 + 2*TT rows in flight
-    static_assert(4 * TT - 1 + 2 * TT <= RING, "timeline ring too small");
+    using TL = MacTiling<TT>;
+    constexpr int RING = TL::kRing;
     __shared__ __align__(16) float2 xs[RING][32];
     __shared__ __align__(16) float2 hs[2][TT][32];
     const int tid = threadIdx.x;
@@ -204,7 +210,7 @@ __global__ void __launch_bounds__(128) pconv_mac_tiled_kernel(const MacParams q,
     if (t0_cta >= t_total) return;
     const float2* xc = q.x + (int64_t)c * q.x_chan_stride + bt * 32;
     const float2* hc = q.h + (int64_t)__ldg(q.ch2ir + c) * P * B + bt * 32;
-    const int64_t base0 = (int64_t)(P - 1) + t0_cta;     // timeline row of the CTA's first output at p = 0
+    const int64_t base0 = TL::base0(P, t0_cta);          // timeline row of the CTA's first output at p = 0
     const int64_t base = base0 + warp * TT;              // ... of this warp's first output
 
     // 16-byte copies: a row of 32 bins is 16 segments
@@ -212,7 +218,7 @@ __global__ void __launch_bounds__(128) pconv_mac_tiled_kernel(const MacParams q,
         for (int idx = tid; idx < count * 16; idx += 128) {
             const int64_t row = first + (idx >> 4);
             const int seg = idx & 15;
-            int64_t src = row > tl_len - 1 ? tl_len - 1 : row;  // rows past the end feed outputs that are never stored
+            const int64_t src = TL::fetch_row(row, tl_len);  // clamped into the channel's own timeline
             __pipeline_memcpy_async(&xs[row & (RING - 1)][seg * 2], xc + src * B + seg * 2, 16);
         }
     };
@@ -224,22 +230,25 @@ __global__ void __launch_bounds__(128) pconv_mac_tiled_kernel(const MacParams q,
         }
     };
 
-    load_x_rows(base0 - TT + 1, 4 * TT - 1 + TT);  // rows of chunk 0: [base0-TT+1, base0+4TT-1]
+    load_x_rows(TL::chunk0_first(P, t0_cta), TL::kChunk0Rows);  // rows of chunk 0: [base0-TT+1, base0+4TT-1]
     load_h_rows(0, 0);
     __pipeline_commit();
     __pipeline_wait_prior(0);
     __syncthreads();
 
     float2 acc[TT], xw[TT];
+    float2 acc2[TWO_LEVEL ? TT : 1];
 #pragma unroll
     for (int i = 0; i < TT; ++i) {
         acc[i] = make_float2(0.f, 0.f);
+        if constexpr (TWO_LEVEL) acc2[i] = make_float2(0.f, 0.f);
         xw[i] = xs[(base + i) & (RING - 1)][lane];
     }
     int buf = 0;
+    int since_flush = 0;
     for (int p0 = 0; p0 < P; p0 += TT) {
         if (p0 + TT < P) {  // stage the next chunk while this one is consumed
-            load_x_rows(base0 - p0 - 2 * TT + 1, TT);
+            load_x_rows(TL::lookahead_first(P, t0_cta, p0), TT);
             load_h_rows(buf ^ 1, p0 + TT);
         }
         __pipeline_commit();
@@ -269,9 +278,27 @@ __global__ void __launch_bounds__(128) pconv_mac_tiled_kernel(const MacParams q,
         };
         if (p0 + TT <= P) chunk(std::true_type{});
         else chunk(std::false_type{});
+        if constexpr (TWO_LEVEL) {
+            if (++since_flush == kFlushChunks) {
+                since_flush = 0;
+#pragma unroll
+                for (int i = 0; i < TT; ++i) {
+                    acc2[i].x += acc[i].x;
+                    acc2[i].y += acc[i].y;
+                    acc[i] = make_float2(0.f, 0.f);
+                }
+            }
+        }
         __pipeline_wait_prior(0);
         __syncthreads();
         buf ^= 1;
+    }
+    if constexpr (TWO_LEVEL) {
+#pragma unroll
+        for (int i = 0; i < TT; ++i) {
+            acc[i].x += acc2[i].x;
+            acc[i].y += acc2[i].y;
+        }
     }
     const int t0 = t0_cta + warp * TT;
     float2* o = q.out + (int64_t)c * q.out_chan_stride + (int64_t)t0 * q.out_t_stride + bt * 32 + lane;
@@ -279,6 +306,8 @@ __global__ void __launch_bounds__(128) pconv_mac_tiled_kernel(const MacParams q,
     for (int i = 0; i < TT; ++i)
         if (t0 + i < t_total) o[(int64_t)i * q.out_t_stride] = acc[i];
 }
+
+constexpr int kTwoLevelFrom = 2048;
 
 static ma_status launch_mac_tiled(ma_pconv* pc, const MacParams& q, int64_t t_count, int64_t tl_len) {
     constexpr int TT = 16;
@@ -294,7 +323,11 @@ static ma_status launch_mac_tiled(ma_pconv* pc, const MacParams& q, int64_t t_co
         qq.out = q.out + t_first * q.out_t_stride;
         qq.x = q.x + t_first * pc->block;  // shifts the timeline origin by t_first rows
         dim3 grid((unsigned)(bin_tiles * pc->channels), (unsigned)ny, 1);
-        pconv_mac_tiled_kernel<TT><<<grid, 128, 0, ctx->stream>>>(qq, (int)(t_count - t_first), tl_len - t_first);
+        // Blocked summation once a running sum would cover more than kTwoLevelFrom partitions.
+        if (pc->partitions >= kTwoLevelFrom)
+            pconv_mac_tiled_kernel<TT, true><<<grid, 128, 0, ctx->stream>>>(qq, (int)(t_count - t_first), tl_len - t_first);
+        else
+            pconv_mac_tiled_kernel<TT, false><<<grid, 128, 0, ctx->stream>>>(qq, (int)(t_count - t_first), tl_len - t_first);
         MA_TRY(after_launch(ctx));
         done += ny;
     }
@@ -708,14 +741,18 @@ ma_status ma_pconv_step_dev(ma_pconv* pc, const float* in_block, int64_t in_stri
     if (pc->write_index < 0 || pc->write_index >= P) return MA_ERR_INVALID_PARTITION_STATE;
     const int w = pc->write_index;
     // The three kernels are chained by programmatic dependent launch: this step's r2c may run
-    // beside the previous step's c2r (see fft_small.cu).  They share no data unless the caller
-    // feeds the previous step's output block straight back in; then r2c is launched plainly.
+    // beside the previous step's c2r (see fft_small.cu).  That is only sound when the kernel right
+    // before this r2c on the stream is that c2r and the two share no data: r2c reads its input
+    // before it waits for the earlier kernel.  So r2c is launched plainly when the caller feeds the
+    // previous step's output block straight back in, and whenever the library queued anything else
+    // on this context since the last step (whose output might be this step's input).
     const float* in_end = in_block + (int64_t)(C - 1) * in_stride + B;
     const bool feeds_back = ctx->step_out != nullptr && in_block < ctx->step_out_end && ctx->step_out < in_end;
+    const bool follows_step = ctx->launch_seq == ctx->step_end_seq;
     // 1. this block's spectrum into ring slot w
     {
         R2CParams p{};
-        p.dependent_launch = feeds_back ? 0 : 1;
+        p.dependent_launch = (follows_step && !feeds_back) ? 1 : 0;
         p.in = in_block;
         p.signal_stride = in_stride;
         p.frames_per_signal = 1;
@@ -767,6 +804,7 @@ ma_status ma_pconv_step_dev(ma_pconv* pc, const float* in_block, int64_t in_stri
         p.dependent_launch = 1;
         MA_TRY(launch_c2r_small(pc->plan, p));
     }
+    ctx->step_end_seq = ctx->launch_seq;
     ctx->step_out = out_block;
     ctx->step_out_end = out_block + (int64_t)(C - 1) * out_stride + B;
     pc->write_index = (w + 1) % P;

@@ -44,6 +44,12 @@ class MetalAudioError(Exception):
     def invalidConfiguration(msg: str) -> "MetalAudioError":
         return MetalAudioError("invalidConfiguration", f"Invalid configuration: {msg}")
 
+    @staticmethod
+    def bufferSizeMismatch(expected: int, actual: int) -> "MetalAudioError":
+        e = MetalAudioError("bufferSizeMismatch", f"Buffer size mismatch: expected {expected} bytes, got {actual}")
+        e.expected, e.actual = expected, actual
+        return e
+
 
 class FFTError(Exception):
     """Sources/MetalDSP/FFT.swift:12-55; ``case`` holds the Swift case name and the payload
@@ -141,6 +147,45 @@ class ConvolutionError(Exception):
                                 f"Output size would overflow: input ({inputSize}) + kernel ({kernelSize}) - 1 exceeds "
                                 "Int.max. Use smaller buffers or process in chunks.",
                                 inputSize=inputSize, kernelSize=kernelSize)
+
+
+# FFT.swift:63: global switch of the sampled NaN / Inf check on transform outputs (the reference
+# always checks in DEBUG builds and only behind this flag in release builds).  Set once at start-up.
+fftValidationEnabled: bool = False
+# Messages of the latest validation warnings (the reference sends them to os.log at debug level).
+fftValidationLog: List[str] = []
+
+
+def validateFFTOutput(buffer, count: int, context: str) -> bool:
+    """FFT.swift:80-134: looks at about 50 evenly spaced values plus the last one (never the whole
+    buffer), reports the first NaN and the first Inf it meets, never raises.  Returns True when
+    either was found.  Does nothing unless ``fftValidationEnabled`` is set."""
+    if not fftValidationEnabled or count <= 0:
+        return False
+    buf = np.asarray(buffer).reshape(-1)
+    sample_count = min(50, count)
+    stride = max(1, count // sample_count)
+    nan_index = inf_index = -1
+    i = 0
+    while i < count and (nan_index < 0 or inf_index < 0):
+        v = buf[i]
+        if nan_index < 0 and np.isnan(v):
+            nan_index = i
+        if inf_index < 0 and np.isinf(v):
+            inf_index = i
+        i += stride
+    if count > 1:
+        last = buf[count - 1]
+        if nan_index < 0 and np.isnan(last):
+            nan_index = count - 1
+        if inf_index < 0 and np.isinf(last):
+            inf_index = count - 1
+    if nan_index >= 0:
+        fftValidationLog.append(f"[FFT] Warning: NaN detected in {context} near index {nan_index}")
+    if inf_index >= 0:
+        fftValidationLog.append(f"[FFT] Warning: Inf detected in {context} near index {inf_index}")
+    del fftValidationLog[:-64]
+    return nan_index >= 0 or inf_index >= 0
 
 
 def _raise_status(st: int, where: str = "") -> None:
@@ -500,6 +545,8 @@ class FFT:
             return
         if self.config.inverse:
             outputImag[:n] *= -1.0
+        validateFFTOutput(outputReal, n, "outputReal")   # FFT.swift:853-854
+        validateFFTOutput(outputImag, n, "outputImag")
 
     def inverse(self, inputReal: np.ndarray, inputImag: np.ndarray, output: np.ndarray) -> None:
         """FFT.swift:889-919: real part of the DFT in the object's direction, times 1/N.
@@ -516,6 +563,7 @@ class FFT:
         if not self.config.inverse:
             out = np.concatenate([out[:1], out[1:][::-1]])
         output[:n] = out
+        validateFFTOutput(output, n, "inverse.output")   # FFT.swift:917-918
 
     def _mag(self, real, imag, out, kind, reference=1.0):
         kh = self.size // 2 + 1
@@ -546,6 +594,77 @@ class FFT:
     @property
     def shouldUseGPU(self) -> bool:
         return True
+
+    @property
+    def shouldUseMetal(self) -> bool:
+        """FFT.swift:1537-1539: the reference's custom-kernel tier (2048 < N <= 8192).  Here the
+        same sizes are the ones whose transform stays in shared memory in a single pass."""
+        return 2048 < self.size <= 8192
+
+    @property
+    def shouldUseMPSGraph(self) -> bool:
+        """FFT.swift:1522-1527: the reference's size class above 8192 points, served here by the
+        multi-pass kernels."""
+        return self.size > 8192
+
+    def _complex(self, input, output, inverse: bool, context: str) -> Backend:
+        n2 = 2 * self.size
+        if len(input) < n2:
+            raise MetalAudioError.bufferSizeMismatch(n2, len(input))
+        x = _f32(np.asarray(input, dtype=np.float32).reshape(-1)[:n2])   # oversized inputs are truncated
+        out = np.empty(n2, dtype=np.float32)
+        st = self._lib.ma_fft_complex_host(self._h, _ptr(x), _ptr(out), 1, 1 if inverse else 0)
+        _raise_status(st, context)
+        if isinstance(output, list):          # the reference resizes its inout array
+            output[:] = out.tolist()
+        else:
+            if len(output) < n2:
+                raise MetalAudioError.bufferSizeMismatch(n2, len(output))
+            output[:n2] = out
+        validateFFTOutput(out, n2, context + ".output")
+        return Backend.cuda
+
+    def forwardGPU(self, input, output) -> Backend:
+        """FFT.swift:945-1107: complex forward DFT of N interleaved (re, im) pairs (2N floats in,
+        2N floats out, unscaled).  Inputs shorter than 2N raise bufferSizeMismatch, longer ones are
+        truncated; ``output`` may be a list (resized) or an array of at least 2N floats."""
+        return self._complex(input, output, False, "forwardGPU")
+
+    def inverseGPU(self, input, output) -> Backend:
+        """FFT.swift:1176-1315: complex inverse DFT with the 1/N scale, same data format."""
+        return self._complex(input, output, True, "inverseGPU")
+
+    def forwardMPSGraph(self, input, outputReal, outputImag) -> None:
+        """FFT.swift:1372-1431: real input, split real / imag output of N values each.  One
+        backend: the same kernels as forward()."""
+        if len(input) < self.size:
+            raise FFTError.inputTooShort(len(input), self.size)
+        self._split_out(np.asarray(input), outputReal, outputImag, "forwardMPSGraph")
+
+    def inverseMPSGraph(self, inputReal, inputImag, output) -> None:
+        """FFT.swift:1445-1515: split spectrum in, N real samples out with the 1/N scale (a true
+        inverse whatever ``config.inverse`` says, as the graph in the reference is)."""
+        n = self.size
+        if len(inputReal) < n or len(inputImag) < n:
+            raise FFTError.inputTooShort(min(len(inputReal), len(inputImag)), n)
+        out = self.inverseBatch(np.asarray(inputReal, dtype=np.float32).reshape(1, -1)[:, :n],
+                                np.asarray(inputImag, dtype=np.float32).reshape(1, -1)[:, :n])[0]
+        if isinstance(output, list):
+            output[:] = out.tolist()
+        else:
+            output[:n] = out
+        validateFFTOutput(out, n, "inverseMPSGraph.output")
+
+    def _split_out(self, x, outputReal, outputImag, context: str) -> None:
+        n = self.size
+        re, im = self.forwardBatch(np.asarray(x, dtype=np.float32).reshape(1, -1)[:, :n])
+        for dst, src in ((outputReal, re[0]), (outputImag, im[0])):
+            if isinstance(dst, list):
+                dst[:] = src.tolist()
+            else:
+                dst[:n] = src
+        validateFFTOutput(re[0], n, context + ".outputReal")
+        validateFFTOutput(im[0], n, context + ".outputImag")
 
     def warmup(self) -> None:
         x = np.zeros(self.size, dtype=np.float32)

@@ -1,10 +1,12 @@
 // CPU execution of the small-FFT kernel bodies through the thread-block emulator.
 // TEST INFRASTRUCTURE ONLY (built by tests/test_kernel_emulation.py into a private .so).
+#include <cstdint>
 #include <cstring>
 #include <vector>
 
 #include "../../metalaudio_b200/csrc/fft_kernels.cuh"
 #include "../../metalaudio_b200/csrc/host_tables.h"
+#include "../../metalaudio_b200/csrc/pconv_tiling.h"
 #include "host_cta.h"
 
 using namespace ma;
@@ -108,6 +110,65 @@ int emul_istft(int n, int hop, const float* in_a, const float* in_b, long long i
     MA_DISPATCH_M(M, RUN)
 #undef RUN
     return rc == 0 ? used_fast : rc;
+}
+
+// Walks the staging schedule of the time-tiled multiply-accumulate for P partitions and t_total
+// output blocks (timeline of P - 1 + t_total rows) exactly as the kernel issues it, and counts
+//   out_of_bounds: fetches whose source row is outside [0, tl_len),
+//   stale:         ring reads that feed a stored output (t < t_total, p < P) but find another
+//                  row, or a clamped one, in the slot.
+// Returns out_of_bounds + stale (0 = sound); the two counts are written to counts[0..1].
+long long emul_tiled_rows(int P, long long t_total, long long* counts) {
+    constexpr int TT = 16;
+    using TL = MacTiling<TT>;
+    const long long tl_len = (long long)P - 1 + t_total;
+    long long oob = 0, stale = 0;
+    const long long t_ctas = (t_total + TL::kWarps * TT - 1) / (TL::kWarps * TT);
+    for (long long y = 0; y < t_ctas; ++y) {
+        const long long t0_cta = y * TL::kWarps * TT;
+        std::vector<long long> want(TL::kRing, INT64_MIN), got(TL::kRing, INT64_MIN);
+        auto stage = [&](long long first, int count) {
+            for (int r = 0; r < count; ++r) {
+                const long long row = first + r;
+                const long long src = TL::fetch_row(row, tl_len);
+                if (src < 0 || src >= tl_len) ++oob;
+                want[row & (TL::kRing - 1)] = row;
+                got[row & (TL::kRing - 1)] = src;
+            }
+        };
+        // a ring read of `row` that feeds output block t at partition p
+        auto read = [&](long long row, long long t, long long p) {
+            if (t >= t_total || p >= P || p < 0) return;  // never stored / never consumed
+            const int slot = (int)(row & (TL::kRing - 1));
+            if (want[slot] != row || got[slot] != row) ++stale;
+        };
+        stage(TL::chunk0_first(P, t0_cta), TL::kChunk0Rows);
+        for (int warp = 0; warp < TL::kWarps; ++warp) {
+            const long long base = TL::base0(P, t0_cta) + warp * TT, t0 = t0_cta + warp * TT;
+            for (int i = 0; i < TT; ++i) read(base + i, t0 + i, 0);  // the initial window
+        }
+        for (int p0 = 0; p0 < P; p0 += TT) {
+            // the kernel issues the look-ahead copies first, but they land in slots the current
+            // chunk does not read (checked here by staging them before the reads)
+            if (p0 + TT < P) stage(TL::lookahead_first(P, t0_cta, p0), TT);
+            for (int warp = 0; warp < TL::kWarps; ++warp) {
+                const long long base = TL::base0(P, t0_cta) + warp * TT, t0 = t0_cta + warp * TT;
+                for (int j = 0; j < TT; ++j) {
+                    const int p = p0 + j;
+                    if (p >= P || p == 0) continue;
+                    // row base - p enters the window and serves output i at partition p + i
+                    for (int i = 0; i < TT; ++i)
+                        if (p + i < P && t0 + i < t_total) {
+                            read(base - p, t0 + i, p + i);
+                            break;  // one genuine consumer is enough to require the row
+                        }
+                }
+            }
+        }
+    }
+    counts[0] = oob;
+    counts[1] = stale;
+    return oob + stale;
 }
 
 }  // extern "C"

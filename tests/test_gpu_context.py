@@ -109,3 +109,50 @@ def test_two_contexts_are_independent_streams(lib):
     [t.start() for t in th]
     [t.join() for t in th]
     assert all(v <= 1e-5 for v in results.values()) and len(results) == 4
+
+
+def test_host_deadline_runs_out_behind_queued_work_and_the_context_recovers(device, lib):
+    """ComputeContext.executeSync's timeout (ComputeContext.swift:137, :176-208): a deadline far
+    shorter than the queued work gives gpuTimeout and leaves the stream draining; a normal wait
+    afterwards succeeds and the results are the ones a run without the timeout gives."""
+    from metalaudio_b200 import FFT, MetalAudioError, Tensor, WindowType
+    from metalaudio_b200 import _lib as L
+    from oracle import float64 as o64
+    n, hop, S, length = 4096, 1024, 32, 1 << 19
+    w = np.hanning(n + 1)[:n].astype(np.float32)
+    fft = FFT(device, FFT.Config(size=n, windowType=WindowType.hann, hopSize=hop), window=w)
+    frames = (length - n) // hop + 1
+    x = np.random.default_rng(3).uniform(-1, 1, (S, length)).astype(np.float32)
+    sig = Tensor(device, (S, length)); sig.copy(x)
+    spec = Tensor(device, (S, frames, n // 2 + 1, 2))
+    device.synchronize()
+    for _ in range(60):                                  # tens of milliseconds of queued kernels
+        fft.stftTensor(sig, spec, None)
+    st = lib.ma_context_sync(device.handle, 1e-4)
+    assert st == L.MA_ERR_TIMEOUT
+    with pytest.raises(MetalAudioError) as e:
+        from metalaudio_b200.dsp import _raise_status
+        _raise_status(st, "synchronize")
+    assert e.value.case == "gpuTimeout"
+    device.synchronize(30)                               # the work itself was never disturbed
+    got = spec.toArray()[:2]
+    assert o64.rel_rms(got[..., 0] + 1j * got[..., 1], o64.stft(x[:2], n, hop, w)) <= 1e-5
+    fft.close(); sig.free(); spec.free()
+
+
+def test_device_side_bounded_wait_gives_up_and_reports_timeout(lib):
+    """A kernel-side wait that nothing satisfies runs into its poll limit, raises the context's
+    error flag and returns; the next synchronisation reports gpuTimeout once, the one after is
+    clean and the context still computes.  The wait is bounded by construction (a few thousand
+    polls of a barrier in one thread): nothing hangs."""
+    from metalaudio_b200 import AudioDevice, FFT, WindowType
+    from metalaudio_b200 import _lib as L
+    dev = AudioDevice(pinnedBytes=1 << 20)
+    assert lib.ma_test_bounded_wait(dev.handle, 0) == L.MA_ERR_INVALID_ARGUMENT
+    assert lib.ma_test_bounded_wait(dev.handle, 2000) == 0
+    assert lib.ma_context_sync(dev.handle, 10.0) == L.MA_ERR_TIMEOUT
+    assert lib.ma_context_sync(dev.handle, 10.0) == 0
+    fft = FFT(dev, FFT.Config(size=256, windowType=WindowType.none))
+    re, im = fft.forwardBatch(np.ones((2, 256), np.float32))
+    assert abs(re[0, 0] - 256) < 1e-3
+    fft.close(); dev.close()

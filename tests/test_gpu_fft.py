@@ -230,3 +230,92 @@ def test_config5_scaled(device, lib):
     y = np.zeros_like(x)
     assert lib.ma_fft_inverse_host(f._h, p(spec), None, p(y), batch, L.LAYOUT_HALF_INTERLEAVED) == 0
     assert o64.rel_rms(y, x) <= TOL
+
+
+@pytest.mark.parametrize("n", [2, 4, 16, 256, 2048, 4096, 8192, 16384, 65536, 1 << 18])
+def test_complex_transform_matches_oracle(device, lib, n):
+    """forwardGPU / inverseGPU (FFT.swift:945-1107, :1176-1315): complex DFT of interleaved
+    (re, im) data, forward unscaled and inverse with 1/N, against numpy's float64 transforms;
+    forward then inverse reproduces the input."""
+    import ctypes
+    rng = np.random.default_rng(7000 + n)
+    batch = 3 if n <= 65536 else 1
+    z = (rng.standard_normal((batch, n)) + 1j * rng.standard_normal((batch, n))).astype(np.complex64)
+    fft = make_fft(device, n)
+    out = np.empty((batch, 2 * n), np.float32)
+    zin = np.ascontiguousarray(z).view(np.float32).reshape(batch, 2 * n)
+    st = lib.ma_fft_complex_host(fft._h, zin.ctypes.data_as(ctypes.c_void_p), out.ctypes.data_as(ctypes.c_void_p),
+                                 batch, 0)
+    assert st == 0
+    got = out.view(np.complex64).reshape(batch, n)
+    assert o64.rel_rms(got, np.fft.fft(z.astype(np.complex128), axis=-1)) <= TOL
+    back = np.empty_like(out)
+    st = lib.ma_fft_complex_host(fft._h, out.ctypes.data_as(ctypes.c_void_p), back.ctypes.data_as(ctypes.c_void_p),
+                                 batch, 1)
+    assert st == 0
+    assert o64.rel_rms(back.view(np.complex64).reshape(batch, n), z) <= TOL
+    inv = np.empty_like(out)
+    st = lib.ma_fft_complex_host(fft._h, zin.ctypes.data_as(ctypes.c_void_p), inv.ctypes.data_as(ctypes.c_void_p),
+                                 batch, 1)
+    assert st == 0
+    assert o64.rel_rms(inv.view(np.complex64).reshape(batch, n), np.fft.ifft(z.astype(np.complex128), axis=-1)) <= TOL
+    fft.close()
+
+
+def test_explicit_backend_api(device):
+    """forwardGPU / inverseGPU / forwardMPSGraph / inverseMPSGraph / shouldUse* on the mirror:
+    data formats, resizing of list outputs, truncation of oversized inputs, bufferSizeMismatch."""
+    from metalaudio_b200 import Backend, FFTError, MetalAudioError
+    n = 4096
+    fft = make_fft(device, n)
+    assert fft.shouldUseMetal and not fft.shouldUseMPSGraph and fft.shouldUseGPU
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal(n).astype(np.float32)
+    inter = np.zeros(2 * n + 10, np.float32)       # real signal as interleaved complex, oversized
+    inter[0:2 * n:2] = x
+    out = []
+    assert fft.forwardGPU(inter, out) is Backend.cuda
+    assert len(out) == 2 * n
+    Z = np.asarray(out, np.float32).view(np.complex64)
+    assert o64.rel_rms(Z, o64.fft_forward(x)) <= TOL
+    back = np.zeros(2 * n, np.float32)
+    fft.inverseGPU(out, back)
+    assert o64.rel_rms(back[0::2], x) <= TOL and np.max(np.abs(back[1::2])) < 1e-5
+    with pytest.raises(MetalAudioError) as e:
+        fft.forwardGPU(np.zeros(100, np.float32), out)
+    assert e.value.case == "bufferSizeMismatch" and (e.value.expected, e.value.actual) == (2 * n, 100)
+    with pytest.raises(MetalAudioError):
+        fft.inverseGPU(np.zeros(2 * n - 1, np.float32), out)
+    re, im, y = [], [], []
+    fft.forwardMPSGraph(x, re, im)
+    assert len(re) == n and o64.rel_rms(np.asarray(re) + 1j * np.asarray(im), o64.fft_forward(x)) <= TOL
+    fft.inverseMPSGraph(re, im, y)
+    assert o64.rel_rms(np.asarray(y), x) <= TOL
+    with pytest.raises(FFTError):
+        fft.forwardMPSGraph(x[:10], re, im)
+    big = make_fft(device, 16384)
+    assert big.shouldUseMPSGraph and not big.shouldUseMetal
+    small = make_fft(device, 1024)
+    assert not small.shouldUseMetal and not small.shouldUseMPSGraph
+    for f in (fft, big, small):
+        f.close()
+
+
+def test_output_validation_flags_non_finite_results(device):
+    """fftValidationEnabled (FFT.swift:63): a NaN in the input reaches every output bin, and the
+    sampled check notices; the call itself neither raises nor alters the result."""
+    from metalaudio_b200 import dsp
+    n = 1024
+    fft = make_fft(device, n)
+    x = np.ones(n, np.float32)
+    x[5] = np.nan
+    re, im = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    dsp.fftValidationEnabled = True
+    try:
+        dsp.fftValidationLog.clear()
+        fft.forward(x, re, im)
+        assert np.isnan(re).all()
+        assert any("NaN detected in outputReal" in m for m in dsp.fftValidationLog)
+    finally:
+        dsp.fftValidationEnabled = False
+    fft.close()

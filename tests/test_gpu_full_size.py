@@ -113,3 +113,52 @@ def test_config3_full_size_impulses(device, lib):
     outside.scatter_(1, idx, 0.0)
     assert float(outside.abs().max()) < 1e-6 * float(want.abs().max()) * 50
     conv.close()
+
+
+def test_config4_full_size_impulses_and_dense_subset(device, lib):
+    """Configuration 4 at full size: 1024 channels, block 64, 512 impulse responses of 262144 taps
+    (one per channel pair, 4096 partitions), 2^19 samples per channel.  A unit impulse at a
+    different position in most channels returns that pair's response at that offset; eight
+    channels carry dense noise and are compared with torch's float64 FFT convolution."""
+    import torch
+    from metalaudio_b200 import Convolution
+    C, B, taps, L = 1024, 64, 262144, 1 << 19
+    n_irs = C // 2
+    g = torch.Generator(device="cuda"); g.manual_seed(1004)
+    decay = torch.exp(-6.907755278982137 * torch.arange(taps, device="cuda", dtype=torch.float64) / 72000.0)
+    irs = torch.randn((n_irs, taps), device="cuda", generator=g, dtype=torch.float64) * decay
+    irs = (irs / irs.pow(2).sum(-1, keepdim=True).sqrt()).float()
+    conv = Convolution(device, Convolution.Mode.partitioned(blockSize=B), channels=C)
+    conv.setKernel(irs.cpu().numpy(), channelToKernel=[c // 2 for c in range(C)])
+    assert conv.partitionCount == 4096
+    assert lib.ma_pconv_reserve(conv._h, L) == 0
+    full = L + taps - 1
+    rng = np.random.default_rng(1014)
+    pos = torch.from_numpy(rng.integers(0, L, C)).cuda()
+    amp = torch.from_numpy(rng.uniform(0.5, 2.0, C).astype(np.float32)).cuda()
+    x = torch.zeros((C, L), device="cuda")
+    x[torch.arange(C, device="cuda"), pos] = amp
+    dense = [0, 1, 510, 511, 512, 513, 1022, 1023]
+    x[dense] = 0.1 * torch.randn((len(dense), L), device="cuda", generator=g)
+    y = torch.empty((C, full), device="cuda")
+    torch.cuda.synchronize()
+    assert lib.ma_pconv_process_dev(conv._h, ptr(x), L, L, ptr(y), full) == 0
+    device.synchronize(120)
+    torch.cuda.synchronize()
+    sparse = torch.tensor([c for c in range(C) if c not in dense], device="cuda")
+    for lo in range(0, sparse.numel(), 128):          # gather in slices: bounded temporary memory
+        ch = sparse[lo:lo + 128]
+        idx = pos[ch][:, None] + torch.arange(taps, device="cuda")[None, :]
+        got = torch.gather(y[ch], 1, idx)
+        want = amp[ch][:, None] * irs[ch // 2]
+        assert rel(got, want) < 1e-5
+        outside = y[ch].clone()
+        outside.scatter_(1, idx, 0.0)
+        assert float(outside.abs().max()) < 1e-6 * float(want.abs().max()) * 50
+    nfft = 1 << 20
+    for c in dense:
+        X = torch.fft.rfft(x[c].double(), n=nfft)
+        H = torch.fft.rfft(irs[c // 2].double(), n=nfft)
+        ref = torch.fft.irfft(X * H, n=nfft)[:full]
+        assert rel(y[c], ref) < 1e-5
+    conv.close()

@@ -159,6 +159,94 @@ def test_config4_scaled(device):
     assert o64.max_over_rms(y, ref) <= 1e-4
 
 
+C4_BLOCK, C4_TAPS = 64, 262144          # configuration 4's own block size and tap count: P = 4096
+
+
+def _c4_case(channels=4, extra_blocks=256):
+    """Input long enough that every one of the 4096 partitions meets a non-zero block spectrum:
+    4096 + extra_blocks input blocks per channel, two impulse responses for four channels."""
+    irs = configs.c4_irs(n_irs=channels // 2, taps=C4_TAPS)
+    x = configs.c4_input(channels=channels, length=(C4_TAPS // C4_BLOCK + extra_blocks) * C4_BLOCK)
+    ref = np.stack([o64.convolve_full(x[i], irs[i // 2]) for i in range(channels)])
+    return irs, x, ref
+
+
+def test_config4_true_partition_count_whole_signal(device):
+    """Configuration 4 at its real partition count (block 64, 262144 taps, 4096 partitions, one
+    impulse response per channel pair): the whole-signal call sums 4096 products per output bin in
+    float32; against the float64 linear convolution and the float32 port of the reference loop."""
+    irs, x, ref = _c4_case()
+    c = conv(device, C4_BLOCK, channels=4)
+    c.setKernel(irs, channelToKernel=[0, 0, 1, 1])
+    assert c.partitionCount == 4096
+    y = c.process(x)
+    assert y.shape == ref.shape
+    assert o64.rel_rms(y, ref) <= TOL
+    assert o64.max_over_rms(y, ref) <= 5e-5
+    # the steady-state part alone (all 4096 partitions active), where the sums are longest
+    lo = C4_TAPS
+    assert o64.rel_rms(y[:, lo:lo + 16384], ref[:, lo:lo + 16384]) <= TOL
+    # the reference's own float32 block loop on one channel's first 32 blocks past the ramp-up
+    port = rp.PartitionedConvolution(C4_BLOCK)
+    port.set_kernel(irs[0])
+    short = x[0, :(4096 + 32) * C4_BLOCK]
+    yp = port.process(short)
+    ys = c.process(np.stack([short] * 4))[0]
+    assert o64.rel_rms(ys, yp) <= TOL
+
+
+def test_config4_true_partition_count_streaming(device, lib):
+    """The same case through the causal streaming step (every step reads all 4096 delay-line
+    spectra of every channel): 4352 steps, compared with the float64 linear convolution."""
+    from metalaudio_b200 import Tensor
+    irs, x, ref = _c4_case()
+    channels, length = x.shape
+    c = conv(device, C4_BLOCK, channels=channels)
+    c.setKernel(irs, channelToKernel=[0, 0, 1, 1])
+    tin = Tensor(device, (channels, length)); tin.copy(x)
+    tout = Tensor(device, (channels, length))
+    for t in range(length // C4_BLOCK):
+        st = lib.ma_pconv_step_dev(c._h, ctypes.c_void_p(tin.pointer + 4 * t * C4_BLOCK), length,
+                                   ctypes.c_void_p(tout.pointer + 4 * t * C4_BLOCK), length)
+        assert st == 0
+    device.synchronize(60)
+    y = tout.toArray()
+    assert o64.rel_rms(y, ref[:, :length]) <= TOL
+    assert o64.max_over_rms(y, ref[:, :length]) <= 5e-5
+    assert o64.rel_rms(y[:, C4_TAPS:], ref[:, C4_TAPS:length]) <= TOL
+
+
+def test_step_after_other_library_work_reads_fresh_input(device, lib):
+    """A streaming step whose input block was produced by another kernel of the library queued
+    just before it (here a biquad) must see that kernel's output: the step's first kernel is only
+    allowed to start early when it directly follows the previous step."""
+    from metalaudio_b200 import Tensor
+    block, taps, channels, steps = 64, 300, 4, 24
+    rng = np.random.default_rng(77)
+    h = (rng.standard_normal(taps) / np.sqrt(taps)).astype(np.float32)
+    x = rng.standard_normal((channels, steps * block)).astype(np.float32)
+    c = conv(device, block, channels=channels)
+    c.setKernel(h)
+    bq = ctypes.c_void_p()
+    assert lib.ma_biquad_create(device.handle, channels, 1, ctypes.byref(bq)) == 0
+    gain = np.array([[0.5, 0.0, 0.0, 0.0, 0.0]], np.float32)    # y = 0.5 x, no memory
+    assert lib.ma_biquad_set_coefficients(bq, gain.ctypes.data_as(ctypes.c_void_p), 1, None) == 0
+    tin = Tensor(device, x.shape); tin.copy(x)
+    mid = Tensor(device, (channels, block))
+    tout = Tensor(device, x.shape)
+    n = steps * block
+    for t in range(steps):
+        assert lib.ma_biquad_process_dev(bq, ctypes.c_void_p(tin.pointer + 4 * t * block), n,
+                                         ctypes.c_void_p(mid.pointer), block, block) == 0
+        assert lib.ma_pconv_step_dev(c._h, ctypes.c_void_p(mid.pointer), block,
+                                     ctypes.c_void_p(tout.pointer + 4 * t * block), n) == 0
+    device.synchronize()
+    y = tout.toArray()
+    lib.ma_biquad_destroy(bq)
+    for i in range(channels):
+        assert o64.rel_rms(y[i], 0.5 * o64.convolve_full(x[i], h)[:n]) <= TOL
+
+
 def test_errors(device):
     from metalaudio_b200 import Convolution, ConvolutionError, MetalAudioError
     c = conv(device, 64)

@@ -176,3 +176,38 @@ def test_biquad_design_matches_port_and_validation():
     assert FilterError.unstable("x").errorDescription == "Filter is unstable: x"
     d = BiquadFilter.Coefficients()
     assert (d.b0, d.b1, d.b2, d.a1, d.a2) == (1, 0, 0, 0, 0)
+
+
+def test_output_validation_samples_like_the_reference():
+    """validateFFTOutput (FFT.swift:80-134): off by default; when enabled it samples about 50 evenly
+    spaced values plus the last one, so a NaN between samples goes unseen, one on a sample or at the
+    end is reported with its index, and nothing ever raises."""
+    from metalaudio_b200 import dsp
+    x = np.zeros(1000, np.float32)
+    x[20] = np.nan
+    assert dsp.validateFFTOutput(x, 1000, "outputReal") is False          # disabled
+    dsp.fftValidationEnabled = True
+    try:
+        dsp.fftValidationLog.clear()
+        assert dsp.validateFFTOutput(x, 1000, "outputReal") is True        # stride 20 lands on index 20
+        assert dsp.fftValidationLog[-1] == "[FFT] Warning: NaN detected in outputReal near index 20"
+        y = np.zeros(1000, np.float32)
+        y[21] = np.inf                                                      # between two samples
+        assert dsp.validateFFTOutput(y, 1000, "outputImag") is False
+        y[999] = np.inf                                                     # the last element is always checked
+        assert dsp.validateFFTOutput(y, 1000, "outputImag") is True
+        assert dsp.fftValidationLog[-1] == "[FFT] Warning: Inf detected in outputImag near index 999"
+        assert dsp.validateFFTOutput(np.zeros(0, np.float32), 0, "empty") is False
+        z = np.array([np.nan, np.inf, 0.0], np.float32)                     # count < 50: every element
+        assert dsp.validateFFTOutput(z, 3, "tiny") is True
+        assert any("NaN" in m and "index 0" in m for m in dsp.fftValidationLog[-2:])
+        assert any("Inf" in m and "index 1" in m for m in dsp.fftValidationLog[-2:])
+        assert dsp.validateFFTOutput(np.ones(4096, np.float32), 4096, "clean") is False
+    finally:
+        dsp.fftValidationEnabled = False
+
+
+def test_buffer_size_mismatch_error_text():
+    e = MetalAudioError.bufferSizeMismatch(8192, 100)
+    assert e.case == "bufferSizeMismatch" and (e.expected, e.actual) == (8192, 100)
+    assert str(e) == "Buffer size mismatch: expected 8192 bytes, got 100"

@@ -30,7 +30,8 @@ def emul():
         pytest.skip("nvcc not available")
     deps = [SRC, os.path.join(HERE, "kernel_emulation", "host_cta.h"),
             os.path.join(HERE, "..", "metalaudio_b200", "csrc", "fft_core.cuh"),
-            os.path.join(HERE, "..", "metalaudio_b200", "csrc", "fft_kernels.cuh")]
+            os.path.join(HERE, "..", "metalaudio_b200", "csrc", "fft_kernels.cuh"),
+            os.path.join(HERE, "..", "metalaudio_b200", "csrc", "pconv_tiling.h")]
     if not os.path.exists(OUT) or any(os.path.getmtime(d) > os.path.getmtime(OUT) for d in deps):
         subprocess.run([nvcc, "-std=c++17", "-O1", "-shared", "-Xcompiler", "-fPIC", "-diag-suppress", "20011,20014",
                         "-Wno-deprecated-gpu-targets", "-o", OUT, SRC, "-lpthread"], check=True)
@@ -40,6 +41,8 @@ def emul():
     lib.emul_c2r.argtypes = [ctypes.c_int, FP, FP, LL, LL, LL, LL, ctypes.c_int, FP, ctypes.c_int]
     lib.emul_istft.argtypes = [ctypes.c_int, ctypes.c_int, FP, FP, LL, LL, LL, LL, ctypes.c_int, FP, ctypes.c_float,
                                FP, LL, LL, ctypes.c_int, ctypes.c_int]
+    lib.emul_tiled_rows.argtypes = [ctypes.c_int, LL, ctypes.POINTER(LL)]
+    lib.emul_tiled_rows.restype = LL
     return lib
 
 
@@ -112,3 +115,14 @@ def test_stft_istft(emul, n, hop, length, chunks, kind):
     ws = rp.window_sum(f, n, hop, w, 0.0)
     msk = ws >= 1e-2 * ws.max()
     assert o64.rel_rms(y[:, msk], yref[:, msk]) <= 1e-5
+
+
+@pytest.mark.parametrize("partitions", [1, 4, 5, 8, 15, 16, 17, 20, 24, 31, 32, 33, 64, 100, 512])
+@pytest.mark.parametrize("blocks", [1, 3, 63, 64, 65, 200])
+def test_tiled_multiply_accumulate_row_schedule(emul, partitions, blocks):
+    """The whole-signal multiply-accumulate stages timeline rows a chunk of 16 partitions ahead.
+    For partition counts that are not multiples of 16 (and below 16) the staged range reaches
+    before the first timeline row: every fetch must stay inside the channel's timeline, and every
+    row that feeds a stored output must be the genuine one."""
+    counts = (LL * 2)()
+    assert emul.emul_tiled_rows(partitions, blocks, counts) == 0, (counts[0], counts[1])
