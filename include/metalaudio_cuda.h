@@ -111,6 +111,12 @@ ma_status ma_context_destroy(ma_context* ctx);
  * reference's default of 2 s, ComputeContext.swift:137).  Polls an event; on expiry
  * returns MA_ERR_TIMEOUT and leaves the stream draining. */
 ma_status ma_context_sync(ma_context* ctx, double timeout_s);
+/* Device workspace of the *_host transforms (ma_stft_host, ma_istft_host): `bytes` of device memory
+ * in two lanes, allocated once here (or, at a default of 2 x 256 MiB, by the first such call) and
+ * kept until the context is destroyed - the "pre-allocated staging" half of AudioDevice /
+ * ComputeContext in this backend.  Grows only when a single signal with its results does not fit a
+ * lane. */
+ma_status ma_context_reserve_workspace(ma_context* ctx, size_t bytes);
 /* Device name into `buf` (AudioDevice.name). */
 ma_status ma_context_device_name(ma_context* ctx, char* buf, size_t buf_len);
 /* The context's cudaStream_t as an opaque pointer, for callers that order their own
@@ -263,6 +269,9 @@ ma_status ma_istft_output_length(ma_fft_plan* plan, int64_t frames, int64_t* len
 ma_status ma_stft_dev(ma_fft_plan* plan, const float* signals, int64_t length,
                       int64_t signal_stride, int64_t n_signals, float* out_a, float* out_b,
                       float* mag, int32_t mag_kind, float db_reference, int32_t layout);
+/* Host form: the signals are cut into chunks that fit a lane of the context's workspace; with
+ * pinned host memory (ma_host_alloc) copy-in, transform and copy-out of successive chunks overlap
+ * on three streams and the host waits once, at the end; nothing is allocated per call. */
 ma_status ma_stft_host(ma_fft_plan* plan, const float* signals, int64_t length,
                        int64_t signal_stride, int64_t n_signals, float* out_a, float* out_b,
                        float* mag, int32_t mag_kind, float db_reference, int32_t layout);

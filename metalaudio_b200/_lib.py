@@ -24,6 +24,7 @@ SIGNATURES = {
     "ma_context_create": (c_int32, [c_int32, c_size_t, POINTER(c_void_p)]),
     "ma_context_destroy": (c_int32, [c_void_p]),
     "ma_context_sync": (c_int32, [c_void_p, c_double]),
+    "ma_context_reserve_workspace": (c_int32, [c_void_p, c_size_t]),
     "ma_context_device_name": (c_int32, [c_void_p, c_char_p, c_size_t]),
     "ma_context_stream": (c_void_p, [c_void_p]),
     "ma_context_mark_lost": (c_int32, [c_void_p]),

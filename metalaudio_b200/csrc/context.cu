@@ -51,7 +51,7 @@ ma_status after_launch(ma_context* ctx) {
     return MA_OK;
 }
 
-static bool is_pinned(const void* p) {
+bool is_pinned(const void* p) {
     cudaPointerAttributes a;
     cudaError_t e = cudaPointerGetAttributes(&a, p);
     if (e != cudaSuccess) {
@@ -117,6 +117,27 @@ ma_status copy_d2h(ma_context* ctx, void* host, const void* dptr, size_t bytes) 
             h ^= 1;
         }
     }
+    return MA_OK;
+}
+
+ma_status workspace_lanes(ma_context* ctx, size_t min_lane_bytes, char** lane0, char** lane1, size_t* lane_bytes) {
+    constexpr size_t kDefaultLane = (size_t)256 << 20;
+    if (ctx->ws == nullptr || ctx->ws_lane_bytes < min_lane_bytes) {
+        if (ctx->fault_site == MA_FAULT_ALLOC) return injected(ctx);
+        size_t want = ctx->ws == nullptr && min_lane_bytes < kDefaultLane ? kDefaultLane : min_lane_bytes;
+        want = (want + 255) & ~(size_t)255;
+        if (ctx->ws != nullptr) {
+            MA_CUDA(cudaDeviceSynchronize());
+            (void)cudaFree(ctx->ws);
+            ctx->ws = nullptr;
+            ctx->ws_lane_bytes = 0;
+        }
+        MA_CUDA(cudaMalloc((void**)&ctx->ws, 2 * want));
+        ctx->ws_lane_bytes = want;
+    }
+    *lane0 = ctx->ws;
+    *lane1 = ctx->ws + ctx->ws_lane_bytes;
+    *lane_bytes = ctx->ws_lane_bytes;
     return MA_OK;
 }
 
@@ -200,6 +221,12 @@ ma_status ma_context_create(int32_t device_index, size_t pinned_bytes, ma_contex
     cudaError_t e = cudaGetDeviceProperties(&prop, device_index);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking);
+    for (int i = 0; i < 2 && e == cudaSuccess; ++i) {
+        e = cudaEventCreateWithFlags(&ctx->ev_in[i], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_k[i], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_out[i], cudaEventDisableTiming);
+    }
     if (e == cudaSuccess) {
         ctx->sm_count = prop.multiProcessorCount;
         std::strncpy(ctx->name, prop.name, sizeof(ctx->name) - 1);
@@ -247,7 +274,14 @@ ma_status ma_context_destroy(ma_context* ctx) {
     if (ctx->pinned) (void)cudaFreeHost(ctx->pinned);
     if (ctx->d_error_flag) (void)cudaFree(ctx->d_error_flag);
     if (ctx->h_error_flag) (void)cudaFreeHost(ctx->h_error_flag);
+    for (int i = 0; i < 2; ++i) {
+        if (ctx->ev_in[i]) (void)cudaEventDestroy(ctx->ev_in[i]);
+        if (ctx->ev_k[i]) (void)cudaEventDestroy(ctx->ev_k[i]);
+        if (ctx->ev_out[i]) (void)cudaEventDestroy(ctx->ev_out[i]);
+    }
+    if (ctx->ws) (void)cudaFree(ctx->ws);
     if (ctx->copy_stream) (void)cudaStreamDestroy(ctx->copy_stream);
+    if (ctx->d2h_stream) (void)cudaStreamDestroy(ctx->d2h_stream);
     if (ctx->stream) (void)cudaStreamDestroy(ctx->stream);
     (void)cudaGetLastError();
     delete ctx;
@@ -328,6 +362,13 @@ ma_status ma_test_bounded_wait(ma_context* ctx, int32_t polls) {
     if (polls < 1 || polls > (1 << 16)) return MA_ERR_INVALID_ARGUMENT;
     bounded_wait_probe_kernel<<<1, 1, 0, ctx->stream>>>(ctx->d_error_flag, polls);
     return after_launch(ctx);
+}
+
+ma_status ma_context_reserve_workspace(ma_context* ctx, size_t bytes) {
+    MA_TRY(enter(ctx, MA_FAULT_ALLOC));
+    char *a, *b;
+    size_t lane;
+    return workspace_lanes(ctx, (bytes + 1) / 2, &a, &b, &lane);
 }
 
 ma_status ma_buffer_alloc(ma_context* ctx, size_t bytes, void** dptr) {

@@ -362,6 +362,102 @@ ma_status ma_fft_magnitude_host(ma_fft_plan* plan, const float* re, const float*
     return st;
 }
 
+// The two calls below cut their signals into chunks that fit one lane of the context's device
+// workspace and run the chunks through a three-stage pipeline when the host memory is pinned:
+// host -> device copies on one stream, the transform on the context's stream, device -> host
+// copies on a third, chained by events, two lanes deep - chunk c's results travel back while chunk
+// c+1 is transformed and chunk c+2 is on its way in (PCIe is full duplex).  Nothing is allocated
+// per call once the workspace exists, and the host waits once, at the end.  Pageable host memory
+// takes the same chunks one after the other through the staging buffer.
+namespace {
+
+size_t round256(size_t b) { return (b + 255) & ~(size_t)255; }
+
+struct Pipe {
+    ma_context* ctx;
+    bool pinned;
+    int64_t chunk;  // signals per chunk
+    char* lane[2];
+    ma_status st = MA_OK;
+
+    void before_copy_in(int64_t c) {
+        const int l = (int)(c & 1);
+        if (pinned && c >= 2 && st == MA_OK) fail(cudaStreamWaitEvent(ctx->copy_stream, ctx->ev_k[l], 0));
+    }
+    void before_kernels(int64_t c) {
+        const int l = (int)(c & 1);
+        if (!pinned || st != MA_OK) return;
+        fail(cudaEventRecord(ctx->ev_in[l], ctx->copy_stream));
+        fail(cudaStreamWaitEvent(ctx->stream, ctx->ev_in[l], 0));
+        if (c >= 2) fail(cudaStreamWaitEvent(ctx->stream, ctx->ev_out[l], 0));
+    }
+    void before_copy_out(int64_t c) {
+        const int l = (int)(c & 1);
+        if (!pinned || st != MA_OK) return;
+        fail(cudaEventRecord(ctx->ev_k[l], ctx->stream));
+        fail(cudaStreamWaitEvent(ctx->d2h_stream, ctx->ev_k[l], 0));
+    }
+    void after_copy_out(int64_t c) {
+        const int l = (int)(c & 1);
+        if (pinned && st == MA_OK) fail(cudaEventRecord(ctx->ev_out[l], ctx->d2h_stream));
+    }
+    // rows x width floats between a strided host array and a dense-strided device array
+    void in2d(void* d, size_t dpitch, const void* h, size_t hpitch, size_t width, size_t rows) {
+        if (st != MA_OK || rows == 0) return;
+        if (pinned) {
+            fail(cudaMemcpy2DAsync(d, dpitch, h, hpitch, width, rows, cudaMemcpyHostToDevice, ctx->copy_stream));
+        } else if (dpitch == width && hpitch == width) {
+            st = copy_h2d(ctx, d, h, width * rows);
+        } else {
+            for (size_t r = 0; r < rows && st == MA_OK; ++r)
+                st = copy_h2d(ctx, (char*)d + r * dpitch, (const char*)h + r * hpitch, width);
+        }
+    }
+    void out2d(void* h, size_t hpitch, const void* d, size_t dpitch, size_t width, size_t rows) {
+        if (st != MA_OK || rows == 0) return;
+        if (pinned) {
+            fail(cudaMemcpy2DAsync(h, hpitch, d, dpitch, width, rows, cudaMemcpyDeviceToHost, ctx->d2h_stream));
+        } else if (dpitch == width && hpitch == width) {
+            st = copy_d2h(ctx, h, d, width * rows);
+        } else {
+            for (size_t r = 0; r < rows && st == MA_OK; ++r)
+                st = copy_d2h(ctx, (char*)h + r * hpitch, (const char*)d + r * dpitch, width);
+        }
+    }
+    // waits for everything the call queued, also after a failure half-way
+    ma_status finish() {
+        cudaError_t e = cudaStreamSynchronize(ctx->copy_stream);
+        cudaError_t e2 = cudaStreamSynchronize(ctx->stream);
+        cudaError_t e3 = cudaStreamSynchronize(ctx->d2h_stream);
+        if (st == MA_OK) {
+            if (e != cudaSuccess) st = cuda_fail(e);
+            else if (e2 != cudaSuccess) st = cuda_fail(e2);
+            else if (e3 != cudaSuccess) st = cuda_fail(e3);
+        }
+        return st;
+    }
+    void fail(cudaError_t e) {
+        if (e != cudaSuccess && st == MA_OK) st = cuda_fail(e);
+    }
+};
+
+// Chunk size and lanes for rows that need `row_bytes` of workspace each (sub-buffers included).
+ma_status pipe_open(Pipe& p, ma_context* ctx, bool pinned, int64_t rows, size_t row_bytes, size_t fixed_bytes) {
+    size_t lane_bytes = 0;
+    MA_TRY(workspace_lanes(ctx, row_bytes + fixed_bytes, &p.lane[0], &p.lane[1], &lane_bytes));
+    int64_t chunk = (int64_t)((lane_bytes - fixed_bytes) / row_bytes);
+    if (chunk < 1) chunk = 1;
+    // at least four chunks when there are rows enough, so that the three stages overlap
+    if (pinned && rows >= 4 && chunk > (rows + 3) / 4) chunk = (rows + 3) / 4;
+    if (chunk > rows) chunk = rows;
+    p.ctx = ctx;
+    p.pinned = pinned;
+    p.chunk = chunk;
+    return MA_OK;
+}
+
+}  // namespace
+
 ma_status ma_stft_host(ma_fft_plan* plan, const float* signals, int64_t length, int64_t signal_stride,
                        int64_t n_signals, float* out_a, float* out_b, float* mag, int32_t mag_kind,
                        float db_reference, int32_t layout) {
@@ -377,34 +473,38 @@ ma_status ma_stft_host(ma_fft_plan* plan, const float* signals, int64_t length, 
     int64_t total, total_out;
     if (mul_overflow(frames, n_signals, &total) || mul_overflow(total, 4 * (int64_t)plan->n, &total_out))
         return MA_ERR_BATCH_OVERFLOW;
-    // Device copy of the signals is dense: signal s at s*dlen (dlen even keeps pairs aligned).
-    const int64_t dlen = length + (length & 1);
-    const size_t a_b = (size_t)(total * floats_a(plan->n, layout)) * sizeof(float);
-    const size_t b_b = two_arrays(layout) ? a_b : 0;
-    const size_t m_b = mag ? (size_t)(total * (plan->n / 2 + 1)) * sizeof(float) : 0;
-    float *d_in = nullptr, *d_a = nullptr, *d_b = nullptr, *d_m = nullptr;
-    ma_status st = temp_alloc(ctx, (size_t)(dlen * n_signals) * sizeof(float), (void**)&d_in);
-    if (st == MA_OK) st = temp_alloc(ctx, a_b, (void**)&d_a);
-    if (st == MA_OK && b_b) st = temp_alloc(ctx, b_b, (void**)&d_b);
-    if (st == MA_OK && m_b) st = temp_alloc(ctx, m_b, (void**)&d_m);
-    if (st == MA_OK) {
-        if (signal_stride == length && dlen == length) {
-            st = copy_h2d(ctx, d_in, signals, (size_t)(length * n_signals) * sizeof(float));
-        } else {
-            for (int64_t s = 0; s < n_signals && st == MA_OK; ++s)
-                st = copy_h2d(ctx, d_in + s * dlen, signals + s * signal_stride, (size_t)length * sizeof(float));
-        }
+    // Device copy of a chunk's signals is dense: signal s at s*dlen, dlen a multiple of 4 floats so
+    // every row keeps the 16-byte alignment the bulk-staged kernels want.
+    const int64_t dlen = (length + 3) & ~(int64_t)3;
+    const int64_t fa = frames * floats_a(plan->n, layout);         // floats per signal in array a (and b)
+    const int64_t fm = mag ? frames * (plan->n / 2 + 1) : 0;
+    const bool two = two_arrays(layout);
+    const size_t row_bytes = sizeof(float) * (size_t)(dlen + fa + (two ? fa : 0) + fm);
+    const bool pinned = is_pinned(signals) && is_pinned(out_a) && (!two || is_pinned(out_b)) && (!mag || is_pinned(mag));
+    Pipe pp;
+    MA_TRY(pipe_open(pp, ctx, pinned, n_signals, row_bytes, 4 * 256));
+    for (int64_t s0 = 0, c = 0; s0 < n_signals && pp.st == MA_OK; s0 += pp.chunk, ++c) {
+        const int64_t cs = n_signals - s0 < pp.chunk ? n_signals - s0 : pp.chunk;
+        char* base = pp.lane[c & 1];
+        float* d_in = reinterpret_cast<float*>(base);
+        float* d_a = reinterpret_cast<float*>(base + round256(sizeof(float) * (size_t)(pp.chunk * dlen)));
+        float* d_b = two ? d_a + ((pp.chunk * fa + 63) & ~(int64_t)63) : nullptr;
+        float* d_m = mag ? (two ? d_b : d_a) + ((pp.chunk * fa + 63) & ~(int64_t)63) : nullptr;
+        pp.before_copy_in(c);
+        pp.in2d(d_in, sizeof(float) * (size_t)dlen, signals + s0 * signal_stride, sizeof(float) * (size_t)signal_stride,
+                sizeof(float) * (size_t)length, (size_t)cs);
+        pp.before_kernels(c);
+        if (pp.st == MA_OK)
+            pp.st = ma_stft_dev(plan, d_in, length, dlen, cs, d_a, d_b, d_m, mag_kind, db_reference, layout);
+        pp.before_copy_out(c);
+        const size_t wa = sizeof(float) * (size_t)(cs * fa);
+        pp.out2d(out_a + s0 * fa, wa, d_a, wa, wa, 1);
+        if (two) pp.out2d(out_b + s0 * fa, wa, d_b, wa, wa, 1);
+        if (mag) pp.out2d(mag + s0 * fm, sizeof(float) * (size_t)(cs * fm), d_m, sizeof(float) * (size_t)(cs * fm),
+                          sizeof(float) * (size_t)(cs * fm), 1);
+        pp.after_copy_out(c);
     }
-    if (st == MA_OK)
-        st = ma_stft_dev(plan, d_in, length, dlen, n_signals, d_a, d_b, d_m, mag_kind, db_reference, layout);
-    if (st == MA_OK) st = copy_d2h(ctx, out_a, d_a, a_b);
-    if (st == MA_OK && b_b) st = copy_d2h(ctx, out_b, d_b, b_b);
-    if (st == MA_OK && m_b) st = copy_d2h(ctx, mag, d_m, m_b);
-    temp_free(ctx, d_in);
-    temp_free(ctx, d_a);
-    temp_free(ctx, d_b);
-    temp_free(ctx, d_m);
-    return st;
+    return pp.finish();
 }
 
 ma_status ma_istft_host(ma_fft_plan* plan, const float* in_a, const float* in_b, int64_t frames,
@@ -422,27 +522,32 @@ ma_status ma_istft_host(ma_fft_plan* plan, const float* in_a, const float* in_b,
     int64_t total, total_in;
     if (mul_overflow(frames, n_signals, &total) || mul_overflow(total, 4 * (int64_t)plan->n, &total_in))
         return MA_ERR_BATCH_OVERFLOW;
-    const size_t a_b = (size_t)(total * floats_a(plan->n, layout)) * sizeof(float);
-    const size_t b_b = two_arrays(layout) ? a_b : 0;
-    float *d_a = nullptr, *d_b = nullptr, *d_o = nullptr;
-    ma_status st = temp_alloc(ctx, a_b, (void**)&d_a);
-    if (st == MA_OK && b_b) st = temp_alloc(ctx, b_b, (void**)&d_b);
-    if (st == MA_OK) st = temp_alloc(ctx, (size_t)(out_len * n_signals) * sizeof(float), (void**)&d_o);
-    if (st == MA_OK) st = copy_h2d(ctx, d_a, in_a, a_b);
-    if (st == MA_OK && b_b) st = copy_h2d(ctx, d_b, in_b, b_b);
-    if (st == MA_OK) st = ma_istft_dev(plan, d_a, d_b, frames, n_signals, d_o, out_len, floor, layout);
-    if (st == MA_OK) {
-        if (out_stride == out_len || n_signals == 1) {
-            st = copy_d2h(ctx, out, d_o, (size_t)(out_len * n_signals) * sizeof(float));
-        } else {
-            for (int64_t s = 0; s < n_signals && st == MA_OK; ++s)
-                st = copy_d2h(ctx, out + s * out_stride, d_o + s * out_len, (size_t)out_len * sizeof(float));
-        }
+    const int64_t fa = frames * floats_a(plan->n, layout);
+    const bool two = two_arrays(layout);
+    const int64_t dol = (out_len + 3) & ~(int64_t)3;  // device row stride of the output
+    const size_t row_bytes = sizeof(float) * (size_t)(fa + (two ? fa : 0) + dol);
+    const bool pinned = is_pinned(in_a) && (!two || is_pinned(in_b)) && is_pinned(out);
+    if (n_signals == 1) out_stride = out_len;
+    Pipe pp;
+    MA_TRY(pipe_open(pp, ctx, pinned, n_signals, row_bytes, 4 * 256));
+    for (int64_t s0 = 0, c = 0; s0 < n_signals && pp.st == MA_OK; s0 += pp.chunk, ++c) {
+        const int64_t cs = n_signals - s0 < pp.chunk ? n_signals - s0 : pp.chunk;
+        char* base = pp.lane[c & 1];
+        float* d_a = reinterpret_cast<float*>(base);
+        float* d_b = two ? d_a + ((pp.chunk * fa + 63) & ~(int64_t)63) : nullptr;
+        float* d_o = (two ? d_b : d_a) + ((pp.chunk * fa + 63) & ~(int64_t)63);
+        pp.before_copy_in(c);
+        const size_t wa = sizeof(float) * (size_t)(cs * fa);
+        pp.in2d(d_a, wa, in_a + s0 * fa, wa, wa, 1);
+        if (two) pp.in2d(d_b, wa, in_b + s0 * fa, wa, wa, 1);
+        pp.before_kernels(c);
+        if (pp.st == MA_OK) pp.st = ma_istft_dev(plan, d_a, d_b, frames, cs, d_o, dol, floor, layout);
+        pp.before_copy_out(c);
+        pp.out2d(out + s0 * out_stride, sizeof(float) * (size_t)out_stride, d_o, sizeof(float) * (size_t)dol,
+                 sizeof(float) * (size_t)out_len, (size_t)cs);
+        pp.after_copy_out(c);
     }
-    temp_free(ctx, d_a);
-    temp_free(ctx, d_b);
-    temp_free(ctx, d_o);
-    return st;
+    return pp.finish();
 }
 
 }  // extern "C"

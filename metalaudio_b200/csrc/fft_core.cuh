@@ -33,8 +33,27 @@
 namespace ma {
 
 // ---------------------------------------------------------------- complex helpers
+// On the device a complex add / subtract is ONE packed two-wide FP32 instruction (add.f32x2 /
+// fma.rn.f32x2 of sm_100): these kernels are bound by instruction issue, and half of a
+// transform's arithmetic is complex additions.  a - b is fma(b, -1, a): exact negation, one
+// rounding, the same result as the subtraction.
+#if defined(__CUDA_ARCH__) && !defined(MA_SCALAR_MATH)
+#define MA_PACKED 1
+MA_HD float2 cadd(float2 a, float2 b) { return __fadd2_rn(a, b); }
+MA_HD float2 csub(float2 a, float2 b) { return __ffma2_rn(b, make_float2(-1.f, -1.f), a); }
+// a + s*t and a - s*t for a real scale s, one instruction each
+MA_HD float2 cfma_scaled(float2 t, float s, float2 a) { return __ffma2_rn(t, make_float2(s, s), a); }
+// element-wise product and multiply-add of pairs
+MA_HD float2 pmul(float2 a, float2 b) { return __fmul2_rn(a, b); }
+MA_HD float2 pfma(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+#else
+#define MA_PACKED 0
 MA_HD float2 cadd(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
 MA_HD float2 csub(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
+MA_HD float2 cfma_scaled(float2 t, float s, float2 a) { return make_float2(fmaf(t.x, s, a.x), fmaf(t.y, s, a.y)); }
+MA_HD float2 pmul(float2 a, float2 b) { return make_float2(a.x * b.x, a.y * b.y); }
+MA_HD float2 pfma(float2 a, float2 b, float2 c) { return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y)); }
+#endif
 MA_HD float2 cmul(float2 a, float2 b) {
     return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
 }
@@ -124,26 +143,47 @@ struct Bfly<2> {
         a[1] = csub(t, a[1]);
     }
 };
+// e + (-i)*d and e - (-i)*d.  (-i)*d = (d.y, -d.x) crosses the components, which a packed add cannot
+// do without first moving registers, so these four sums stay scalar.
+MA_HD void add_sub_mi(float2 e, float2 d, float2& plus, float2& minus) {
+    plus = make_float2(e.x + d.y, e.y - d.x);
+    minus = make_float2(e.x - d.y, e.y + d.x);
+}
+
 template <>
 struct Bfly<4> {
     static MA_HD void run(float2* a) {
         float2 t0 = cadd(a[0], a[2]);
         float2 t1 = csub(a[0], a[2]);
         float2 t2 = cadd(a[1], a[3]);
-        float2 t3 = cmul_mi(csub(a[1], a[3]));
+        float2 d = csub(a[1], a[3]);
         a[0] = cadd(t0, t2);
-        a[1] = cadd(t1, t3);
         a[2] = csub(t0, t2);
-        a[3] = csub(t1, t3);
+        add_sub_mi(t1, d, a[1], a[3]);
     }
 };
 
+// a[K] = e[K] + W_R^K o[K], a[K + R/2] = e[K] - W_R^K o[K], with the constant twiddle folded into
+// the sums where that saves instructions.
 template <int R, int K>
 struct BflyCombine {
     static MA_HD void run(float2* a, const float2* e, const float2* o) {
-        float2 t = mul_wconst<R, K>(o[K]);
-        a[K] = cadd(e[K], t);
-        a[K + R / 2] = csub(e[K], t);
+        constexpr float kS = 0.70710678118654752440f;  // sqrt(1/2)
+        if constexpr (4 * K == R) {  // -i
+            add_sub_mi(e[K], o[K], a[K], a[K + R / 2]);
+        } else if constexpr (8 * K == R) {  // (1 - i)/sqrt2: t = (x + y, y - x) * kS
+            const float2 t = make_float2(o[K].x + o[K].y, o[K].y - o[K].x);
+            a[K] = cfma_scaled(t, kS, e[K]);
+            a[K + R / 2] = cfma_scaled(t, -kS, e[K]);
+        } else if constexpr (8 * K == 3 * R) {  // (-1 - i)/sqrt2: t = (y - x, -(x + y)) * kS
+            const float2 t = make_float2(o[K].y - o[K].x, -(o[K].x + o[K].y));
+            a[K] = cfma_scaled(t, kS, e[K]);
+            a[K + R / 2] = cfma_scaled(t, -kS, e[K]);
+        } else {
+            float2 t = mul_wconst<R, K>(o[K]);
+            a[K] = cadd(e[K], t);
+            a[K + R / 2] = csub(e[K], t);
+        }
         if constexpr (K + 1 < R / 2) BflyCombine<R, K + 1>::run(a, e, o);
     }
 };

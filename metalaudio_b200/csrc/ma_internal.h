@@ -11,7 +11,14 @@ struct ma_context {
     int device = 0;
     int sm_count = 0;
     cudaStream_t stream = nullptr;
-    cudaStream_t copy_stream = nullptr;
+    cudaStream_t copy_stream = nullptr;   // host -> device leg of the pipelined *_host calls
+    cudaStream_t d2h_stream = nullptr;    // device -> host leg
+    // Device workspace of the *_host calls: two lanes of ws_lane_bytes each, allocated once
+    // (ma_context_reserve_workspace or the first *_host call) and grown only when a single row
+    // does not fit.  Lane events: input copied, kernels done, output copied.
+    char* ws = nullptr;
+    size_t ws_lane_bytes = 0;
+    cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_k[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
     void* pinned = nullptr;       // staging buffer, used as two halves
     size_t pinned_bytes = 0;
     cudaEvent_t ev_half[2] = {nullptr, nullptr};
@@ -50,6 +57,12 @@ ma_status after_launch(ma_context* ctx);
 // through the pinned buffer otherwise).  Synchronous with respect to the host buffer.
 ma_status copy_h2d(ma_context* ctx, void* dptr, const void* host, size_t bytes);
 ma_status copy_d2h(ma_context* ctx, void* host, const void* dptr, size_t bytes);
+
+// True when the pointer is page-locked host memory the runtime knows (cudaHostAlloc / registered).
+bool is_pinned(const void* p);
+// Makes sure the context's two workspace lanes hold at least `min_lane_bytes` each (grow-only; a
+// growth waits for all queued work first).  Returns the lanes.
+ma_status workspace_lanes(ma_context* ctx, size_t min_lane_bytes, char** lane0, char** lane1, size_t* lane_bytes);
 
 // Stream-ordered temporary device memory for the *_host entry points.
 ma_status temp_alloc(ma_context* ctx, size_t bytes, void** dptr);
