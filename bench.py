@@ -538,9 +538,12 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         x = host_in[:sample].numpy()
         cpu_port_stft_istft(x[:cores], window, cores)
         best = min(cpu_port_stft_istft(x, window, cores) for _ in range(3))
+        one = min(cpu_port_stft_istft(x[:2], window, 1) for _ in range(2))
         cpu = {"value": sample * FRAMES / best, "unit": "frames/s", "cores": cores, "kind": "port",
+               "one_thread": 2 * FRAMES / one,
                "sample": f"{sample} of the 256 signals ({sample * FRAMES} frames), float32 scipy.fft + numpy port of "
-                         f"the reference's stft/istft, {cores} threads, best of 3"}
+                         f"the reference's stft/istft, {cores} threads, best of 3; one_thread: 2 signals on one thread, "
+                         "best of 2"}
     rig.unpin(host_in)
 
     if rig.dist is not None:

@@ -276,8 +276,30 @@ public:
 
     int size() const { return config_.size; }
     const std::vector<float>& window() const { return window_; }
+
+private:
+    Backend complexTransform(const std::vector<float>& input, std::vector<float>& output, int inverse) {
+        const size_t n2 = 2 * (size_t)config_.size;
+        if (input.size() < n2)
+            throw MetalAudioError("bufferSizeMismatch", "Buffer size mismatch: expected " + std::to_string(n2) +
+                                                            " bytes, got " + std::to_string(input.size()));
+        output.assign(n2, 0.f);
+        throwStatus(ma_fft_complex_host(plan_, input.data(), output.data(), 1, inverse), inverse ? "inverseGPU" : "forwardGPU");
+        return Backend::cuda;
+    }
+
+public:
     Backend optimalBackend() const { return Backend::cuda; }
     bool shouldUseGPU() const { return true; }
+    // FFT.swift:1522-1539: the reference's size classes, kept as queries (one backend serves all).
+    bool shouldUseMetal() const { return config_.size > 2048 && config_.size <= 8192; }
+    bool shouldUseMPSGraph() const { return config_.size > 8192; }
+
+    // FFT.swift:945-1107, :1176-1315: complex transform of N interleaved (re, im) pairs, forward
+    // unscaled / inverse with 1/N.  Short inputs throw bufferSizeMismatch, longer ones are
+    // truncated, the output is resized to 2N.
+    Backend forwardGPU(const std::vector<float>& input, std::vector<float>& output) { return complexTransform(input, output, 0); }
+    Backend inverseGPU(const std::vector<float>& input, std::vector<float>& output) { return complexTransform(input, output, 1); }
 
     // FFT.swift:818-855.  Non-throwing pointer API: outputs are zeroed on failure.  Direction
     // follows Config::inverse (one setup serves both methods in the reference).

@@ -68,12 +68,16 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
             failed.append(src)
     if failed:
         raise RuntimeError(f"nvcc failed for {failed}")
-    link = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-Wno-deprecated-gpu-targets",
+    tmp = LIB_PATH + f".tmp{os.getpid()}"   # linked beside the target, then moved into place in one step
+    link = [nvcc, "-shared", "-o", tmp, *objs, "-Wno-deprecated-gpu-targets",
             "-gencode", "arch=compute_100a,code=sm_100a"]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         sys.stderr.write(r.stdout)
+        if os.path.exists(tmp):
+            os.remove(tmp)
         raise RuntimeError("link of libmetalaudio_cuda.so failed")
+    os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

@@ -72,6 +72,10 @@ ma_status ma_fft_plan_create(ma_context* ctx, int32_t n, const float* window, in
         p->h_window.assign(window, window + n);
         st = upload(ctx, window, sizeof(float) * (size_t)n, (void**)&p->d_window);
     }
+    if (st == MA_OK && !p->large && window != nullptr) {
+        const std::vector<float> syn = make_synthesis_table(window, p->m);
+        if (!syn.empty()) st = upload(ctx, syn.data(), syn.size() * sizeof(float), (void**)&p->d_window_syn);
+    }
     if (st == MA_OK && !p->large) {
         cudaError_t e = cudaMalloc((void**)&p->d_norm, 2 * sizeof(float) * (size_t)hop);
         if (e != cudaSuccess) st = cuda_fail(e);
@@ -101,6 +105,7 @@ ma_status ma_fft_plan_destroy(ma_fft_plan* plan) {
     }
     large_plan_destroy(plan);
     if (plan->d_window) (void)cudaFree(plan->d_window);
+    if (plan->d_window_syn) (void)cudaFree(plan->d_window_syn);
     if (plan->d_twM) (void)cudaFree(plan->d_twM);
     if (plan->d_twInv) (void)cudaFree(plan->d_twInv);
     if (plan->d_twN) (void)cudaFree(plan->d_twN);

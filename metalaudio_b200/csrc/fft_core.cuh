@@ -37,7 +37,7 @@ namespace ma {
 // fma.rn.f32x2 of sm_100): these kernels are bound by instruction issue, and half of a
 // transform's arithmetic is complex additions.  a - b is fma(b, -1, a): exact negation, one
 // rounding, the same result as the subtraction.
-#if defined(__CUDA_ARCH__) && !defined(MA_SCALAR_MATH)
+#if defined(__CUDA_ARCH__) && __CUDA_ARCH__ >= 1000 && !defined(MA_SCALAR_MATH)
 #define MA_PACKED 1
 MA_HD float2 cadd(float2 a, float2 b) { return __fadd2_rn(a, b); }
 MA_HD float2 csub(float2 a, float2 b) { return __ffma2_rn(b, make_float2(-1.f, -1.f), a); }

@@ -182,10 +182,11 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
         for (int q = 0; q < R; ++q) wreg[q] = make_float2(1.0f, 1.0f);
     }
 
-    // Kernels with the layout fixed at compile time also prefetch their input.
+    // Kernels with the layout fixed at compile time keep their twiddles in registers and have the
+    // whole next frame staged by one bulk asynchronous copy (TMA unit).  (Per-thread 8-byte
+    // asynchronous copies were tried instead: they cost more load/store-pipe wavefronts than they hide.)
     constexpr bool TWALU = ALIGNED && LAYOUT >= 0 && plan_pairable<M>();
-    constexpr bool PREFETCH = false;  // per-thread 8-byte async copies cost more load/store-pipe wavefronts than they hide
-    constexpr bool BULK = TWALU;      // whole next frame staged by one bulk async copy (TMA unit)
+    constexpr bool BULK = TWALU;
     float2 twb[tw_base_count<P>()];
     float2 wherm[R / 2 + 1];
     (void)wherm;
@@ -206,14 +207,6 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
     int64_t f = g - s * p.frames_per_signal;
     const int64_t ds = stride_frames / p.frames_per_signal;
     const int64_t df = stride_frames - ds * p.frames_per_signal;
-    if constexpr (PREFETCH) {
-        if (g < p.total_frames) {
-            const float2* src0 = reinterpret_cast<const float2*>(p.in + s * p.signal_stride + f * (int64_t)p.hop);
-#pragma unroll
-            for (int q = 0; q < R; ++q) MA_ASYNC_COPY8(stage + q * S::THREADS + tid, src0 + t + q * T);
-        }
-        MA_ASYNC_COMMIT();
-    }
     // Bulk staging: slot-private frame buffer and mbarrier; thread 0 of the slot issues copies.
     float2* stage_slot = stage + slot * M;
     uint64_t* bar = reinterpret_cast<uint64_t*>(stage + S::STAGE) + 2 * slot;
@@ -236,29 +229,7 @@ MA_HD void r2c_body(const R2CParams& p, Cta& cta, float2* smem) {
         const float* src = p.in + (active ? s * p.signal_stride + start : 0);
 
         float2 v[R];
-        if constexpr (PREFETCH) {
-            // This frame's samples were copied asynchronously into this thread's staging slots
-            // while the previous frame was transformed; queue the next frame's right away.
-            MA_ASYNC_WAIT_ALL();
-#pragma unroll
-            for (int q = 0; q < R; ++q) {
-                const float2 x = active ? stage[q * S::THREADS + tid] : make_float2(0.f, 0.f);
-                v[q] = make_float2(x.x * wreg[q].x, x.y * wreg[q].y);
-            }
-            {
-                int64_t fn = f + df, sn = s + ds;
-                if (fn >= p.frames_per_signal) {
-                    fn -= p.frames_per_signal;
-                    ++sn;
-                }
-                if (g + stride_frames < p.total_frames) {
-                    const float2* nsrc = reinterpret_cast<const float2*>(p.in + sn * p.signal_stride + fn * (int64_t)p.hop);
-#pragma unroll
-                    for (int q = 0; q < R; ++q) MA_ASYNC_COPY8(stage + q * S::THREADS + tid, nsrc + t + q * T);
-                }
-                MA_ASYNC_COMMIT();
-            }
-        } else if (bulk) {
+        if (bulk) {
             if (active) {
                 if (!cta.bulk_wait(bar, phase) && p.error_flag != nullptr) *p.error_flag = 1;
                 phase ^= 1;
@@ -380,6 +351,8 @@ struct C2RParams {
     const float* norm_mid_inv;  // iSTFT: their reciprocals
     int32_t* error_flag;        // set to 1 when a bounded wait ran out
     int32_t dependent_launch;   // launched with programmatic stream serialization (see fft_small.cu)
+    const float4* window_syn;   // register-ring iSTFT: synthesis window in thread order with 1/N folded in
+                                // (host_tables.h make_synthesis_table), or nullptr for no window
     const float2* mul;          // HALF_INTERLEAVED input only: every bin is multiplied by mul[k] on load (N/2+1 values), or nullptr
     const float2* twM;          // stage tables: FftPlanRev<M> when plan_pairable<M>(), else FftPlan<M>
     const float2* twN;
@@ -838,19 +811,29 @@ MA_HD void istft_body(const C2RParams& p, Cta& cta, float2* smem) {
 
 // Fast iSTFT for paired plans when hop/2 is a multiple of T (e.g. N = 4096, hop = 1024) and the
 // spectra are in a half layout.  Differences from istft_body:
-//  * thread t only ever touches overlap-add positions congruent to t modulo T, so the ring is
-//    thread-private: no barrier for accumulate or emit, only the two FFT exchanges remain;
+//  * thread t only ever touches overlap-add positions congruent to t modulo T, so the overlap-add
+//    ring is thread-private: no barrier for accumulate or emit, only the two FFT exchanges remain;
 //  * completed samples go straight from registers to HBM, multiplied by the precomputed
 //    reciprocal of the interior window sum (frames near the ends of the signal take the exact
 //    per-sample path);
 //  * twiddles live in registers (power chains) and the layout is fixed at compile time.
 // OVT is the overlap count N/hop when fixed at compile time (0: read it from p.hop).
-// smem: exchange buffer(s) | ring [R][T] float2 | staged row [M+2] float2 | mbarrier.
-template <int M>
+//  * OVT > 0: the ring lives in REGISTERS.  Slots are numbered from the current frame's start, a
+//    frame completes the first H = R/OVT of them, and the sum for slot q >= H is written to
+//    register q - H, which is where the next frame expects it: the rotation costs nothing.  Window
+//    multiply and accumulate are one packed multiply-add per sample pair.  The registers the ring
+//    takes are the ones the window used to hold: the window (in thread order, 1/N folded in) sits
+//    in the shared memory the ring used to take and is read with 16-byte loads.  (Reading it from
+//    global memory through L1 instead, to afford a second exchange buffer, measured 27 % slower:
+//    the loads' latency is exposed at four warps per scheduler.)
+//  * OVT == 0: ring [R][T] float2 in shared memory, window in registers.
+// smem: exchange buffer | ring or window table [R*T] float2 | staged row [M+2] float2 | mbarrier.
+template <int M, int OVT = 0>
 struct IstftFastShape {
     using P = FftPlan<M>;
+    static constexpr bool REGRING = OVT > 0;
     static constexpr int ELEMS = smem_elems_per_fft<M, 1>();
-    static constexpr int RING = P::R * P::T;
+    static constexpr int RING = P::R * P::T;  // the ring, or (REGRING) the window table
     static constexpr int ROW = M + 2;  // staged spectrum row with the alignment slack
     static constexpr int EXCH = 1;  // exchange buffers (1: a barrier before each write instead of a second buffer)
     static constexpr int EXCH_ELEMS = (EXCH * ELEMS + 1) & ~1;  // keeps the staged row 16-byte aligned
@@ -882,11 +865,11 @@ inline bool istft_fast_ok(const C2RParams& p) {
 template <int M, int LAYOUT, int OVT, class Cta>
 MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
     using P = FftPlan<M>;
-    using SH = IstftFastShape<M>;
+    using SH = IstftFastShape<M, OVT>;
     constexpr int R = P::R, T = P::T, N = 2 * M;
+    constexpr bool REGRING = SH::REGRING;
     // Every layout stages the next frame's spectrum row(s) with bulk copies: one copy of the complex
     // row, or one each of the magnitude and the phase row.
-    constexpr bool STAGED = true;
     constexpr bool POLAR = LAYOUT == LAYOUT_HALF_POLAR;
     float2* ring = smem + SH::EXCH_ELEMS;
     float2* stage = ring + SH::RING;
@@ -913,14 +896,22 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
     const int64_t F = p.frames_per_signal;
     const bool normalise = !(p.window == nullptr && p.floor < 0.f);
 
-    float2 wreg[R];
+    float2 wreg[REGRING ? 1 : R];
+    if constexpr (REGRING) {
+        // window table into shared memory, once: entry [q2*T + t] is read by thread t alone
+        float4* wtab = reinterpret_cast<float4*>(ring);
 #pragma unroll
-    for (int q = 0; q < R; ++q) {
-        const int n = t + q * T;
-        if (p.window != nullptr)
-            wreg[q] = make_float2(MA_LDG(p.window + 2 * n) * scale, MA_LDG(p.window + 2 * n + 1) * scale);
-        else
-            wreg[q] = make_float2(scale, scale);
+        for (int q2 = 0; q2 < R / 2; ++q2)
+            wtab[q2 * T + t] = p.window_syn != nullptr ? MA_LDG(p.window_syn + q2 * T + t) : make_float4(scale, scale, scale, scale);
+    } else {
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int n = t + q * T;
+            if (p.window != nullptr)
+                wreg[q] = make_float2(MA_LDG(p.window + 2 * n) * scale, MA_LDG(p.window + 2 * n + 1) * scale);
+            else
+                wreg[q] = make_float2(scale, scale);
+        }
     }
     float2 twb[tw_base_count<FftPlanRev<M>>()];
     float2 wherm[R / 2 + 1];
@@ -950,40 +941,49 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
     f -= lead;
     int64_t G = G0 - lead;
 
-    if (STAGED && t == 0) cta.bulk_init(bar);
+    if (t == 0) cta.bulk_init(bar);
+    // register ring (REGRING): racc[i] = (odd sample, even sample) partial sums of slot i of the next
+    // frame, in the pair order the inverse transform produces
+    constexpr int HR = REGRING ? R / OVT : R;
+    float2 racc[REGRING ? R - HR : 1];
+    if constexpr (REGRING) {
 #pragma unroll
-    for (int q = 0; q < R; ++q) ring[q * T + t] = make_float2(0.f, 0.f);
+        for (int i = 0; i < R - HR; ++i) racc[i] = make_float2(0.f, 0.f);
+    } else {
+#pragma unroll
+        for (int q = 0; q < R; ++q) ring[q * T + t] = make_float2(0.f, 0.f);
+    }
     cta.sync();
-    if (STAGED && t == 0) start_copy(s, f);
+    if (t == 0) start_copy(s, f);
 
     for (; G < G1; ++G, ++f) {
         if (f == F) {  // next signal: nothing overlaps across signals
             f = 0;
             ++s;
+            if constexpr (REGRING) {
 #pragma unroll
-            for (int q = 0; q < R; ++q) ring[q * T + t] = make_float2(0.f, 0.f);
+                for (int i = 0; i < R - HR; ++i) racc[i] = make_float2(0.f, 0.f);
+            } else {
+#pragma unroll
+                for (int q = 0; q < R; ++q) ring[q * T + t] = make_float2(0.f, 0.f);
+            }
         }
         float2 v[R];
-        if constexpr (STAGED) {
-            if (!cta.bulk_wait(bar, phase) && p.error_flag != nullptr) *p.error_flag = 1;
-            phase ^= 1;
-            auto issue_next = [&]() {
-                if (t == 0 && G + 1 < G1) {
-                    const bool wrap = f + 1 == F;
-                    start_copy(wrap ? s + 1 : s, wrap ? 0 : f + 1);
-                }
-            };
-            if constexpr (POLAR) {
-                c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1>(
-                    p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage, issue_next, nullptr);
-            } else {
-                const StagedRow r = staged_row<M>(p, s, f);
-                c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1>(
-                    p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage + r.shift, issue_next, r.row);
+        if (!cta.bulk_wait(bar, phase) && p.error_flag != nullptr) *p.error_flag = 1;
+        phase ^= 1;
+        auto issue_next = [&]() {
+            if (t == 0 && G + 1 < G1) {
+                const bool wrap = f + 1 == F;
+                start_copy(wrap ? s + 1 : s, wrap ? 0 : f + 1);
             }
+        };
+        if constexpr (POLAR) {
+            c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1>(
+                p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage, issue_next, nullptr);
         } else {
-            c2r_frame<M, LAYOUT, true, Cta, false, NoHook, SH::EXCH == 1>(p, true, s, f, G, t, smem, SH::ELEMS, parity,
-                                                                         v, cta, twb, wherm);
+            const StagedRow r = staged_row<M>(p, s, f);
+            c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1>(
+                p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage + r.shift, issue_next, r.row);
         }
 
         // v[q] = (x[2n+1], x[2n]) * N for n = t + q*T.  Overlap-add in this thread's ring column.
@@ -994,31 +994,63 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
         // every sample this frame completes has all its overlapping frames present
         const bool interior = !last && start >= (int64_t)(N - hop);
         float* out = p.out + s * p.out_signal_stride + start;
-        if (OVT > 0 && emit && interior && normalise) {
-            // The common frame (all overlapping frames present, inside this CTA's range): no
-            // per-slot decisions, reciprocals of the window sum already in registers.
-            constexpr int H = OVT > 0 ? R / OVT : 1;
+        if constexpr (REGRING) {
+            const float4* wtab = reinterpret_cast<const float4*>(ring) + t;
+            if (emit && interior && normalise) {
+                // The common frame (every overlapping frame present, inside this CTA's range): no
+                // per-slot decisions, reciprocals of the window sum already in registers.
 #pragma unroll
-            for (int q = 0; q < R; ++q) {
-                float2* slot = ring + ((q + rot) & (R - 1)) * T + t;
-                float2 acc = make_float2(v[q].y * wreg[q].x, v[q].x * wreg[q].y);
-                if (q < R - H) {  // slot already holds earlier frames
-                    const float2 old = *slot;
-                    acc.x += old.x;
-                    acc.y += old.y;
+                for (int q2 = 0; q2 < R / 2; ++q2) {
+                    const float4 w4 = wtab[q2 * T];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int q = 2 * q2 + e;
+                        const float2 wsw = e == 0 ? make_float2(w4.x, w4.y) : make_float2(w4.z, w4.w);
+                        // (odd, even) sample pair of slot q with every frame up to this one
+                        const float2 acc = q < R - HR ? pfma(v[q], wsw, racc[q]) : pmul(v[q], wsw);
+                        if (q < HR)
+                            *reinterpret_cast<float2*>(out + 2 * (t + q * T)) =
+                                make_float2(acc.y * ninv[q < HN ? q : 0].x, acc.x * ninv[q < HN ? q : 0].y);
+                        else
+                            racc[q - HR] = acc;  // slot q is slot q - H of the next frame
+                    }
                 }
-                if (q < H) {  // complete after this frame
-                    *reinterpret_cast<float2*>(out + 2 * (t + q * T)) = make_float2(acc.x * ninv[q].x, acc.y * ninv[q].y);
-                } else {
-                    *slot = acc;
+                continue;
+            }
+#pragma unroll
+            for (int q2 = 0; q2 < R / 2; ++q2) {
+                const float4 w4 = wtab[q2 * T];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int q = 2 * q2 + e;
+                    const float2 wsw = e == 0 ? make_float2(w4.x, w4.y) : make_float2(w4.z, w4.w);
+                    const float2 acc = q < R - HR ? pfma(v[q], wsw, racc[q]) : pmul(v[q], wsw);
+                    const int i0 = 2 * (t + q * T);
+                    if ((q < HR || last) && emit) {
+                        float2 r2 = make_float2(acc.y, acc.x);
+                        if (normalise) {
+                            if (interior) {
+                                const float2 inv = MA_LDG(reinterpret_cast<const float2*>(p.norm_mid_inv + i0));
+                                r2.x *= inv.x;
+                                r2.y *= inv.y;
+                            } else {
+                                const int64_t o = start + i0;
+                                r2.x = r2.x / window_sum_at(p.window, o, N, hop, F, p.floor);
+                                r2.y = r2.y / window_sum_at(p.window, o + 1, N, hop, F, p.floor);
+                            }
+                        }
+                        *reinterpret_cast<float2*>(out + i0) = r2;
+                    }
+                    if (q >= HR) racc[q - HR] = acc;
                 }
             }
             continue;
         }
+        // shared-memory ring (overlap count known only at run time)
 #pragma unroll
-        for (int q = 0; q < R; ++q) {
+        for (int q = 0; q < (REGRING ? 0 : R); ++q) {
             float2* slot = ring + ((q + rot) & (R - 1)) * T + t;
-            float2 acc = make_float2(v[q].y * wreg[q].x, v[q].x * wreg[q].y);
+            float2 acc = make_float2(v[q].y * wreg[REGRING ? 0 : q].x, v[q].x * wreg[REGRING ? 0 : q].y);
             if (q < R - h) {  // slot already holds earlier frames
                 const float2 old = *slot;
                 acc.x += old.x;

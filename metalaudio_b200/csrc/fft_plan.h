@@ -12,6 +12,7 @@ struct ma_fft_plan {
     int hop = 0;
     bool large = false;         // N > 8192: multi-pass path
     float* d_window = nullptr;  // N floats or nullptr
+    float* d_window_syn = nullptr;  // the same window in the register-ring iSTFT's thread order, times 1/N (paired plans)
     float2* d_twM = nullptr;    // stage twiddle tables, forward radix order (fft_core.cuh layout)
     float2* d_twInv = nullptr;  // stage tables the inverse kernels use (reversed order when pairable)
     float2* d_twN = nullptr;    // small path: exp(-2 pi i k/N), k <= M/2

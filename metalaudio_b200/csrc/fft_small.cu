@@ -199,25 +199,31 @@ template <int M>
 static ma_status launch_istft_t(ma_fft_plan* plan, C2RParams& p) {
     constexpr int T = FftPlan<M>::T;
     const bool fast = istft_fast_ok<M>(p);
-    const size_t smem = fast ? (size_t)IstftFastShape<M>::SMEM_BYTES
-                             : 2 * smem_elems_per_fft<M, 1>() * sizeof(float2) + 2 * M * sizeof(float);
-    static int per_sm[2][64] = {{0}, {0}};
-    ma_context* ctx = plan->ctx;
-    int& occ = per_sm[fast ? 1 : 0][ctx->device & 63];
     const int ov = fast ? (2 * M) / p.hop : 0;
+    // 0: general kernel; 1: fast, overlap count read at run time; 2: fast with the overlap count 4
+    // fixed at compile time (register ring)
+    const int kind = !fast ? 0 : (ov == 4 ? 2 : 1);
+    const size_t smem = kind == 2 ? (size_t)IstftFastShape<M, 4>::SMEM_BYTES
+                      : kind == 1 ? (size_t)IstftFastShape<M, 0>::SMEM_BYTES
+                                  : 2 * smem_elems_per_fft<M, 1>() * sizeof(float2) + 2 * M * sizeof(float);
+    static int per_sm[3][64] = {{0}, {0}, {0}};
+    ma_context* ctx = plan->ctx;
+    int& occ = per_sm[kind][ctx->device & 63];
     const int variant = !fast ? 0
                               : (p.layout == LAYOUT_HALF_INTERLEAVED ? 1 : (p.layout == LAYOUT_HALF_PACKED ? 3 : 5)) +
                                     (ov == 4 ? 1 : 0);
-    if (occ == 0) {
-        if (fast) MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_INTERLEAVED, 4>, T, smem, &occ));
-        else MA_TRY(occupancy(istft_kernel<M>, T, smem, &occ));
-        if (fast) {  // the other variants share the footprint; raise their shared-memory limit too
-            int dummy;
-            MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_INTERLEAVED, 0>, T, smem, &dummy));
+    if (occ == 0) {  // the layout variants of a kind share its footprint; raise every one's shared-memory limit
+        int dummy;
+        if (kind == 2) {
+            MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_INTERLEAVED, 4>, T, smem, &occ));
             MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_PACKED, 4>, T, smem, &dummy));
-            MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_PACKED, 0>, T, smem, &dummy));
             MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_POLAR, 4>, T, smem, &dummy));
+        } else if (kind == 1) {
+            MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_INTERLEAVED, 0>, T, smem, &occ));
+            MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_PACKED, 0>, T, smem, &dummy));
             MA_TRY(occupancy(istft_fast_kernel<M, LAYOUT_HALF_POLAR, 0>, T, smem, &dummy));
+        } else {
+            MA_TRY(occupancy(istft_kernel<M>, T, smem, &occ));
         }
     }
     // Chunks per signal: enough CTAs to fill the device a few times over, but chunks long
@@ -273,6 +279,7 @@ ma_status launch_istft_small(ma_fft_plan* plan, C2RParams p) {
     }
     p.norm_mid = plan->d_norm;
     p.norm_mid_inv = plan->d_norm + plan->hop;
+    p.window_syn = p.window != nullptr ? reinterpret_cast<const float4*>(plan->d_window_syn) : nullptr;
     p.error_flag = plan->ctx->d_error_flag;
     ma_status st = MA_ERR_UNSUPPORTED;
 #define RUN(MM) st = launch_istft_t<MM>(plan, p);

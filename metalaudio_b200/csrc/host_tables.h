@@ -9,6 +9,25 @@
 
 #include "fft_core.cuh"
 
+// Compile-time dispatch over the supported in-shared-memory complex lengths.
+#define MA_DISPATCH_M(M_VALUE, MACRO)   \
+    switch (M_VALUE) {                  \
+        case 1: MACRO(1); break;        \
+        case 2: MACRO(2); break;        \
+        case 4: MACRO(4); break;        \
+        case 8: MACRO(8); break;        \
+        case 16: MACRO(16); break;      \
+        case 32: MACRO(32); break;      \
+        case 64: MACRO(64); break;      \
+        case 128: MACRO(128); break;    \
+        case 256: MACRO(256); break;    \
+        case 512: MACRO(512); break;    \
+        case 1024: MACRO(1024); break;  \
+        case 2048: MACRO(2048); break;  \
+        case 4096: MACRO(4096); break;  \
+        default: break;                 \
+    }
+
 namespace ma {
 
 // exp(-2*pi*i*j/len) for j in [0, count)
@@ -120,6 +139,35 @@ inline bool plan_pairable_rt(int m) {
     }
 }
 
+// Synthesis-window table of the register-ring iSTFT (istft_fast_body with a compile-time overlap
+// count): thread t of a frame reads, for q2 < R/2, one 16-byte entry [q2*T + t] =
+// (w[2n0+1], w[2n0], w[2n1+1], w[2n1]) / N with n0 = t + 2*q2*T, n1 = n0 + T - the pair order the
+// inverse transform leaves its samples in, and the 1/N scale folded in.  2M floats; empty when the
+// complex length has no paired plan.  window == nullptr means all ones.
+inline std::vector<float> make_synthesis_table(const float* window, int m) {
+    std::vector<float> tab;
+    int R = 0, T = 0;
+#define MA_RT_CASE(MM)                  \
+    if (plan_pairable<MM>()) {          \
+        R = FftPlan<MM>::R;             \
+        T = FftPlan<MM>::T;             \
+    }
+    MA_DISPATCH_M(m, MA_RT_CASE)
+#undef MA_RT_CASE
+    if (R < 2) return tab;
+    const float scale = 1.0f / (float)(2 * m);
+    tab.resize((size_t)(2 * m));
+    for (int q2 = 0; q2 < R / 2; ++q2)
+        for (int t = 0; t < T; ++t)
+            for (int e = 0; e < 2; ++e) {
+                const int n = t + (2 * q2 + e) * T;
+                float* dst = &tab[(size_t)(4 * (q2 * T + t) + 2 * e)];
+                dst[0] = (window ? window[2 * n + 1] : 1.0f) * scale;
+                dst[1] = (window ? window[2 * n] : 1.0f) * scale;
+            }
+    return tab;
+}
+
 // Interior window-sum table of the iSTFT normaliser: for an output position with every
 // overlapping frame present the sum of squared window depends only on the position modulo
 // hop.  Accumulated in float32 in increasing frame order (largest window offset first), as the
@@ -141,22 +189,3 @@ inline std::vector<float> make_norm_table(const float* window, int n, int hop, f
 }
 
 }  // namespace ma
-
-// Compile-time dispatch over the supported in-shared-memory complex lengths.
-#define MA_DISPATCH_M(M_VALUE, MACRO)   \
-    switch (M_VALUE) {                  \
-        case 1: MACRO(1); break;        \
-        case 2: MACRO(2); break;        \
-        case 4: MACRO(4); break;        \
-        case 8: MACRO(8); break;        \
-        case 16: MACRO(16); break;      \
-        case 32: MACRO(32); break;      \
-        case 64: MACRO(64); break;      \
-        case 128: MACRO(128); break;    \
-        case 256: MACRO(256); break;    \
-        case 512: MACRO(512); break;    \
-        case 1024: MACRO(1024); break;  \
-        case 2048: MACRO(2048); break;  \
-        case 4096: MACRO(4096); break;  \
-        default: break;                 \
-    }

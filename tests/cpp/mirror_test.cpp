@@ -80,6 +80,23 @@ static double rel_rms(const std::vector<double>& a, const std::vector<double>& b
 }
 
 static void gpu_tests() {
+    {   // explicit-backend complex transform: a real impulse train as interleaved complex data
+        AudioDevice dev;
+        FFT fft(dev, FFT::Config(256, false, WindowType::none));
+        std::vector<float> in(2 * 256 + 4, 0.f), out, back;
+        in[2 * 3] = 1.f;                                   // delta at n = 3 -> X[k] = exp(-2 pi i 3k/256)
+        CHECK(fft.forwardGPU(in, out) == Backend::cuda && out.size() == 512);
+        for (int k = 0; k < 256; k += 17) {
+            const double a = -2.0 * M_PI * 3.0 * k / 256.0;
+            CHECK(std::fabs(out[2 * k] - std::cos(a)) < 1e-5 && std::fabs(out[2 * k + 1] - std::sin(a)) < 1e-5);
+        }
+        fft.inverseGPU(out, back);
+        CHECK(std::fabs(back[6] - 1.f) < 1e-5f && std::fabs(back[8]) < 1e-5f && std::fabs(back[7]) < 1e-5f);
+        bool threw = false;
+        try { fft.forwardGPU(std::vector<float>(10), out); } catch (const MetalAudioError& e) { threw = e.errorCase == "bufferSizeMismatch"; }
+        CHECK(threw);
+        CHECK(!fft.shouldUseMetal() && !fft.shouldUseMPSGraph());
+    }
     AudioDevice dev;
     std::printf("device: %s\n", dev.name().c_str());
     const int n = 1024;

@@ -88,6 +88,8 @@ int emul_istft(int n, int hop, const float* in_a, const float* in_b, long long i
     for (int r = 0; r < hop; ++r) norm[(size_t)(hop + r)] = 1.0f / norm[(size_t)r];
     p.norm_mid = norm.data();
     p.norm_mid_inv = norm.data() + hop;
+    auto syn = make_synthesis_table(window, M);
+    p.window_syn = (window != nullptr && !syn.empty()) ? reinterpret_cast<const float4*>(syn.data()) : nullptr;
     p.twM = twM.data(); p.twN = twN.data();
     int rc = -1;
     int used_fast = 0;
@@ -95,7 +97,7 @@ int emul_istft(int n, int hop, const float* in_a, const float* in_b, long long i
     {                                                                                            \
         constexpr int ELEMS = smem_elems_per_fft<MM, 1>();                                       \
         const bool fast = istft_fast_ok<MM>(p);                                                  \
-        const size_t smem = fast ? (size_t)IstftFastShape<MM>::SMEM_BYTES                        \
+        const size_t smem = fast ? (size_t)(2 * MM / hop == 4 ? IstftFastShape<MM, 4>::SMEM_BYTES : IstftFastShape<MM, 0>::SMEM_BYTES) \
                                  : 2 * ELEMS * sizeof(float2) + (size_t)n * sizeof(float);       \
         used_fast = fast ? 1 : 0;                                                                \
         run_grid(nblocks, FftPlan<MM>::T, smem, [&](HostCta& cta, void* sm) {                    \

@@ -211,3 +211,30 @@ def test_buffer_size_mismatch_error_text():
     e = MetalAudioError.bufferSizeMismatch(8192, 100)
     assert e.case == "bufferSizeMismatch" and (e.expected, e.actual) == (8192, 100)
     assert str(e) == "Buffer size mismatch: expected 8192 bytes, got 100"
+
+
+def test_swift_package_calls_only_declared_entry_points():
+    """The Swift sources (written against the header, never compiled here) may only call functions
+    and use constants the C header declares."""
+    header = open(os.path.join(ROOT, "include", "metalaudio_cuda.h")).read()
+    declared = set(re.findall(r"\b(ma_[a-z0-9_]+)\s*\(", header))
+    constants = set(re.findall(r"\b(MA_[A-Z0-9_]+)\b", header))
+    swift_dir = os.path.join(ROOT, "swift", "Sources")
+    seen = set()
+    for dirpath, _, files in os.walk(swift_dir):
+        for f in files:
+            if not f.endswith(".swift"):
+                continue
+            text = open(os.path.join(dirpath, f)).read()
+            assert "NOT COMPILED" in text.splitlines()[0], f
+            for name in re.findall(r"\b(ma_[a-z0-9_]+)\s*\(", text):
+                if name == "ma_status":      # the status type used as a converting initialiser
+                    continue
+                assert name in declared, (f, name)
+                seen.add(name)
+            for name in re.findall(r"\b(MA_[A-Z0-9_]+)\b", text):
+                assert name in constants, (f, name)
+    assert {"ma_context_create", "ma_fft_plan_create", "ma_stft_host", "ma_istft_host", "ma_pconv_process_host",
+            "ma_fft_complex_host", "ma_fftconv_process_host"} <= seen
+    assert os.path.exists(os.path.join(ROOT, "swift", "Package.swift"))
+    assert os.path.exists(os.path.join(ROOT, "swift", "Sources", "CMetalAudioCUDA", "module.modulemap"))
