@@ -402,9 +402,37 @@ MA_HD void stage_write(const float2* v, int t, float2* sbuf) {
     }
 }
 
-template <class P, int W, int S, bool PAIRED, bool TWALU>
+// Stage-1 twiddles from shared memory.  The first twiddled stage has only Ns = radix(0) distinct
+// twiddle sets (j = jv % Ns), so a table of Ns * r entries (1-2 KB) serves every thread of the CTA:
+// r/2 16-byte loads per butterfly, all lanes of a warp inside one or two wavefronts, instead of the
+// r-2 complex multiplications of a power chain.  Used by the inverse kernels (measured 1 % faster
+// there and exact table values instead of chained products; in the forward kernel, whose
+// load/store pipe is busier, the extra shared-memory reads cost 2 %).  Layout: entry [kp*Ns + j] (float4) =
+// (w^(2kp+1), w^(2kp+2)) for butterfly-local twiddle base j; powers >= r are filled with 1.
+template <class P>
+constexpr __host__ __device__ bool stage1_table_ok() {
+    return P::NS >= 2 && P::ns_before(1) <= 16 && P::radix(1) >= 4;
+}
+template <class P>
+constexpr __host__ __device__ int stage1_table_elems() {  // float2 units, a multiple of 2
+    return stage1_table_ok<P>() ? P::radix(1) * P::ns_before(1) : 0;
+}
+// Cooperative fill from the plan's global stage table (layout [k-1][j]); the caller synchronises.
+template <class P>
+MA_HD void stage1_table_fill(float2* tab, const float2* __restrict__ tws, int tid, int nthreads) {
+    if constexpr (stage1_table_ok<P>()) {
+        constexpr int r = P::radix(1), Ns = P::ns_before(1), off = stage_tw_offset<P>(1);
+        for (int i = tid; i < r * Ns; i += nthreads) {
+            const int e = i & 1, j = (i >> 1) % Ns, kp = (i >> 1) / Ns;
+            const int k = 2 * kp + 1 + e;
+            tab[i] = k < r ? MA_LDG(tws + off + (k - 1) * Ns + j) : make_float2(1.f, 0.f);
+        }
+    }
+}
+
+template <class P, int W, int S, bool PAIRED, bool TWALU, bool TWS1 = false>
 MA_HD void stage_read_compute(float2* v, int t, const float2* sbuf,
-                              const float2* __restrict__ twM, const float2* twb) {
+                              const float2* __restrict__ twM, const float2* twb, const float2* tw_s1 = nullptr) {
     constexpr int M = P::M, r = P::radix(S), Ns = P::ns_before(S), NB = P::R / r;
     constexpr int stride = M / r;
     using A = ExchangeAddr<W, stride, r>;
@@ -420,7 +448,15 @@ MA_HD void stage_read_compute(float2* v, int t, const float2* sbuf,
             for (int k = 0; k < r; ++k) v[b * r + k] = sbuf[saddr<W>(jv + k * stride)];
         }
         float2 w[r];
-        if constexpr (TWALU) twiddle_powers<r>(w, twb[tw_base_index<P>(S, b)]);
+        if constexpr (TWS1 && S == 1 && stage1_table_ok<P>()) {
+            const float4* tab = reinterpret_cast<const float4*>(tw_s1) + (jv % Ns);
+#pragma unroll
+            for (int kp = 0; kp < r / 2; ++kp) {
+                const float4 w4 = tab[kp * Ns];
+                w[2 * kp + 1] = make_float2(w4.x, w4.y);
+                if (2 * kp + 2 < r) w[2 * kp + 2] = make_float2(w4.z, w4.w);
+            }
+        } else if constexpr (TWALU) twiddle_powers<r>(w, twb[tw_base_index<P>(S, b)]);
         else load_stage_twiddles<P, S>(w, twM, jv % Ns);
 #pragma unroll
         for (int k = 1; k < r; ++k) v[b * r + k] = cmul(v[b * r + k], w[k]);
@@ -446,10 +482,11 @@ struct NoHook {
 };
 
 template <class P, int W, int S, bool PAIR0, bool PAIRL, bool TWALU, class Cta, class Hook = NoHook,
-          bool SINGLE = false>
+          bool SINGLE = false, bool TWS1 = false>
 struct StageChain {
     static MA_HD void run(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
-                          const float2* __restrict__ twM, const float2* twb, Cta& cta, const Hook& hook = Hook()) {
+                          const float2* __restrict__ twM, const float2* twb, Cta& cta, const Hook& hook = Hook(),
+                          const float2* tw_s1 = nullptr) {
         if constexpr (S < P::NS) {
             // SINGLE: one exchange buffer only; a barrier before each write keeps it from
             // overtaking the previous exchange's reads (costs a barrier, saves a buffer).
@@ -458,9 +495,9 @@ struct StageChain {
             stage_write<P, W, S - 1, (S == 1) && PAIR0>(v, t, sbuf);
             cta.sync();
             if constexpr (S == 1) hook();  // every thread is past its reads of the frame's input
-            stage_read_compute<P, W, S, (S == P::NS - 1) && PAIRL, TWALU>(v, t, sbuf, twM, twb);
+            stage_read_compute<P, W, S, (S == P::NS - 1) && PAIRL, TWALU, TWS1>(v, t, sbuf, twM, twb, tw_s1);
             parity ^= 1;
-            StageChain<P, W, S + 1, PAIR0, PAIRL, TWALU, Cta, Hook, SINGLE>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta, hook);
+            StageChain<P, W, S + 1, PAIR0, PAIRL, TWALU, Cta, Hook, SINGLE, TWS1>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta, hook, tw_s1);
         }
     }
 };
@@ -479,16 +516,17 @@ MA_HD void load_tw_bases(float2* twb, int t, const float2* __restrict__ tws) {
 // sbuf0 is the transform's exchange region (already offset by the slot when W > 1);
 // buf_stride is the distance in float2 between the two exchange buffers; parity selects the
 // buffer of the next exchange and is updated.
+// tw_s1 (with TWS1): the stage-1 twiddle table in shared memory (stage1_table_fill).
 template <class P, int W, bool PAIR0, bool PAIRL, class Cta, bool TWALU = false, class Hook = NoHook,
-          bool SINGLE = false>
+          bool SINGLE = false, bool TWS1 = false>
 MA_HD void fft_run(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
                    const float2* __restrict__ twM, Cta& cta, const float2* twb = nullptr,
-                   const Hook& hook = Hook()) {
+                   const Hook& hook = Hook(), const float2* tw_s1 = nullptr) {
     constexpr int r0 = P::radix(0), NB0 = P::R / r0;
     static_assert(!(PAIRL && P::NS < 2), "a paired last stage needs at least two stages");
 #pragma unroll
     for (int b = 0; b < NB0; ++b) Bfly<r0>::run(v + b * r0);  // stage 0: no twiddles
-    StageChain<P, W, 1, PAIR0, PAIRL, TWALU, Cta, Hook, SINGLE>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta, hook);
+    StageChain<P, W, 1, PAIR0, PAIRL, TWALU, Cta, Hook, SINGLE, TWS1>::run(v, t, sbuf0, buf_stride, parity, twM, twb, cta, hook, tw_s1);
 }
 
 // Complex forward FFT of length M in natural order.  In: v[q] = z[t + q*T].

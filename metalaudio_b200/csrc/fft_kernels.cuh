@@ -61,7 +61,8 @@ struct CtaShape {
     static constexpr int SMEM_BYTES_PREFETCH = SMEM_BYTES + STAGE * (int)sizeof(float2) + 16 * FPC;
     // Staged inverse kernels: one spectrum row (M+2 bins with the alignment slack) per slot.
     static constexpr int ROW = M + 2;
-    static constexpr int SMEM_BYTES_STAGED = SMEM_BYTES + FPC * ROW * (int)sizeof(float2) + 16 * FPC;
+    static constexpr int TW1_INV = stage1_table_elems<FftPlanRev<M>>();
+    static constexpr int SMEM_BYTES_STAGED = SMEM_BYTES + FPC * ROW * (int)sizeof(float2) + 16 * FPC + TW1_INV * (int)sizeof(float2);
     static_assert(SMEM_BYTES % 16 == 0 && (ROW * sizeof(float2)) % 16 == 0 && (M * sizeof(float2)) % 16 == 0 || M < 2,
                   "bulk copy destinations must be 16-byte aligned");
 };
@@ -468,11 +469,13 @@ MA_HD StagedRow staged_row(const C2RParams& p, int64_t s, int64_t f) {
 // Pre-process + FFT of one frame: leaves v[q] = (x[2n+1], x[2n]) * N for n = t + q*T
 // (real and imaginary parts swapped: the inverse transform is run as a forward transform
 // of the swapped spectrum).
-template <int M, int LAYOUT, bool TWALU, class Cta, bool STAGED = false, class Hook = NoHook, bool SINGLE = false>
+template <int M, int LAYOUT, bool TWALU, class Cta, bool STAGED = false, class Hook = NoHook, bool SINGLE = false,
+          bool TWS1 = false>
 MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int64_t g, int t,
                      float2* sbuf0, int buf_stride, int& parity, float2* v, Cta& cta,
                      const float2* twb = nullptr, const float2* wherm = nullptr,
-                     const float2* staged = nullptr, const Hook& hook = Hook(), const float2* xg = nullptr) {
+                     const float2* staged = nullptr, const Hook& hook = Hook(), const float2* xg = nullptr,
+                     const float2* tw_s1 = nullptr) {
     using P = FftPlan<M>;
     constexpr int R = P::R, T = P::T;
     const float2* x = STAGED ? staged
@@ -526,7 +529,7 @@ MA_HD void c2r_frame(const C2RParams& p, bool active, int64_t s, int64_t f, int6
                 }
             }
         }
-        fft_run<PR, 1, true, false, Cta, TWALU, Hook, SINGLE>(v, t, sbuf0, buf_stride, parity, p.twM, cta, twb, hook);
+        fft_run<PR, 1, true, false, Cta, TWALU, Hook, SINGLE, TWS1>(v, t, sbuf0, buf_stride, parity, p.twM, cta, twb, hook, tw_s1);
     } else {
         float2* sb = sbuf0 + parity * buf_stride;
         parity ^= 1;
@@ -628,7 +631,10 @@ MA_HD void c2r_body(const C2RParams& p, Cta& cta, float2* smem) {
     uint32_t phase = 0;
     (void)stage_slot;
     (void)bar;
+    float2* tw1 = smem + 2 * S::BUF_STRIDE + S::FPC * S::ROW + 2 * S::FPC;  // stage-1 twiddle table (staged variant)
+    (void)tw1;
     if constexpr (STAGED) {
+        stage1_table_fill<FftPlanRev<M>>(tw1, p.twM, tid, S::THREADS);
         if (t == 0) cta.bulk_init(bar);
         cta.sync();
         if (t == 0 && g < total) {
@@ -664,8 +670,8 @@ MA_HD void c2r_body(const C2RParams& p, Cta& cta, float2* smem) {
                     cta.bulk_copy(stage_slot, rn.src, rn.bytes, bar);
                 }
             };
-            c2r_frame<M, LAYOUT, TWALU, Cta, true>(p, active, s, f, g, t, sbuf0, S::BUF_STRIDE, parity, v, cta, twb,
-                                                   wherm, stage_slot + r.shift, issue_next, r.row);
+            c2r_frame<M, LAYOUT, TWALU, Cta, true, decltype(issue_next), false, true>(
+                p, active, s, f, g, t, sbuf0, S::BUF_STRIDE, parity, v, cta, twb, wherm, stage_slot + r.shift, issue_next, r.row, tw1);
         } else {
             c2r_frame<M, LAYOUT, TWALU, Cta>(p, active, s, f, g, t, sbuf0, S::BUF_STRIDE, parity, v, cta, twb, wherm);
         }
@@ -837,7 +843,8 @@ struct IstftFastShape {
     static constexpr int ROW = M + 2;  // staged spectrum row with the alignment slack
     static constexpr int EXCH = 1;  // exchange buffers (1: a barrier before each write instead of a second buffer)
     static constexpr int EXCH_ELEMS = (EXCH * ELEMS + 1) & ~1;  // keeps the staged row 16-byte aligned
-    static constexpr int SMEM_BYTES = (EXCH_ELEMS + RING + ROW) * (int)sizeof(float2) + 16;
+    static constexpr int TW1 = stage1_table_elems<FftPlanRev<M>>();  // stage-1 twiddle table behind the mbarrier
+    static constexpr int SMEM_BYTES = (EXCH_ELEMS + RING + ROW + TW1) * (int)sizeof(float2) + 16;
     static_assert(!plan_pairable<M>() || ((EXCH_ELEMS + RING) * sizeof(float2)) % 16 == 0,
                   "bulk copy destination must be 16-byte aligned");
 };
@@ -874,6 +881,7 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
     float2* ring = smem + SH::EXCH_ELEMS;
     float2* stage = ring + SH::RING;
     uint64_t* bar = reinterpret_cast<uint64_t*>(stage + SH::ROW);
+    float2* tw1 = stage + SH::ROW + 2;  // 16 bytes of barrier, then the stage-1 twiddle table
     auto start_copy = [&](int64_t s_, int64_t f_) {  // called by thread 0
         if constexpr (POLAR) {
             const int64_t g_ = s_ * p.frames_per_signal + f_;
@@ -942,6 +950,7 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
     int64_t G = G0 - lead;
 
     if (t == 0) cta.bulk_init(bar);
+    stage1_table_fill<FftPlanRev<M>>(tw1, p.twM, t, T);
     // register ring (REGRING): racc[i] = (odd sample, even sample) partial sums of slot i of the next
     // frame, in the pair order the inverse transform produces
     constexpr int HR = REGRING ? R / OVT : R;
@@ -978,12 +987,12 @@ MA_HD void istft_fast_body(const C2RParams& p, Cta& cta, float2* smem) {
             }
         };
         if constexpr (POLAR) {
-            c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1>(
-                p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage, issue_next, nullptr);
+            c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1, true>(
+                p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage, issue_next, nullptr, tw1);
         } else {
             const StagedRow r = staged_row<M>(p, s, f);
-            c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1>(
-                p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage + r.shift, issue_next, r.row);
+            c2r_frame<M, LAYOUT, true, Cta, true, decltype(issue_next), SH::EXCH == 1, true>(
+                p, true, s, f, G, t, smem, SH::ELEMS, parity, v, cta, twb, wherm, stage + r.shift, issue_next, r.row, tw1);
         }
 
         // v[q] = (x[2n+1], x[2n]) * N for n = t + q*T.  Overlap-add in this thread's ring column.

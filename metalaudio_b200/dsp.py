@@ -1278,11 +1278,20 @@ class BiquadFilter:
 class FilterBank:
     """Filters.swift:736.  ``processSeries`` runs the bands as one cascade of sections on the GPU;
     ``processParallel`` feeds one signal to every band (one channel per band) and mixes them with
-    1/bandCount (:845-868)."""
+    1/bandCount (:845-868).  Both run over the same per-band filters in the reference, so a band's
+    (z1, z2) state carries over when a caller alternates between the two: the two device objects
+    here hand their state to each other on every switch.  At most ``maxBands`` bands (the cascade
+    length one kernel launch serves); the reference has no such limit."""
+
+    maxBands = 32
 
     def __init__(self, device: AudioDevice, bandCount: int):
+        if int(bandCount) > FilterBank.maxBands:
+            raise FilterError.invalidParameter("bandCount", float(bandCount),
+                                               f"must be <= {FilterBank.maxBands} on the CUDA backend (one cascade per launch)")
         self.device = device
         self.bandCount = int(bandCount)
+        self._last = None
         self._lib = device._lib
         self._coeffs = [BiquadFilter.Coefficients() for _ in range(max(self.bandCount, 0))]
         self._series = None
@@ -1305,6 +1314,17 @@ class FilterBank:
             cmap = np.arange(self.bandCount, dtype=np.int32)
             _raise_status(self._lib.ma_biquad_set_coefficients(self._parallel, _ptr(c), self.bandCount, _ptr(cmap)), "FilterBank")
             self._dirty = False
+
+    def _switch_to(self, which: str):
+        """Makes `which` ("series" / "parallel") the object holding the bands' current state: both
+        lay it out as bandCount x (z1, z2)."""
+        if self._last is not None and self._last != which:
+            st = np.empty((self.bandCount, 2), np.float32)
+            src = self._series if self._last == "series" else self._parallel
+            dst = self._series if which == "series" else self._parallel
+            _raise_status(self._lib.ma_biquad_get_state(src, _ptr(st)), "FilterBank")
+            _raise_status(self._lib.ma_biquad_set_state(dst, _ptr(st)), "FilterBank")
+        self._last = which
 
     def configureAsEQ(self, lowFreq: float, highFreq: float, sampleRate: float, q: float = 1.414) -> None:
         """Logarithmically spaced 0 dB peaking bands (Filters.swift:768-812)."""
@@ -1338,6 +1358,7 @@ class FilterBank:
         if x.size == 0 or self.bandCount <= 0:
             return x.copy()
         self._handles()
+        self._switch_to("series")
         out = np.empty_like(x)
         _raise_status(self._lib.ma_biquad_process_host(self._series, _ptr(x), x.size, _ptr(out), x.size, x.size),
                       "FilterBank.processSeries")
@@ -1348,6 +1369,7 @@ class FilterBank:
         if x.size == 0 or self.bandCount <= 0:
             return np.zeros_like(x)
         self._handles()
+        self._switch_to("parallel")
         n = x.size
         dev = self.device
         tin, bands, mix = Tensor(dev, (n,)), Tensor(dev, (self.bandCount, n)), Tensor(dev, (n,))
@@ -1369,6 +1391,7 @@ class FilterBank:
         for h in (self._series, self._parallel):
             if h is not None:
                 _raise_status(self._lib.ma_biquad_reset(h), "FilterBank.reset")
+        self._last = None
 
     def close(self) -> None:
         for h in (getattr(self, "_series", None), getattr(self, "_parallel", None)):

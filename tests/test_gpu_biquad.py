@@ -146,3 +146,36 @@ def test_filter_bank_series_and_parallel(device):
     assert e.value.name == "band"
     with pytest.raises(FilterError):
         FilterBank(device, bandCount=1).configureAsEQ(100.0, 1000.0, 44100.0)
+
+
+def test_filter_bank_state_carries_between_series_and_parallel(device):
+    """The reference runs processSeries and processParallel over the same per-band filters, so a
+    band's state survives a switch between the two.  Mirrored by handing the state across: a
+    parallel call after a series call continues every band from the state the series call left."""
+    from metalaudio_b200 import FilterBank, FilterError
+    rng = np.random.default_rng(12)
+    bands, n = 4, 3000
+    bank = FilterBank(device, bandCount=bands)
+    bank.configureAsEQ(100.0, 8000.0, 44100.0)
+    for b in range(bands):
+        bank.setBandGain(b, 6.0 - 3.0 * b, 200.0 * (b + 1), 44100.0)
+    coeffs = np.stack([c.asArray() for c in bank._coeffs])
+    x1 = rng.standard_normal(n).astype(np.float32)
+    x2 = rng.standard_normal(n).astype(np.float32)
+    y1 = bank.processSeries(x1)
+    y2 = bank.processParallel(x2)
+    # oracle: the cascade on x1 leaves per-band states; each band then filters x2 from its own state
+    cur, states = x1.astype(np.float64), []
+    for b in range(bands):
+        cur, st = rp.biquad_process(cur, coeffs[b], dtype=np.float64)
+        states.append(st)
+    assert o64.rel_rms(y1, cur) <= TOL
+    mix = np.zeros(n)
+    for b in range(bands):
+        yb, _ = rp.biquad_process(x2.astype(np.float64), coeffs[b], state=states[b], dtype=np.float64)
+        mix += yb
+    assert o64.rel_rms(y2, mix / bands) <= TOL
+    with pytest.raises(FilterError) as e:
+        FilterBank(device, bandCount=33)
+    assert e.value.name == "bandCount"
+    bank.close()
