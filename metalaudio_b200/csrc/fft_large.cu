@@ -179,16 +179,21 @@ __device__ __forceinline__ void store_bin(const LargeParams& p, int64_t b, int64
 // spectrum.  Bin k = k1*n2 + kk2 lies in the lower half for k1 < N1/2 and is stored as is; for
 // k1 >= N1/2 its conjugate is bin n-k of the lower half (stored for interior rows only, the edge
 // rows' mirrors being produced directly).  Which case applies is known per unrolled iteration.
+// A tile is W2 consecutive rows of the chunk's global row list (row g = transform * (N2/2+1) + k2),
+// so it may span the end of one transform and the start of the next: every thread derives the
+// transform and the row of its own column.
 template <int N1, int W2, int THREADS, bool PACKED>
-__device__ __forceinline__ void store_half_tile(const LargeParams& p, int64_t b, int r0, const float2* tile) {
+__device__ __forceinline__ void store_half_tile(const LargeParams& p, int64_t g0, int64_t rows_total, const float2* tile) {
     static_assert(THREADS % W2 == 0 && (N1 * W2) % THREADS == 0, "tile shape");
     constexpr int ITER = N1 * W2 / THREADS, KSTEP = THREADS / W2;
     static_assert(ITER % 2 == 0 && (N1 / 2) % KSTEP == 0, "the halves must split between iterations");
     const int s = threadIdx.x % W2;
     const int k1base = threadIdx.x / W2;
-    const int kk2 = r0 + s;
     const int m2 = p.n2 / 2;
-    if (kk2 > m2) return;
+    const int64_t g = g0 + s;
+    if (g >= rows_total) return;
+    const int64_t b = g / (m2 + 1);
+    const int kk2 = (int)(g - b * (m2 + 1));
     const int n = (int)p.n, half = n / 2;
     const bool interior = kk2 > 0 && kk2 < m2;
     float2* o = reinterpret_cast<float2*>(p.out_a) + b * (int64_t)(PACKED ? half : half + 1);
@@ -231,14 +236,16 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
     const int slot = threadIdx.x / T;
     const int t = threadIdx.x % T;
     const int m2 = p.n2 / 2;
-    const int tiles = (m2 + 1 + W2 - 1) / W2;
+    // Tiles run over the chunk's global row list (row g = transform * (m2+1) + k2, which is also the
+    // scratch's row order), so only the chunk's last tile can be ragged.
+    const int64_t rows_total = p.batch * (int64_t)(m2 + 1);
+    const int64_t tiles = (rows_total + W2 - 1) / W2;
     DevCtaL cta;
-    for (int64_t blk = blockIdx.x; blk < p.batch * tiles; blk += gridDim.x) {
-        const int64_t b = blk / tiles;
-        const int r0 = (int)(blk - b * tiles) * W2;
-        const int k2 = r0 + slot;
-        const bool active = k2 <= m2;
-        const float2* row = p.scratch + (b * (int64_t)(m2 + 1) + (active ? k2 : 0)) * N1;
+    for (int64_t blk = blockIdx.x; blk < tiles; blk += gridDim.x) {
+        const int64_t g0 = blk * W2;
+        const int64_t g = g0 + slot;
+        const bool active = g < rows_total;
+        const float2* row = p.scratch + (active ? g : 0) * N1;
         float2 v[R];
 #pragma unroll
         for (int q = 0; q < R; ++q) v[q] = active ? row[t + q * T] : make_float2(0.f, 0.f);
@@ -253,14 +260,16 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
             for (int idx = threadIdx.x; idx < N1 * W2; idx += THREADS) {
                 const int s = idx % W2;
                 const int k1 = idx / W2;
-                const int kk2 = r0 + s;
-                if (kk2 > m2) continue;
+                const int64_t gs = g0 + s;
+                if (gs >= rows_total) continue;
+                const int64_t b = gs / (m2 + 1);
+                const int kk2 = (int)(gs - b * (m2 + 1));
                 store_bin(p, b, (int64_t)k1 * p.n2 + kk2, kk2, tile[k1 * (W2 + 1) + s]);
             }
         } else if (p.layout == LAYOUT_HALF_PACKED) {
-            store_half_tile<N1, W2, THREADS, true>(p, b, r0, tile);
+            store_half_tile<N1, W2, THREADS, true>(p, g0, rows_total, tile);
         } else {
-            store_half_tile<N1, W2, THREADS, false>(p, b, r0, tile);
+            store_half_tile<N1, W2, THREADS, false>(p, g0, rows_total, tile);
         }
         cta.sync();
     }
@@ -303,11 +312,12 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
     const int slot = threadIdx.x / T;
     const int t = threadIdx.x % T;
     const int m2 = p.n2 / 2;
-    const int tiles = (m2 + 1 + W2 - 1) / W2;
+    // tiles over the chunk's global row list (row g = transform * (m2+1) + k2), as in rows_fwd_kernel
+    const int64_t rows_total = p.batch * (int64_t)(m2 + 1);
+    const int64_t tiles = (rows_total + W2 - 1) / W2;
     DevCtaL cta;
-    for (int64_t blk = blockIdx.x; blk < p.batch * tiles; blk += gridDim.x) {
-        const int64_t b = blk / tiles;
-        const int r0 = (int)(blk - b * tiles) * W2;
+    for (int64_t blk = blockIdx.x; blk < tiles; blk += gridDim.x) {
+        const int64_t g0 = blk * W2;
         float2* tile = smem;
         // All of a thread's loads are issued before the first use: one memory latency per tile
         // instead of one per element.
@@ -316,8 +326,10 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
             constexpr int ITER = N1 * W2 / THREADS, KSTEP = THREADS / W2;
             const int s = threadIdx.x % W2;
             const int k1base = threadIdx.x / W2;
-            const int kk2 = r0 + s;
-            const bool live = kk2 <= m2;
+            const int64_t gs = g0 + s;
+            const bool live = gs < rows_total;
+            const int64_t b = live ? gs / (m2 + 1) : 0;
+            const int kk2 = live ? (int)(gs - b * (m2 + 1)) : 0;
             const int64_t n = p.n, half = n / 2;
             float2 x[ITER];
             if (p.layout == LAYOUT_FULL_SPLIT) {
@@ -362,9 +374,10 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
         cta.sync();
         int parity = 0;
         fft_forward_regs<N1, 1, DevCtaL>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
-        const int k2 = r0 + slot;
-        if (k2 <= m2) {
-            float2* row = p.scratch + (b * (int64_t)(m2 + 1) + k2) * N1;
+        const int64_t g = g0 + slot;
+        if (g < rows_total) {
+            const int k2 = (int)(g % (m2 + 1));
+            float2* row = p.scratch + g * N1;
             float2 wq[R];
             geometric_twiddles<R>(wq, __ldg(p.twL + (int64_t)k2 * t), __ldg(p.twL + (int64_t)k2 * T));
 #pragma unroll
@@ -393,13 +406,15 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
     const int slot = threadIdx.x / T;
     const int t = threadIdx.x % T;
     const int m2 = p.n2 / 2;
-    const int tiles = (m2 + 1 + W2 - 1) / W2;
+    // tiles over the chunk's global row list (row g = transform * (m2+1) + k2), as in rows_fwd_kernel
+    const int64_t rows_total = p.batch * (int64_t)(m2 + 1);
+    const int64_t tiles = (rows_total + W2 - 1) / W2;
     DevCtaL cta;
-    for (int64_t blk = blockIdx.x; blk < p.batch * tiles; blk += gridDim.x) {
-        const int64_t b = blk / tiles;
-        const int k2 = (int)(blk - b * tiles) * W2 + slot;
-        const bool active = k2 <= m2;
-        float2* row = p.scratch + (b * (int64_t)(m2 + 1) + (active ? k2 : 0)) * N1;
+    for (int64_t blk = blockIdx.x; blk < tiles; blk += gridDim.x) {
+        const int64_t g = blk * W2 + slot;
+        const bool active = g < rows_total;
+        const int k2 = active ? (int)(g % (m2 + 1)) : 0;
+        float2* row = p.scratch + (active ? g : 0) * N1;
         const float2* hrow = p.spec_rows + (int64_t)(active ? k2 : 0) * N1;
         float2 v[R], h[R];
 #pragma unroll
@@ -562,7 +577,7 @@ static ma_status run_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse)
         occ = n > 0 ? n : 1;
     }
     const int m2 = p.n2 / 2;
-    const int64_t work = p.batch * ((m2 + 1 + W2 - 1) / W2);
+    const int64_t work = (p.batch * (int64_t)(m2 + 1) + W2 - 1) / W2;  // tiles over the chunk's global row list
     const int64_t cap = (int64_t)ctx->sm_count * occ;
     // forward passes: one CTA per tile (measured 5 % faster than persistent CTAs); inverse passes: persistent
     const int grid = !inverse ? (int)work : (int)(work < cap ? work : cap);
@@ -593,7 +608,7 @@ static ma_status run_rows_mul(ma_fft_plan* plan, const LargeParams& p, bool stor
     if (store_spectrum) MA_TRY(kernel_occupancy(rows_mul_kernel<N1, W2, true>, threads, smem, o));
     else MA_TRY(kernel_occupancy(rows_mul_kernel<N1, W2, false>, threads, smem, o));
     const int m2 = p.n2 / 2;
-    const int64_t work = p.batch * ((m2 + 1 + W2 - 1) / W2);
+    const int64_t work = (p.batch * (int64_t)(m2 + 1) + W2 - 1) / W2;  // tiles over the chunk's global row list
     const int64_t cap = (int64_t)ctx->sm_count * *o;
     const int grid = (int)(work < cap ? work : cap);
     if (store_spectrum) rows_mul_kernel<N1, W2, true><<<grid, threads, smem, ctx->stream>>>(p);

@@ -378,6 +378,32 @@ static ma_status launch_mac(ma_pconv* pc, MacParams q, bool stream, int64_t t_co
     return MA_ERR_UNSUPPORTED;
 }
 
+// Streaming step with many partition splits: adds the partial spectra up, split 0 first, and
+// leaves the total in slot 0, one thread per 16 bytes with eight loads in flight.  The inverse
+// transform behind it then reads one spectrum per channel; walking `splits` partials inside that
+// kernel costs a memory round trip per partial on a handful of CTAs, which with few channels per
+// GPU (many splits) was the longest part of a step.  Same summation order as that walk.
+__global__ void __launch_bounds__(256) pconv_sum_partials_kernel(float4* __restrict__ partial, int64_t n4,
+                                                                 int64_t split_stride4, int splits) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the multiply-accumulate before this kernel has finished
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    float4 acc = __ldcg(partial + i);
+#pragma unroll 8
+    for (int sp = 1; sp < splits; ++sp) {
+        const float4 v = __ldcg(partial + sp * split_stride4 + i);
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+    }
+    partial[i] = acc;
+}
+
+// Partial spectra are summed by their own kernel from this many splits up.
+constexpr int kSumKernelFromSplits = 16;  // measured: 9 splits are faster summed inside the inverse kernel, 19 and 37 by this one
+
 // Ordered copies between the ring and the timeline.
 // to_timeline: tl[c][j] = ring[c][(w - (P-1-j)) mod P], j < P-1.
 // to_ring:     ring[c][j] = tl[c][first + j], j < P.
@@ -788,6 +814,22 @@ ma_status ma_pconv_step_dev(ma_pconv* pc, const float* in_block, int64_t in_stri
         MA_TRY(launch_mac(pc, q, true, 1));
     }
     // 3. sum the partials, inverse transform, add the kept tail, keep the new one
+    const bool own_sum = pc->splits >= kSumKernelFromSplits && ((int64_t)C * B) % 2 == 0;
+    if (own_sum) {
+        const int64_t n4 = (int64_t)C * B / 2;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)((n4 + 255) / 256));
+        cfg.blockDim = dim3(256);
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        (void)cudaLaunchKernelEx(&cfg, pconv_sum_partials_kernel, reinterpret_cast<float4*>(pc->d_partial), n4, n4,
+                                 pc->splits);  // an error is picked up by after_launch
+        MA_TRY(after_launch(ctx));
+    }
     {
         C2RParams p{};
         p.in_a = reinterpret_cast<const float*>(pc->d_partial);
@@ -796,7 +838,7 @@ ma_status ma_pconv_step_dev(ma_pconv* pc, const float* in_block, int64_t in_stri
         p.frames_per_signal = 1;
         p.n_signals = C;
         p.layout = LAYOUT_HALF_PACKED;
-        p.n_partials = pc->splits;
+        p.n_partials = own_sum ? 1 : pc->splits;
         p.partial_stride = (int64_t)C * B;
         p.out = out_block;
         p.out_signal_stride = out_stride;
