@@ -100,7 +100,8 @@ def test_multichannel_shared_and_per_pair_irs(device):
         assert o64.rel_rms(y3[i], o64.convolve_full(x[i], hs[ir])) <= TOL
 
 
-@pytest.mark.parametrize("block,taps,channels", [(64, 1000, 4), (256, 5000, 3), (1, 3, 2), (2, 9, 5), (32, 700, 8)])
+@pytest.mark.parametrize("block,taps,channels", [(64, 1000, 4), (256, 5000, 3), (1, 3, 2), (2, 9, 5), (32, 700, 8), (64, 30, 2),
+                                                 (128, 128, 3), (128, 129, 4)])
 def test_streaming_step_equals_whole_signal(device, lib, block, taps, channels):
     """The causal one-block step (the HBM-streaming kernel) produces the same samples as
     the whole-signal call."""
