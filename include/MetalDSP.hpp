@@ -211,6 +211,34 @@ struct STFTResult {  // STFT.swift:10-22: full-N split rows
     int binCount() const { return real.empty() ? 0 : (int)real[0].size(); }
 };
 
+// FFT.swift:63-134: sampled NaN / Inf check on transform outputs, off unless the flag is set.  Looks
+// at about 50 evenly spaced values plus the last one, reports the first of each kind, never throws.
+inline bool& fftValidationEnabled() {
+    static bool enabled = false;
+    return enabled;
+}
+inline std::vector<std::string>& fftValidationLog() {
+    static std::vector<std::string> log;
+    return log;
+}
+inline bool validateFFTOutput(const float* buffer, int64_t count, const std::string& context) {
+    if (!fftValidationEnabled() || count <= 0) return false;
+    const int64_t sampleCount = count < 50 ? count : 50;
+    const int64_t stride = std::max<int64_t>(1, count / sampleCount);
+    int64_t nanAt = -1, infAt = -1;
+    for (int64_t i = 0; i < count && (nanAt < 0 || infAt < 0); i += stride) {
+        if (nanAt < 0 && std::isnan(buffer[i])) nanAt = i;
+        if (infAt < 0 && std::isinf(buffer[i])) infAt = i;
+    }
+    if (count > 1) {
+        if (nanAt < 0 && std::isnan(buffer[count - 1])) nanAt = count - 1;
+        if (infAt < 0 && std::isinf(buffer[count - 1])) infAt = count - 1;
+    }
+    if (nanAt >= 0) fftValidationLog().push_back("[FFT] Warning: NaN detected in " + context + " near index " + std::to_string(nanAt));
+    if (infAt >= 0) fftValidationLog().push_back("[FFT] Warning: Inf detected in " + context + " near index " + std::to_string(infAt));
+    return nanAt >= 0 || infAt >= 0;
+}
+
 class FFT {
 public:
     static constexpr int maxFFTSize = 1 << 24;  // FFT.swift:422
@@ -312,6 +340,8 @@ public:
         }
         if (config_.inverse)
             for (int i = 0; i < n; ++i) outputImag[i] = -outputImag[i];
+        validateFFTOutput(outputReal, n, "outputReal");  // FFT.swift:853-854
+        validateFFTOutput(outputImag, n, "outputImag");
     }
     // FFT.swift:889-919: real part of the transform in the object's direction, times 1/N.
     void inverse(const float* inputReal, const float* inputImag, float* output) {

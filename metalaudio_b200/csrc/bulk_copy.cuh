@@ -23,9 +23,14 @@ __device__ __forceinline__ void bulk_barrier_init(uint64_t* bar) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
+// Orders this thread's earlier ordinary shared-memory accesses (and, through the CTA barrier the
+// callers place in front, everyone's) before the copy unit's writes to the same buffer.
+__device__ __forceinline__ void bulk_proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // Arms the barrier for `bytes` and starts the copy.  Called by one thread.
 __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     const uint32_t b = smem_u32(bar);
+    bulk_proxy_fence();
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(bytes) : "memory");
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -37,6 +42,7 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32
 // Several copies on one phase: one thread arms the barrier once for the total and then starts each
 // copy with bulk_copy_part.
 __device__ __forceinline__ void bulk_barrier_expect(uint64_t* bar, uint32_t total_bytes) {
+    bulk_proxy_fence();
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(total_bytes) : "memory");
 }
 __device__ __forceinline__ void bulk_copy_part(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {

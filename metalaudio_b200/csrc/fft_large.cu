@@ -15,9 +15,12 @@
 // A batch is cut into chunks of about 192 MB of pass data (about 4*N bytes per transform).  Up to
 // roughly 100 MB that scratch stays in the 126 MB L2 between the two passes; larger batches let it
 // spill to HBM, which the passes - bound by instruction issue and latency, not by HBM - do not feel.
-// Plain loads and stores only: no TMA, no multicast.
+// The forward row pass stages its tile (W2 consecutive scratch rows: one contiguous block) with a
+// single bulk asynchronous copy of the TMA unit into its idle exchange buffer; the strided tiles of
+// the other passes use plain coalesced loads and stores.  No multicast anywhere.
 #include <new>
 
+#include "bulk_copy.cuh"
 #include "fft_plan.h"
 #include "host_tables.h"
 
@@ -42,6 +45,7 @@ struct LargeParams {
     int64_t valid;       // forward pass 1: samples present per transform, the rest reads as zero
     float2* spec_rows;   // convolution: kernel spectrum in pass-2 row order [N2/2+1][N1]
     const float* window; // forward pass 1: analysis window applied by the loader (STFT), or nullptr
+    int32_t* error_flag; // set to 1 when a bounded wait for a staged tile ran out
 };
 
 // w[q] = base * step^q for q < n (n <= 17), products of depth <= 3 from step, step^4, step^8, step^12, step^16.
@@ -241,14 +245,27 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
     const int64_t rows_total = p.batch * (int64_t)(m2 + 1);
     const int64_t tiles = (rows_total + W2 - 1) / W2;
     DevCtaL cta;
+    // The tile - W2 consecutive scratch rows, one contiguous block - is staged by ONE bulk asynchronous
+    // copy (the TMA unit's untiled form) into the exchange buffer, which is idle until the first
+    // exchange; every thread then picks its points from shared memory.
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + (P::NS > 2 ? 2 : 1) * BUF);
+    uint32_t phase = 0;
+    if (threadIdx.x == 0) bulk_barrier_init(bar);
+    __syncthreads();
     for (int64_t blk = blockIdx.x; blk < tiles; blk += gridDim.x) {
         const int64_t g0 = blk * W2;
         const int64_t g = g0 + slot;
         const bool active = g < rows_total;
-        const float2* row = p.scratch + (active ? g : 0) * N1;
+        if (threadIdx.x == 0) {
+            const int64_t rows_here = rows_total - g0 < W2 ? rows_total - g0 : W2;
+            bulk_copy_g2s(smem, p.scratch + g0 * N1, (uint32_t)(rows_here * N1 * sizeof(float2)), bar);
+        }
+        if (!bulk_barrier_wait(bar, phase) && p.error_flag != nullptr) *p.error_flag = 1;
+        phase ^= 1;
         float2 v[R];
 #pragma unroll
-        for (int q = 0; q < R; ++q) v[q] = active ? row[t + q * T] : make_float2(0.f, 0.f);
+        for (int q = 0; q < R; ++q) v[q] = active ? smem[slot * N1 + t + q * T] : make_float2(0.f, 0.f);
+        cta.sync();  // every thread has its points: the exchange buffer may be written
         int parity = 0;
         fft_forward_regs<N1, 1, DevCtaL>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
         cta.sync();  // everyone is done with the exchange buffers: reuse them as the tile
@@ -558,8 +575,9 @@ template <int N1, int W2>
 static ma_status run_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse) {
     constexpr int threads = W2 * FftPlan<N1>::T;
     // plans with a single exchange (two stages) never touch the second exchange buffer
-    constexpr size_t smem = (FftPlan<N1>::NS > 2 ? 2 : 1) * (size_t)smem_elems_per_fft<N1, 1>() * W2 * sizeof(float2);
-    static_assert((size_t)N1 * (W2 + 1) * sizeof(float2) <= smem, "transposed tile must fit the exchange buffers");
+    // exchange buffer(s) plus 16 bytes for the staging barrier of the forward pass
+    constexpr size_t smem = (FftPlan<N1>::NS > 2 ? 2 : 1) * (size_t)smem_elems_per_fft<N1, 1>() * W2 * sizeof(float2) + 16;
+    static_assert((size_t)N1 * (W2 + 1) * sizeof(float2) <= smem - 16, "transposed tile must fit the exchange buffers");
     ma_context* ctx = plan->ctx;
     auto kf = rows_fwd_kernel<N1, W2>;
     auto ki = rows_inv_kernel<N1, W2>;
@@ -707,6 +725,7 @@ static void fill_tables(ma_fft_plan* plan, LargeParams& p) {
     p.twL = plan->d_twL;
     p.in_stride = plan->n;
     p.valid = plan->n;
+    p.error_flag = plan->ctx->d_error_flag;
 }
 
 ma_status launch_r2c_large(ma_fft_plan* plan, const float* in, float* out_a, float* out_b, float* mag,

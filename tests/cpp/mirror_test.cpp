@@ -57,6 +57,19 @@ static void host_logic() {
     }
     CHECK(caught);
     CHECK(std::string(FilterError::unstable("x").what()) == "Filter is unstable: x");
+    // sampled output validation: off by default; a NaN on a sampled index and an Inf at the end are found
+    std::vector<float> buf(1000, 0.f);
+    buf[20] = std::nanf("");
+    CHECK(!validateFFTOutput(buf.data(), 1000, "outputReal"));
+    fftValidationEnabled() = true;
+    CHECK(validateFFTOutput(buf.data(), 1000, "outputReal"));
+    CHECK(fftValidationLog().back() == "[FFT] Warning: NaN detected in outputReal near index 20");
+    std::vector<float> buf2(1000, 0.f);
+    buf2[21] = INFINITY;
+    CHECK(!validateFFTOutput(buf2.data(), 1000, "outputImag"));   // between two samples
+    buf2[999] = INFINITY;
+    CHECK(validateFFTOutput(buf2.data(), 1000, "outputImag"));
+    fftValidationEnabled() = false;
 }
 
 static void no_device() {
