@@ -531,12 +531,13 @@ MA_HD void fft_run(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
 
 // Complex forward FFT of length M in natural order.  In: v[q] = z[t + q*T].
 // Out: v[q] = Z[t + q*T].
-template <int M, int W, class Cta>
+// SINGLE: one exchange buffer (buf_stride is ignored), a barrier in front of every exchange write.
+template <int M, int W, class Cta, bool SINGLE = false>
 MA_HD void fft_forward_regs(float2* v, int t, float2* sbuf0, int buf_stride, int& parity,
                             const float2* __restrict__ twM, Cta& cta) {
     using P = FftPlan<M>;
     constexpr int R = P::R;
-    fft_run<P, W, false, false, Cta>(v, t, sbuf0, buf_stride, parity, twM, cta);
+    fft_run<P, W, false, false, Cta, false, NoHook, SINGLE>(v, t, sbuf0, buf_stride, parity, twM, cta);
     // After the last stage, element (b, k) of the flat array is Z[t + (b + k*NB)*T].
     constexpr int rl = P::radix(P::NS - 1), NB = R / rl;
     if constexpr (NB > 1) {

@@ -74,9 +74,21 @@ struct DevCtaL {
 
 extern __shared__ float4 ma_large_smem[];
 
+// Column passes of two-stage plans (one exchange per transform, M2 <= 256) run through ONE exchange
+// buffer: the Hermitian step reuses it behind a barrier, which halves the shared memory of a CTA
+// and lets a fourth CTA onto an SM.
+template <int M2>
+constexpr __host__ __device__ bool cols_single_buffer() { return FftPlan<M2>::NS <= 2; }
+#ifndef MA_COLS_R2C_CTAS
+#define MA_COLS_R2C_CTAS 3
+#endif
+#ifndef MA_COLS_C2R_CTAS
+#define MA_COLS_C2R_CTAS 4
+#endif
+
 // ---------------------------------------------------------------- forward pass 1
 template <int M2, int W1>
-__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? 3 : 1) cols_r2c_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? (cols_single_buffer<M2>() ? MA_COLS_R2C_CTAS : 3) : 1) cols_r2c_kernel(const LargeParams p) {
     using P = FftPlan<M2>;
     constexpr int R = P::R, T = P::T;
     float2* smem = reinterpret_cast<float2*>(ma_large_smem);
@@ -114,8 +126,10 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
         }
         int parity = 0;
         float2* sbuf0 = smem + i;
-        fft_forward_regs<M2, W1, DevCtaL>(v, t, sbuf0, M2 * W1, parity, p.twM2, cta);
-        float2* sb = sbuf0 + parity * (M2 * W1);
+        constexpr bool ONE = cols_single_buffer<M2>();
+        fft_forward_regs<M2, W1, DevCtaL, ONE>(v, t, sbuf0, M2 * W1, parity, p.twM2, cta);
+        float2* sb = ONE ? sbuf0 : sbuf0 + parity * (M2 * W1);
+        if constexpr (ONE) cta.sync();  // the exchange's reads are done before the buffer is rewritten
 #pragma unroll
         for (int q = 0; q < R; ++q) sb[saddr<W1>(t + q * T)] = v[q];
         cta.sync();
@@ -468,7 +482,7 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
 
 // ---------------------------------------------------------------- inverse pass B
 template <int M2, int W1>
-__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? 3 : 1) cols_c2r_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? (cols_single_buffer<M2>() ? MA_COLS_C2R_CTAS : 3) : 1) cols_c2r_kernel(const LargeParams p) {
     using P = FftPlan<M2>;
     constexpr int R = P::R, T = P::T;
     float2* smem = reinterpret_cast<float2*>(ma_large_smem);
@@ -512,7 +526,7 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
         float2 v[R];
 #pragma unroll
         for (int q = 0; q < R; ++q) v[q] = sb[saddr<W1>(t + q * T)];
-        fft_forward_regs<M2, W1, DevCtaL>(v, t, sbuf0, M2 * W1, parity, p.twM2, cta);
+        fft_forward_regs<M2, W1, DevCtaL, cols_single_buffer<M2>()>(v, t, sbuf0, M2 * W1, parity, p.twM2, cta);
         float* x = p.out_a + b * (int64_t)p.n + n1;
 #pragma unroll
         for (int q = 0; q < R; ++q) {
@@ -545,7 +559,7 @@ static bool large_shape(int n, LargeShape* s) {
 template <int M2, int W1>
 static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse) {
     constexpr int threads = W1 * FftPlan<M2>::T;
-    constexpr size_t smem = 2 * (size_t)M2 * W1 * sizeof(float2);
+    constexpr size_t smem = (cols_single_buffer<M2>() ? 1 : 2) * (size_t)M2 * W1 * sizeof(float2);
     ma_context* ctx = plan->ctx;
     auto kf = cols_r2c_kernel<M2, W1>;
     auto ki = cols_c2r_kernel<M2, W1>;
