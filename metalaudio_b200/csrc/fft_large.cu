@@ -79,16 +79,13 @@ extern __shared__ float4 ma_large_smem[];
 // and lets a fourth CTA onto an SM.
 template <int M2>
 constexpr __host__ __device__ bool cols_single_buffer() { return FftPlan<M2>::NS <= 2; }
-#ifndef MA_COLS_R2C_CTAS
-#define MA_COLS_R2C_CTAS 3
-#endif
-#ifndef MA_COLS_C2R_CTAS
-#define MA_COLS_C2R_CTAS 4
-#endif
+// Resident CTAs per SM asked of the compiler for those plans: the inverse pass fits 64 registers; the
+// forward pass would spill 208 bytes there and measured slower than at 3.
+constexpr int kColsR2cCtas = 3, kColsC2rCtas = 4;
 
 // ---------------------------------------------------------------- forward pass 1
 template <int M2, int W1>
-__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? (cols_single_buffer<M2>() ? MA_COLS_R2C_CTAS : 3) : 1) cols_r2c_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? (cols_single_buffer<M2>() ? kColsR2cCtas : 3) : 1) cols_r2c_kernel(const LargeParams p) {
     using P = FftPlan<M2>;
     constexpr int R = P::R, T = P::T;
     float2* smem = reinterpret_cast<float2*>(ma_large_smem);
@@ -482,7 +479,7 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
 
 // ---------------------------------------------------------------- inverse pass B
 template <int M2, int W1>
-__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? (cols_single_buffer<M2>() ? MA_COLS_C2R_CTAS : 3) : 1) cols_c2r_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? (cols_single_buffer<M2>() ? kColsC2rCtas : 3) : 1) cols_c2r_kernel(const LargeParams p) {
     using P = FftPlan<M2>;
     constexpr int R = P::R, T = P::T;
     float2* smem = reinterpret_cast<float2*>(ma_large_smem);
