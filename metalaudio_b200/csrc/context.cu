@@ -222,6 +222,11 @@ ma_status ma_context_create(int32_t device_index, size_t pinned_bytes, ma_contex
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking);
+    for (int i = 0; i < kAuxStreams && e == cudaSuccess; ++i) {
+        e = cudaStreamCreateWithFlags(&ctx->aux_stream[i], cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_join[i], cudaEventDisableTiming);
+    }
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming);
     for (int i = 0; i < 2 && e == cudaSuccess; ++i) {
         e = cudaEventCreateWithFlags(&ctx->ev_in[i], cudaEventDisableTiming);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_k[i], cudaEventDisableTiming);
@@ -282,6 +287,11 @@ ma_status ma_context_destroy(ma_context* ctx) {
     if (ctx->ws) (void)cudaFree(ctx->ws);
     if (ctx->copy_stream) (void)cudaStreamDestroy(ctx->copy_stream);
     if (ctx->d2h_stream) (void)cudaStreamDestroy(ctx->d2h_stream);
+    for (int i = 0; i < kAuxStreams; ++i) {
+        if (ctx->aux_stream[i]) (void)cudaStreamDestroy(ctx->aux_stream[i]);
+        if (ctx->ev_join[i]) (void)cudaEventDestroy(ctx->ev_join[i]);
+    }
+    if (ctx->ev_fork) (void)cudaEventDestroy(ctx->ev_fork);
     if (ctx->stream) (void)cudaStreamDestroy(ctx->stream);
     (void)cudaGetLastError();
     delete ctx;

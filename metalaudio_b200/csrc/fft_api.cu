@@ -118,7 +118,7 @@ ma_status ma_fft_plan_destroy(ma_fft_plan* plan) {
 
 ma_status ma_fft_plan_scratch_bytes(ma_fft_plan* plan, size_t* bytes) {
     if (plan == nullptr || bytes == nullptr) return MA_ERR_INVALID_ARGUMENT;
-    *bytes = plan->large ? (size_t)plan->scratch_batch * (size_t)(plan->n2 / 2 + 1) * plan->n1 * sizeof(float2) : 0;
+    *bytes = plan->large ? (size_t)plan->scratch_batch * (size_t)plan->scratch_lanes * (size_t)(plan->n2 / 2 + 1) * plan->n1 * sizeof(float2) : 0;
     return MA_OK;
 }
 

@@ -12,9 +12,9 @@
 //                                transform over k1, times exp(+2 pi i n1 k2 / N) -> D[k2][n1]
 //            pass B (cols_c2r):  N2-point real inverse over k2 -> x[n1 + N1*n2] / N
 //
-// A batch is cut into chunks of about 192 MB of pass data (about 4*N bytes per transform).  Up to
-// roughly 100 MB that scratch stays in the 126 MB L2 between the two passes; larger batches let it
-// spill to HBM, which the passes - bound by instruction issue and latency, not by HBM - do not feel.
+// A batch is cut into chunks of about 96 MB of pass data (about 4*N bytes per transform); consecutive
+// chunks alternate between two lanes (streams, each with its own scratch), so that one chunk's
+// launch gaps and last wave are filled by the other's kernels.
 // The forward row pass stages its tile (W2 consecutive scratch rows: one contiguous block) with a
 // single bulk asynchronous copy of the TMA unit into its idle exchange buffer; the strided tiles of
 // the other passes use plain coalesced loads and stores.  No multicast anywhere.
@@ -554,7 +554,7 @@ static bool large_shape(int n, LargeShape* s) {
 }
 
 template <int M2, int W1>
-static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse) {
+static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse, cudaStream_t st) {
     constexpr int threads = W1 * FftPlan<M2>::T;
     constexpr size_t smem = (cols_single_buffer<M2>() ? 1 : 2) * (size_t)M2 * W1 * sizeof(float2);
     ma_context* ctx = plan->ctx;
@@ -577,13 +577,13 @@ static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse)
     const int64_t cap = (int64_t)ctx->sm_count * occ;
     // forward passes: one CTA per tile (measured 5 % faster than persistent CTAs); inverse passes: persistent
     const int grid = !inverse ? (int)work : (int)(work < cap ? work : cap);
-    if (inverse) ki<<<grid, threads, smem, ctx->stream>>>(p);
-    else kf<<<grid, threads, smem, ctx->stream>>>(p);
+    if (inverse) ki<<<grid, threads, smem, st>>>(p);
+    else kf<<<grid, threads, smem, st>>>(p);
     return after_launch(ctx);
 }
 
 template <int N1, int W2>
-static ma_status run_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse) {
+static ma_status run_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse, cudaStream_t st) {
     constexpr int threads = W2 * FftPlan<N1>::T;
     // plans with a single exchange (two stages) never touch the second exchange buffer
     // exchange buffer(s) plus 16 bytes for the staging barrier of the forward pass
@@ -610,8 +610,8 @@ static ma_status run_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse)
     const int64_t cap = (int64_t)ctx->sm_count * occ;
     // forward passes: one CTA per tile (measured 5 % faster than persistent CTAs); inverse passes: persistent
     const int grid = !inverse ? (int)work : (int)(work < cap ? work : cap);
-    if (inverse) ki<<<grid, threads, smem, ctx->stream>>>(p);
-    else kf<<<grid, threads, smem, ctx->stream>>>(p);
+    if (inverse) ki<<<grid, threads, smem, st>>>(p);
+    else kf<<<grid, threads, smem, st>>>(p);
     return after_launch(ctx);
 }
 
@@ -628,7 +628,7 @@ static ma_status kernel_occupancy(K kernel, int threads, size_t smem, int* occ) 
 }
 
 template <int N1, int W2>
-static ma_status run_rows_mul(ma_fft_plan* plan, const LargeParams& p, bool store_spectrum) {
+static ma_status run_rows_mul(ma_fft_plan* plan, const LargeParams& p, bool store_spectrum, cudaStream_t st) {
     constexpr int threads = W2 * FftPlan<N1>::T;
     constexpr size_t smem = 2 * (size_t)smem_elems_per_fft<N1, 1>() * W2 * sizeof(float2);
     ma_context* ctx = plan->ctx;
@@ -640,43 +640,43 @@ static ma_status run_rows_mul(ma_fft_plan* plan, const LargeParams& p, bool stor
     const int64_t work = (p.batch * (int64_t)(m2 + 1) + W2 - 1) / W2;  // tiles over the chunk's global row list
     const int64_t cap = (int64_t)ctx->sm_count * *o;
     const int grid = (int)(work < cap ? work : cap);
-    if (store_spectrum) rows_mul_kernel<N1, W2, true><<<grid, threads, smem, ctx->stream>>>(p);
-    else rows_mul_kernel<N1, W2, false><<<grid, threads, smem, ctx->stream>>>(p);
+    if (store_spectrum) rows_mul_kernel<N1, W2, true><<<grid, threads, smem, st>>>(p);
+    else rows_mul_kernel<N1, W2, false><<<grid, threads, smem, st>>>(p);
     return after_launch(ctx);
 }
 
-static ma_status dispatch_rows_mul(ma_fft_plan* plan, const LargeParams& p, bool store_spectrum) {
+static ma_status dispatch_rows_mul(ma_fft_plan* plan, const LargeParams& p, bool store_spectrum, cudaStream_t st) {
     switch (p.n1) {
-        case 128: return run_rows_mul<128, 16>(plan, p, store_spectrum);
-        case 256: return run_rows_mul<256, 16>(plan, p, store_spectrum);
-        case 512: return run_rows_mul<512, 16>(plan, p, store_spectrum);
-        case 1024: return run_rows_mul<1024, 8>(plan, p, store_spectrum);
-        case 2048: return run_rows_mul<2048, 4>(plan, p, store_spectrum);
-        case 4096: return run_rows_mul<4096, 2>(plan, p, store_spectrum);
+        case 128: return run_rows_mul<128, 16>(plan, p, store_spectrum, st);
+        case 256: return run_rows_mul<256, 16>(plan, p, store_spectrum, st);
+        case 512: return run_rows_mul<512, 16>(plan, p, store_spectrum, st);
+        case 1024: return run_rows_mul<1024, 8>(plan, p, store_spectrum, st);
+        case 2048: return run_rows_mul<2048, 4>(plan, p, store_spectrum, st);
+        case 4096: return run_rows_mul<4096, 2>(plan, p, store_spectrum, st);
         default: return MA_ERR_UNSUPPORTED;
     }
 }
 
-static ma_status dispatch_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse) {
+static ma_status dispatch_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse, cudaStream_t st) {
     switch (p.n2 / 2) {
-        case 64: return run_cols<64, 32>(plan, p, inverse);
-        case 128: return run_cols<128, 32>(plan, p, inverse);
-        case 256: return run_cols<256, 32>(plan, p, inverse);
-        case 512: return run_cols<512, 16>(plan, p, inverse);
-        case 1024: return run_cols<1024, 8>(plan, p, inverse);
-        case 2048: return run_cols<2048, 4>(plan, p, inverse);
+        case 64: return run_cols<64, 32>(plan, p, inverse, st);
+        case 128: return run_cols<128, 32>(plan, p, inverse, st);
+        case 256: return run_cols<256, 32>(plan, p, inverse, st);
+        case 512: return run_cols<512, 16>(plan, p, inverse, st);
+        case 1024: return run_cols<1024, 8>(plan, p, inverse, st);
+        case 2048: return run_cols<2048, 4>(plan, p, inverse, st);
         default: return MA_ERR_UNSUPPORTED;
     }
 }
 
-static ma_status dispatch_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse) {
+static ma_status dispatch_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse, cudaStream_t st) {
     switch (p.n1) {
-        case 128: return run_rows<128, 16>(plan, p, inverse);
-        case 256: return run_rows<256, 16>(plan, p, inverse);
-        case 512: return run_rows<512, 16>(plan, p, inverse);
-        case 1024: return run_rows<1024, 8>(plan, p, inverse);
-        case 2048: return run_rows<2048, 4>(plan, p, inverse);
-        case 4096: return run_rows<4096, 2>(plan, p, inverse);
+        case 128: return run_rows<128, 16>(plan, p, inverse, st);
+        case 256: return run_rows<256, 16>(plan, p, inverse, st);
+        case 512: return run_rows<512, 16>(plan, p, inverse, st);
+        case 1024: return run_rows<1024, 8>(plan, p, inverse, st);
+        case 2048: return run_rows<2048, 4>(plan, p, inverse, st);
+        case 4096: return run_rows<4096, 2>(plan, p, inverse, st);
         default: return MA_ERR_UNSUPPORTED;
     }
 }
@@ -703,14 +703,19 @@ ma_status large_plan_init(ma_fft_plan* plan) {
     }
     MA_TRY(upload_tw(ctx, 2 * s.m2, s.m2 / 2 + 1, &plan->d_twN)); // column Hermitian twiddles
     MA_TRY(upload_tw(ctx, plan->n, plan->n / 2, &plan->d_twL));
-    // Chunk size: about 192 MB of pass data.  An L2-sized chunk (48 MB) keeps the scratch out of HBM,
-    // but the passes are issue- and latency-bound rather than HBM-bound, and fewer, longer launches
-    // measured 9 % faster for 4096 transforms of 65536 points although the scratch then crosses HBM.
+    // Two lanes of about 96 MB of pass data each.  The passes are bound by latency and instruction
+    // issue, not by HBM, so whether the scratch stays in the 126 MB L2 matters little (measured for
+    // 4096 transforms of 65536 points: one lane of 192 MB 1.79 ms per forward + inverse pair, of 48 MB
+    // 2.06 ms, of 16 MB 2.90 ms: every extra launch costs about 5 us of ramp-up and drain).  A second
+    // lane on its own stream fills those gaps with the other chunk's kernels: 1.62 ms, flat from
+    // 24 to 192 MB per lane and from two to four lanes.
     const size_t per = (size_t)(s.m2 + 1) * s.n1 * sizeof(float2);
-    int64_t chunk = (int64_t)(((size_t)192 << 20) / per);
+    const size_t chunk_mb = 96;
+    plan->scratch_lanes = 2;
+    int64_t chunk = (int64_t)((chunk_mb << 20) / per);
     if (chunk < 1) chunk = 1;
     plan->scratch_batch = chunk;
-    MA_CUDA(cudaMalloc((void**)&plan->d_scratch, per * (size_t)chunk));
+    MA_CUDA(cudaMalloc((void**)&plan->d_scratch, per * (size_t)chunk * (size_t)plan->scratch_lanes));
     return MA_OK;
 }
 
@@ -723,6 +728,36 @@ void large_plan_destroy(ma_fft_plan* plan) {
     plan->d_tw1 = nullptr;
     plan->d_twL = nullptr;
     plan->d_scratch = nullptr;
+}
+
+// Cuts a batch into chunks of `chunk` transforms and runs body(first, count, scratch, stream) on each.
+// With several lanes (the plan's own scratch), consecutive chunks rotate over the context's stream
+// and its auxiliary streams, each lane with its own part of the scratch: one chunk's launch gaps and
+// last, partly filled wave are covered by the other lanes' kernels.  The auxiliary streams start
+// behind everything queued on the context's stream and are joined back before returning - also when
+// a launch failed - so callers see one stream.
+template <class Body>
+static ma_status for_chunks(ma_fft_plan* plan, int64_t batch, float2* scratch, int64_t chunk, int lanes, Body&& body) {
+    ma_context* ctx = plan->ctx;
+    if (lanes > 1 + kAuxStreams) lanes = 1 + kAuxStreams;
+    const int64_t chunks = (batch + chunk - 1) / chunk;
+    const int used = chunks < lanes ? (int)chunks : lanes;  // lanes that get work
+    if (used > 1) {
+        MA_CUDA(cudaEventRecord(ctx->ev_fork, ctx->stream));
+        for (int l = 1; l < used; ++l) MA_CUDA(cudaStreamWaitEvent(ctx->aux_stream[l - 1], ctx->ev_fork, 0));
+    }
+    const int64_t lane_elems = chunk * (int64_t)(plan->n2 / 2 + 1) * plan->n1;
+    ma_status st = MA_OK;
+    int lane = 0;
+    for (int64_t done = 0; done < batch && st == MA_OK; done += chunk, lane = (lane + 1) % used) {
+        const int64_t count = batch - done < chunk ? batch - done : chunk;
+        st = body(done, count, scratch + lane * lane_elems, lane == 0 ? ctx->stream : ctx->aux_stream[lane - 1]);
+    }
+    for (int l = 1; l < used; ++l) {
+        MA_CUDA(cudaEventRecord(ctx->ev_join[l - 1], ctx->aux_stream[l - 1]));
+        MA_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_join[l - 1], 0));
+    }
+    return st;
 }
 
 static void fill_tables(ma_fft_plan* plan, LargeParams& p) {
@@ -743,12 +778,13 @@ ma_status launch_r2c_large(ma_fft_plan* plan, const float* in, float* out_a, flo
                            int mag_kind, float db_scale, int64_t batch, int layout, float2* scratch,
                            int64_t scratch_batch) {
     const int64_t n = plan->n, half = n / 2;
-    const int64_t chunk = scratch != nullptr ? scratch_batch : plan->scratch_batch;
-    for (int64_t done = 0; done < batch; done += chunk) {
+    const bool own = scratch == nullptr;  // a caller-provided pass buffer is used as one lane
+    return for_chunks(plan, batch, own ? plan->d_scratch : scratch, own ? plan->scratch_batch : scratch_batch,
+                      own ? plan->scratch_lanes : 1, [&](int64_t done, int64_t count, float2* lane_scratch, cudaStream_t st) {
         LargeParams p{};
         fill_tables(plan, p);
-        if (scratch != nullptr) p.scratch = scratch;  // caller-provided pass buffer instead of the plan's
-        p.batch = batch - done < chunk ? batch - done : chunk;
+        p.scratch = lane_scratch;
+        p.batch = count;
         p.in = in + done * n;
         p.layout = layout;
         p.mag_kind = mag_kind;
@@ -760,19 +796,20 @@ ma_status launch_r2c_large(ma_fft_plan* plan, const float* in, float* out_a, flo
             p.out_a = out_a + done * 2 * (layout == LAYOUT_HALF_PACKED ? half : half + 1);
         }
         p.mag = mag ? mag + done * (half + 1) : nullptr;
-        MA_TRY(dispatch_cols(plan, p, false));
-        MA_TRY(dispatch_rows(plan, p, false));
-    }
-    return MA_OK;
+        MA_TRY(dispatch_cols(plan, p, false, st));
+        return dispatch_rows(plan, p, false, st);
+    });
 }
 
 ma_status launch_c2r_large(ma_fft_plan* plan, const float* in_a, const float* in_b, float* out, int64_t batch,
                            int layout) {
     const int64_t n = plan->n, half = n / 2;
-    for (int64_t done = 0; done < batch; done += plan->scratch_batch) {
+    return for_chunks(plan, batch, plan->d_scratch, plan->scratch_batch, plan->scratch_lanes,
+                      [&](int64_t done, int64_t count, float2* lane_scratch, cudaStream_t st) {
         LargeParams p{};
         fill_tables(plan, p);
-        p.batch = batch - done < plan->scratch_batch ? batch - done : plan->scratch_batch;
+        p.scratch = lane_scratch;
+        p.batch = count;
         p.layout = layout;
         if (layout == LAYOUT_FULL_SPLIT) {
             p.in = in_a + done * n;
@@ -781,10 +818,9 @@ ma_status launch_c2r_large(ma_fft_plan* plan, const float* in_a, const float* in
             p.in = in_a + done * 2 * (layout == LAYOUT_HALF_PACKED ? half : half + 1);
         }
         p.out_a = out + done * n;
-        MA_TRY(dispatch_rows(plan, p, true));
-        MA_TRY(dispatch_cols(plan, p, true));
-    }
-    return MA_OK;
+        MA_TRY(dispatch_rows(plan, p, true, st));
+        return dispatch_cols(plan, p, true, st);
+    });
 }
 
 // Overlap-add of `count` inverse frames (frame f0 + i at frames[i*n]) into one signal's output:
@@ -824,11 +860,13 @@ ma_status launch_stft_large(ma_fft_plan* plan, const float* signals, int64_t sig
                             float db_scale, int layout) {
     const int64_t n = plan->n, half = n / 2;
     for (int64_t s = 0; s < n_signals; ++s) {
-        for (int64_t f0 = 0; f0 < frames; f0 += plan->scratch_batch) {
+        MA_TRY(for_chunks(plan, frames, plan->d_scratch, plan->scratch_batch, plan->scratch_lanes,
+                          [&](int64_t f0, int64_t count, float2* lane_scratch, cudaStream_t st) {
             const int64_t g = s * frames + f0;  // global frame index of the chunk's first frame
             LargeParams p{};
             fill_tables(plan, p);
-            p.batch = frames - f0 < plan->scratch_batch ? frames - f0 : plan->scratch_batch;
+            p.scratch = lane_scratch;
+            p.batch = count;
             p.in = signals + s * signal_stride + f0 * plan->hop;
             p.in_stride = plan->hop;
             p.window = plan->d_window;
@@ -842,9 +880,9 @@ ma_status launch_stft_large(ma_fft_plan* plan, const float* signals, int64_t sig
                 p.out_a = out_a + g * 2 * (layout == LAYOUT_HALF_PACKED ? half : half + 1);
             }
             p.mag = mag ? mag + g * (half + 1) : nullptr;
-            MA_TRY(dispatch_cols(plan, p, false));
-            MA_TRY(dispatch_rows(plan, p, false));
-        }
+            MA_TRY(dispatch_cols(plan, p, false, st));
+            return dispatch_rows(plan, p, false, st);
+        }));
     }
     return MA_OK;
 }
@@ -854,14 +892,15 @@ ma_status launch_istft_large(ma_fft_plan* plan, const float* in_a, const float* 
                              int layout) {
     ma_context* ctx = plan->ctx;
     const int64_t n = plan->n, half = n / 2;
+    const int64_t step = plan->scratch_batch * plan->scratch_lanes;  // inverse frames per round: every lane's chunk
     if (plan->d_frames == nullptr)  // first overlap-add through this plan
-        MA_CUDA(cudaMalloc((void**)&plan->d_frames, sizeof(float) * (size_t)n * (size_t)plan->scratch_batch));
+        MA_CUDA(cudaMalloc((void**)&plan->d_frames, sizeof(float) * (size_t)n * (size_t)step));
     const int64_t per_frame = layout == LAYOUT_FULL_SPLIT ? n : 2 * (layout == LAYOUT_HALF_PACKED ? half : half + 1);
     for (int64_t s = 0; s < n_signals; ++s) {
         float* row = out + s * out_stride;
         MA_CUDA(cudaMemsetAsync(row, 0, sizeof(float) * (size_t)out_len, ctx->stream));
-        for (int64_t f0 = 0; f0 < frames; f0 += plan->scratch_batch) {
-            const int64_t count = frames - f0 < plan->scratch_batch ? frames - f0 : plan->scratch_batch;
+        for (int64_t f0 = 0; f0 < frames; f0 += step) {
+            const int64_t count = frames - f0 < step ? frames - f0 : step;
             const int64_t g = s * frames + f0;
             MA_TRY(launch_c2r_large(plan, in_a + g * per_frame, in_b ? in_b + g * per_frame : nullptr, plan->d_frames,
                                     count, layout));
@@ -885,8 +924,8 @@ ma_status launch_spec_rows_large(ma_fft_plan* plan, const float* in, int64_t val
     p.in = in;
     p.valid = valid;
     p.spec_rows = spec_rows;
-    MA_TRY(dispatch_cols(plan, p, false));
-    return dispatch_rows_mul(plan, p, true);
+    MA_TRY(dispatch_cols(plan, p, false, plan->ctx->stream));
+    return dispatch_rows_mul(plan, p, true, plan->ctx->stream);
 }
 
 // out[b][0..N) = inverse(forward(zero-padded in[b][0..valid)) * spectrum) for `batch` signals: three
@@ -895,21 +934,22 @@ ma_status launch_spec_rows_large(ma_fft_plan* plan, const float* in, int64_t val
 ma_status launch_conv_large(ma_fft_plan* plan, const float* in, int64_t valid, int64_t in_stride,
                             const float2* spec_rows, float* out, int64_t batch) {
     const int64_t n = plan->n;
-    for (int64_t done = 0; done < batch; done += plan->scratch_batch) {
+    return for_chunks(plan, batch, plan->d_scratch, plan->scratch_batch, plan->scratch_lanes,
+                      [&](int64_t done, int64_t count, float2* lane_scratch, cudaStream_t st) {
         LargeParams p{};
         fill_tables(plan, p);
-        p.batch = batch - done < plan->scratch_batch ? batch - done : plan->scratch_batch;
+        p.scratch = lane_scratch;
+        p.batch = count;
         p.in = in + done * in_stride;
         p.in_stride = in_stride;
         p.valid = valid;
         p.spec_rows = const_cast<float2*>(spec_rows);
         p.out_a = out + done * n;
         p.layout = LAYOUT_HALF_INTERLEAVED;
-        MA_TRY(dispatch_cols(plan, p, false));
-        MA_TRY(dispatch_rows_mul(plan, p, false));
-        MA_TRY(dispatch_cols(plan, p, true));
-    }
-    return MA_OK;
+        MA_TRY(dispatch_cols(plan, p, false, st));
+        MA_TRY(dispatch_rows_mul(plan, p, false, st));
+        return dispatch_cols(plan, p, true, st);
+    });
 }
 
 }  // namespace ma

@@ -25,7 +25,8 @@ struct ma_fft_plan {
     float2* d_tw1 = nullptr;          // exp(-2 pi i j/n1), j < n1
     float2* d_twL = nullptr;          // exp(-2 pi i j/N),  j < N (pass twiddles)
     float2* d_scratch = nullptr;      // (n2/2+1) x n1 complex per transform in a pass
-    int64_t scratch_batch = 0;        // transforms the scratch holds
+    int64_t scratch_batch = 0;        // transforms one lane of the scratch holds
+    int scratch_lanes = 1;            // lanes (chunks in flight on separate streams)
     float* d_frames = nullptr;        // iSTFT above 8192 points: scratch_batch inverse frames (allocated on first use)
     float* d_cwork = nullptr;         // complex-input transforms: real rows + half spectra of one chunk (allocated on first use)
 };

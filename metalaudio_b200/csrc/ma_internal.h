@@ -7,12 +7,18 @@
 
 #include "../../include/metalaudio_cuda.h"
 
+constexpr int kAuxStreams = 3;
+
 struct ma_context {
     int device = 0;
     int sm_count = 0;
     cudaStream_t stream = nullptr;
     cudaStream_t copy_stream = nullptr;   // host -> device leg of the pipelined *_host calls
     cudaStream_t d2h_stream = nullptr;    // device -> host leg
+    // Further lanes of the large transforms: chunks of a batch rotate over `stream` and these, forked
+    // from and joined back to `stream` inside each call.
+    cudaStream_t aux_stream[kAuxStreams] = {};
+    cudaEvent_t ev_fork = nullptr, ev_join[kAuxStreams] = {};
     // Device workspace of the *_host calls: two lanes of ws_lane_bytes each, allocated once
     // (ma_context_reserve_workspace or the first *_host call) and grown only when a single row
     // does not fit.  Lane events: input copied, kernels done, output copied.
