@@ -74,18 +74,18 @@ struct DevCtaL {
 
 extern __shared__ float4 ma_large_smem[];
 
-// Column passes of two-stage plans (one exchange per transform, M2 <= 256) run through ONE exchange
-// buffer: the Hermitian step reuses it behind a barrier, which halves the shared memory of a CTA
-// and lets a fourth CTA onto an SM.
-template <int M2>
-constexpr __host__ __device__ bool cols_single_buffer() { return FftPlan<M2>::NS <= 2; }
-// Resident CTAs per SM asked of the compiler for those plans: the inverse pass fits 64 registers; the
-// forward pass would spill 208 bytes there and measured slower than at 3.
-constexpr int kColsR2cCtas = 3, kColsC2rCtas = 4;
+// Every pass runs its transforms through ONE exchange buffer (a barrier in front of each exchange
+// write keeps it behind the previous exchange's reads): half the shared memory of two buffers, which
+// is what lets a fourth 256-thread CTA, or a second 512-thread CTA, onto an SM.
+// Resident CTAs per SM asked of the compiler.  256 threads: the inverse column pass fits 64 registers;
+// the forward one would spill 208 bytes there and measured slower than at 3.  512 threads (transforms
+// of 131072 points and more): 2, i.e. 64 registers with at most 300 bytes of spills - measured 12 to
+// 26 % faster per forward + inverse pair from 2^17 to 2^22 points than one CTA with 128 registers.
+constexpr int kColsR2cCtas = 3, kColsC2rCtas = 4, kBigCtas = 2;
 
 // ---------------------------------------------------------------- forward pass 1
 template <int M2, int W1>
-__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? (cols_single_buffer<M2>() ? kColsR2cCtas : 3) : 1) cols_r2c_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? kColsR2cCtas : kBigCtas) cols_r2c_kernel(const LargeParams p) {
     using P = FftPlan<M2>;
     constexpr int R = P::R, T = P::T;
     float2* smem = reinterpret_cast<float2*>(ma_large_smem);
@@ -123,10 +123,9 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
         }
         int parity = 0;
         float2* sbuf0 = smem + i;
-        constexpr bool ONE = cols_single_buffer<M2>();
-        fft_forward_regs<M2, W1, DevCtaL, ONE>(v, t, sbuf0, M2 * W1, parity, p.twM2, cta);
-        float2* sb = ONE ? sbuf0 : sbuf0 + parity * (M2 * W1);
-        if constexpr (ONE) cta.sync();  // the exchange's reads are done before the buffer is rewritten
+        fft_forward_regs<M2, W1, DevCtaL, true>(v, t, sbuf0, 0, parity, p.twM2, cta);
+        float2* sb = sbuf0;
+        cta.sync();  // the exchange's reads are done before the buffer is rewritten
 #pragma unroll
         for (int q = 0; q < R; ++q) sb[saddr<W1>(t + q * T)] = v[q];
         cta.sync();
@@ -239,9 +238,19 @@ __device__ __forceinline__ void store_half_tile(const LargeParams& p, int64_t g0
     }
 }
 
+// Shared memory of a row-pass CTA: its exchange buffer, and room for the transposed tile
+// [N1][W2+1] the passes build in the same place.
+template <int N1, int W2>
+constexpr __host__ __device__ size_t rows_smem_bytes() {
+    size_t x = (size_t)smem_elems_per_fft<N1, 1>() * W2 * sizeof(float2);
+    size_t tile = (size_t)N1 * (W2 + 1) * sizeof(float2);
+    size_t b = x > tile ? x : tile;
+    return (b + 15) & ~(size_t)15;
+}
+
 // ---------------------------------------------------------------- forward pass 2
 template <int N1, int W2>
-__global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 256 ? 4 : 1) rows_fwd_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 256 ? 4 : kBigCtas) rows_fwd_kernel(const LargeParams p) {
     using P = FftPlan<N1>;
     constexpr int R = P::R, T = P::T;
     constexpr int ELEMS = smem_elems_per_fft<N1, 1>();
@@ -259,7 +268,7 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
     // The tile - W2 consecutive scratch rows, one contiguous block - is staged by ONE bulk asynchronous
     // copy (the TMA unit's untiled form) into the exchange buffer, which is idle until the first
     // exchange; every thread then picks its points from shared memory.
-    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + (P::NS > 2 ? 2 : 1) * BUF);
+    uint64_t* bar = reinterpret_cast<uint64_t*>(reinterpret_cast<char*>(smem) + rows_smem_bytes<N1, W2>());
     uint32_t phase = 0;
     if (threadIdx.x == 0) bulk_barrier_init(bar);
     __syncthreads();
@@ -278,7 +287,7 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
         for (int q = 0; q < R; ++q) v[q] = active ? smem[slot * N1 + t + q * T] : make_float2(0.f, 0.f);
         cta.sync();  // every thread has its points: the exchange buffer may be written
         int parity = 0;
-        fft_forward_regs<N1, 1, DevCtaL>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
+        fft_forward_regs<N1, 1, DevCtaL, true>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
         cta.sync();  // everyone is done with the exchange buffers: reuse them as the tile
         float2* tile = smem;  // [k1][W2+1]
 #pragma unroll
@@ -330,7 +339,7 @@ __device__ __forceinline__ float2 load_bin(const LargeParams& p, int64_t b, int6
 
 // ---------------------------------------------------------------- inverse pass A
 template <int N1, int W2>
-__global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 256 ? 3 : 1) rows_inv_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 256 ? 3 : kBigCtas) rows_inv_kernel(const LargeParams p) {
     using P = FftPlan<N1>;
     constexpr int R = P::R, T = P::T;
     constexpr int ELEMS = smem_elems_per_fft<N1, 1>();
@@ -401,7 +410,7 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
         for (int q = 0; q < R; ++q) v[q] = tile[(t + q * T) * (W2 + 1) + slot];
         cta.sync();
         int parity = 0;
-        fft_forward_regs<N1, 1, DevCtaL>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
+        fft_forward_regs<N1, 1, DevCtaL, true>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
         const int64_t g = g0 + slot;
         if (g < rows_total) {
             const int k2 = (int)(g % (m2 + 1));
@@ -425,7 +434,7 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
 // never leaves the registers.  STORE_SPECTRUM: stop after the forward transform and write the row
 // to p.spec_rows (how the kernel's own spectrum is prepared).
 template <int N1, int W2, bool STORE_SPECTRUM>
-__global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 256 ? 3 : 1) rows_mul_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 256 ? 3 : kBigCtas) rows_mul_kernel(const LargeParams p) {
     using P = FftPlan<N1>;
     constexpr int R = P::R, T = P::T;
     constexpr int ELEMS = smem_elems_per_fft<N1, 1>();
@@ -452,7 +461,7 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
             for (int q = 0; q < R; ++q) h[q] = __ldg(hrow + t + q * T);
         }
         int parity = 0;
-        fft_forward_regs<N1, 1, DevCtaL>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
+        fft_forward_regs<N1, 1, DevCtaL, true>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
         if constexpr (STORE_SPECTRUM) {
             if (active) {
 #pragma unroll
@@ -465,7 +474,7 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
                 v[q] = make_float2(y.y, y.x);  // swapped: the inverse runs as a forward transform
             }
             cta.sync();  // the first transform's exchange reads are done before the buffers are rewritten
-            fft_forward_regs<N1, 1, DevCtaL>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
+            fft_forward_regs<N1, 1, DevCtaL, true>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
             if (active) {
                 float2 wq[R];
                 geometric_twiddles<R>(wq, __ldg(p.twL + (int64_t)k2 * t), __ldg(p.twL + (int64_t)k2 * T));
@@ -479,7 +488,7 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
 
 // ---------------------------------------------------------------- inverse pass B
 template <int M2, int W1>
-__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? (cols_single_buffer<M2>() ? kColsC2rCtas : 3) : 1) cols_c2r_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? kColsC2rCtas : kBigCtas) cols_c2r_kernel(const LargeParams p) {
     using P = FftPlan<M2>;
     constexpr int R = P::R, T = P::T;
     float2* smem = reinterpret_cast<float2*>(ma_large_smem);
@@ -494,8 +503,7 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
         const float2* d = p.scratch + b * (int64_t)(M2 + 1) * p.n1 + n1;
         int parity = 0;
         float2* sbuf0 = smem + i;
-        float2* sb = sbuf0 + parity * (M2 * W1);
-        parity ^= 1;
+        float2* sb = sbuf0;
         float2 ra[R / 2 + 1], rb[R / 2 + 1];
 #pragma unroll
         for (int q = 0; q <= R / 2; ++q) {  // every load in flight before the first use
@@ -523,7 +531,7 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
         float2 v[R];
 #pragma unroll
         for (int q = 0; q < R; ++q) v[q] = sb[saddr<W1>(t + q * T)];
-        fft_forward_regs<M2, W1, DevCtaL, cols_single_buffer<M2>()>(v, t, sbuf0, M2 * W1, parity, p.twM2, cta);
+        fft_forward_regs<M2, W1, DevCtaL, true>(v, t, sbuf0, 0, parity, p.twM2, cta);
         float* x = p.out_a + b * (int64_t)p.n + n1;
 #pragma unroll
         for (int q = 0; q < R; ++q) {
@@ -556,7 +564,7 @@ static bool large_shape(int n, LargeShape* s) {
 template <int M2, int W1>
 static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse, cudaStream_t st) {
     constexpr int threads = W1 * FftPlan<M2>::T;
-    constexpr size_t smem = (cols_single_buffer<M2>() ? 1 : 2) * (size_t)M2 * W1 * sizeof(float2);
+    constexpr size_t smem = (size_t)M2 * W1 * sizeof(float2);
     ma_context* ctx = plan->ctx;
     auto kf = cols_r2c_kernel<M2, W1>;
     auto ki = cols_c2r_kernel<M2, W1>;
@@ -587,8 +595,7 @@ static ma_status run_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse,
     constexpr int threads = W2 * FftPlan<N1>::T;
     // plans with a single exchange (two stages) never touch the second exchange buffer
     // exchange buffer(s) plus 16 bytes for the staging barrier of the forward pass
-    constexpr size_t smem = (FftPlan<N1>::NS > 2 ? 2 : 1) * (size_t)smem_elems_per_fft<N1, 1>() * W2 * sizeof(float2) + 16;
-    static_assert((size_t)N1 * (W2 + 1) * sizeof(float2) <= smem - 16, "transposed tile must fit the exchange buffers");
+    constexpr size_t smem = rows_smem_bytes<N1, W2>() + 16;
     ma_context* ctx = plan->ctx;
     auto kf = rows_fwd_kernel<N1, W2>;
     auto ki = rows_inv_kernel<N1, W2>;
@@ -630,7 +637,7 @@ static ma_status kernel_occupancy(K kernel, int threads, size_t smem, int* occ) 
 template <int N1, int W2>
 static ma_status run_rows_mul(ma_fft_plan* plan, const LargeParams& p, bool store_spectrum, cudaStream_t st) {
     constexpr int threads = W2 * FftPlan<N1>::T;
-    constexpr size_t smem = 2 * (size_t)smem_elems_per_fft<N1, 1>() * W2 * sizeof(float2);
+    constexpr size_t smem = rows_smem_bytes<N1, W2>();
     ma_context* ctx = plan->ctx;
     static int occ[2][64] = {};
     int* o = &occ[store_spectrum ? 1 : 0][ctx->device & 63];
