@@ -239,6 +239,21 @@ MA_DEFINE_PLAN(2048, 16, 3, 16, 16, 8)
 MA_DEFINE_PLAN(4096, 16, 3, 16, 16, 16)
 #undef MA_DEFINE_PLAN
 
+// Threads per transform of the plan for length m (0 for a length without a plan).
+inline int fft_plan_threads(int m) {
+    switch (m) {
+        case 32: return FftPlan<32>::T;
+        case 64: return FftPlan<64>::T;
+        case 128: return FftPlan<128>::T;
+        case 256: return FftPlan<256>::T;
+        case 512: return FftPlan<512>::T;
+        case 1024: return FftPlan<1024>::T;
+        case 2048: return FftPlan<2048>::T;
+        case 4096: return FftPlan<4096>::T;
+        default: return 0;
+    }
+}
+
 // The same radices in reverse order (first stage the smallest radix, possibly several
 // butterflies per thread).  Used by the inverse transforms, whose Hermitian pre-process
 // feeds a paired first stage.

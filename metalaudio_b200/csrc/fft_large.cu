@@ -18,7 +18,9 @@
 // The forward row pass stages its tile (W2 consecutive scratch rows: one contiguous block) with a
 // single bulk asynchronous copy of the TMA unit into its idle exchange buffer; the strided tiles of
 // the other passes use plain coalesced loads and stores.  No multicast anywhere.
+#include <cmath>
 #include <new>
+#include <vector>
 
 #include "bulk_copy.cuh"
 #include "fft_plan.h"
@@ -40,7 +42,11 @@ struct LargeParams {
     const float2* twM2;  // stage twiddle tables of FftPlan<M2>
     const float2* twN2;  // exp(-2 pi i k/N2), k <= M2/2
     const float2* tw1;   // stage twiddle tables of FftPlan<N1>
-    const float2* twL;   // exp(-2 pi i j/N),  j < N/2
+    // Pass twiddles exp(-2 pi i n1 k2 / N) as geometric sequences in k2 (column pass) or n1 (row passes),
+    // laid out so that a warp's loads are contiguous:
+    const float2* twc;       // [T(M2) + 2][N1]: rows t < T: n1*t; row T: the step n1*T; row T+1: n1*M2
+    const float2* twr;       // [N2/2 + 1][T(N1)]: k2*t for t < T
+    const float2* twr_step;  // [N2/2 + 1]: the step k2*T
     int64_t in_stride;   // forward pass 1: floats between consecutive transforms' inputs
     int64_t valid;       // forward pass 1: samples present per transform, the rest reads as zero
     float2* spec_rows;   // convolution: kernel spectrum in pass-2 row order [N2/2+1][N1]
@@ -130,12 +136,13 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
         for (int q = 0; q < R; ++q) sb[saddr<W1>(t + q * T)] = v[q];
         cta.sync();
         float2* c = p.scratch + b * (int64_t)(M2 + 1) * p.n1 + n1;
-        // pass twiddles exp(-2 pi i n1 k / N) for k = t + q*T as a geometric sequence from three
-        // table values (a gather per output would cost an L1 wavefront per lane)
+        // pass twiddles exp(-2 pi i n1 k / N) for k = t + q*T as a geometric sequence from two table
+        // values (lanes run along n1, so each load is one contiguous row segment; a gather from a
+        // single N/2-entry table cost up to an L1 wavefront per lane)
+        const float2* tc = p.twc + n1;
         float2 wk[R / 2 + 1];
-        geometric_twiddles<R / 2 + 1>(wk, __ldg(p.twL + (int64_t)n1 * t), __ldg(p.twL + (int64_t)n1 * T));
-        const float2 wtop = __ldg(p.twL + (int64_t)n1 * (M2 / 2));
-        const float2 wm2 = cmul(wtop, wtop);  // exp(-2 pi i n1 M2 / N); index n1*M2 may reach N/2, the table's end
+        geometric_twiddles<R / 2 + 1>(wk, __ldg(tc + t * p.n1), __ldg(tc + T * p.n1));
+        const float2 wm2 = __ldg(tc + (T + 1) * p.n1);  // exp(-2 pi i n1 M2 / N)
 #pragma unroll
         for (int q = 0; q <= R / 2; ++q) {
             const int k = t + q * T;
@@ -416,7 +423,7 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
             const int k2 = (int)(g % (m2 + 1));
             float2* row = p.scratch + g * N1;
             float2 wq[R];
-            geometric_twiddles<R>(wq, __ldg(p.twL + (int64_t)k2 * t), __ldg(p.twL + (int64_t)k2 * T));
+            geometric_twiddles<R>(wq, __ldg(p.twr + k2 * T + t), __ldg(p.twr_step + k2));
 #pragma unroll
             for (int q = 0; q < R; ++q) {
                 const int n1 = t + q * T;
@@ -477,7 +484,7 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
             fft_forward_regs<N1, 1, DevCtaL, true>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
             if (active) {
                 float2 wq[R];
-                geometric_twiddles<R>(wq, __ldg(p.twL + (int64_t)k2 * t), __ldg(p.twL + (int64_t)k2 * T));
+                geometric_twiddles<R>(wq, __ldg(p.twr + k2 * T + t), __ldg(p.twr_step + k2));
 #pragma unroll
                 for (int q = 0; q < R; ++q) row[t + q * T] = cmul(make_float2(v[q].y, v[q].x), cconj(wq[q]));
             }
@@ -709,7 +716,30 @@ ma_status large_plan_init(ma_fft_plan* plan) {
         MA_TRY(copy_h2d(ctx, plan->d_tw1, t1.data(), t1.size() * sizeof(float2)));
     }
     MA_TRY(upload_tw(ctx, 2 * s.m2, s.m2 / 2 + 1, &plan->d_twN)); // column Hermitian twiddles
-    MA_TRY(upload_tw(ctx, plan->n, plan->n / 2, &plan->d_twL));
+    {
+        // pass twiddles in the layouts the kernels load them in (see LargeParams); angles reduced in
+        // integers, values rounded once from double precision
+        const int64_t n = plan->n;
+        const int t1 = fft_plan_threads(s.m2), t2 = fft_plan_threads(s.n1);
+        auto w = [n](int64_t j) {
+            const double a = -2.0 * 3.14159265358979323846 * (double)(j % n) / (double)n;
+            return make_float2((float)std::cos(a), (float)std::sin(a));
+        };
+        std::vector<float2> twc((size_t)(t1 + 2) * s.n1), twr((size_t)(s.m2 + 1) * t2), step((size_t)s.m2 + 1);
+        for (int64_t n1 = 0; n1 < s.n1; ++n1) {
+            for (int t = 0; t <= t1; ++t) twc[(size_t)t * s.n1 + n1] = w(n1 * t);
+            twc[(size_t)(t1 + 1) * s.n1 + n1] = w(n1 * s.m2);
+        }
+        for (int64_t k2 = 0; k2 <= s.m2; ++k2) {
+            for (int t = 0; t < t2; ++t) twr[(size_t)k2 * t2 + t] = w(k2 * t);
+            step[(size_t)k2] = w(k2 * t2);
+        }
+        MA_CUDA(cudaMalloc((void**)&plan->d_twc, twc.size() * sizeof(float2)));
+        MA_TRY(copy_h2d(ctx, plan->d_twc, twc.data(), twc.size() * sizeof(float2)));
+        MA_CUDA(cudaMalloc((void**)&plan->d_twr, (twr.size() + step.size()) * sizeof(float2)));
+        MA_TRY(copy_h2d(ctx, plan->d_twr, twr.data(), twr.size() * sizeof(float2)));
+        MA_TRY(copy_h2d(ctx, plan->d_twr + twr.size(), step.data(), step.size() * sizeof(float2)));
+    }
     // Two lanes of about 96 MB of pass data each.  The passes are bound by latency and instruction
     // issue, not by HBM, so whether the scratch stays in the 126 MB L2 matters little (measured for
     // 4096 transforms of 65536 points: one lane of 192 MB 1.79 ms per forward + inverse pair, of 48 MB
@@ -728,12 +758,14 @@ ma_status large_plan_init(ma_fft_plan* plan) {
 
 void large_plan_destroy(ma_fft_plan* plan) {
     if (plan->d_tw1) (void)cudaFree(plan->d_tw1);
-    if (plan->d_twL) (void)cudaFree(plan->d_twL);
+    if (plan->d_twc) (void)cudaFree(plan->d_twc);
+    if (plan->d_twr) (void)cudaFree(plan->d_twr);
     if (plan->d_frames) (void)cudaFree(plan->d_frames);
     plan->d_frames = nullptr;
     if (plan->d_scratch) (void)cudaFree(plan->d_scratch);
     plan->d_tw1 = nullptr;
-    plan->d_twL = nullptr;
+    plan->d_twc = nullptr;
+    plan->d_twr = nullptr;
     plan->d_scratch = nullptr;
 }
 
@@ -775,7 +807,9 @@ static void fill_tables(ma_fft_plan* plan, LargeParams& p) {
     p.twM2 = plan->d_twM;
     p.twN2 = plan->d_twN;
     p.tw1 = plan->d_tw1;
-    p.twL = plan->d_twL;
+    p.twc = plan->d_twc;
+    p.twr = plan->d_twr;
+    p.twr_step = plan->d_twr + (size_t)(plan->n2 / 2 + 1) * fft_plan_threads(plan->n1);
     p.in_stride = plan->n;
     p.valid = plan->n;
     p.error_flag = plan->ctx->d_error_flag;

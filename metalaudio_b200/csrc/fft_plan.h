@@ -23,7 +23,8 @@ struct ma_fft_plan {
     int n1 = 0, n2 = 0;
     ma_fft_plan* sub_cols = nullptr;  // tables for the n2-point real transforms
     float2* d_tw1 = nullptr;          // exp(-2 pi i j/n1), j < n1
-    float2* d_twL = nullptr;          // exp(-2 pi i j/N),  j < N (pass twiddles)
+    float2* d_twc = nullptr;          // pass twiddles in the column pass's layout
+    float2* d_twr = nullptr;          // pass twiddles in the row passes' layout, then their steps
     float2* d_scratch = nullptr;      // (n2/2+1) x n1 complex per transform in a pass
     int64_t scratch_batch = 0;        // transforms one lane of the scratch holds
     int scratch_lanes = 1;            // lanes (chunks in flight on separate streams)
