@@ -661,7 +661,7 @@ static ma_status run_rows_mul(ma_fft_plan* plan, const LargeParams& p, bool stor
 
 static ma_status dispatch_rows_mul(ma_fft_plan* plan, const LargeParams& p, bool store_spectrum, cudaStream_t st) {
     switch (p.n1) {
-        case 128: return run_rows_mul<128, 16>(plan, p, store_spectrum, st);
+        case 128: return run_rows_mul<128, 32>(plan, p, store_spectrum, st);
         case 256: return run_rows_mul<256, 16>(plan, p, store_spectrum, st);
         case 512: return run_rows_mul<512, 16>(plan, p, store_spectrum, st);
         case 1024: return run_rows_mul<1024, 8>(plan, p, store_spectrum, st);
@@ -685,7 +685,7 @@ static ma_status dispatch_cols(ma_fft_plan* plan, const LargeParams& p, bool inv
 
 static ma_status dispatch_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse, cudaStream_t st) {
     switch (p.n1) {
-        case 128: return run_rows<128, 16>(plan, p, inverse, st);
+        case 128: return run_rows<128, 32>(plan, p, inverse, st);
         case 256: return run_rows<256, 16>(plan, p, inverse, st);
         case 512: return run_rows<512, 16>(plan, p, inverse, st);
         case 1024: return run_rows<1024, 8>(plan, p, inverse, st);

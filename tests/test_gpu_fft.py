@@ -232,6 +232,29 @@ def test_config5_scaled(device, lib):
     assert o64.rel_rms(y, x) <= TOL
 
 
+def test_large_batch_over_several_chunks(device, lib):
+    """A batch that needs three scratch chunks (23 + 23 + 4 transforms of 2^20 points): chunks alternate
+    between the two lanes, the third reuses the first lane's scratch behind the first chunk, and the
+    last one is ragged.  Transforms on both sides of every chunk boundary are checked against the
+    float64 definition, the whole batch by its round trip."""
+    import ctypes
+    from metalaudio_b200 import _lib as L
+    n, batch = 1 << 20, 50
+    rng = np.random.default_rng(50)
+    x = rng.standard_normal((batch, n)).astype(np.float32)
+    f = make_fft(device, n)
+    spec = np.zeros((batch, n // 2 + 1, 2), np.float32)
+    p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    assert lib.ma_fft_forward_host(f._h, p(x), p(spec), None, None, 0, 1.0, batch, L.LAYOUT_HALF_INTERLEAVED) == 0
+    pick = [0, 22, 23, 45, 46, 49]
+    ref = o64.rfft(x[pick])
+    assert o64.rel_rms(spec[pick, :, 0] + 1j * spec[pick, :, 1], ref) <= TOL
+    y = np.zeros_like(x)
+    assert lib.ma_fft_inverse_host(f._h, p(spec), None, p(y), batch, L.LAYOUT_HALF_INTERLEAVED) == 0
+    for b in range(batch):
+        assert o64.rel_rms(y[b], x[b]) <= TOL, b
+
+
 @pytest.mark.parametrize("n", [2, 4, 16, 256, 2048, 4096, 8192, 16384, 65536, 1 << 18])
 def test_complex_transform_matches_oracle(device, lib, n):
     """forwardGPU / inverseGPU (FFT.swift:945-1107, :1176-1315): complex DFT of interleaved
