@@ -165,8 +165,11 @@ ma_status ma_host_free(ma_context* ctx, void* hptr);
 ma_status ma_fft_plan_create(ma_context* ctx, int32_t n, const float* window, int32_t hop,
                              ma_fft_plan** out);
 ma_status ma_fft_plan_destroy(ma_fft_plan* plan);
-/* Bytes of device scratch the plan holds for N > 8192 (0 below), and the largest batch
- * one launch of the large-N path processes per pass. */
+/* Bytes of device scratch the plan holds for N > 8192 (0 below): two lanes of pass data.  A batch
+ * of such transforms is cut into chunks that alternate between the context's stream and a second,
+ * internal stream (one lane of the scratch each); the internal stream starts behind everything
+ * queued on the context's stream and is joined back to it before the call returns, so callers
+ * keep seeing one stream. */
 ma_status ma_fft_plan_scratch_bytes(ma_fft_plan* plan, size_t* bytes);
 
 /* Unnormalised forward DFT of `batch` contiguous real frames of N samples.

@@ -552,7 +552,7 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
 
 // ---------------------------------------------------------------- host side
 struct LargeShape {
-    int n1, m2, w1, w2;
+    int n1, m2;  // the tile widths of the passes are chosen per size in dispatch_cols / dispatch_rows
 };
 
 static bool large_shape(int n, LargeShape* s) {
@@ -563,8 +563,6 @@ static bool large_shape(int n, LargeShape* s) {
     const int n2 = 1 << lg2;
     s->n1 = n >> lg2;
     s->m2 = n2 / 2;
-    s->w1 = 8192 / s->m2 < 32 ? 8192 / s->m2 : 32;
-    s->w2 = 8192 / s->n1 < 16 ? 8192 / s->n1 : 16;
     return true;
 }
 
