@@ -111,7 +111,8 @@ ma_status ma_context_destroy(ma_context* ctx);
  * reference's default of 2 s, ComputeContext.swift:137).  Polls an event; on expiry
  * returns MA_ERR_TIMEOUT and leaves the stream draining. */
 ma_status ma_context_sync(ma_context* ctx, double timeout_s);
-/* Device workspace of the *_host transforms (ma_stft_host, ma_istft_host): `bytes` of device memory
+/* Device workspace of the pipelined *_host calls (ma_stft_host, ma_istft_host, ma_pconv_process_host,
+ * and ma_fft_forward_host / ma_fft_inverse_host for batches of 16 MiB and more): `bytes` of device memory
  * in two lanes, allocated once here (or, at a default of 2 x 256 MiB, by the first such call) and
  * kept until the context is destroyed - the "pre-allocated staging" half of AudioDevice /
  * ComputeContext in this backend.  Grows only when a single signal with its results does not fit a
@@ -310,7 +311,10 @@ ma_status ma_pconv_partition_count(ma_pconv* pc, int32_t* partitions);
  * (row c at in + c*in_stride) and produces the full len + taps - 1 output samples
  * (row c at out + c*out_stride), ceil((len+taps-1)/B) blocks pushed through the delay
  * line; the delay line keeps its state for the next call.  `max_len` passed to
- * ma_pconv_reserve bounds len for the _dev form, which never allocates. */
+ * ma_pconv_reserve bounds len for the _dev form, which never allocates.  The _host form sends
+ * groups of channels through the context's workspace lanes; with both host arrays pinned the
+ * groups' copies in, convolutions and copies out overlap on three streams (see
+ * ma_context_reserve_workspace). */
 ma_status ma_pconv_reserve(ma_pconv* pc, int64_t max_len);
 ma_status ma_pconv_process_dev(ma_pconv* pc, const float* in, int64_t len, int64_t in_stride,
                                float* out, int64_t out_stride);

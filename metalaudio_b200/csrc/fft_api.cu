@@ -3,6 +3,7 @@
 #include <new>
 
 #include "fft_plan.h"
+#include "host_pipe.h"
 #include "host_tables.h"
 
 namespace ma {
@@ -24,6 +25,10 @@ static bool valid_layout(int layout) {
            layout == MA_LAYOUT_HALF_POLAR;
 }
 // Layouts that use the second array.
+// The plain transforms' host forms go through the pipeline from this many bytes per call (pinned arrays,
+// at least four transforms); smaller calls copy, transform and copy back on the context's stream.
+constexpr size_t kPipelineFromBytes = (size_t)16 << 20;
+
 static bool two_arrays(int layout) { return layout == MA_LAYOUT_FULL_SPLIT || layout == MA_LAYOUT_HALF_POLAR; }
 
 // Output floats per frame in array a / b for a layout.
@@ -295,6 +300,34 @@ ma_status ma_fft_forward_host(ma_fft_plan* plan, const float* in, float* out_a, 
     const size_t a_b = (size_t)(batch * floats_a(plan->n, layout)) * sizeof(float);
     const size_t b_b = two_arrays(layout) ? a_b : 0;
     const size_t m_b = mag ? (size_t)(batch * (plan->n / 2 + 1)) * sizeof(float) : 0;
+    if (batch >= 4 && in_b_ + a_b + b_b + m_b >= kPipelineFromBytes && is_pinned(in) && is_pinned(out_a) &&
+        (!b_b || is_pinned(out_b)) && (!m_b || is_pinned(mag))) {
+        // Large batches between pinned arrays: chunks of transforms through the three-stage pipeline.
+        const int64_t fa = floats_a(plan->n, layout), fm = mag ? plan->n / 2 + 1 : 0;
+        const bool two = b_b != 0;
+        Pipe pp;
+        MA_TRY(pipe_open(pp, ctx, true, batch, sizeof(float) * (size_t)(plan->n + fa + (two ? fa : 0) + fm), 4 * 256));
+        for (int64_t b0 = 0, c = 0; b0 < batch && pp.st == MA_OK; b0 += pp.chunk, ++c) {
+            const int64_t cb = batch - b0 < pp.chunk ? batch - b0 : pp.chunk;
+            char* base = pp.lane[c & 1];
+            float* c_in = reinterpret_cast<float*>(base);
+            float* c_a = reinterpret_cast<float*>(base + round256(sizeof(float) * (size_t)(pp.chunk * plan->n)));
+            float* c_b = two ? c_a + ((pp.chunk * fa + 63) & ~(int64_t)63) : nullptr;
+            float* c_m = mag ? (two ? c_b : c_a) + ((pp.chunk * fa + 63) & ~(int64_t)63) : nullptr;
+            pp.before_copy_in(c);
+            const size_t wi = sizeof(float) * (size_t)(cb * plan->n), wa = sizeof(float) * (size_t)(cb * fa);
+            pp.in2d(c_in, wi, in + b0 * plan->n, wi, wi, 1);
+            pp.before_kernels(c);
+            if (pp.st == MA_OK) pp.st = ma_fft_forward_dev(plan, c_in, c_a, c_b, c_m, mag_kind, db_reference, cb, layout);
+            pp.before_copy_out(c);
+            pp.out2d(out_a + b0 * fa, wa, c_a, wa, wa, 1);
+            if (two) pp.out2d(out_b + b0 * fa, wa, c_b, wa, wa, 1);
+            if (mag) pp.out2d(mag + b0 * fm, sizeof(float) * (size_t)(cb * fm), c_m, sizeof(float) * (size_t)(cb * fm),
+                              sizeof(float) * (size_t)(cb * fm), 1);
+            pp.after_copy_out(c);
+        }
+        return pp.finish();
+    }
     float *d_in = nullptr, *d_a = nullptr, *d_b = nullptr, *d_m = nullptr;
     ma_status st = temp_alloc(ctx, in_b_, (void**)&d_in);
     if (st == MA_OK) st = temp_alloc(ctx, a_b, (void**)&d_a);
@@ -326,6 +359,30 @@ ma_status ma_fft_inverse_host(ma_fft_plan* plan, const float* in_a, const float*
     const size_t a_b = (size_t)(batch * floats_a(plan->n, layout)) * sizeof(float);
     const size_t b_b = two_arrays(layout) ? a_b : 0;
     const size_t o_b = (size_t)total * sizeof(float);
+    if (batch >= 4 && a_b + b_b + o_b >= kPipelineFromBytes && is_pinned(in_a) && (!b_b || is_pinned(in_b)) &&
+        is_pinned(out)) {
+        const int64_t fa = floats_a(plan->n, layout);
+        const bool two = b_b != 0;
+        Pipe pp;
+        MA_TRY(pipe_open(pp, ctx, true, batch, sizeof(float) * (size_t)(fa + (two ? fa : 0) + plan->n), 4 * 256));
+        for (int64_t b0 = 0, c = 0; b0 < batch && pp.st == MA_OK; b0 += pp.chunk, ++c) {
+            const int64_t cb = batch - b0 < pp.chunk ? batch - b0 : pp.chunk;
+            char* base = pp.lane[c & 1];
+            float* c_a = reinterpret_cast<float*>(base);
+            float* c_b = two ? c_a + ((pp.chunk * fa + 63) & ~(int64_t)63) : nullptr;
+            float* c_o = (two ? c_b : c_a) + ((pp.chunk * fa + 63) & ~(int64_t)63);
+            pp.before_copy_in(c);
+            const size_t wa = sizeof(float) * (size_t)(cb * fa), wo = sizeof(float) * (size_t)(cb * plan->n);
+            pp.in2d(c_a, wa, in_a + b0 * fa, wa, wa, 1);
+            if (two) pp.in2d(c_b, wa, in_b + b0 * fa, wa, wa, 1);
+            pp.before_kernels(c);
+            if (pp.st == MA_OK) pp.st = ma_fft_inverse_dev(plan, c_a, c_b, c_o, cb, layout);
+            pp.before_copy_out(c);
+            pp.out2d(out + b0 * plan->n, wo, c_o, wo, wo, 1);
+            pp.after_copy_out(c);
+        }
+        return pp.finish();
+    }
     float *d_a = nullptr, *d_b = nullptr, *d_o = nullptr;
     ma_status st = temp_alloc(ctx, a_b, (void**)&d_a);
     if (st == MA_OK && b_b) st = temp_alloc(ctx, b_b, (void**)&d_b);
@@ -366,102 +423,6 @@ ma_status ma_fft_magnitude_host(ma_fft_plan* plan, const float* re, const float*
     temp_free(ctx, d_o);
     return st;
 }
-
-// The two calls below cut their signals into chunks that fit one lane of the context's device
-// workspace and run the chunks through a three-stage pipeline when the host memory is pinned:
-// host -> device copies on one stream, the transform on the context's stream, device -> host
-// copies on a third, chained by events, two lanes deep - chunk c's results travel back while chunk
-// c+1 is transformed and chunk c+2 is on its way in (PCIe is full duplex).  Nothing is allocated
-// per call once the workspace exists, and the host waits once, at the end.  Pageable host memory
-// takes the same chunks one after the other through the staging buffer.
-namespace {
-
-size_t round256(size_t b) { return (b + 255) & ~(size_t)255; }
-
-struct Pipe {
-    ma_context* ctx;
-    bool pinned;
-    int64_t chunk;  // signals per chunk
-    char* lane[2];
-    ma_status st = MA_OK;
-
-    void before_copy_in(int64_t c) {
-        const int l = (int)(c & 1);
-        if (pinned && c >= 2 && st == MA_OK) fail(cudaStreamWaitEvent(ctx->copy_stream, ctx->ev_k[l], 0));
-    }
-    void before_kernels(int64_t c) {
-        const int l = (int)(c & 1);
-        if (!pinned || st != MA_OK) return;
-        fail(cudaEventRecord(ctx->ev_in[l], ctx->copy_stream));
-        fail(cudaStreamWaitEvent(ctx->stream, ctx->ev_in[l], 0));
-        if (c >= 2) fail(cudaStreamWaitEvent(ctx->stream, ctx->ev_out[l], 0));
-    }
-    void before_copy_out(int64_t c) {
-        const int l = (int)(c & 1);
-        if (!pinned || st != MA_OK) return;
-        fail(cudaEventRecord(ctx->ev_k[l], ctx->stream));
-        fail(cudaStreamWaitEvent(ctx->d2h_stream, ctx->ev_k[l], 0));
-    }
-    void after_copy_out(int64_t c) {
-        const int l = (int)(c & 1);
-        if (pinned && st == MA_OK) fail(cudaEventRecord(ctx->ev_out[l], ctx->d2h_stream));
-    }
-    // rows x width floats between a strided host array and a dense-strided device array
-    void in2d(void* d, size_t dpitch, const void* h, size_t hpitch, size_t width, size_t rows) {
-        if (st != MA_OK || rows == 0) return;
-        if (pinned) {
-            fail(cudaMemcpy2DAsync(d, dpitch, h, hpitch, width, rows, cudaMemcpyHostToDevice, ctx->copy_stream));
-        } else if (dpitch == width && hpitch == width) {
-            st = copy_h2d(ctx, d, h, width * rows);
-        } else {
-            for (size_t r = 0; r < rows && st == MA_OK; ++r)
-                st = copy_h2d(ctx, (char*)d + r * dpitch, (const char*)h + r * hpitch, width);
-        }
-    }
-    void out2d(void* h, size_t hpitch, const void* d, size_t dpitch, size_t width, size_t rows) {
-        if (st != MA_OK || rows == 0) return;
-        if (pinned) {
-            fail(cudaMemcpy2DAsync(h, hpitch, d, dpitch, width, rows, cudaMemcpyDeviceToHost, ctx->d2h_stream));
-        } else if (dpitch == width && hpitch == width) {
-            st = copy_d2h(ctx, h, d, width * rows);
-        } else {
-            for (size_t r = 0; r < rows && st == MA_OK; ++r)
-                st = copy_d2h(ctx, (char*)h + r * hpitch, (const char*)d + r * dpitch, width);
-        }
-    }
-    // waits for everything the call queued, also after a failure half-way
-    ma_status finish() {
-        cudaError_t e = cudaStreamSynchronize(ctx->copy_stream);
-        cudaError_t e2 = cudaStreamSynchronize(ctx->stream);
-        cudaError_t e3 = cudaStreamSynchronize(ctx->d2h_stream);
-        if (st == MA_OK) {
-            if (e != cudaSuccess) st = cuda_fail(e);
-            else if (e2 != cudaSuccess) st = cuda_fail(e2);
-            else if (e3 != cudaSuccess) st = cuda_fail(e3);
-        }
-        return st;
-    }
-    void fail(cudaError_t e) {
-        if (e != cudaSuccess && st == MA_OK) st = cuda_fail(e);
-    }
-};
-
-// Chunk size and lanes for rows that need `row_bytes` of workspace each (sub-buffers included).
-ma_status pipe_open(Pipe& p, ma_context* ctx, bool pinned, int64_t rows, size_t row_bytes, size_t fixed_bytes) {
-    size_t lane_bytes = 0;
-    MA_TRY(workspace_lanes(ctx, row_bytes + fixed_bytes, &p.lane[0], &p.lane[1], &lane_bytes));
-    int64_t chunk = (int64_t)((lane_bytes - fixed_bytes) / row_bytes);
-    if (chunk < 1) chunk = 1;
-    // at least four chunks when there are rows enough, so that the three stages overlap
-    if (pinned && rows >= 4 && chunk > (rows + 3) / 4) chunk = (rows + 3) / 4;
-    if (chunk > rows) chunk = rows;
-    p.ctx = ctx;
-    p.pinned = pinned;
-    p.chunk = chunk;
-    return MA_OK;
-}
-
-}  // namespace
 
 ma_status ma_stft_host(ma_fft_plan* plan, const float* signals, int64_t length, int64_t signal_stride,
                        int64_t n_signals, float* out_a, float* out_b, float* mag, int32_t mag_kind,

@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "fft_plan.h"
+#include "host_pipe.h"
 #include "pconv_tiling.h"
 
 struct ma_pconv {
@@ -309,7 +310,7 @@ __global__ void __launch_bounds__(128) pconv_mac_tiled_kernel(const MacParams q,
 
 constexpr int kTwoLevelFrom = 2048;
 
-static ma_status launch_mac_tiled(ma_pconv* pc, const MacParams& q, int64_t t_count, int64_t tl_len) {
+static ma_status launch_mac_tiled(ma_pconv* pc, const MacParams& q, int channels, int64_t t_count, int64_t tl_len) {
     constexpr int TT = 16;
     ma_context* ctx = pc->ctx;
     const int bin_tiles = pc->block >> 5;
@@ -322,7 +323,7 @@ static ma_status launch_mac_tiled(ma_pconv* pc, const MacParams& q, int64_t t_co
         const int64_t t_first = done * 4 * TT;
         qq.out = q.out + t_first * q.out_t_stride;
         qq.x = q.x + t_first * pc->block;  // shifts the timeline origin by t_first rows
-        dim3 grid((unsigned)(bin_tiles * pc->channels), (unsigned)ny, 1);
+        dim3 grid((unsigned)(bin_tiles * channels), (unsigned)ny, 1);
         // Blocked summation once a running sum would cover more than kTwoLevelFrom partitions.
         if (pc->partitions >= kTwoLevelFrom)
             pconv_mac_tiled_kernel<TT, true><<<grid, 128, 0, ctx->stream>>>(qq, (int)(t_count - t_first), tl_len - t_first);
@@ -360,14 +361,14 @@ static ma_status launch_mac_t(ma_context* ctx, const MacParams& q, int chan_tile
     return MA_OK;
 }
 
-static ma_status launch_mac(ma_pconv* pc, MacParams q, bool stream, int64_t t_count) {
+static ma_status launch_mac(ma_pconv* pc, MacParams q, int channels, bool stream, int64_t t_count) {
     const int B = pc->block;
     const int vec = B >= 2 ? 2 : 1;
     const int bp = B / vec;  // threads per spectrum
     q.bpt = bp < kMacThreads ? bp : kMacThreads;
     q.bin_tiles = bp / q.bpt;
     const int ct = pc->share;
-    const int chan_tiles = pc->channels / ct;
+    const int chan_tiles = channels / ct;
     ma_context* ctx = pc->ctx;
 #define MAC_CASE(CT_, VEC_)                                                                        \
     if (ct == CT_ && vec == VEC_)                                                                  \
@@ -630,6 +631,96 @@ ma_status ma_pconv_reserve(ma_pconv* pc, int64_t max_len) {
     return MA_OK;
 }
 
+}  // extern "C"
+
+// Whole-signal convolution of channels [c0, c0 + nc) (nc a multiple of the IR-sharing group): `in`
+// and `out` point at channel c0's rows.  Every buffer of the object is per channel, so a range runs
+// on its own slices; the delay-line position is reset by the caller once all ranges are queued.
+static ma_status process_range(ma_pconv* pc, int c0, int nc, const float* in, int64_t len, int64_t in_stride,
+                               float* out, int64_t out_stride, int64_t full) {
+    ma_context* ctx = pc->ctx;
+    const int B = pc->block, P = pc->partitions;
+    const int64_t T = (full + B - 1) / B;
+    const int64_t tl_len = (int64_t)P - 1 + T;
+    const int64_t tl_stride = tl_len * B;
+    float2* ring = pc->d_ring + (int64_t)c0 * P * B;
+    float2* timeline = pc->d_timeline + (int64_t)c0 * tl_stride;
+    float2* y = pc->d_y + (int64_t)c0 * T * B;
+
+    // 1. history -> timeline prefix
+    if (P > 1) {
+        const int64_t total = (int64_t)nc * (P - 1) * B;
+        int grid = (int)((total + 255) / 256 < (int64_t)ctx->sm_count * 8 ? (total + 255) / 256 : (int64_t)ctx->sm_count * 8);
+        pconv_history_kernel<<<grid, 256, 0, ctx->stream>>>(ring, timeline, tl_stride, P, B, pc->write_index, 0, 1, nc);
+        MA_TRY(after_launch(ctx));
+    }
+    // 2. all input blocks -> spectra
+    {
+        R2CParams p{};
+        p.in = in;
+        p.signal_stride = in_stride;
+        p.frames_per_signal = T;
+        p.total_frames = T * nc;
+        p.signal_len = len;
+        p.hop = B;
+        p.frame_valid = B;
+        p.out_a = reinterpret_cast<float*>(timeline + (int64_t)(P - 1) * B);
+        p.out_signal_stride = tl_stride;
+        p.out_frame_stride = B;
+        p.layout = LAYOUT_HALF_PACKED;
+        p.mag_kind = MAG_NONE;
+        MA_TRY(launch_r2c_small(pc->plan, p));
+    }
+    // 3. delay-line multiply-accumulate for every (channel, block)
+    {
+        MacParams q{};
+        q.x = timeline;
+        q.x_chan_stride = tl_stride;
+        q.h = pc->d_h;
+        q.ch2ir = pc->d_ch2ir + c0;
+        q.out = y;
+        q.out_split_stride = 0;
+        q.out_chan_stride = T * B;
+        q.out_t_stride = B;
+        q.block = B;
+        q.partitions = P;
+        q.w0 = P - 1;
+        q.wrap = 0;
+        q.splits = 1;
+        q.p_per_split = P;
+        if (B >= 32 && T < (int64_t)1 << 30) MA_TRY(launch_mac_tiled(pc, q, nc, T, tl_len));
+        else MA_TRY(launch_mac(pc, q, nc, false, T));
+    }
+    // 4. inverse transform + block overlap-add, truncated at len + taps - 1
+    {
+        C2RParams p{};
+        p.in_a = reinterpret_cast<const float*>(y);
+        p.in_signal_stride = T * B;
+        p.in_frame_stride = B;
+        p.frames_per_signal = T;
+        p.n_signals = nc;
+        p.layout = LAYOUT_HALF_PACKED;
+        p.hop = B;
+        p.window = nullptr;
+        p.out = out;
+        p.out_signal_stride = out_stride;
+        p.out_len = full;
+        p.floor = -1.0f;
+        MA_TRY(launch_istft_small(pc->plan, p));
+    }
+    // 5. the last P block spectra become the delay line
+    {
+        const int64_t total = (int64_t)nc * P * B;
+        int grid = (int)((total + 255) / 256 < (int64_t)ctx->sm_count * 8 ? (total + 255) / 256 : (int64_t)ctx->sm_count * 8);
+        pconv_history_kernel<<<grid, 256, 0, ctx->stream>>>(ring, timeline, tl_stride, P, B, 0, T - 1, 0, nc);
+        MA_TRY(after_launch(ctx));
+        MA_CUDA(cudaMemsetAsync(pc->d_tail + (int64_t)c0 * B, 0, sizeof(float) * (size_t)nc * B, ctx->stream));
+    }
+    return MA_OK;
+}
+
+extern "C" {
+
 ma_status ma_pconv_process_dev(ma_pconv* pc, const float* in, int64_t len, int64_t in_stride, float* out,
                                int64_t out_stride) {
     if (pc == nullptr) return MA_ERR_INVALID_ARGUMENT;
@@ -643,86 +734,15 @@ ma_status ma_pconv_process_dev(ma_pconv* pc, const float* in, int64_t len, int64
     if (__builtin_add_overflow(len, pc->taps - 1, &full)) return MA_ERR_OUTPUT_OVERFLOW;
     if (len > pc->reserved_len) return MA_ERR_INVALID_ARGUMENT;
     if (pc->channels > 1 && (in_stride < len || out_stride < full)) return MA_ERR_INVALID_ARGUMENT;
-    const int B = pc->block, P = pc->partitions, C = pc->channels;
-    const int64_t T = (full + B - 1) / B;
-    const int64_t tl_len = (int64_t)P - 1 + T;
-    const int64_t tl_stride = tl_len * B;
-
-    // 1. history -> timeline prefix
-    if (P > 1) {
-        const int64_t total = (int64_t)C * (P - 1) * B;
-        int grid = (int)((total + 255) / 256 < (int64_t)ctx->sm_count * 8 ? (total + 255) / 256 : (int64_t)ctx->sm_count * 8);
-        pconv_history_kernel<<<grid, 256, 0, ctx->stream>>>(pc->d_ring, pc->d_timeline, tl_stride, P, B,
-                                                            pc->write_index, 0, 1, C);
-        MA_TRY(after_launch(ctx));
-    }
-    // 2. all input blocks -> spectra
-    {
-        R2CParams p{};
-        p.in = in;
-        p.signal_stride = in_stride;
-        p.frames_per_signal = T;
-        p.total_frames = T * C;
-        p.signal_len = len;
-        p.hop = B;
-        p.frame_valid = B;
-        p.out_a = reinterpret_cast<float*>(pc->d_timeline + (int64_t)(P - 1) * B);
-        p.out_signal_stride = tl_stride;
-        p.out_frame_stride = B;
-        p.layout = LAYOUT_HALF_PACKED;
-        p.mag_kind = MAG_NONE;
-        MA_TRY(launch_r2c_small(pc->plan, p));
-    }
-    // 3. delay-line multiply-accumulate for every (channel, block)
-    {
-        MacParams q{};
-        q.x = pc->d_timeline;
-        q.x_chan_stride = tl_stride;
-        q.h = pc->d_h;
-        q.ch2ir = pc->d_ch2ir;
-        q.out = pc->d_y;
-        q.out_split_stride = 0;
-        q.out_chan_stride = T * B;
-        q.out_t_stride = B;
-        q.block = B;
-        q.partitions = P;
-        q.w0 = P - 1;
-        q.wrap = 0;
-        q.splits = 1;
-        q.p_per_split = P;
-        if (B >= 32 && T < (int64_t)1 << 30) MA_TRY(launch_mac_tiled(pc, q, T, tl_len));
-        else MA_TRY(launch_mac(pc, q, false, T));
-    }
-    // 4. inverse transform + block overlap-add, truncated at len + taps - 1
-    {
-        C2RParams p{};
-        p.in_a = reinterpret_cast<const float*>(pc->d_y);
-        p.in_signal_stride = T * B;
-        p.in_frame_stride = B;
-        p.frames_per_signal = T;
-        p.n_signals = C;
-        p.layout = LAYOUT_HALF_PACKED;
-        p.hop = B;
-        p.window = nullptr;
-        p.out = out;
-        p.out_signal_stride = out_stride;
-        p.out_len = full;
-        p.floor = -1.0f;
-        MA_TRY(launch_istft_small(pc->plan, p));
-    }
-    // 5. the last P block spectra become the delay line
-    {
-        const int64_t total = (int64_t)C * P * B;
-        int grid = (int)((total + 255) / 256 < (int64_t)ctx->sm_count * 8 ? (total + 255) / 256 : (int64_t)ctx->sm_count * 8);
-        pconv_history_kernel<<<grid, 256, 0, ctx->stream>>>(pc->d_ring, pc->d_timeline, tl_stride, P, B, 0, T - 1,
-                                                            0, C);
-        MA_TRY(after_launch(ctx));
-        pc->write_index = 0;
-        MA_CUDA(cudaMemsetAsync(pc->d_tail, 0, sizeof(float) * (size_t)C * B, ctx->stream));
-    }
+    MA_TRY(process_range(pc, 0, pc->channels, in, len, in_stride, out, out_stride, full));
+    pc->write_index = 0;
     return MA_OK;
 }
 
+// Host form: groups of channels go through the context's three-stage pipeline (copy in, convolve,
+// copy out on three streams, two workspace lanes deep) when both host arrays are pinned, so the
+// transfers of neighbouring groups run under the convolution of the current one; pageable arrays
+// take the same groups one after the other through the staging buffer.
 ma_status ma_pconv_process_host(ma_pconv* pc, const float* in, int64_t len, int64_t in_stride, float* out,
                                 int64_t out_stride) {
     if (pc == nullptr) return MA_ERR_INVALID_ARGUMENT;
@@ -731,27 +751,36 @@ ma_status ma_pconv_process_host(ma_pconv* pc, const float* in, int64_t len, int6
     if (pc->d_h == nullptr) return MA_ERR_KERNEL_NOT_CONFIGURED;
     if (len == 0) return MA_OK;
     if (len < 0 || in == nullptr || out == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (pc->write_index < 0 || pc->write_index >= pc->partitions) return MA_ERR_INVALID_PARTITION_STATE;
     int64_t full;
     if (__builtin_add_overflow(len, pc->taps - 1, &full)) return MA_ERR_OUTPUT_OVERFLOW;
     const int C = pc->channels;
     if (C > 1 && (in_stride < len || out_stride < full)) return MA_ERR_INVALID_ARGUMENT;
     MA_TRY(ma_pconv_reserve(pc, len));
-    float *d_in = nullptr, *d_out = nullptr;
-    ma_status st = temp_alloc(ctx, sizeof(float) * (size_t)(len * C), (void**)&d_in);
-    if (st == MA_OK) st = temp_alloc(ctx, sizeof(float) * (size_t)(full * C), (void**)&d_out);
-    for (int c = 0; c < C && st == MA_OK; ++c) {
-        if (in_stride == len && c > 0) break;
-        const size_t n = in_stride == len ? (size_t)(len * C) : (size_t)len;
-        st = copy_h2d(ctx, d_in + (int64_t)c * len, in + (int64_t)c * in_stride, n * sizeof(float));
+    const int group = pc->share;  // channels that must stay together (they share one impulse response)
+    const size_t in_row = round256(sizeof(float) * (size_t)len), out_row = round256(sizeof(float) * (size_t)full);
+    const bool pinned = is_pinned(in) && is_pinned(out);
+    Pipe pp;
+    MA_TRY(pipe_open(pp, ctx, pinned, C / group, (in_row + out_row) * (size_t)group, 0));
+    const int64_t step = pp.chunk * group;
+    int64_t i = 0;
+    for (int64_t c0 = 0; c0 < C && pp.st == MA_OK; c0 += step, ++i) {
+        const int nc = (int)(C - c0 < step ? C - c0 : step);
+        char* lane = pp.lane[i & 1];
+        float* d_in = reinterpret_cast<float*>(lane);
+        float* d_out = reinterpret_cast<float*>(lane + in_row * (size_t)nc);
+        pp.before_copy_in(i);
+        pp.in2d(d_in, in_row, in + c0 * in_stride, sizeof(float) * (size_t)in_stride, sizeof(float) * (size_t)len, (size_t)nc);
+        pp.before_kernels(i);
+        if (pp.st == MA_OK)
+            pp.st = process_range(pc, (int)c0, nc, d_in, len, (int64_t)(in_row / sizeof(float)), d_out,
+                                  (int64_t)(out_row / sizeof(float)), full);
+        pp.before_copy_out(i);
+        pp.out2d(out + c0 * out_stride, sizeof(float) * (size_t)out_stride, d_out, out_row, sizeof(float) * (size_t)full, (size_t)nc);
+        pp.after_copy_out(i);
     }
-    if (st == MA_OK) st = ma_pconv_process_dev(pc, d_in, len, len, d_out, full);
-    for (int c = 0; c < C && st == MA_OK; ++c) {
-        if (out_stride == full && c > 0) break;
-        const size_t n = out_stride == full ? (size_t)(full * C) : (size_t)full;
-        st = copy_d2h(ctx, out + (int64_t)c * out_stride, d_out + (int64_t)c * full, n * sizeof(float));
-    }
-    temp_free(ctx, d_in);
-    temp_free(ctx, d_out);
+    const ma_status st = pp.finish();
+    if (st == MA_OK) pc->write_index = 0;
     return st;
 }
 
@@ -811,7 +840,7 @@ ma_status ma_pconv_step_dev(ma_pconv* pc, const float* in_block, int64_t in_stri
         q.splits = pc->splits;
         q.p_per_split = (P + pc->splits - 1) / pc->splits;
         q.dependent_launch = 1;
-        MA_TRY(launch_mac(pc, q, true, 1));
+        MA_TRY(launch_mac(pc, q, pc->channels, true, 1));
     }
     // 3. sum the partials, inverse transform, add the kept tail, keep the new one
     const bool own_sum = pc->splits >= kSumKernelFromSplits && ((int64_t)C * B) % 2 == 0;
