@@ -1,7 +1,8 @@
 // One-dimensional bulk asynchronous copies global -> shared (the TMA unit's untiled form,
 // cp.async.bulk) completed on an mbarrier.  One elected thread moves a whole frame with a single
 // instruction: no registers, and none of the load/store-pipe wavefronts a per-thread copy costs.
-// No multicast, no tensor map; source, destination and size must be multiples of 16 bytes.
+// No multicast; source, destination and size must be multiples of 16 bytes.  (The tiled form,
+// through a tensor map, is bulk_tensor_load_3d below.)
 //
 // Every wait is bounded: after kBulkWaitLimit polls the waiter gives up, records the failure
 // in a device flag the host reads at the next synchronisation, and carries on (the frame's
@@ -50,6 +51,18 @@ __device__ __forceinline__ void bulk_copy_part(void* dst, const void* src, uint3
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
             smem_u32(dst)),
         "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Tiled form: one box of a three-dimensional tensor (described by a host-built tensor map) lands in
+// shared memory, row after row, dense.  Called by one thread after bulk_barrier_expect with the box's
+// byte count.  x counts elements of the innermost dimension and x * element size must be a multiple
+// of 16 bytes; dst must be 128-byte aligned.  No multicast.
+__device__ __forceinline__ void bulk_tensor_load_3d(void* dst, const void* tensor_map, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+            smem_u32(dst)),
+        "l"(tensor_map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
         : "memory");
 }
 

@@ -18,6 +18,9 @@
 // The forward row pass stages its tile (W2 consecutive scratch rows: one contiguous block) with a
 // single bulk asynchronous copy of the TMA unit into its idle exchange buffer; the strided tiles of
 // the other passes use plain coalesced loads and stores.  No multicast anywhere.
+#include <cuda.h>
+
+#include <atomic>
 #include <cmath>
 #include <new>
 #include <vector>
@@ -78,7 +81,7 @@ struct DevCtaL {
     __device__ __forceinline__ void sync() { __syncthreads(); }
 };
 
-extern __shared__ float4 ma_large_smem[];
+extern __shared__ __align__(128) float4 ma_large_smem[];
 
 // Every pass runs its transforms through ONE exchange buffer (a barrier in front of each exchange
 // write keeps it behind the previous exchange's reads): half the shared memory of two buffers, which
@@ -88,6 +91,10 @@ extern __shared__ float4 ma_large_smem[];
 // of 131072 points and more): 2, i.e. 64 registers with at most 300 bytes of spills - measured 12 to
 // 26 % faster per forward + inverse pair from 2^17 to 2^22 points than one CTA with 128 registers.
 constexpr int kColsR2cCtas = 3, kColsC2rCtas = 4, kBigCtas = 2;
+#ifndef MA_TMA_CTAS
+#define MA_TMA_CTAS 4
+#endif
+constexpr int kColsR2cTmaCtas = MA_TMA_CTAS;
 
 // ---------------------------------------------------------------- forward pass 1
 template <int M2, int W1>
@@ -156,6 +163,76 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
             c[(int64_t)km * p.n1] = cmul(xm, cmul(wm2, cconj(wk[q])));
         }
         cta.sync();  // the exchange buffers are reused by the next tile
+    }
+}
+
+// The same pass with its tile staged by the copy unit through a tensor map (cp.async.bulk.tensor): for
+// dense, 16-byte aligned inputs without window or zero padding and tiles of 32 columns.  Launched with
+// one CTA per tile (the grid-stride loop runs once).
+template <int M2, int W1>
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? kColsR2cTmaCtas : kBigCtas) cols_r2c_tma_kernel(const LargeParams p, const __grid_constant__ CUtensorMap in_map) {
+    using P = FftPlan<M2>;
+    constexpr int R = P::R, T = P::T;
+    float2* smem = reinterpret_cast<float2*>(ma_large_smem);
+    const int i = threadIdx.x % W1;
+    const int t = threadIdx.x / W1;
+    const int tiles = p.n1 / W1;
+    DevCtaL cta;
+    {
+        const int64_t blk = blockIdx.x;  // one tile per CTA
+        if (blk >= p.batch * tiles) return;
+        const int64_t b = blk / tiles;
+        const int n1 = (int)(blk - b * tiles) * W1 + i;
+        // The tile - W1 adjacent samples of every one of the N2 rows of this transform's N2 x N1 view - is
+        // one box (two for 512 rows) of the input's tensor map: the copy unit gathers the strided row
+        // segments into the exchange buffer, which is idle until the first exchange, and every thread
+        // picks its points from there.  One tile per CTA, so the barrier sees a single phase.
+        constexpr int ROWS = 2 * M2, BOX_ROWS = ROWS < 256 ? ROWS : 256;
+        float* land = reinterpret_cast<float*>(smem);
+        uint64_t* bar = reinterpret_cast<uint64_t*>(smem + M2 * W1);
+        if (threadIdx.x == 0) {
+            bulk_barrier_init(bar);
+            bulk_barrier_expect(bar, (uint32_t)(ROWS * W1 * sizeof(float)));
+#pragma unroll
+            for (int r0 = 0; r0 < ROWS; r0 += BOX_ROWS)
+                bulk_tensor_load_3d(land + r0 * W1, &in_map, n1 - i, r0, (int)b, bar);
+        }
+        __syncthreads();  // the barrier is initialised before anyone polls it
+        if (!bulk_barrier_wait(bar, 0) && p.error_flag != nullptr) *p.error_flag = 1;
+        float2 v[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int j = t + q * T;
+            v[q] = make_float2(land[(2 * j) * W1 + i], land[(2 * j + 1) * W1 + i]);
+        }
+        int parity = 0;
+        float2* sbuf0 = smem + i;
+        fft_forward_regs<M2, W1, DevCtaL, true>(v, t, sbuf0, 0, parity, p.twM2, cta);
+        float2* sb = sbuf0;
+        cta.sync();  // the exchange's reads are done before the buffer is rewritten
+#pragma unroll
+        for (int q = 0; q < R; ++q) sb[saddr<W1>(t + q * T)] = v[q];
+        cta.sync();
+        float2* c = p.scratch + b * (int64_t)(M2 + 1) * p.n1 + n1;
+        // pass twiddles exp(-2 pi i n1 k / N) for k = t + q*T as a geometric sequence from two table
+        // values (lanes run along n1, so each load is one contiguous row segment; a gather from a
+        // single N/2-entry table cost up to an L1 wavefront per lane)
+        const float2* tc = p.twc + n1;
+        float2 wk[R / 2 + 1];
+        geometric_twiddles<R / 2 + 1>(wk, __ldg(tc + t * p.n1), __ldg(tc + T * p.n1));
+        const float2 wm2 = __ldg(tc + (T + 1) * p.n1);  // exp(-2 pi i n1 M2 / N)
+#pragma unroll
+        for (int q = 0; q <= R / 2; ++q) {
+            const int k = t + q * T;
+            if (k > M2 / 2) continue;
+            const float2 a = sb[saddr<W1>(k)];
+            const float2 bb = sb[saddr<W1>((M2 - k) & (M2 - 1))];
+            float2 xk, xm;
+            herm_post(a, bb, __ldg(p.twN2 + k), xk, xm);
+            const int km = M2 - k;
+            c[(int64_t)k * p.n1] = cmul(xk, wk[q]);
+            c[(int64_t)km * p.n1] = cmul(xm, cmul(wm2, cconj(wk[q])));
+        }
     }
 }
 
@@ -566,6 +643,44 @@ static bool large_shape(int n, LargeShape* s) {
     return true;
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against the driver
+// library); nullptr when the driver does not offer it.
+using TensorMapEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TensorMapEncodeFn tensor_map_encoder() {
+    static std::atomic<void*> cached{nullptr};
+    static std::atomic<bool> looked{false};
+    if (!looked.load(std::memory_order_acquire)) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            fn = nullptr;
+        (void)cudaGetLastError();
+        cached.store(fn, std::memory_order_release);
+        looked.store(true, std::memory_order_release);
+    }
+    return reinterpret_cast<TensorMapEncodeFn>(cached.load(std::memory_order_acquire));
+}
+
+// Tensor map of a chunk's real input seen as [batch][N2][N1] floats with boxes of `box_rows` x 32 samples;
+// false when the input does not qualify (alignment, stride) or the driver cannot encode it.
+static bool input_tensor_map(const LargeParams& p, int box_rows, CUtensorMap* map) {
+    if (p.window != nullptr || p.valid < p.n || (reinterpret_cast<uintptr_t>(p.in) & 15) != 0 || (p.in_stride & 3) != 0 ||
+        p.in_stride < p.n || p.batch > (int64_t)1 << 30)
+        return false;
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (enc == nullptr) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)p.n1, (cuuint64_t)p.n2, (cuuint64_t)p.batch};
+    const cuuint64_t strides[2] = {(cuuint64_t)p.n1 * sizeof(float), (cuuint64_t)p.in_stride * sizeof(float)};
+    const cuuint32_t box[3] = {32u, (cuuint32_t)box_rows, 1u};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(p.in), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int M2, int W1>
 static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse, cudaStream_t st) {
     constexpr int threads = W1 * FftPlan<M2>::T;
@@ -583,6 +698,8 @@ static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse,
         } else {
             MA_CUDA(cudaFuncSetAttribute(kf, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             MA_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kf, threads, smem));
+            if constexpr (W1 == 32)
+                MA_CUDA(cudaFuncSetAttribute(cols_r2c_tma_kernel<M2, W1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem + 16));
         }
         occ = n > 0 ? n : 1;
     }
@@ -590,8 +707,17 @@ static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse,
     const int64_t cap = (int64_t)ctx->sm_count * occ;
     // forward passes: one CTA per tile (measured 5 % faster than persistent CTAs); inverse passes: persistent
     const int grid = !inverse ? (int)work : (int)(work < cap ? work : cap);
-    if (inverse) ki<<<grid, threads, smem, st>>>(p);
-    else kf<<<grid, threads, smem, st>>>(p);
+    if (inverse) {
+        ki<<<grid, threads, smem, st>>>(p);
+    } else {
+        CUtensorMap map;
+        bool staged = false;
+        if constexpr (W1 == 32) staged = input_tensor_map(p, 2 * M2 < 256 ? 2 * M2 : 256, &map);
+        if constexpr (W1 == 32) {
+            if (staged) cols_r2c_tma_kernel<M2, W1><<<grid, threads, smem + 16, st>>>(p, map);
+        }
+        if (!staged) kf<<<grid, threads, smem, st>>>(p);
+    }
     return after_launch(ctx);
 }
 
