@@ -66,6 +66,20 @@ __device__ __forceinline__ void bulk_tensor_load_3d(void* dst, const void* tenso
         : "memory");
 }
 
+// Tiled store: a dense box in shared memory goes to its place in a three-dimensional tensor.  Every
+// thread that wrote the box calls bulk_proxy_fence() and the CTA synchronises; then one thread calls
+// this, which also waits until the copy unit has read the box (the shared memory may then be reused
+// or released; the global writes complete on their own).  Coordinates must not be negative.
+__device__ __forceinline__ void bulk_tensor_store_3d(const void* tensor_map, int x, int y, int z, const void* src) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(tensor_map),
+                 "r"(x), "r"(y), "r"(z), "r"(smem_u32(src))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_store_commit_and_wait_read() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 // Waits for the phase with the given parity; false when the poll limit ran out.
 __device__ __forceinline__ bool bulk_barrier_wait(uint64_t* bar, uint32_t parity, int limit = kBulkWaitLimit) {
     const uint32_t b = smem_u32(bar);

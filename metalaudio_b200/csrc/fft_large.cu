@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
 }
 
 // The same pass with its tile staged by the copy unit through a tensor map (cp.async.bulk.tensor): for
-// dense, 16-byte aligned inputs without window or zero padding and tiles of 32 columns.  Launched with
+// 16-byte aligned inputs without window and tiles of 16 or 32 columns.  Launched with
 // one CTA per tile (the grid-stride loop runs once).
 template <int M2, int W1>
 __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? kColsR2cTmaCtas : kBigCtas) cols_r2c_tma_kernel(const LargeParams p, const __grid_constant__ CUtensorMap in_map) {
@@ -204,6 +204,16 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
         for (int q = 0; q < R; ++q) {
             const int j = t + q * T;
             v[q] = make_float2(land[(2 * j) * W1 + i], land[(2 * j + 1) * W1 + i]);
+        }
+        if (p.valid < p.n) {
+            // zero-padded input: rows beyond the tensor's extent arrived as zeros; the row that holds sample
+            // `valid` is only partly the transform's own
+#pragma unroll
+            for (int q = 0; q < R; ++q) {
+                const int64_t j = t + q * T;
+                if (n1 + (2 * j) * p.n1 >= p.valid) v[q].x = 0.f;
+                if (n1 + (2 * j + 1) * p.n1 >= p.valid) v[q].y = 0.f;
+            }
         }
         int parity = 0;
         float2* sbuf0 = smem + i;
@@ -627,6 +637,77 @@ __global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 2
     }
 }
 
+// The same pass with both of its strided tiles moved by the copy unit through tensor maps: the scratch
+// rows k2 < M2 of W1 columns land in the exchange buffer as one box (the row k2 = M2 as a plain bulk copy
+// behind it), the Hermitian step rewrites that buffer in place (each (k, M2-k) pair of a column belongs to
+// one thread), and the real output tile - N2 rows of W1 samples - is assembled in the same buffer and
+// stored as boxes.  For 16-byte aligned dense outputs and tiles of 32 columns; one tile per CTA.
+template <int M2, int W1>
+__global__ void __launch_bounds__(W1* FftPlan<M2>::T, (W1 * FftPlan<M2>::T) <= 256 ? kColsC2rCtas : kBigCtas)
+    cols_c2r_tma_kernel(const LargeParams p, const __grid_constant__ CUtensorMap scratch_map,
+                        const __grid_constant__ CUtensorMap out_map) {
+    using P = FftPlan<M2>;
+    constexpr int R = P::R, T = P::T;
+    constexpr int ROWS = 2 * M2, BOX_ROWS = ROWS < 256 ? ROWS : 256;
+    float2* smem = reinterpret_cast<float2*>(ma_large_smem);
+    float2* last_row = smem + M2 * W1;  // scratch row k2 = M2
+    uint64_t* bar = reinterpret_cast<uint64_t*>(last_row + W1);
+    const int i = threadIdx.x % W1;
+    const int t = threadIdx.x / W1;
+    const int tiles = p.n1 / W1;
+    const float scale = 1.0f / (float)p.n;
+    DevCtaL cta;
+    const int64_t blk = blockIdx.x;  // one tile per CTA
+    if (blk >= p.batch * tiles) return;
+    const int64_t b = blk / tiles;
+    const int n1_0 = (int)(blk - b * tiles) * W1;
+    if (threadIdx.x == 0) {
+        bulk_barrier_init(bar);
+        bulk_barrier_expect(bar, (uint32_t)((M2 + 1) * W1 * sizeof(float2)));
+        bulk_tensor_load_3d(smem, &scratch_map, 2 * n1_0, 0, (int)b, bar);
+        bulk_copy_part(last_row, p.scratch + (b * (int64_t)(M2 + 1) + M2) * p.n1 + n1_0, (uint32_t)(W1 * sizeof(float2)), bar);
+    }
+    __syncthreads();  // the barrier is initialised before anyone polls it
+    if (!bulk_barrier_wait(bar, 0) && p.error_flag != nullptr) *p.error_flag = 1;
+    int parity = 0;
+    float2* sbuf0 = smem + i;
+#pragma unroll
+    for (int q = 0; q <= R / 2; ++q) {
+        const int k = t + q * T;
+        if (k > M2 / 2) continue;
+        float2 a = sbuf0[k * W1];
+        float2 bb = k == 0 ? last_row[i] : sbuf0[(M2 - k) * W1];
+        if (k == 0) {
+            a.y = 0.f;
+            bb.y = 0.f;
+        }
+        float2 zk, zm;
+        herm_pre(a, bb, __ldg(p.twN2 + k), zk, zm);
+        sbuf0[saddr<W1>(k)] = make_float2(zk.y, zk.x);
+        if (k > 0) sbuf0[saddr<W1>(M2 - k)] = make_float2(zm.y, zm.x);
+    }
+    cta.sync();
+    float2 v[R];
+#pragma unroll
+    for (int q = 0; q < R; ++q) v[q] = sbuf0[saddr<W1>(t + q * T)];
+    fft_forward_regs<M2, W1, DevCtaL, true>(v, t, sbuf0, 0, parity, p.twM2, cta);
+    cta.sync();  // the last exchange's reads are done: the buffer becomes the output tile [N2][W1]
+    float* tile = reinterpret_cast<float*>(smem);
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+        const int j = t + q * T;
+        tile[(2 * j) * W1 + i] = v[q].y * scale;
+        tile[(2 * j + 1) * W1 + i] = v[q].x * scale;
+    }
+    bulk_proxy_fence();
+    cta.sync();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int r0 = 0; r0 < ROWS; r0 += BOX_ROWS) bulk_tensor_store_3d(&out_map, n1_0, r0, (int)b, tile + r0 * W1);
+        bulk_store_commit_and_wait_read();
+    }
+}
+
 // ---------------------------------------------------------------- host side
 struct LargeShape {
     int n1, m2;  // the tile widths of the passes are chosen per size in dispatch_cols / dispatch_rows
@@ -664,21 +745,33 @@ static TensorMapEncodeFn tensor_map_encoder() {
     return reinterpret_cast<TensorMapEncodeFn>(cached.load(std::memory_order_acquire));
 }
 
-// Tensor map of a chunk's real input seen as [batch][N2][N1] floats with boxes of `box_rows` x 32 samples;
-// false when the input does not qualify (alignment, stride) or the driver cannot encode it.
-static bool input_tensor_map(const LargeParams& p, int box_rows, CUtensorMap* map) {
-    if (p.window != nullptr || p.valid < p.n || (reinterpret_cast<uintptr_t>(p.in) & 15) != 0 || (p.in_stride & 3) != 0 ||
-        p.in_stride < p.n || p.batch > (int64_t)1 << 30)
+// Tensor map of `batch` dense [rows][row_floats] float arrays `batch_stride` floats apart, with boxes of
+// box_rows x box_floats; false when the array does not qualify (alignment, stride) or the driver cannot
+// encode it.
+static bool tile_tensor_map(const float* base, int64_t row_floats, int64_t rows, int64_t batch, int64_t batch_stride,
+                            int box_floats, int box_rows, CUtensorMap* map) {
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (batch_stride & 3) != 0 || (row_floats & 3) != 0 ||
+        batch_stride < rows * row_floats || batch > (int64_t)1 << 30)
         return false;
     TensorMapEncodeFn enc = tensor_map_encoder();
     if (enc == nullptr) return false;
-    const cuuint64_t dims[3] = {(cuuint64_t)p.n1, (cuuint64_t)p.n2, (cuuint64_t)p.batch};
-    const cuuint64_t strides[2] = {(cuuint64_t)p.n1 * sizeof(float), (cuuint64_t)p.in_stride * sizeof(float)};
-    const cuuint32_t box[3] = {32u, (cuuint32_t)box_rows, 1u};
+    const cuuint64_t dims[3] = {(cuuint64_t)row_floats, (cuuint64_t)rows, (cuuint64_t)batch};
+    const cuuint64_t strides[2] = {(cuuint64_t)row_floats * sizeof(float), (cuuint64_t)batch_stride * sizeof(float)};
+    const cuuint32_t box[3] = {(cuuint32_t)box_floats, (cuuint32_t)box_rows, 1u};
     const cuuint32_t estr[3] = {1u, 1u, 1u};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(p.in), dims, strides, box, estr,
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The forward pass's real input seen as [batch][rows][N1] floats (no window).  Zero-padded inputs get
+// only the rows that hold samples: boxes reaching beyond them are filled with zeros by the copy unit.
+static bool input_tensor_map(const LargeParams& p, int box_floats, int box_rows, CUtensorMap* map) {
+    if (p.window != nullptr || p.valid <= 0) return false;
+    const int64_t rows = p.valid >= p.n ? p.n2 : (p.valid + p.n1 - 1) / p.n1;
+    // the last transform's last row must still lie inside the caller's array
+    if (p.valid < p.n && rows * p.n1 > p.valid && p.in_stride < rows * p.n1) return false;
+    return tile_tensor_map(p.in, p.n1, rows, p.batch, p.in_stride, box_floats, box_rows, map);
 }
 
 template <int M2, int W1>
@@ -695,10 +788,13 @@ static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse,
         if (inverse) {
             MA_CUDA(cudaFuncSetAttribute(ki, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             MA_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, ki, threads, smem));
+            if constexpr (W1 == 32 && M2 <= 128)
+                MA_CUDA(cudaFuncSetAttribute(cols_c2r_tma_kernel<M2, W1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)(smem + W1 * sizeof(float2) + 16)));
         } else {
             MA_CUDA(cudaFuncSetAttribute(kf, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             MA_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kf, threads, smem));
-            if constexpr (W1 == 32)
+            if constexpr (W1 >= 16)
                 MA_CUDA(cudaFuncSetAttribute(cols_r2c_tma_kernel<M2, W1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem + 16));
         }
         occ = n > 0 ? n : 1;
@@ -708,12 +804,21 @@ static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse,
     // forward passes: one CTA per tile (measured 5 % faster than persistent CTAs); inverse passes: persistent
     const int grid = !inverse ? (int)work : (int)(work < cap ? work : cap);
     if (inverse) {
-        ki<<<grid, threads, smem, st>>>(p);
+        CUtensorMap smap, omap;
+        bool staged = false;
+        if constexpr (W1 == 32 && M2 <= 128) {  // the 512-thread plans measured 2 % slower staged
+            const int64_t per = (int64_t)(M2 + 1) * p.n1 * 2;  // floats of scratch per transform
+            staged = tile_tensor_map(reinterpret_cast<const float*>(p.scratch), 2 * (int64_t)p.n1, M2 + 1, p.batch, per, 2 * W1, M2, &smap) &&
+                     tile_tensor_map(p.out_a, p.n1, p.n2, p.batch, p.n, W1, 2 * M2 < 256 ? 2 * M2 : 256, &omap);
+            if (staged)
+                cols_c2r_tma_kernel<M2, W1><<<(int)work, threads, smem + W1 * sizeof(float2) + 16, st>>>(p, smap, omap);
+        }
+        if (!staged) ki<<<grid, threads, smem, st>>>(p);
     } else {
         CUtensorMap map;
         bool staged = false;
-        if constexpr (W1 == 32) staged = input_tensor_map(p, 2 * M2 < 256 ? 2 * M2 : 256, &map);
-        if constexpr (W1 == 32) {
+        if constexpr (W1 >= 16) staged = input_tensor_map(p, W1, 2 * M2 < 256 ? 2 * M2 : 256, &map);
+        if constexpr (W1 >= 16) {
             if (staged) cols_r2c_tma_kernel<M2, W1><<<grid, threads, smem + 16, st>>>(p, map);
         }
         if (!staged) kf<<<grid, threads, smem, st>>>(p);
