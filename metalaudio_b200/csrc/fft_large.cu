@@ -19,6 +19,7 @@
 // single bulk asynchronous copy of the TMA unit into its idle exchange buffer; the strided tiles of
 // the other passes use plain coalesced loads and stores.  No multicast anywhere.
 #include <cuda.h>
+#include <cuda_pipeline.h>
 
 #include <atomic>
 #include <cmath>
@@ -433,7 +434,7 @@ __device__ __forceinline__ float2 load_bin(const LargeParams& p, int64_t b, int6
 
 // ---------------------------------------------------------------- inverse pass A
 template <int N1, int W2>
-__global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 256 ? 3 : kBigCtas) rows_inv_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 256 ? 4 : kBigCtas) rows_inv_kernel(const LargeParams p) {
     using P = FftPlan<N1>;
     constexpr int R = P::R, T = P::T;
     constexpr int ELEMS = smem_elems_per_fft<N1, 1>();
@@ -450,11 +451,16 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
     for (int64_t blk = blockIdx.x; blk < tiles; blk += gridDim.x) {
         const int64_t g0 = blk * W2;
         float2* tile = smem;
-        // All of a thread's loads are issued before the first use: one memory latency per tile
-        // instead of one per element.
+        // The gather goes from global to shared memory by asynchronous 4- and 8-byte copies (no registers
+        // hold it, which is what lets a fourth CTA onto an SM); the conjugation of the mirrored half, the
+        // two real bins and the real / imaginary swap (the inverse runs as a forward transform of the
+        // swapped spectrum) are applied when a thread picks up its points.
+        const bool full_split = p.layout == LAYOUT_FULL_SPLIT;
+        const bool packed = p.layout == LAYOUT_HALF_PACKED;
         {
             static_assert(THREADS % W2 == 0 && (N1 * W2) % THREADS == 0, "tile load shape");
             constexpr int ITER = N1 * W2 / THREADS, KSTEP = THREADS / W2;
+            static_assert(ITER % 2 == 0 && (N1 / 2) % KSTEP == 0, "the halves must split between iterations");
             const int s = threadIdx.x % W2;
             const int k1base = threadIdx.x / W2;
             const int64_t gs = g0 + s;
@@ -462,46 +468,49 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
             const int64_t b = live ? gs / (m2 + 1) : 0;
             const int kk2 = live ? (int)(gs - b * (m2 + 1)) : 0;
             const int64_t n = p.n, half = n / 2;
-            float2 x[ITER];
-            if (p.layout == LAYOUT_FULL_SPLIT) {
+            if (!live) {
+#pragma unroll
+                for (int it = 0; it < ITER; ++it) tile[(k1base + it * KSTEP) * (W2 + 1) + s] = make_float2(0.f, 0.f);
+            } else if (full_split) {
                 const float* re = p.in + b * n;
                 const float* im = p.in_b + b * n;
 #pragma unroll
                 for (int it = 0; it < ITER; ++it) {
-                    const int64_t k = live ? (int64_t)(k1base + it * KSTEP) * p.n2 + kk2 : 0;
-                    x[it] = make_float2(__ldg(re + k), __ldg(im + k));
-                    if (k == 0 || k == half) x[it].y = 0.f;
+                    const int64_t k = (int64_t)(k1base + it * KSTEP) * p.n2 + kk2;
+                    float* dst = reinterpret_cast<float*>(tile + (k1base + it * KSTEP) * (W2 + 1) + s);
+                    __pipeline_memcpy_async(dst, re + k, 4);
+                    __pipeline_memcpy_async(dst + 1, im + k, 4);
                 }
             } else {
-                static_assert(ITER % 2 == 0 && (N1 / 2) % KSTEP == 0, "the halves must split between iterations");
-                const bool packed = p.layout == LAYOUT_HALF_PACKED;
                 const float2* src = reinterpret_cast<const float2*>(p.in) + b * (packed ? half : half + 1);
                 const int nn = (int)n, hh = (int)half;
-                // lower half (k1 < N1/2): bin k itself; upper half: the conjugate of bin n-k
+                // lower half (k1 < N1/2): bin k itself; upper half: bin n-k (conjugated on pick-up)
 #pragma unroll
                 for (int it = 0; it < ITER; ++it) {
-                    const int k = live ? (k1base + it * KSTEP) * p.n2 + kk2 : (it < ITER / 2 ? 0 : hh);
+                    const int k = (k1base + it * KSTEP) * p.n2 + kk2;
                     int idx = it < ITER / 2 ? k : nn - k;
                     if (packed && idx == hh) idx = 0;
-                    x[it] = __ldg(src + idx);
+                    __pipeline_memcpy_async(tile + (k1base + it * KSTEP) * (W2 + 1) + s, src + idx, 8);
                 }
-                if (kk2 == 0 && k1base == 0) {  // the two real bins
-                    x[0].y = 0.f;
-                    x[ITER / 2] = make_float2(packed ? x[ITER / 2].y : x[ITER / 2].x, 0.f);
-                }
-#pragma unroll
-                for (int it = ITER / 2; it < ITER; ++it) x[it].y = -x[it].y;
             }
-#pragma unroll
-            for (int it = 0; it < ITER; ++it) {
-                const float2 val = live ? x[it] : make_float2(0.f, 0.f);
-                tile[(k1base + it * KSTEP) * (W2 + 1) + s] = make_float2(val.y, val.x);  // swapped: inverse as forward
-            }
+            __pipeline_commit();
+            __pipeline_wait_prior(0);
         }
         cta.sync();
         float2 v[R];
+        {
+            const int64_t gr = g0 + slot;
+            // the row's two real bins (k = 0 and k = N/2) sit in thread 0's points 0 and R/2 when k2 = 0
+            const bool real_bins = t == 0 && gr < rows_total && gr % (m2 + 1) == 0;
 #pragma unroll
-        for (int q = 0; q < R; ++q) v[q] = tile[(t + q * T) * (W2 + 1) + slot];
+            for (int q = 0; q < R; ++q) {
+                float2 val = tile[(t + q * T) * (W2 + 1) + slot];
+                if (q == 0 && real_bins) val.y = 0.f;
+                if (q == R / 2 && real_bins) val = make_float2(packed ? val.y : val.x, 0.f);
+                if (q >= R / 2 && !full_split) val.y = -val.y;  // k1 >= N1/2: the conjugate mirror
+                v[q] = make_float2(val.y, val.x);
+            }
+        }
         cta.sync();
         int parity = 0;
         fft_forward_regs<N1, 1, DevCtaL, true>(v, t, smem + slot * ELEMS, BUF, parity, p.tw1, cta);
