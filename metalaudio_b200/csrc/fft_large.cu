@@ -838,8 +838,7 @@ static ma_status run_cols(ma_fft_plan* plan, const LargeParams& p, bool inverse,
 template <int N1, int W2>
 static ma_status run_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse, cudaStream_t st) {
     constexpr int threads = W2 * FftPlan<N1>::T;
-    // plans with a single exchange (two stages) never touch the second exchange buffer
-    // exchange buffer(s) plus 16 bytes for the staging barrier of the forward pass
+    // the exchange buffer plus 16 bytes for the staging barrier of the forward pass
     constexpr size_t smem = rows_smem_bytes<N1, W2>() + 16;
     ma_context* ctx = plan->ctx;
     auto kf = rows_fwd_kernel<N1, W2>;
@@ -860,8 +859,9 @@ static ma_status run_rows(ma_fft_plan* plan, const LargeParams& p, bool inverse,
     const int m2 = p.n2 / 2;
     const int64_t work = (p.batch * (int64_t)(m2 + 1) + W2 - 1) / W2;  // tiles over the chunk's global row list
     const int64_t cap = (int64_t)ctx->sm_count * occ;
-    // forward passes: one CTA per tile (measured 5 % faster than persistent CTAs); inverse passes: persistent
-    const int grid = !inverse ? (int)work : (int)(work < cap ? work : cap);
+    // one CTA per tile (measured 3-5 % faster than persistent CTAs), except the inverse pass of the
+    // 512-thread plans (1 % slower that way): persistent
+    const int grid = (!inverse || threads <= 256) ? (int)work : (int)(work < cap ? work : cap);
     if (inverse) ki<<<grid, threads, smem, st>>>(p);
     else kf<<<grid, threads, smem, st>>>(p);
     return after_launch(ctx);
