@@ -232,6 +232,35 @@ def test_config5_scaled(device, lib):
     assert o64.rel_rms(y, x) <= TOL
 
 
+@pytest.mark.parametrize("offset", [0, 1, 2])
+def test_large_forward_inverse_on_unaligned_device_rows(device, lib, offset):
+    """65536-point transforms whose input (forward) or output (inverse) starts `offset` floats past a
+    16-byte boundary: the column passes stage their tiles through tensor maps only for aligned arrays
+    and must fall back to plain loads / stores otherwise, with identical results."""
+    import ctypes
+    import torch
+    from metalaudio_b200 import _lib as L
+    n, batch = 65536, 3
+    rng = np.random.default_rng(offset)
+    x = rng.standard_normal((batch, n)).astype(np.float32)
+    f = make_fft(device, n)
+    buf = torch.zeros(batch * n + 4, device="cuda")
+    buf[offset:offset + batch * n] = torch.from_numpy(x.ravel()).cuda()
+    spec = torch.empty((batch, n // 2 + 1, 2), device="cuda")
+    out = torch.zeros(batch * n + 4, device="cuda")
+    torch.cuda.synchronize()
+    assert lib.ma_fft_forward_dev(f._h, ctypes.c_void_p(buf.data_ptr() + 4 * offset), ctypes.c_void_p(spec.data_ptr()), None,
+                                  None, 0, 1.0, batch, L.LAYOUT_HALF_INTERLEAVED) == 0
+    assert lib.ma_fft_inverse_dev(f._h, ctypes.c_void_p(spec.data_ptr()), None, ctypes.c_void_p(out.data_ptr() + 4 * offset),
+                                  batch, L.LAYOUT_HALF_INTERLEAVED) == 0
+    device.synchronize(10)
+    z = spec.cpu().numpy()
+    assert o64.rel_rms(z[..., 0] + 1j * z[..., 1], o64.rfft(x)) <= TOL
+    y = out.cpu().numpy()
+    assert o64.rel_rms(y[offset:offset + batch * n].reshape(batch, n), x) <= TOL
+    assert np.all(y[:offset] == 0) and np.all(y[offset + batch * n:] == 0)  # nothing written outside the rows
+
+
 def test_large_batch_over_several_chunks(device, lib):
     """A batch that needs three scratch chunks (23 + 23 + 4 transforms of 2^20 points): chunks alternate
     between the two lanes, the third reuses the first lane's scratch behind the first chunk, and the

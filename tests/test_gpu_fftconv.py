@@ -114,3 +114,32 @@ def test_many_signals_device_pointers(device, lib):
     bad = ctypes.c_void_p()
     assert lib.ma_fftconv_create(device.handle, h.ctypes.data_as(ctypes.c_void_p), 0, 10, 1, ctypes.byref(bad)) == L.MA_ERR_EMPTY_KERNEL
     assert lib.ma_fftconv_create(device.handle, h.ctypes.data_as(ctypes.c_void_p), taps, 1 << 24, 1, ctypes.byref(bad)) == L.MA_ERR_SIZE_TOO_LARGE
+
+
+@pytest.mark.parametrize("length,stride", [(40000, 40192), (40192, 40192), (40000, 40000), (39999, 40004)])
+def test_large_transform_loader_variants(device, lib, length, stride):
+    """131072-point transforms (kernel of 30000 taps): the forward column pass stages its tile through a
+    tensor map when the rows are 16-byte aligned and long enough for the row that holds the last sample
+    - with a partly filled last row (40000 = 156 * 256 + 64), with none (40192 = 157 * 256) - and falls
+    back to plain loads otherwise (dense rows shorter than the padded row count; a length that is not a
+    multiple of four samples).  Every variant must give the same convolution."""
+    import torch
+    rng = np.random.default_rng(length + stride)
+    taps, sig = 30000, 5
+    h = (rng.standard_normal(taps) * np.exp(-np.arange(taps) / 6000.0)).astype(np.float32)
+    x = rng.standard_normal((sig, stride)).astype(np.float32)
+    fc = ctypes.c_void_p()
+    assert lib.ma_fftconv_create(device.handle, h.ctypes.data_as(ctypes.c_void_p), taps, length, sig, ctypes.byref(fc)) == 0
+    n = ctypes.c_int64(0)
+    assert lib.ma_fftconv_fft_size(fc, ctypes.byref(n)) == 0 and n.value == 131072
+    dx = torch.from_numpy(x).cuda()
+    dy = torch.empty((sig, n.value), device="cuda")
+    torch.cuda.synchronize()
+    assert lib.ma_fftconv_process_dev(fc, ctypes.c_void_p(dx.data_ptr()), length, stride, sig, ctypes.c_void_p(dy.data_ptr())) == 0
+    device.synchronize(10)
+    y = dy.cpu().numpy()
+    for s in (0, sig - 1):
+        full = o64.convolve_full(x[s, :length], h)
+        assert o64.rel_rms(y[s, :full.size], full) < TOL
+        assert np.max(np.abs(y[s, full.size:])) < 1e-3 * np.max(np.abs(full))  # the zero padding stayed zero
+    assert lib.ma_fftconv_destroy(fc) == 0
