@@ -701,6 +701,10 @@ def bench_conv(rig, cfg, seed_ir: int, seed_x: int):
         conv.setKernel(irs, channelToKernel=[c // group for c in range(C)])
         del irs
         sharing = group
+    if cfg.get("splits", 0) > 0:
+        st = lib.ma_pconv_step_splits(conv._h, int(cfg["splits"]), None)
+        if st != 0:
+            raise RuntimeError(f"ma_pconv_step_splits failed: {st}")
     steps, warm = cfg["steps"], cfg["warm"]
     n = (steps + warm) * B
     gen = torch.Generator(device=rig.device).manual_seed(seed_x + rig.rank)
@@ -977,6 +981,8 @@ def main():
     ap.add_argument("--signals", type=int, default=SIGNALS_PER_GPU,
                     help="signals per GPU (default: the benchmark configuration's 256; smaller for profiler captures)")
     ap.add_argument("--conv-channels", type=int, default=CONV3["channels"])
+    ap.add_argument("--conv-splits", type=int, default=0,
+                    help="with --only conv: force the streaming step's partition splits (0: the library's choice)")
     ap.add_argument("--large-batch", type=int, default=LARGE["batch"])
     ap.add_argument("--small", action="store_true", help="with --only next / conv4: a quarter-size case for profiler captures")
     ap.add_argument("--whole", action="store_true", help="with --only conv / conv4: also run the whole-signal call")
@@ -995,6 +1001,7 @@ def main():
         run_reference(args, rank, world)
         return
     CONV3["channels"] = args.conv_channels
+    CONV3["splits"] = args.conv_splits
     LARGE["batch"] = args.large_batch
     if args.only is not None:
         run_only(args, local_rank)

@@ -307,6 +307,12 @@ ma_status ma_pconv_destroy(ma_pconv* pc);
 ma_status ma_pconv_set_kernels(ma_pconv* pc, const float* irs, int64_t taps, int32_t n_irs,
                                const int32_t* channel_to_ir);
 ma_status ma_pconv_partition_count(ma_pconv* pc, int32_t* partitions);
+/* Tuning knob of the streaming step (no counterpart in the reference): into how many ranges of
+ * partitions the multiply-accumulate of one step is split (ranges run as separate CTAs and their
+ * partial spectra are added up afterwards).  ma_pconv_set_kernels picks a count that puts about five
+ * CTAs on every SM; set_to > 0 replaces it (1 <= set_to <= min(64, partitions)), set_to <= 0 only
+ * reports.  Results do not depend on it beyond float32 summation order. */
+ma_status ma_pconv_step_splits(ma_pconv* pc, int32_t set_to, int32_t* splits);
 /* Whole-signal call, as process(input:output:): every channel receives len samples
  * (row c at in + c*in_stride) and produces the full len + taps - 1 output samples
  * (row c at out + c*out_stride), ceil((len+taps-1)/B) blocks pushed through the delay

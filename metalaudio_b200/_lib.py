@@ -64,6 +64,7 @@ SIGNATURES = {
     "ma_pconv_destroy": (c_int32, [c_void_p]),
     "ma_pconv_set_kernels": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
     "ma_pconv_partition_count": (c_int32, [c_void_p, c_int32_p]),
+    "ma_pconv_step_splits": (c_int32, [c_void_p, c_int32, c_int32_p]),
     "ma_pconv_reserve": (c_int32, [c_void_p, c_int64]),
     "ma_pconv_process_dev": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64]),
     "ma_pconv_process_host": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64]),

@@ -596,6 +596,27 @@ ma_status ma_pconv_partition_count(ma_pconv* pc, int32_t* partitions) {
     return MA_OK;
 }
 
+ma_status ma_pconv_step_splits(ma_pconv* pc, int32_t set_to, int32_t* splits) {
+    if (pc == nullptr) return MA_ERR_INVALID_ARGUMENT;
+    if (pc->d_h == nullptr) return MA_ERR_KERNEL_NOT_CONFIGURED;
+    if (set_to > 0) {
+        ma_context* ctx = pc->ctx;
+        MA_TRY(enter(ctx, MA_FAULT_ALLOC));
+        if (set_to > pc->partitions || set_to > 64) return MA_ERR_INVALID_ARGUMENT;
+        if (set_to != pc->splits) {
+            // the partial spectra of earlier steps may still be in use: wait, then resize
+            MA_CUDA(cudaStreamSynchronize(ctx->stream));
+            float2* fresh = nullptr;
+            MA_CUDA(cudaMalloc((void**)&fresh, sizeof(float2) * (size_t)set_to * (size_t)pc->channels * pc->block));
+            if (pc->d_partial) (void)cudaFree(pc->d_partial);
+            pc->d_partial = fresh;
+            pc->splits = set_to;
+        }
+    }
+    if (splits != nullptr) *splits = pc->splits;
+    return MA_OK;
+}
+
 ma_status ma_pconv_reset(ma_pconv* pc) {
     if (pc == nullptr) return MA_ERR_INVALID_ARGUMENT;
     MA_TRY(enter(pc->ctx, MA_FAULT_LAUNCH));

@@ -130,6 +130,38 @@ def test_streaming_step_equals_whole_signal(device, lib, block, taps, channels):
     assert o64.rel_rms(y, z[:, :length]) <= TOL
 
 
+@pytest.mark.parametrize("splits", [1, 3, 16, 40])
+def test_streaming_step_with_forced_partition_splits(device, lib, splits):
+    """ma_pconv_step_splits: the step's multiply-accumulate split into 1, 3, 16 (the count from which the
+    partial spectra get their own summing kernel) or 40 ranges of the 100 partitions gives the same
+    samples; changing the count between steps of a running stream is allowed."""
+    from metalaudio_b200 import Tensor
+    block, taps, channels, n_blocks = 64, 6400, 8, 30
+    rng = np.random.default_rng(splits)
+    h = (rng.standard_normal(taps) / np.sqrt(taps)).astype(np.float32)
+    length = n_blocks * block
+    x = rng.standard_normal((channels, length)).astype(np.float32)
+    c = conv(device, block, channels=channels)
+    c.setKernel(h)
+    got = ctypes.c_int32(0)
+    assert lib.ma_pconv_step_splits(c._h, 0, ctypes.byref(got)) == 0 and got.value >= 1
+    chosen = got.value
+    assert lib.ma_pconv_step_splits(c._h, 101, None) != 0 and lib.ma_pconv_step_splits(c._h, 65, None) != 0
+    tin = Tensor(device, (channels, length)); tin.copy(x)
+    tout = Tensor(device, (channels, length))
+    for t in range(n_blocks):
+        if t == 10:   # switch in mid-stream
+            assert lib.ma_pconv_step_splits(c._h, splits, ctypes.byref(got)) == 0 and got.value == splits
+        if t == 20:
+            assert lib.ma_pconv_step_splits(c._h, chosen, None) == 0
+        assert lib.ma_pconv_step_dev(c._h, ctypes.c_void_p(tin.pointer + 4 * t * block), length,
+                                     ctypes.c_void_p(tout.pointer + 4 * t * block), length) == 0
+    device.synchronize()
+    y = tout.toArray()
+    for i in range(channels):
+        assert o64.rel_rms(y[i], o64.convolve_full(x[i], h)[:length]) <= TOL
+
+
 def test_config3_scaled(device):
     """Configuration 3 at reduced channel count / length: one shared exponentially decaying
     noise IR, block 256, float64 oracle plus exact dot-product spot checks."""
