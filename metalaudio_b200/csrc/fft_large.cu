@@ -96,6 +96,10 @@ constexpr int kColsR2cCtas = 3, kColsC2rCtas = 4, kBigCtas = 2;
 #define MA_TMA_CTAS 4
 #endif
 constexpr int kColsR2cTmaCtas = MA_TMA_CTAS;
+// The fused row pass of the convolution (two transforms and a product on the registers) spills 200-300 bytes
+// at 64 registers: its 512-thread plans stay at one CTA per SM (2^20-point convolution of 256 signals:
+// 1.82 ms against 1.96 ms at two).
+constexpr int kRowsMulBigCtas = 1;
 
 // ---------------------------------------------------------------- forward pass 1
 template <int M2, int W1>
@@ -537,7 +541,7 @@ __global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 2
 // never leaves the registers.  STORE_SPECTRUM: stop after the forward transform and write the row
 // to p.spec_rows (how the kernel's own spectrum is prepared).
 template <int N1, int W2, bool STORE_SPECTRUM>
-__global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 256 ? 3 : kBigCtas) rows_mul_kernel(const LargeParams p) {
+__global__ void __launch_bounds__(W2* FftPlan<N1>::T, (W2 * FftPlan<N1>::T) <= 256 ? 3 : kRowsMulBigCtas) rows_mul_kernel(const LargeParams p) {
     using P = FftPlan<N1>;
     constexpr int R = P::R, T = P::T;
     constexpr int ELEMS = smem_elems_per_fft<N1, 1>();
