@@ -88,14 +88,12 @@ extern __shared__ __align__(128) float4 ma_large_smem[];
 // write keeps it behind the previous exchange's reads): half the shared memory of two buffers, which
 // is what lets a fourth 256-thread CTA, or a second 512-thread CTA, onto an SM.
 // Resident CTAs per SM asked of the compiler.  256 threads: the inverse column pass fits 64 registers;
-// the forward one would spill 208 bytes there and measured slower than at 3.  512 threads (transforms
-// of 131072 points and more): 2, i.e. 64 registers with at most 300 bytes of spills - measured 12 to
-// 26 % faster per forward + inverse pair from 2^17 to 2^22 points than one CTA with 128 registers.
-constexpr int kColsR2cCtas = 3, kColsC2rCtas = 4, kBigCtas = 2;
-#ifndef MA_TMA_CTAS
-#define MA_TMA_CTAS 4
-#endif
-constexpr int kColsR2cTmaCtas = MA_TMA_CTAS;
+// the forward one with plain loads would spill 196 bytes there and measured slower than at 3, while its
+// tensor-map staged form needs no registers for the tile and fits 64 without spills.  512 threads
+// (transforms of 131072 points and more): 2, i.e. 64 registers with at most 300 bytes of spills -
+// measured 12 to 26 % faster per forward + inverse pair from 2^17 to 2^22 points than one CTA with 128
+// registers.
+constexpr int kColsR2cCtas = 3, kColsR2cTmaCtas = 4, kColsC2rCtas = 4, kBigCtas = 2;
 // The fused row pass of the convolution (two transforms and a product on the registers) spills 200-300 bytes
 // at 64 registers: its 512-thread plans stay at one CTA per SM (2^20-point convolution of 256 signals:
 // 1.82 ms against 1.96 ms at two).
