@@ -15,7 +15,10 @@
 // host-built table) and a short serial pass over the 8 warps, which gives every thread the true
 // state in front of its samples; it then runs the recurrence again from that state and keeps the
 // outputs.  States and recurrences are double precision (see biquad_kernel), data is float32.
-// Cascaded sections run back to back on the registers.  Loads and stores of a tile are contiguous;
+// Cascaded sections run back to back on the registers.  Cascades of three and more sections use a
+// variant with 16 samples per thread that keeps the data in double precision from one section to
+// the next (the float <-> double conversions, 16 per clock and SM, otherwise cost more than the
+// recurrences themselves).  Loads and stores of a tile are contiguous;
 // the tile is re-indexed through swizzled shared memory, and the next tile is fetched
 // asynchronously while the current one is filtered.
 #include <cuda_pipeline.h>
@@ -29,13 +32,16 @@
 
 namespace ma {
 
-constexpr int kBqThreads = 256, kBqPer = 32, kBqTile = kBqThreads * kBqPer, kBqWarps = kBqThreads / 32;
+constexpr int kBqThreads = 256, kBqWarps = kBqThreads / 32;
+// samples per thread: 32 for short cascades (data exchanged between sections as float32, like the
+// reference's arrays), 16 for cascades kept in double precision (the doubles need the registers)
+constexpr int kBqPerShort = 32, kBqPerLong = 16, kBqLongFrom = 3;
 constexpr int kBqMaxSections = 32;
 // Table of one (coefficient set, section), doubles:
 //   [0..4]     b0 b1 b2 a1 a2 (the float32 coefficients, widened)
 //   [5..6]     c1 = b1 - a1*b0, c2 = b2 - a2*b0 (the state update with the output substituted)
-//   [8..135]   A^(32*l) row-major 2x2, l < 32
-//   [136..139] A^1024
+//   [8..135]   A^(PER*l) row-major 2x2, l < 32 (PER: samples per thread)
+//   [136..139] A^(PER*32)
 constexpr int kBqCoef = 0, kBqPl = 8, kBqPw = 136, kBqTable = 140;
 
 struct BiquadLaunch {
@@ -52,8 +58,8 @@ __device__ __forceinline__ double2 mat_vec(const double* m, double2 v) {
     return make_double2(fma(m[0], v.x, m[1] * v.y), fma(m[2], v.x, m[3] * v.y));
 }
 
-// Tile layout in shared memory: 16-byte chunks of four samples; chunk c of row r (a row is one
-// thread's 32 samples) sits at column c ^ (r & 7).  Both access patterns are then conflict-free
+// Tile layout in shared memory: 16-byte chunks of four samples; chunk c of row r (a row is 32
+// consecutive samples: one thread's, or two threads' in the 16-sample variant) sits at column c ^ (r & 7).  Both access patterns are then conflict-free
 // with 16-byte accesses: a thread walking its own row, and consecutive threads touching
 // consecutive chunks of the signal.
 __device__ __forceinline__ int swizzled(int i) {
@@ -68,7 +74,10 @@ __device__ __forceinline__ int swizzled(int i) {
 // order of magnitude further from the exact filter than the serial float32 walk.  With the state
 // in double the steps vanish and every section's output is the exact filter's, rounded once to
 // float32 (the precision sections exchange data in, as the reference's float arrays do).
+template <int kBqPer, bool DBL>
 __global__ void __launch_bounds__(kBqThreads, 2) biquad_kernel(const BiquadLaunch p) {
+    constexpr int kBqTile = kBqThreads * kBqPer;
+    using X = typename std::conditional<DBL, double, float>::type;  // how a thread holds its samples between sections
     extern __shared__ __align__(16) double bq_smem[];
     double* tab = bq_smem;                                              // n_sections * kBqTable
     double2* warp_end = reinterpret_cast<double2*>(tab + p.n_sections * kBqTable);  // [2][kBqWarps]
@@ -131,11 +140,12 @@ __global__ void __launch_bounds__(kBqThreads, 2) biquad_kernel(const BiquadLaunc
             fetched = true;
         }
         __syncthreads();
-        float x[kBqPer];
+        X x[kBqPer];
 #pragma unroll
         for (int k = 0; k < kBqPer / 4; ++k) {
-            const float4 v = reinterpret_cast<const float4*>(tile)[tid * (kBqPer / 4) + (k ^ (tid & 7))];
-            x[4 * k] = v.x; x[4 * k + 1] = v.y; x[4 * k + 2] = v.z; x[4 * k + 3] = v.w;
+            const int g = tid * (kBqPer / 4) + k, r = g >> 3;  // 16-byte chunk g of the tile: row r, column g & 7
+            const float4 v = reinterpret_cast<const float4*>(tile)[(r << 3) | ((g & 7) ^ (r & 7))];
+            x[4 * k] = (X)v.x; x[4 * k + 1] = (X)v.y; x[4 * k + 2] = (X)v.z; x[4 * k + 3] = (X)v.w;
         }
         const bool last_tile = left <= kBqTile;
         const int last_local = valid - 1 - tid * kBqPer;  // index of the signal's last sample in this thread
@@ -195,7 +205,7 @@ __global__ void __launch_bounds__(kBqThreads, 2) biquad_kernel(const BiquadLaunc
                     const double s1n = fma(-a1, s1, fma(c1, xv, s2));
                     s2 = fma(-a2, s1, c2 * xv);
                     s1 = s1n;
-                    x[j] = (float)yv;  // input of the next section
+                    x[j] = (X)yv;  // input of the next section
                     if (CAPTURE && j == last_local) {
                         f1 = s1;
                         f2 = s2;
@@ -216,9 +226,11 @@ __global__ void __launch_bounds__(kBqThreads, 2) biquad_kernel(const BiquadLaunc
         }
         // ---- contiguous store through the same tile
 #pragma unroll
-        for (int k = 0; k < kBqPer / 4; ++k)
-            reinterpret_cast<float4*>(tile)[tid * (kBqPer / 4) + (k ^ (tid & 7))] =
-                make_float4(x[4 * k], x[4 * k + 1], x[4 * k + 2], x[4 * k + 3]);
+        for (int k = 0; k < kBqPer / 4; ++k) {
+            const int g = tid * (kBqPer / 4) + k, r = g >> 3;
+            reinterpret_cast<float4*>(tile)[(r << 3) | ((g & 7) ^ (r & 7))] =
+                make_float4((float)x[4 * k], (float)x[4 * k + 1], (float)x[4 * k + 2], (float)x[4 * k + 3]);
+        }
         __syncthreads();
         if (vec_out && valid == kBqTile) {
 #pragma unroll
@@ -248,7 +260,7 @@ __global__ void __launch_bounds__(256) channel_mix_kernel(const float* __restric
 }
 
 // Builds the table of one section in double precision from float32 coefficients.
-static void build_table(const float* c, double* t) {
+static void build_table(const float* c, double* t, int per) {
     for (int i = 0; i < kBqTable; ++i) t[i] = 0.0;
     for (int i = 0; i < 5; ++i) t[kBqCoef + i] = (double)c[i];
     const double a1 = c[3], a2 = c[4];
@@ -261,13 +273,13 @@ static void build_table(const float* c, double* t) {
     };
     const double A[4] = {-a1, 1.0, -a2, 0.0};
     double P[4] = {1.0, 0.0, 0.0, 1.0};
-    for (int n = 0; n < kBqPer; ++n) mul(A, P, P);  // A^32
+    for (int n = 0; n < per; ++n) mul(A, P, P);  // A^per
     double pl[4] = {1.0, 0.0, 0.0, 1.0};
     for (int l = 0; l < 32; ++l) {
         for (int i = 0; i < 4; ++i) t[kBqPl + 4 * l + i] = pl[i];
         mul(P, pl, pl);
     }
-    for (int i = 0; i < 4; ++i) t[kBqPw + i] = pl[i];  // A^1024
+    for (int i = 0; i < 4; ++i) t[kBqPw + i] = pl[i];  // A^(32*per)
 }
 
 }  // namespace ma
@@ -281,10 +293,11 @@ struct ma_biquad {
     int32_t* d_map = nullptr;
     float2* d_state = nullptr;
     bool smem_raised = false;
+    int per = kBqPerShort;  // samples per thread: the kernel variant, fixed by the section count
 };
 
-static size_t biquad_smem(int sections) {
-    return sizeof(float) * (size_t)(2 * kBqTile) + sizeof(double) * (size_t)(sections * kBqTable) +
+static size_t biquad_smem(int sections, int per) {
+    return sizeof(float) * (size_t)(2 * kBqThreads * per) + sizeof(double) * (size_t)(sections * kBqTable) +
            sizeof(double2) * (size_t)(2 * kBqWarps + 2 * sections);
 }
 
@@ -300,6 +313,7 @@ ma_status ma_biquad_create(ma_context* ctx, int32_t n_channels, int32_t n_sectio
     bq->ctx = ctx;
     bq->channels = n_channels;
     bq->sections = n_sections;
+    bq->per = n_sections >= kBqLongFrom ? kBqPerLong : kBqPerShort;
     cudaError_t e = cudaMalloc((void**)&bq->d_state, sizeof(float2) * (size_t)n_channels * n_sections);
     if (e == cudaSuccess) e = cudaMemsetAsync(bq->d_state, 0, sizeof(float2) * (size_t)n_channels * n_sections, ctx->stream);  // ordered before the first kernel of the context
     if (e != cudaSuccess) {
@@ -330,7 +344,7 @@ ma_status ma_biquad_set_coefficients(ma_biquad* bq, const float* coeffs, int32_t
         for (int32_t c = 0; c < bq->channels; ++c)
             if (channel_to_set[c] < 0 || channel_to_set[c] >= n_sets) return MA_ERR_INVALID_ARGUMENT;
     std::vector<double> tables((size_t)n_sets * bq->sections * kBqTable);
-    for (int64_t i = 0; i < (int64_t)n_sets * bq->sections; ++i) build_table(coeffs + 5 * i, tables.data() + kBqTable * i);
+    for (int64_t i = 0; i < (int64_t)n_sets * bq->sections; ++i) build_table(coeffs + 5 * i, tables.data() + kBqTable * i, bq->per);
     MA_TRY(ma_context_sync(ctx, 30.0));  // nothing in flight may still read the old tables
     if (bq->d_tables) (void)cudaFree(bq->d_tables);
     if (bq->d_map) (void)cudaFree(bq->d_map);
@@ -356,9 +370,15 @@ ma_status ma_biquad_process_dev(ma_biquad* bq, const float* in, int64_t in_strid
     if (samples < 0 || in == nullptr || out == nullptr || in_stride < 0) return MA_ERR_INVALID_ARGUMENT;
     if (bq->channels > 1 && out_stride < samples) return MA_ERR_INVALID_ARGUMENT;
     if (in_stride != 0 && bq->channels > 1 && in_stride < samples) return MA_ERR_INVALID_ARGUMENT;
-    const size_t smem = biquad_smem(bq->sections);
+    const size_t smem = biquad_smem(bq->sections, bq->per);
+    const bool long_cascade = bq->per == kBqPerLong;
     if (!bq->smem_raised) {
-        MA_CUDA(cudaFuncSetAttribute(biquad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)biquad_smem(kBqMaxSections)));
+        if (long_cascade)
+            MA_CUDA(cudaFuncSetAttribute(biquad_kernel<kBqPerLong, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)biquad_smem(kBqMaxSections, kBqPerLong)));
+        else
+            MA_CUDA(cudaFuncSetAttribute(biquad_kernel<kBqPerShort, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)biquad_smem(kBqMaxSections, kBqPerShort)));
         bq->smem_raised = true;
     }
     BiquadLaunch p{};
@@ -371,7 +391,8 @@ ma_status ma_biquad_process_dev(ma_biquad* bq, const float* in, int64_t in_strid
     p.channel_to_set = bq->d_map;
     p.state = bq->d_state;
     p.n_sections = bq->sections;
-    biquad_kernel<<<(unsigned)bq->channels, kBqThreads, smem, ctx->stream>>>(p);
+    if (long_cascade) biquad_kernel<kBqPerLong, true><<<(unsigned)bq->channels, kBqThreads, smem, ctx->stream>>>(p);
+    else biquad_kernel<kBqPerShort, false><<<(unsigned)bq->channels, kBqThreads, smem, ctx->stream>>>(p);
     return after_launch(ctx);
 }
 
