@@ -116,11 +116,14 @@ class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons through NVML while the timed region runs
     (read-only queries)."""
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.01):
         super().__init__(daemon=True)
         self.index, self.period = index, period_s
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._halt = threading.Event()
+        # The thread is started ahead of the timed region (NVML's first queries take tens of
+        # milliseconds) and keeps only what it reads while `recording` is set.
+        self.recording = False
         self.ok = False
         try:
             import pynvml
@@ -144,11 +147,13 @@ class ClockSampler(threading.Thread):
         }
         while not self._halt.is_set():
             try:
-                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                mhz = int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
                 mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
-                for bit, name in names.items():
-                    if mask & bit:
-                        self.reasons.add(name)
+                if self.recording:
+                    self.samples.append(mhz)
+                    for bit, name in names.items():
+                        if mask & bit:
+                            self.reasons.add(name)
             except Exception:
                 pass
             self._halt.wait(self.period)
@@ -439,6 +444,8 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         fft.istftTensor(spec, rec)
 
     warmup = max(args.warmup, 3) if S == SIGNALS_PER_GPU else max(args.warmup, 1)
+    sampler = ClockSampler(local_rank)   # started here so that NVML is warm when the timed region opens
+    sampler.start()
     for _ in range(warmup):
         step()
     rig.barrier()
@@ -446,8 +453,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     # ---- timed region: EXACTLY K steps between two CUDA events on the launching stream, barrier +
     # device synchronisation on both sides; clocks sampled while it runs
     K = args.steps
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler.recording = True
     launches0 = lib.ma_kernel_launch_count()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_wall0 = time.perf_counter()
@@ -459,6 +465,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     torch.cuda.synchronize()
     t_wall = time.perf_counter() - t_wall0
     launches = int(lib.ma_kernel_launch_count() - launches0)
+    sampler.recording = False
     clocks = sampler.stop()
     if rig.dist is not None:
         rig.dist.barrier()
