@@ -309,7 +309,8 @@ ma_status ma_pconv_set_kernels(ma_pconv* pc, const float* irs, int64_t taps, int
 ma_status ma_pconv_partition_count(ma_pconv* pc, int32_t* partitions);
 /* Tuning knob of the streaming step (no counterpart in the reference): into how many ranges of
  * partitions the multiply-accumulate of one step is split (ranges run as separate CTAs and their
- * partial spectra are added up afterwards).  ma_pconv_set_kernels picks a count that puts about five
+ * partial spectra are added up afterwards; from 16 ranges up, groups of eight ranges form thread-block
+ * clusters that add their sums up on chip).  ma_pconv_set_kernels picks a count that puts about five
  * CTAs on every SM; set_to > 0 replaces it (1 <= set_to <= min(64, partitions)), set_to <= 0 only
  * reports.  Results do not depend on it beyond float32 summation order. */
 ma_status ma_pconv_step_splits(ma_pconv* pc, int32_t set_to, int32_t* splits);

@@ -130,11 +130,13 @@ def test_streaming_step_equals_whole_signal(device, lib, block, taps, channels):
     assert o64.rel_rms(y, z[:, :length]) <= TOL
 
 
-@pytest.mark.parametrize("splits", [1, 3, 16, 40])
+@pytest.mark.parametrize("splits", [1, 3, 16, 18, 20, 37, 40])
 def test_streaming_step_with_forced_partition_splits(device, lib, splits):
-    """ma_pconv_step_splits: the step's multiply-accumulate split into 1, 3, 16 (the count from which the
-    partial spectra get their own summing kernel) or 40 ranges of the 100 partitions gives the same
-    samples; changing the count between steps of a running stream is allowed."""
+    """ma_pconv_step_splits: the step's multiply-accumulate split into 1, 3, 16, 18, 20, 37 or 40 ranges of
+    the 100 partitions gives the same samples.  From 16 splits up, consecutive splits form thread-block
+    clusters of 8, 4 or 2 CTAs (16 and 40: eight; 20: four; 18: two; 37: none, and then the partial spectra
+    go through their own summing kernel) that add their sums up on chip.  Changing the count between steps
+    of a running stream is allowed."""
     from metalaudio_b200 import Tensor
     block, taps, channels, n_blocks = 64, 6400, 8, 30
     rng = np.random.default_rng(splits)
