@@ -967,7 +967,8 @@ def run_only(args, local_rank: int):
     if args.only == "next":
         res = bench_next_rows(rig.dev, rig.lib, torch, rig.stream, rig.peak, small=args.small)
     elif args.only == "conv4":
-        cfg = dict(CONV4, channels=256 if args.small else CONV4["channels"], skip_whole=not args.whole)
+        cfg = dict(CONV4, channels=256 if args.small else (args.conv4_channels or CONV4["channels"]),
+                   splits=args.conv_splits, skip_whole=not args.whole)
         res = bench_conv(rig, cfg, seed_ir=1004, seed_x=1014)
     elif args.only == "conv":
         cfg = dict(CONV3, skip_whole=not (args.whole or CONV3["channels"] >= 256))
@@ -989,7 +990,9 @@ def main():
                     help="signals per GPU (default: the benchmark configuration's 256; smaller for profiler captures)")
     ap.add_argument("--conv-channels", type=int, default=CONV3["channels"])
     ap.add_argument("--conv-splits", type=int, default=0,
-                    help="with --only conv: force the streaming step's partition splits (0: the library's choice)")
+                    help="with --only conv / conv4: force the streaming step's partition splits (0: the library's choice)")
+    ap.add_argument("--conv4-channels", type=int, default=0,
+                    help="with --only conv4: channels of the low-latency case (0: the configuration's 1024)")
     ap.add_argument("--large-batch", type=int, default=LARGE["batch"])
     ap.add_argument("--small", action="store_true", help="with --only next / conv4: a quarter-size case for profiler captures")
     ap.add_argument("--whole", action="store_true", help="with --only conv / conv4: also run the whole-signal call")
